@@ -1,0 +1,202 @@
+// Drives the UNMODIFIED reference library (oracle/_ref/libdnnl_ref.so, built
+// from the oneDNN checkout by oracle/Makefile.ref) through its public C++ API
+// on a problem described by qmm_problem_t.  TEST INFRASTRUCTURE ONLY: it is
+// used to (a) pin the C restatement in qmm_oracle.c to real reference output,
+// (b) generate the fixtures in tests/golden/, (c) time the reference's CPU
+// matmul as the benchmark's CPU baseline.  Nothing in the product links to it.
+//
+// Build (done by oracle/build_oracle.py):
+//   g++ -std=c++17 -O2 -fPIC -shared ref_runner.cpp -I<ref>/include
+//       -I_ref/include -L_ref -ldnnl_ref -Wl,-rpath,'$ORIGIN' -o _ref/libref_runner.so
+#include <chrono>
+#include <cstring>
+#include <string>
+#include <unordered_map>
+#include <vector>
+
+#include "oneapi/dnnl/dnnl.hpp"
+#include "qmm_oracle.h"
+
+using namespace dnnl;
+using dt = memory::data_type;
+using dims = memory::dims;
+
+namespace {
+
+dt to_dt(int32_t c) { return static_cast<dt>(c); }
+
+memory make_mem(const memory::desc &md, const engine &eng, const void *p) {
+    return memory(md, eng, const_cast<void *>(p));
+}
+
+struct built_t {
+    matmul prim;
+    std::unordered_map<int, memory> args;
+    std::string impl;
+};
+
+// quant parameter buffer descriptor: dense row-major over the masked dims,
+// last two divided by the groups (what primitive_attr::set_scales documents)
+memory::desc quant_md(const qmm_quant_t &q, int64_t d0, int64_t d1) {
+    int64_t a = (q.mask & 1) ? d0 / q.g0 : 1;
+    int64_t b = (q.mask & 2) ? d1 / q.g1 : 1;
+    return memory::desc({a, b}, to_dt(q.dt), memory::format_tag::ab);
+}
+
+void add_quant(primitive_attr &attr, std::unordered_map<int, memory> &args,
+        const engine &eng, const qmm_quant_t &q, int arg, int kind,
+        int64_t d0, int64_t d1, int lead_dims /*grouped weights: 1*/,
+        int64_t G) {
+    if (!q.ptr) return;
+    int mask = 0;
+    if (q.mask & 1) mask |= 1 << (lead_dims + 0);
+    if (q.mask & 2) mask |= 1 << (lead_dims + 1);
+    if (lead_dims) mask |= 1;
+    const bool grouped = q.g0 > 1 || q.g1 > 1;
+    dims groups = grouped ? dims {q.g0, q.g1} : dims {};
+    if (kind == 0)
+        attr.set_scales(arg, mask, groups, to_dt(q.dt));
+    else if (kind == 1)
+        attr.set_zero_points(arg, mask, groups, to_dt(q.dt));
+    else
+        attr.set_precomputed_reductions(arg, mask, groups, to_dt(q.dt));
+    memory::desc md = quant_md(q, d0, d1);
+    if (lead_dims) {
+        auto d = md.get_dims();
+        md = memory::desc({G, d[0], d[1]}, to_dt(q.dt), memory::format_tag::abc);
+    }
+    const int base = kind == 0 ? DNNL_ARG_ATTR_SCALES
+            : kind == 1        ? DNNL_ARG_ATTR_ZERO_POINTS
+                               : DNNL_ARG_ATTR_PRECOMPUTED_REDUCTIONS;
+    args.emplace(base | arg, make_mem(md, eng, q.ptr));
+}
+
+built_t build(const qmm_problem_t &p, const engine &eng, int pin_ref) {
+    const bool grouped = p.group_count > 0;
+    std::unordered_map<int, memory> args;
+    primitive_attr attr;
+    if (p.apply_to_int) attr.set_fpmath_mode(fpmath_mode::bf16, true);
+
+    memory::desc src_md, wei_md, dst_md, bia_md;
+    if (grouped) {
+        src_md = memory::desc::grouped(
+                {p.M, p.K}, to_dt(p.src_dt), 0, p.group_count);
+        dst_md = memory::desc::grouped(
+                {p.M, p.N}, to_dt(p.dst_dt), 0, p.group_count);
+        wei_md = memory::desc({p.group_count, p.K, p.N}, to_dt(p.wei_dt),
+                dims {p.wei_sg, p.wei_sk, p.wei_sn});
+        if (p.bias)
+            bia_md = memory::desc({p.group_count, p.N}, to_dt(p.bias_dt),
+                    memory::format_tag::ab);
+    } else {
+        src_md = memory::desc(
+                {p.M, p.K}, to_dt(p.src_dt), dims {p.src_sm, p.src_sk});
+        wei_md = memory::desc(
+                {p.K, p.N}, to_dt(p.wei_dt), dims {p.wei_sk, p.wei_sn});
+        dst_md = memory::desc(
+                {p.M, p.N}, to_dt(p.dst_dt), dims {p.dst_sm, p.dst_sn});
+        if (p.bias)
+            bia_md = memory::desc({p.bias_sm ? p.M : 1, p.bias_sn ? p.N : 1},
+                    to_dt(p.bias_dt), memory::format_tag::ab);
+    }
+
+    add_quant(attr, args, eng, p.src_scale, DNNL_ARG_SRC, 0, p.M, p.K, 0, 0);
+    add_quant(attr, args, eng, p.wei_scale, DNNL_ARG_WEIGHTS, 0, p.K, p.N,
+            grouped ? 1 : 0, p.group_count);
+    add_quant(attr, args, eng, p.dst_scale, DNNL_ARG_DST, 0, p.M, p.N, 0, 0);
+    add_quant(attr, args, eng, p.src_zp, DNNL_ARG_SRC, 1, p.M, p.K, 0, 0);
+    add_quant(attr, args, eng, p.wei_zp, DNNL_ARG_WEIGHTS, 1, p.K, p.N,
+            grouped ? 1 : 0, p.group_count);
+    add_quant(attr, args, eng, p.dst_zp, DNNL_ARG_DST, 1, p.M, p.N, 0, 0);
+    add_quant(attr, args, eng, p.src_pr, DNNL_ARG_SRC, 2, p.M, p.K, 0, 0);
+
+    post_ops po;
+    for (int i = 0; i < p.n_po; ++i) {
+        const qmm_postop_t &e = p.po[i];
+        if (e.kind == QMM_PO_SUM) {
+            po.append_sum(e.scale, e.zero_point, to_dt(p.sum_dt));
+        } else if (e.kind == QMM_PO_ELTWISE) {
+            po.append_eltwise(static_cast<algorithm>(e.alg), e.alpha, e.beta);
+        } else {
+            memory::desc md({e.src1_sm ? p.M : 1, e.src1_sn ? p.N : 1},
+                    to_dt(e.src1_dt), memory::format_tag::ab);
+            po.append_binary(static_cast<algorithm>(e.alg), md);
+            args.emplace(DNNL_ARG_ATTR_MULTIPLE_POST_OP(i) | DNNL_ARG_SRC_1,
+                    make_mem(md, eng, e.src1));
+        }
+    }
+    if (p.n_po) attr.set_post_ops(po);
+
+    matmul::primitive_desc pd = p.bias
+            ? matmul::primitive_desc(eng, src_md, wei_md, bia_md, dst_md, attr)
+            : matmul::primitive_desc(eng, src_md, wei_md, dst_md, attr);
+    if (pin_ref) {
+        // walk the implementation list until a scalar reference one
+        while (std::string(pd.impl_info_str()).rfind("ref", 0) != 0)
+            if (!pd.next_impl()) throw error(dnnl_unimplemented, "no ref impl");
+    }
+
+    if (grouped) {
+        void *sh[2] = {const_cast<void *>(p.src), const_cast<int32_t *>(p.offsets)};
+        void *dh[2] = {p.dst, const_cast<int32_t *>(p.offsets)};
+        args.emplace(DNNL_ARG_SRC,
+                memory(src_md, eng, std::vector<void *>(sh, sh + 2)));
+        args.emplace(DNNL_ARG_DST,
+                memory(dst_md, eng, std::vector<void *>(dh, dh + 2)));
+    } else {
+        args.emplace(DNNL_ARG_SRC, make_mem(src_md, eng, p.src));
+        args.emplace(DNNL_ARG_DST, make_mem(dst_md, eng, p.dst));
+    }
+    args.emplace(DNNL_ARG_WEIGHTS, make_mem(wei_md, eng, p.wei));
+    if (p.bias) args.emplace(DNNL_ARG_BIAS, make_mem(bia_md, eng, p.bias));
+
+    built_t b {matmul(pd), std::move(args), pd.impl_info_str()};
+    return b;
+}
+
+} // namespace
+
+extern "C" {
+
+// Runs the problem on the reference CPU engine.
+//   pin_ref != 0 : use the scalar ref* implementation (the parity oracle)
+//   pin_ref == 0 : use the first implementation the library dispatches
+// iters > 0 additionally times `iters` executions after one warm-up and
+// stores the best wall time in *best_ms.  The implementation name is copied
+// into impl_name.  Returns 0, or the dnnl status code of the failing call.
+int ref_runner_run(const qmm_problem_t *p, int pin_ref, int iters,
+        double *best_ms, char *impl_name, int impl_len) {
+    try {
+        engine eng(engine::kind::cpu, 0);
+        stream s(eng);
+        built_t b = build(*p, eng, pin_ref);
+        if (impl_name && impl_len > 0) {
+            std::strncpy(impl_name, b.impl.c_str(), impl_len - 1);
+            impl_name[impl_len - 1] = 0;
+        }
+        b.prim.execute(s, b.args);
+        s.wait();
+        if (iters > 0 && best_ms) {
+            double best = 1e30;
+            for (int i = 0; i < iters; ++i) {
+                auto t0 = std::chrono::steady_clock::now();
+                b.prim.execute(s, b.args);
+                s.wait();
+                auto t1 = std::chrono::steady_clock::now();
+                double ms = std::chrono::duration<double, std::milli>(t1 - t0)
+                                    .count();
+                if (ms < best) best = ms;
+            }
+            *best_ms = best;
+        }
+        return 0;
+    } catch (const error &e) {
+        if (impl_name && impl_len > 0) {
+            std::strncpy(impl_name, e.message, impl_len - 1);
+            impl_name[impl_len - 1] = 0;
+        }
+        return e.status ? (int)e.status : -1;
+    }
+}
+
+} // extern "C"
