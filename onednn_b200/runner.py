@@ -1,0 +1,144 @@
+"""Runs a :class:`workloads.Problem` through the library's public API.
+
+``Prepared`` holds everything a caller of ``dnnl::matmul`` would hold: the
+memory descriptors, the attributes, the primitive and one memory object per
+execution argument.  Buffers are either allocated by the library and filled
+through map/unmap (``upload``), or wrap device pointers the caller owns
+(``bind_device``; used with torch tensors by the benchmark).
+"""
+import numpy as np
+
+from . import api
+from . import workloads as W
+
+
+def _md(t: W.QTensor):
+    return api.memory.desc(t.dims, t.dt, tuple(t.strides))
+
+
+class Prepared:
+    def __init__(self, p: W.Problem, eng, impl=None):
+        self.p, self.eng = p, eng
+        grouped = p.offsets is not None
+        if grouped:
+            self.src_md = api.memory.desc.grouped((p.M, p.K), p.src.dt, 0, p.groups)
+            self.dst_md = api.memory.desc.grouped((p.M, p.N), p.dst_dt, 0, p.groups)
+        else:
+            self.src_md = _md(p.src)
+            self.dst_md = api.memory.desc((p.M, p.N), p.dst_dt, api.tag.ab)
+        self.wei_md = _md(p.wei)
+        self.bias_md = _md(p.bias) if p.bias is not None else None
+
+        attr = api.primitive_attr()
+        if p.apply_to_int or p.fpmath:
+            attr.set_fpmath_mode(p.fpmath, p.apply_to_int)
+        arg_of = {"src": api.ARG_SRC, "wei": api.ARG_WEIGHTS, "dst": api.ARG_DST}
+        self.quant_args = {}
+        for name, q in p.quant.items():
+            arg = arg_of[name[:3]]
+            groups = tuple(q.groups) if tuple(q.groups) != (1, 1) else ()
+            if name.endswith("scale"):
+                attr.set_scales(arg, q.mask, groups, q.dt)
+                key = api.ARG_ATTR_SCALES | arg
+            elif name.endswith("zp"):
+                attr.set_zero_points(arg, q.mask, groups, q.dt)
+                key = api.ARG_ATTR_ZERO_POINTS | arg
+            else:
+                attr.set_precomputed_reductions(arg, q.mask, groups, q.dt)
+                key = api.ARG_ATTR_PRECOMPUTED_REDUCTIONS | arg
+            self.quant_args[key] = q
+        po = api.post_ops()
+        self.binary_args = {}
+        for i, e in enumerate(p.post_ops):
+            if e.kind == W.PO_SUM:
+                po.append_sum(e.scale, e.zero_point, 0)
+            elif e.kind == W.PO_ELTWISE:
+                po.append_eltwise(e.alg, e.alpha, e.beta)
+            else:
+                po.append_binary(e.alg, _md(e.src1))
+                self.binary_args[api.ARG_ATTR_MULTIPLE_POST_OP(i) | api.ARG_SRC_1] = e.src1
+        if p.post_ops:
+            attr.set_post_ops(po)
+        self.attr = attr
+        self.pd = api.matmul.primitive_desc(eng, self.src_md, self.wei_md, self.dst_md, self.bias_md, attr)
+        if impl is not None:
+            while impl not in self.pd.impl_info_str():
+                if not self.pd.next_impl():
+                    raise api.error(api.unimplemented, "no implementation named *%s*" % impl)
+        self.impl = self.pd.impl_info_str()
+        self.prim = api.matmul(self.pd)
+        self.args = {}
+        self._keep = []
+
+    # ---- buffers owned by the library, filled through map/unmap
+    def upload(self):
+        p, eng = self.p, self.eng
+        grouped = p.offsets is not None
+
+        def put(md, arrays):
+            m = api.memory(md, eng)
+            for i, a in enumerate(arrays):
+                if a is not None and a.nbytes:
+                    m.write(np.ascontiguousarray(a), i)
+            return m
+
+        self.args[api.ARG_SRC] = put(self.src_md, [p.src.data, p.offsets] if grouped else [p.src.data])
+        self.args[api.ARG_WEIGHTS] = put(self.wei_md, [p.wei.data])
+        dst_init = p.dst_init
+        if dst_init is None:
+            dst_init = np.zeros(self.dst_md.get_size(0), np.uint8)
+        self.args[api.ARG_DST] = put(self.dst_md, [dst_init, p.offsets] if grouped else [dst_init])
+        if p.bias is not None:
+            self.args[api.ARG_BIAS] = put(self.bias_md, [p.bias.data])
+        for key, q in self.quant_args.items():
+            md = self.pd.query_md(api.QUERY_EXEC_ARG_MD, key)
+            self.args[key] = put(md, [q.data])
+        for key, t in self.binary_args.items():
+            self.args[key] = put(_md(t), [t.data])
+        return self
+
+    # ---- buffers owned by the caller (device pointers)
+    def bind_device(self, ptrs):
+        """ptrs: dict with device pointers (int) for 'src', 'wei', 'dst',
+        optional 'bias', 'offsets', each quant name, and 'po<i>' for binary
+        post-op operands."""
+        p, eng = self.p, self.eng
+        grouped = p.offsets is not None
+        if grouped:
+            self.args[api.ARG_SRC] = api.memory(self.src_md, eng, handles=[ptrs["src"], ptrs["offsets"]])
+            self.args[api.ARG_DST] = api.memory(self.dst_md, eng, handles=[ptrs["dst"], ptrs["offsets"]])
+        else:
+            self.args[api.ARG_SRC] = api.memory(self.src_md, eng, ptrs["src"])
+            self.args[api.ARG_DST] = api.memory(self.dst_md, eng, ptrs["dst"])
+        self.args[api.ARG_WEIGHTS] = api.memory(self.wei_md, eng, ptrs["wei"])
+        if p.bias is not None:
+            self.args[api.ARG_BIAS] = api.memory(self.bias_md, eng, ptrs["bias"])
+        arg_of = {"src": api.ARG_SRC, "wei": api.ARG_WEIGHTS, "dst": api.ARG_DST}
+        for name in p.quant:
+            arg = arg_of[name[:3]]
+            base = (api.ARG_ATTR_SCALES if name.endswith("scale") else
+                    api.ARG_ATTR_ZERO_POINTS if name.endswith("zp") else api.ARG_ATTR_PRECOMPUTED_REDUCTIONS)
+            md = self.pd.query_md(api.QUERY_EXEC_ARG_MD, base | arg)
+            self.args[base | arg] = api.memory(md, eng, ptrs[name])
+        for i, e in enumerate(p.post_ops):
+            if e.kind == W.PO_BINARY:
+                self.args[api.ARG_ATTR_MULTIPLE_POST_OP(i) | api.ARG_SRC_1] = api.memory(_md(e.src1), eng, ptrs["po%d" % i])
+        return self
+
+    def execute(self, strm):
+        self.prim.execute(strm, self.args)
+
+    def download(self):
+        dt = self.p.dst_dt
+        raw = self.args[api.ARG_DST].read(np.uint8, 0)
+        if dt in (W.S4, W.U4):
+            return raw
+        return raw.view(W.NP_STORAGE[dt]).reshape(self.p.M, self.p.N)
+
+
+def run_problem(p: W.Problem, eng, strm, impl=None):
+    """Uploads, executes, waits, downloads.  Returns (dst, implementation)."""
+    r = Prepared(p, eng, impl).upload()
+    r.execute(strm)
+    strm.wait()
+    return r.download(), r.impl

@@ -171,6 +171,7 @@ class Problem:
     quant: Dict[str, Quant] = field(default_factory=dict)
     post_ops: List[PostOp] = field(default_factory=list)
     apply_to_int: bool = False
+    fpmath: int = 0  # dnnl_fpmath_mode_t: 0 strict, 1 bf16, 2 f16, 3 any, 4 tf32
     # grouped (MoE) problems: cumulative END row of each group
     offsets: Optional[np.ndarray] = None
     dst_init: Optional[np.ndarray] = None  # dst contents before the call (sum)
@@ -262,7 +263,7 @@ def fp8_prefill(M=4096, K=4096, N=14336, seed=20262, src_dt=F8_E4M3, wei_dt=F8_E
 
 
 def int4_decode(M=1, K=8192, N=28672, group=128, seed=20263, wei_dt=S4, zp_dt=U4,
-                src_dt=BF16, with_zp=True) -> Problem:
+                src_dt=BF16, with_zp=True, dst_dt=BF16) -> Problem:
     """bf16 src x s4 weights with bf16 scales and u4 zero-points per
     (K/group, N); fpmath bf16 with apply_to_int (weights decompression)."""
     r = _rng(seed)
@@ -283,7 +284,8 @@ def int4_decode(M=1, K=8192, N=28672, group=128, seed=20263, wei_dt=S4, zp_dt=U4
         z = r.integers(0, 16, (G, N), dtype=np.int64)
         q["wei_zp"] = Quant(to_storage(z, zp_dt), zp_dt, 3, (group, 1))
     return Problem("int4_decode", M, N, K, QTensor(src, src_dt, (M, K)),
-                   QTensor(wei, wei_dt, (K, N)), BF16, quant=q, apply_to_int=True)
+                   QTensor(wei, wei_dt, (K, N)), dst_dt, quant=q, apply_to_int=True,
+                   fpmath=2 if src_dt == F16 else 1)
 
 
 def int8_postops(M=2048, K=4096, N=11008, seed=20264, dst_scale=None) -> Problem:
@@ -331,5 +333,5 @@ def moe_grouped(total_M=8192, K=4096, N=14336, experts=64, seed=20265, sizes=Non
     ws = r.uniform(0.001, 0.01, (experts, 1, N)).astype(np.float32)
     q = {"wei_scale": Quant(ws, F32, 0b101)}
     return Problem("moe_grouped", total_M, N, K, QTensor(src, BF16, (total_M, K)),
-                   QTensor(wei, S8, (experts, K, N)), BF16, quant=q, apply_to_int=True,
+                   QTensor(wei, S8, (experts, K, N)), BF16, quant=q, apply_to_int=True, fpmath=1,
                    offsets=offsets)

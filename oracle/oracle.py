@@ -45,7 +45,7 @@ class _Problem(C.Structure):
                 ("sum_dt", C.c_int32), ("n_po", C.c_int32), ("po", _PostOp * 32),
                 ("rows", C.c_void_p), ("n_rows", C.c_int64),
                 ("group_count", C.c_int64), ("offsets", C.c_void_p),
-                ("wei_sg", C.c_int64), ("bias_sg", C.c_int64)]
+                ("wei_sg", C.c_int64), ("bias_sg", C.c_int64), ("fpmath_mode", C.c_int32)]
 
 
 _port = None
@@ -121,6 +121,7 @@ def _marshal(p: W.Problem, rows=None):
         d1 = {"src": p.K, "wei": p.N, "dst": p.N}[name[:3]]
         cq.ld = (d1 // cq.g1) if (mask & 2) else 1
     s.apply_to_int = int(p.apply_to_int)
+    s.fpmath_mode = p.fpmath
     s.non_default_attr = int(bool(p.quant) or bool(p.post_ops) or p.apply_to_int)
     s.sum_dt = p.dst_dt
     s.n_po = len(p.post_ops)

@@ -93,6 +93,9 @@ typedef struct {
     const int32_t *offsets; /* cumulative END row per group */
     int64_t wei_sg; /* weights stride between groups */
     int64_t bias_sg;
+    /* dnnl_fpmath_mode_t value (0 strict, 1 bf16, 2 f16, 3 any, 4 tf32); only
+     * the reference runner needs it, to build the same attribute */
+    int32_t fpmath_mode;
 } qmm_problem_t;
 
 /* src in {s8,u8}: follows ref_matmul_int8.cpp:40-309. returns 0 on success */

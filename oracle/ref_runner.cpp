@@ -75,7 +75,8 @@ built_t build(const qmm_problem_t &p, const engine &eng, int pin_ref) {
     const bool grouped = p.group_count > 0;
     std::unordered_map<int, memory> args;
     primitive_attr attr;
-    if (p.apply_to_int) attr.set_fpmath_mode(fpmath_mode::bf16, true);
+    if (p.apply_to_int || p.fpmath_mode)
+        attr.set_fpmath_mode(static_cast<fpmath_mode>(p.fpmath_mode), p.apply_to_int != 0);
 
     memory::desc src_md, wei_md, dst_md, bia_md;
     if (grouped) {
