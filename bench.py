@@ -1,0 +1,389 @@
+"""Benchmark of the quantized matmul hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl reference]
+
+A step is one execution of the workload's matmul through the library's C API.
+Default workload: the fp8 prefill GEMM (e4m3 [4096,4096] x e4m3 [4096,14336]
+-> bf16, per-tensor scales, bf16 bias).  For N > 1 (launched under torchrun)
+the weights are sharded by output columns, every rank computes its N-slice
+and the slices are assembled with an NCCL all-gather; the total problem is
+fixed, so scaling is "strong".
+
+One JSON line is printed by rank 0:
+  value     whole-job throughput with inputs resident in HBM, timed with CUDA
+            events on the launching stream (max over ranks)
+  e2e       the same metric with the step's src copied from pinned host memory
+            and the dst read back to the host inside the timed region
+  roofline  algorithmic work of one launch / its average duration, against the
+            measured peak in MEASURED_PEAKS.json
+  cpu_baseline  the reference's CPU matmul on a bounded sample of the workload
+`--impl reference` times that CPU implementation alone (rank 0 only).
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+from onednn_b200 import workloads as W  # noqa: E402
+
+WORKLOADS = {
+    # name: (factory, metric, unit, bound, compute dtype)
+    "fp8_prefill": (lambda **kw: W.fp8_prefill(**kw), "fp8_matmul_tflops", "TFLOP/s", "tensor", "f8_e4m3"),
+    "int8_postops": (lambda **kw: W.int8_postops(**kw), "int8_matmul_tops", "TOP/s", "tensor", "s8"),
+    "int8_zp": (lambda **kw: W.int8_zp(**kw), "int8_matmul_tops", "TOP/s", "tensor", "u8"),
+    "int4_decode": (lambda **kw: W.int4_decode(**kw), "int4_decode_hbm_gbs", "GB/s", "hbm", "bf16"),
+    "moe_grouped": (lambda **kw: W.moe_grouped(**kw), "moe_matmul_tflops", "TFLOP/s", "tensor", "bf16"),
+}
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--workload", default="fp8_prefill", choices=sorted(WORKLOADS))
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--kernel", default=None, help="pin an implementation by name substring")
+    ap.add_argument("--M", type=int, default=None, help="override M (decode: 1, 8 or 32)")
+    ap.add_argument("--small", action="store_true", help="reduced sizes (profiling captures)")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    return ap.parse_args()
+
+
+def make_problem(args):
+    kw = {}
+    if args.M is not None:
+        kw["total_M" if args.workload == "moe_grouped" else "M"] = args.M
+    if args.small:
+        small = {"fp8_prefill": dict(M=2048, K=2048, N=8192), "int8_postops": dict(M=1024, K=2048, N=4096),
+                 "int4_decode": dict(K=8192, N=16384), "moe_grouped": dict(total_M=2048, K=2048, N=4096, experts=16),
+                 "int8_zp": {}}[args.workload]
+        small.update(kw)
+        kw = small
+    return WORKLOADS[args.workload][0](**kw)
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while a region runs."""
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.proc, self.lines = index, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.Q, "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.t = threading.Thread(target=self._read, daemon=True)
+            self.t.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 7:
+                continue
+            try:
+                sm.append(float(f[0]))
+                mx.append(float(f[1]))
+            except ValueError:
+                continue
+            for n, v in zip(names, f[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        d = json.load(open(path))
+        return {"hbm_gbs": d["hbm_gbs"], "bf16_tflops": d["bf16_tflops"],
+                "bf16_tflops_sustained": d.get("bf16_tflops_sustained", d["bf16_tflops"]), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+# ------------------------------------------------------------------ GPU arm
+def device_buffers(p, torch, dev):
+    """Uploads every tensor of the problem once; returns (ptr dict, keepalive)."""
+    keep, ptrs = {}, {}
+
+    def up(name, arr):
+        t = torch.from_numpy(np.ascontiguousarray(arr).view(np.uint8).reshape(-1)).to(dev)
+        keep[name] = t
+        ptrs[name] = t.data_ptr()
+        return t
+
+    up("src", p.src.data)
+    up("wei", p.wei.data)
+    if p.bias is not None:
+        up("bias", p.bias.data)
+    for name, q in p.quant.items():
+        up(name, q.data)
+    for i, po in enumerate(p.post_ops):
+        if po.src1 is not None:
+            up("po%d" % i, po.src1.data)
+    if p.offsets is not None:
+        up("offsets", p.offsets)
+    dst = torch.zeros(max(1, W.nbytes(p.dst_dt, p.M * p.N)), dtype=torch.uint8, device=dev)
+    keep["dst"] = dst
+    ptrs["dst"] = dst.data_ptr()
+    return ptrs, keep
+
+
+def run_gpu(args):
+    import torch
+    import torch.distributed as dist
+    from onednn_b200 import api, sharding
+    from onednn_b200.runner import Prepared
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    name = args.workload
+    _, metric, unit, bound, dtype = WORKLOADS[name]
+    full = make_problem(args)
+    p = sharding.shard(full, rank, world)
+
+    eng = api.engine(api.engine.kind.gpu, local_rank)
+    tstream = torch.cuda.current_stream()
+    strm = api.stream(eng, tstream.cuda_stream)
+    ptrs, keep = device_buffers(p, torch, dev)
+    prep = Prepared(p, eng, args.kernel).bind_device(ptrs)
+    # decode streams ~L2-sized weights: rotate among copies so no step finds them in L2
+    rotate = []
+    if name == "int4_decode":
+        for _ in range(3):
+            w2 = keep["wei"].clone()
+            keep["wei%d" % len(rotate)] = w2
+            pr2 = dict(ptrs)
+            pr2["wei"] = w2.data_ptr()
+            rotate.append(Prepared(p, eng, args.kernel).bind_device(pr2))
+    preps = rotate or [prep]
+
+    dst_t = keep["dst"]
+    elem = {W.BF16: torch.bfloat16, W.F16: torch.float16, W.F32: torch.float32, W.S32: torch.int32,
+            W.S8: torch.int8, W.U8: torch.uint8}[p.dst_dt]
+    rows_per_rank = None
+    if full.offsets is not None and world > 1:
+        ends = full.offsets.astype(np.int64)
+        rows_per_rank = []
+        for r in range(world):
+            e0, e1 = sharding.expert_range(full.groups, r, world)
+            rows_per_rank.append(int((ends[e1 - 1] if e1 > e0 else (ends[e0 - 1] if e0 else 0)) - (ends[e0 - 1] if e0 else 0)))
+
+    def gather():
+        if world == 1:
+            return None
+        local = dst_t.view(elem).view(p.M, p.N)
+        if rows_per_rank is not None:
+            return sharding.gather_rows(local, rows_per_rank)
+        return sharding.gather_columns(local, full.N, world)
+
+    def step(i):
+        preps[i % len(preps)].execute(strm)
+        return gather()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for i in range(max(3, args.warmup)):
+        step(i)
+    barrier()
+
+    # ---- device-timed region: inputs resident in HBM
+    sampler = ClockSampler(local_rank).start() if rank == 0 else None
+    launches0 = api.launch_count()
+    k_ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for i in range(args.steps):
+        k_ev[i][0].record()
+        preps[i % len(preps)].execute(strm)
+        k_ev[i][1].record()
+        gather()
+    e1.record()
+    barrier()
+    launches = api.launch_count() - launches0
+    clocks = sampler.stop() if sampler else None
+    total_ms = e0.elapsed_time(e1)
+    kernel_ms = float(np.mean([a.elapsed_time(b) for a, b in k_ev]))
+
+    # ---- end-to-end: src from pinned host memory, dst back to the host, every step
+    src_host = torch.from_numpy(p.src.data.view(np.uint8).reshape(-1).copy()).pin_memory()
+    out_bytes = W.nbytes(full.dst_dt, full.M * full.N) if world > 1 else dst_t.numel()
+    dst_host = torch.empty(out_bytes, dtype=torch.uint8).pin_memory()
+    e2e_steps = max(3, min(args.steps, 10))
+
+    def e2e_step(i):
+        keep["src"].copy_(src_host, non_blocking=True)
+        g = step(i)
+        res = dst_t if g is None else g.view(torch.uint8).view(-1)
+        dst_host[:res.numel()].copy_(res, non_blocking=True)
+
+    e2e_step(0)
+    barrier()
+    f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    f0.record()
+    for i in range(e2e_steps):
+        e2e_step(i)
+    f1.record()
+    barrier()
+    e2e_ms = f0.elapsed_time(f1) / e2e_steps
+
+    t = torch.tensor([total_ms, kernel_ms, e2e_ms], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    total_ms, kernel_ms, e2e_ms = [float(x) for x in t.tolist()]
+    ms_per_step = total_ms / args.steps
+
+    if rank == 0:
+        pk = peaks()
+        if bound == "hbm":
+            work_full, work_launch, per = full.algorithmic_bytes() / 1e9, p.algorithmic_bytes() / 1e9, 1e-3
+            peak, runit = pk["hbm_gbs"], "GB/s"
+        else:
+            work_full, work_launch, per = full.ops() / 1e12, p.ops() / 1e12, 1e-3
+            # fp8 / int8 tensor peak: twice the measured dense bf16 figure (the
+            # 8-bit MMA rate is twice the 16-bit one); bf16 workloads use it as is
+            mult = 1.0 if dtype == "bf16" else 2.0
+            peak, runit = mult * pk["bf16_tflops"], "TFLOP/s"
+        value = work_full / (ms_per_step * per)
+        achieved = work_launch / (kernel_ms * per)
+        line = {
+            "metric": metric, "value": value, "unit": unit, "n_gpus": world, "steps": args.steps,
+            "warmup": max(3, args.warmup), "ms_per_step": ms_per_step, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": dtype, "data": "synthetic",
+            "config": {"workload": "%s M=%d K=%d N=%d" % (name, full.M, full.K, full.N),
+                       "kernel": prep.impl, "parallelism": "n-shard x%d + all-gather" % world if world > 1 else "single",
+                       "l2": "weight copies rotated (3 x %.0f MB)" % (p.wei.data.nbytes / 1e6) if rotate
+                             else "working set %.0f MB > 126 MB L2" % (p.algorithmic_bytes() / 1e6),
+                       "e2e": "src H2D from pinned memory and dst D2H every step; weights resident"},
+            "roofline": {"bound": bound, "achieved": achieved, "peak": peak, "unit": runit,
+                         "frac": achieved / peak, "traffic": None, "peak_source": pk["source"],
+                         "kernel_ms": kernel_ms},
+            "e2e": {"value": work_full / (e2e_ms * per), "unit": unit,
+                    "h2d_bytes_per_step": int(src_host.numel()), "d2h_bytes_per_step": int(out_bytes),
+                    "ms_per_step": e2e_ms},
+            "gpu_launches": int(launches), "clocks": clocks,
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            line["cpu_baseline"] = cpu_baseline(full, name, bound, seconds=15.0)
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+# ------------------------------------------------------- CPU reference arm
+def cpu_sample(full, name, target_s):
+    """A bounded sample of the workload for the CPU: a seeded subset of src
+    rows (dense) or a smaller token count (grouped); K, N and every attribute
+    are those of the full problem.  Sized from a short probe so one execution
+    takes about target_s seconds."""
+    if full.offsets is not None:
+        def make(m):
+            return W.moe_grouped(total_M=m, K=full.K, N=full.N, experts=full.groups), "total_M=%d of %d" % (m, full.M)
+    else:
+        def make(m):
+            rows = np.sort(np.random.Generator(np.random.PCG64(7)).choice(full.M, size=m, replace=False))
+            return full.take_rows(rows), "%d of %d src rows" % (m, full.M)
+    return make
+
+
+def time_cpu(p, iters):
+    """(ms, implementation, kind) of the reference CPU matmul on problem p:
+    the unmodified reference library when a build of it is present (first
+    implementation it dispatches), else the C restatement of its scalar code."""
+    from oracle import oracle as O
+    if O.ref_available():
+        _, impl, ms = O.run_ref(p, pin_ref=False, iters=iters)
+        return ms, impl, "reference"
+    best = 1e30
+    for _ in range(iters):
+        t0 = time.perf_counter()
+        O.run_port(p)
+        best = min(best, (time.perf_counter() - t0) * 1e3)
+    return best, "oracle port of ref*:any", "port"
+
+
+def cpu_baseline(full, name, bound, seconds=15.0, iters=2):
+    os.environ.setdefault("OMP_NUM_THREADS", str(os.cpu_count() or 1))
+    make = cpu_sample(full, name, seconds)
+    m = 1 if full.offsets is None else full.groups
+    m = min(m, full.M)
+    p, what = make(m)
+    ms, impl, kind = time_cpu(p, 1)
+    # grow the sample until one execution is worth timing, within the budget
+    while ms * 4 < seconds * 1e3 / (iters + 1) and m < full.M:
+        m = min(full.M, m * 4)
+        p, what = make(m)
+        ms, impl, kind = time_cpu(p, 1)
+    if ms * (iters + 1) < seconds * 1e3:
+        ms2, impl, kind = time_cpu(p, iters)
+        ms = min(ms, ms2)
+    work = (p.algorithmic_bytes() / 1e9) if bound == "hbm" else (p.ops() / 1e12)
+    return {"value": work / (ms * 1e-3), "unit": "GB/s" if bound == "hbm" else "TFLOP/s",
+            "cores": int(os.environ["OMP_NUM_THREADS"]), "kind": kind, "impl": impl,
+            "ms": ms, "sample": "%s, K=%d N=%d, %.1f ms per execution" % (what, p.K, p.N, ms)}
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    name = args.workload
+    _, metric, unit, bound, dtype = WORKLOADS[name]
+    full = make_problem(args)
+    budget = 20.0
+    base = cpu_baseline(full, name, bound, seconds=budget, iters=max(1, min(args.steps, 3)))
+    world = int(os.environ.get("WORLD_SIZE", str(args.gpus)))
+    line = {"impl": "reference", "metric": metric, "value": base["value"], "unit": unit, "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": base["ms"], "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": dtype, "data": "synthetic",
+            "config": {"workload": "%s M=%d K=%d N=%d" % (name, full.M, full.K, full.N), "sample": base["sample"]},
+            "cpu_baseline": base,
+            "e2e": {"value": base["value"], "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line), flush=True)
+
+
+if __name__ == "__main__":
+    a = parse_args()
+    if a.impl == "reference":
+        run_reference(a)
+    else:
+        run_gpu(a)
