@@ -53,6 +53,8 @@ def parse_args():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--kernel", default=None, help="pin an implementation by name substring")
     ap.add_argument("--M", type=int, default=None, help="override M (decode: 1, 8 or 32)")
+    ap.add_argument("--K", type=int, default=None)
+    ap.add_argument("--N", type=int, default=None)
     ap.add_argument("--small", action="store_true", help="reduced sizes (profiling captures)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     return ap.parse_args()
@@ -62,6 +64,10 @@ def make_problem(args):
     kw = {}
     if args.M is not None:
         kw["total_M" if args.workload == "moe_grouped" else "M"] = args.M
+    if args.K is not None:
+        kw["K"] = args.K
+    if args.N is not None:
+        kw["N"] = args.N
     if args.small:
         small = {"fp8_prefill": dict(M=2048, K=2048, N=8192), "int8_postops": dict(M=1024, K=2048, N=4096),
                  "int4_decode": dict(K=8192, N=16384), "moe_grouped": dict(total_M=2048, K=2048, N=4096, experts=16),

@@ -352,8 +352,40 @@ dnnl_status_t ref_grouped_accepts(const dnnl_primitive_desc &pd) {
     return dnnl_success;
 }
 
+// tcgen05 GEMM: dense 2D, 8-bit x 8-bit, quantization parameters constant
+// along K; everything the reference implementation of the same problem
+// accepts, minus K-grouped parameters and precomputed reductions.
+dnnl_status_t tc_accepts(const dnnl_primitive_desc &pd) {
+    if (ref_dense_accepts(pd) != dnnl_success) return dnnl_unimplemented;
+    const auto s = pd.src.data_type, w = pd.wei.data_type;
+    const auto &attr = pd.attr;
+    const bool int_path = is_int8(s);
+    UNIMPL_IF(!((int_path && is_int8(w)) || (is_fp8(s) && is_fp8(w))));
+    const dnnl_dim_t M = pd.M(), N = pd.N(), K = pd.K();
+    UNIMPL_IF(M == 0 || N == 0 || K == 0);
+    UNIMPL_IF(M >= (1LL << 31) || N >= (1LL << 31) || K >= (1LL << 31));
+    // TMA: rows of 16-byte multiples; src K-contiguous, weights `ab` or `ba`
+    UNIMPL_IF(pd.src.strides[1] != 1 || pd.src.strides[0] % 16 != 0 || pd.src.strides[0] < K);
+    const bool ab = pd.wei.strides[1] == 1 && pd.wei.strides[0] % 16 == 0 && pd.wei.strides[0] >= N;
+    const bool ba = pd.wei.strides[0] == 1 && pd.wei.strides[1] % 16 == 0 && pd.wei.strides[1] >= K && N > 1;
+    UNIMPL_IF(!ab && !ba);
+    const auto &ss = attr.scale(DNNL_ARG_SRC), &ws = attr.scale(DNNL_ARG_WEIGHTS);
+    if (ss.set) UNIMPL_IF(ss.group_ndims || !(ss.mask == 0 || (ss.mask == 1 && int_path)));
+    if (ws.set) UNIMPL_IF(ws.group_ndims || !(ws.mask == 0 || ws.mask == 2));
+    const auto &sz = attr.zp(DNNL_ARG_SRC), &wz = attr.zp(DNNL_ARG_WEIGHTS);
+    if (sz.set) UNIMPL_IF(sz.group_ndims || sz.mask != 0 || sz.dt != dnnl_s32 || sz.on_host);
+    if (wz.set) UNIMPL_IF(wz.group_ndims || !(wz.mask == 0 || wz.mask == 2) || wz.on_host);
+    UNIMPL_IF(!attr.reductions.empty());
+    // |acc - compensation| must stay within s32 as in the reference's own sum
+    return dnnl_success;
+}
+
 dnnl_status_t impl_accepts(const dnnl_primitive_desc &pd, int impl, std::string &name) {
     switch (impl) {
+        case IMPL_TCGEN05_GEMM:
+            if (pd.grouped) return dnnl_unimplemented;
+            name = is_int8(pd.src.data_type) ? "cuda:tcgen05:int8" : "cuda:tcgen05:fp8";
+            return tc_accepts(pd);
         case IMPL_REF:
             name = pd.grouped ? "cuda:ref_grouped:any" : is_int8(pd.src.data_type) ? "cuda:ref_int8:any" : "cuda:ref:any";
             return pd.grouped ? ref_grouped_accepts(pd) : ref_dense_accepts(pd);
@@ -367,6 +399,19 @@ dnnl_status_t select_impl(dnnl_primitive_desc &pd, int first) {
         if (impl_accepts(pd, i, name) == dnnl_success) {
             pd.impl = i;
             pd.impl_name = name;
+            // scratchpad: the tensor-core GEMM keeps its zero-point
+            // compensation sums there
+            pd.scratch_bytes = 0;
+            if (i == IMPL_TCGEN05_GEMM && (pd.attr.zp(DNNL_ARG_SRC).set || pd.attr.zp(DNNL_ARG_WEIGHTS).set))
+                pd.scratch_bytes = gemm_tc_scratch_bytes(pd.M(), pd.N());
+            pd.scratchpad = dnnl_memory_desc();
+            if (pd.scratch_bytes && pd.attr.scratchpad_mode == dnnl_scratchpad_mode_user) {
+                pd.scratchpad.ndims = 1;
+                pd.scratchpad.dims[0] = (dnnl_dim_t)pd.scratch_bytes;
+                pd.scratchpad.strides[0] = 1;
+                pd.scratchpad.data_type = dnnl_u8;
+                pd.scratchpad.format_kind = dnnl_blocked;
+            }
             return dnnl_success;
         }
     }
@@ -543,6 +588,16 @@ dnnl_status_t dnnl_primitive_create(dnnl_primitive_t *primitive, const_dnnl_prim
     if (!primitive || !pd) return dnnl_invalid_arguments;
     auto *p = new dnnl_primitive;
     p->pd = *pd;
+    if (pd->scratch_bytes && pd->attr.scratchpad_mode == dnnl_scratchpad_mode_library) {
+        if (pd->engine->device < 0) { /* device-less engine: nothing to allocate */ }
+        else {
+            cudaSetDevice(pd->engine->device);
+            if (!cuda_ok(cudaMalloc(&p->scratch, pd->scratch_bytes), "cudaMalloc(scratchpad)")) {
+                delete p;
+                return dnnl_out_of_memory;
+            }
+        }
+    }
     *primitive = p;
     return dnnl_success;
 }
@@ -561,6 +616,7 @@ dnnl_status_t dnnl_primitive_get_primitive_desc(const_dnnl_primitive_t primitive
 }
 
 dnnl_status_t dnnl_primitive_destroy(dnnl_primitive_t primitive) {
+    if (primitive && primitive->scratch) cudaFree(primitive->scratch);
     delete primitive;
     return dnnl_success;
 }
@@ -723,9 +779,21 @@ extern "C" dnnl_status_t dnnl_primitive_execute(const_dnnl_primitive_t primitive
         cudaEventCreate(&ev0); cudaEventCreate(&ev1);
         cudaEventRecord(ev0, stream->stream);
     }
+    void *scratch = primitive->scratch;
+    if (pd.scratch_bytes && pd.attr.scratchpad_mode == dnnl_scratchpad_mode_user) {
+        dnnl_memory_t sp = am.find(DNNL_ARG_SCRATCHPAD);
+        if (!sp || !sp->handles[0]) return dnnl_invalid_arguments;
+        scratch = sp->handles[0];
+    }
     int rc;
     switch (pd.impl) {
         case IMPL_REF: rc = launch_ref(a, stream->stream); break;
+        case IMPL_TCGEN05_GEMM:
+            // TMA needs 16-byte aligned base pointers; a misaligned user
+            // pointer is served by the generic kernel instead
+            if (!gemm_tc_pointers_ok(a)) rc = launch_ref(a, stream->stream);
+            else rc = launch_gemm_tc(a, scratch, pd.engine->sm_count, stream->stream);
+            break;
         default: rc = dnnl_unimplemented;
     }
     if (verbose) {

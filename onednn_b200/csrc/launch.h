@@ -14,4 +14,11 @@ void count_launch(int n = 1);
 // generic one-thread-per-element kernels, every attribute (ref_kernel.cu)
 int launch_ref(const MatmulArgs &a, cudaStream_t st);
 
+// tcgen05 int8 / fp8 GEMM (gemm_tc.cu).  `scratch` holds the zero-point
+// compensation terms: gemm_tc_scratch_bytes(M, N) bytes, may be null when the
+// problem has no zero-points.
+int launch_gemm_tc(const MatmulArgs &a, void *scratch, int sm_count, cudaStream_t st);
+size_t gemm_tc_scratch_bytes(int64_t M, int64_t N);
+bool gemm_tc_pointers_ok(const MatmulArgs &a);
+
 } // namespace qmm

@@ -138,6 +138,7 @@ struct dnnl_primitive_desc {
     int impl = IMPL_REF;
     std::string impl_name;
     std::map<int, dnnl_memory_desc> quant_mds; // exec-arg id -> parameter md
+    size_t scratch_bytes = 0; // device scratch the chosen implementation needs
     dnnl_dim_t M() const { return dst.dims[dst.ndims - 2]; }
     dnnl_dim_t N() const { return dst.dims[dst.ndims - 1]; }
     dnnl_dim_t K() const { return src.dims[src.ndims - 1]; }
@@ -145,6 +146,10 @@ struct dnnl_primitive_desc {
 
 struct dnnl_primitive {
     dnnl_primitive_desc pd;
+    // scratch owned by the primitive (scratchpad_mode_library); like oneDNN's
+    // library scratchpad it makes concurrent execute calls of ONE primitive
+    // object unsafe
+    void *scratch = nullptr;
 };
 
 namespace qmm {

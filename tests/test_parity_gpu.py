@@ -6,7 +6,15 @@ import pytest
 from onednn_b200 import workloads as W
 from onednn_b200.runner import run_problem
 from oracle import oracle as O
-from util import assert_parity
+from util import assert_parity, summation_slack
+
+
+def slack_for(p, impl):
+    """Summation slack only for floating-point sums taken in another order
+    than the reference's (every implementation but the cuda:ref kernels)."""
+    if impl.startswith("cuda:ref") or p.src.dt in (W.S8, W.U8) or p.offsets is not None:
+        return None
+    return summation_slack(p)
 
 pytestmark = pytest.mark.gpu
 
@@ -44,7 +52,51 @@ def test_default_impl_matches_oracle(gpu, name):
     p = CASES[name]()
     want = O.run_port(p)
     got, impl = run_problem(p, eng, strm)
-    assert_parity(got, want, p.dst_dt, "%s via %s" % (name, impl))
+    assert_parity(got, want, p.dst_dt, "%s via %s" % (name, impl), slack_for(p, impl))
+
+
+def _ba(p):
+    """Same problem with the weights stored K-contiguous (format tag `ba`)."""
+    w = p.wei.data.reshape(p.K, p.N)
+    p.wei = W.QTensor(np.ascontiguousarray(w.T), p.wei.dt, (p.K, p.N), (1, p.K))
+    return p
+
+
+def _wei_zp(p, per_n):
+    r = np.random.Generator(np.random.PCG64(3))
+    z = r.integers(-5, 6, (1, p.N) if per_n else (1,)).astype(np.int32)
+    p.quant["wei_zp"] = W.Quant(z, W.S32, 2 if per_n else 0)
+    return p
+
+
+TC_CASES = {
+    "cfg1_s32": lambda: W.int8_zp(256, 1024, 1024),
+    "cfg1_f32": lambda: W.int8_zp(256, 1024, 1024, per_n_scales=True),
+    "int8_tails": lambda: W.int8_zp(200, 272, 176),
+    "int8_one_tile": lambda: W.int8_zp(5, 16, 16),
+    "int8_wide": lambda: W.int8_zp(384, 512, 9984),
+    "int8_ba": lambda: _ba(W.int8_zp(130, 256, 320)),
+    "int8_wzp": lambda: _wei_zp(W.int8_zp(96, 256, 160), False),
+    "int8_wzp_per_n": lambda: _wei_zp(W.int8_zp(96, 256, 160, per_n_scales=True), True),
+    "int8_postops": lambda: W.int8_postops(256, 512, 512),
+    "int8_postops_tails": lambda: W.int8_postops(77, 144, 208),
+    "fp8": lambda: W.fp8_prefill(256, 512, 512),
+    "fp8_tails": lambda: W.fp8_prefill(300, 528, 272),
+    "fp8_wide": lambda: W.fp8_prefill(256, 256, 10240),
+    "fp8_ba": lambda: _ba(W.fp8_prefill(128, 384, 256)),
+    "fp8_e5m2": lambda: W.fp8_prefill(64, 256, 128, src_dt=W.F8_E5M2, wei_dt=W.F8_E5M2),
+    "fp8_mixed": lambda: W.fp8_prefill(64, 256, 128, src_dt=W.F8_E4M3, wei_dt=W.F8_E5M2),
+}
+
+
+@pytest.mark.parametrize("name", sorted(TC_CASES))
+def test_tcgen05_gemm_matches_oracle(gpu, name):
+    eng, strm = gpu
+    p = TC_CASES[name]()
+    want = O.run_port(p)
+    got, impl = run_problem(p, eng, strm, impl="tcgen05")
+    assert impl.startswith("cuda:tcgen05")
+    assert_parity(got, want, p.dst_dt, name, slack_for(p, impl))
 
 
 def test_grouped_bad_offsets_reports_invalid_arguments(gpu):
