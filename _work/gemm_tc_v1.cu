@@ -1,0 +1,475 @@
+// "cuda:tcgen05" GEMM for 8-bit operands: int8 (u8/s8 x u8/s8 -> s32
+// accumulate) and fp8 (e4m3/e5m2 -> f32 accumulate).
+//
+// One persistent CTA per SM walks output tiles of 128 x BN.  Three roles:
+//   warp 0     TMA producer: src tile [128 rows x 128 B of K] and weights tile
+//              ([128 k x BN] for N-contiguous `ab` weights, [BN x 128 B of K]
+//              for `ba`) into a ring of 128B-swizzled shared-memory stages
+//   warp 1     issues tcgen05.mma (M=128, N=BN, K=32 per instruction) into one
+//              of two TMEM accumulator buffers and commits to mbarriers
+//   warps 2-5  epilogue: TMEM -> registers, zero-point compensation, scales,
+//              bias, post-op chain, dst scale / zero-point, saturating store;
+//              runs while the next tile is being multiplied
+// Arithmetic of the epilogue follows the reference (ref_matmul_int8.cpp:
+// 241-304, ref_matmul.cpp:218-332): integer sums are exact, so int8 results
+// are the reference's bit for bit; fp8 differs only by f32 summation order.
+#include <cuda.h>
+
+#include "device_math.cuh"
+#include "launch.h"
+#include "sm100_ptx.cuh"
+
+namespace qmm {
+
+namespace {
+
+constexpr int BM = 128; // tile rows = TMEM lanes
+constexpr int BKB = 128; // bytes (= 8-bit elements) of K per stage: one swizzle row
+constexpr int UMMA_K = 32; // K per tcgen05.mma for 8-bit operands
+constexpr int NUM_EPI_WARPS = 8; // two per TMEM lane quarter, each half of the tile's columns
+constexpr int NUM_THREADS = 64 + 32 * NUM_EPI_WARPS;
+
+struct TcParams {
+    int num_m_tiles, num_n_tiles, num_k_blocks;
+    uint32_t idesc;
+    int b_kmajor; // weights are `ba` (K contiguous)
+    int int_path; // s32 accumulators
+    int mainloop_only; // ONEDNN_CUDA_TC_MAINLOOP_ONLY=1: skip the epilogue (profiling aid)
+    const int32_t *colsum; // sum_k w[k][n]       (src zero-point compensation)
+    const int32_t *rowsum; // sum_k s[m][k]       (weights zero-point compensation)
+};
+
+template <int BN, int STAGES>
+struct SmemLayout {
+    static constexpr int A_BYTES = BM * BKB;
+    static constexpr int B_BYTES = BN * BKB;
+    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+    static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES;
+    static constexpr int EPI_OFFSET = BAR_OFFSET + 256; // after the barriers
+    static constexpr int EPI_PITCH = 33; // words per row of a warp's 32x32 transpose tile
+    static constexpr int EPI_BYTES = NUM_EPI_WARPS * 32 * EPI_PITCH * 4;
+    static constexpr int TOTAL = EPI_OFFSET + EPI_BYTES + 1024; // + alignment slack
+};
+
+// Per-column terms of the epilogue, held by the lane that owns the column.
+struct ColTerms {
+    float wei_scale; // 1 when absent
+    float bias; // bias[n] when the bias is a row vector
+    int zs_colsum; // src_zp * colsum[n] - K * src_zp * wei_zp[n]
+    int wei_zp; // wei_zp[n]
+    float dst_zp; // dst_zp[n] when per-N
+};
+
+__device__ __forceinline__ ColTerms load_col_terms(const MatmulArgs &a, const TcParams &tp, int64_t n) {
+    ColTerms c;
+    c.wei_scale = 1.f;
+    c.bias = 0.f;
+    c.zs_colsum = 0;
+    c.wei_zp = 0;
+    c.dst_zp = 0.f;
+    if (n >= a.N) return c;
+    if (a.dst_zp.ptr && a.dst_zp.mask > 0) c.dst_zp = (float)((const int *)a.dst_zp.ptr)[n];
+    if (a.wei_scale.ptr) c.wei_scale = load_float(a.wei_scale.dt, a.wei_scale.ptr, (a.wei_scale.mask & 2) ? n : 0);
+    else if (a.wei_scale.on_host) c.wei_scale = a.wei_scale.host_value;
+    if (a.bias && a.bias_sm == 0) c.bias = load_float(a.bias_dt, a.bias, n * a.bias_sn);
+    if (tp.int_path) {
+        if (a.wei_zp.ptr) c.wei_zp = load_int(a.wei_zp.dt, a.wei_zp.ptr, (a.wei_zp.mask & 2) ? n : 0);
+        if (a.src_zp.ptr) {
+            const int zs = ((const int *)a.src_zp.ptr)[0];
+            c.zs_colsum = zs * tp.colsum[n] - (int)a.K * zs * c.wei_zp;
+        }
+    }
+    return c;
+}
+
+// Per-tensor terms of the epilogue, read once per thread.
+struct TensorTerms {
+    bool has_dst_scale, has_dst_zp, dst_zp_per_n;
+    float dst_scale, dst_zp;
+};
+
+__device__ __forceinline__ TensorTerms load_tensor_terms(const MatmulArgs &a, bool int_path) {
+    TensorTerms t;
+    t.has_dst_scale = a.non_default_attr && (a.dst_scale.ptr || a.dst_scale.on_host);
+    t.dst_scale = a.dst_scale.ptr ? load_float(a.dst_scale.dt, a.dst_scale.ptr, 0) : a.dst_scale.host_value;
+    // the floating-point reference path has no dst zero-point
+    t.has_dst_zp = a.non_default_attr && int_path && a.dst_zp.ptr;
+    t.dst_zp_per_n = a.dst_zp.mask > 0;
+    t.dst_zp = (t.has_dst_zp && !t.dst_zp_per_n) ? (float)((const int *)a.dst_zp.ptr)[0] : 0.f;
+    return t;
+}
+
+// Typed stores of one f32 value, saturating / rounding as the reference does
+// (src/cpu/simple_q10n.hpp:41-81, src/common/bfloat16.cpp:22-47: f32
+// subnormals flush to signed zero before the bf16 rounding).
+template <int DST>
+__device__ __forceinline__ void store_typed(void *p, float v) {
+    if constexpr (DST == DT_F32) {
+        *(float *)p = v;
+    } else if constexpr (DST == DT_BF16) {
+        if (fabsf(v) < 1.17549435e-38f) v = copysignf(0.f, v);
+        *(__nv_bfloat16 *)p = __float2bfloat16_rn(v);
+    } else if constexpr (DST == DT_F16) {
+        *(__half *)p = __float2half_rn(v);
+    } else if constexpr (DST == DT_S32) {
+        v = fminf(fmaxf(v, -2147483648.f), 2147483520.f);
+        *(int *)p = __float2int_rn(v);
+    } else if constexpr (DST == DT_S8) {
+        *(signed char *)p = (signed char)__float2int_rn(fminf(fmaxf(v, -128.f), 127.f));
+    } else {
+        *(unsigned char *)p = (unsigned char)__float2int_rn(fminf(fmaxf(v, 0.f), 255.f));
+    }
+}
+template <int DST> struct dst_size { static constexpr int value = (DST == DT_F32 || DST == DT_S32) ? 4 : (DST == DT_BF16 || DST == DT_F16) ? 2 : 1; };
+
+// The rows of one transposed 32x32 accumulator tile: lane = dst column n,
+// loop over the warp's rows.  Per element: zero-point compensation (INT),
+// src / weights scales, bias, post-op chain (CHAIN), dst scale and
+// zero-point, saturating store.  Absent scales are 1 and an absent bias is 0,
+// which leaves the value unchanged bit for bit.
+template <bool INT, bool CHAIN, int DST>
+__device__ __forceinline__ void epilogue_rows(const MatmulArgs &a, const TensorTerms &t, const ColTerms &c,
+        const uint32_t *tile_col, int pitch, int rows, int64_t m0, int64_t n, float ss, int rsum) {
+    const bool valid = n < a.N;
+    char *dptr = (char *)a.dst + (m0 * a.dst_sm + n * a.dst_sn) * dst_size<DST>::value;
+    const int64_t dstep = a.dst_sm * dst_size<DST>::value;
+    const bool bias_by_row = a.bias && a.bias_sm != 0;
+#pragma unroll 8
+    for (int i = 0; i < rows; ++i) {
+        const uint32_t raw = tile_col[i * pitch];
+        const float ss_i = __shfl_sync(0xffffffffu, ss, i);
+        float d;
+        if constexpr (INT) {
+            const int rs_i = __shfl_sync(0xffffffffu, rsum, i);
+            d = (float)((int)raw - c.zs_colsum - c.wei_zp * rs_i);
+        } else {
+            d = __uint_as_float(raw);
+        }
+        d = __fmul_rn(__fmul_rn(d, ss_i), c.wei_scale);
+        d = __fadd_rn(d, c.bias);
+        if (valid) {
+            if constexpr (CHAIN) {
+                const int64_t m = m0 + i;
+                if (bias_by_row) d = __fadd_rn(d, load_float(a.bias_dt, a.bias, m * a.bias_sm + n * a.bias_sn));
+                float old = 0.f;
+                if (has_sum(a)) old = load_float(a.sum_dt, a.dst, m * a.dst_sm + n * a.dst_sn);
+                d = apply_post_ops(a, d, old, m, n, 0);
+            }
+            if (t.has_dst_scale) d = __fdiv_rn(d, t.dst_scale); // the reference divides
+            if (t.has_dst_zp) d = __fadd_rn(d, t.dst_zp_per_n ? c.dst_zp : t.dst_zp);
+            store_typed<DST>(dptr, d);
+        }
+        dptr += dstep;
+    }
+}
+
+template <bool INT, bool CHAIN>
+__device__ __forceinline__ void epilogue_rows_any(const MatmulArgs &a, const TensorTerms &t, const ColTerms &c,
+        const uint32_t *tile_col, int pitch, int rows, int64_t m0, int64_t n, float ss, int rsum) {
+    switch (a.dst_dt) {
+        case DT_BF16: epilogue_rows<INT, CHAIN, DT_BF16>(a, t, c, tile_col, pitch, rows, m0, n, ss, rsum); break;
+        case DT_F32: epilogue_rows<INT, CHAIN, DT_F32>(a, t, c, tile_col, pitch, rows, m0, n, ss, rsum); break;
+        case DT_S8: epilogue_rows<INT, CHAIN, DT_S8>(a, t, c, tile_col, pitch, rows, m0, n, ss, rsum); break;
+        case DT_S32: epilogue_rows<INT, CHAIN, DT_S32>(a, t, c, tile_col, pitch, rows, m0, n, ss, rsum); break;
+        case DT_F16: epilogue_rows<INT, CHAIN, DT_F16>(a, t, c, tile_col, pitch, rows, m0, n, ss, rsum); break;
+        default: epilogue_rows<INT, CHAIN, DT_U8>(a, t, c, tile_col, pitch, rows, m0, n, ss, rsum); break;
+    }
+}
+
+template <int KIND, int BN, int STAGES, bool CHAIN>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+        const __grid_constant__ MatmulArgs a, const __grid_constant__ TcParams tp) {
+    using L = SmemLayout<BN, STAGES>;
+    constexpr int ACC_STAGES = 2;
+    constexpr uint32_t TMEM_COLS = ACC_STAGES * BN; // 256 or 512, a power of two
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint64_t *full_bar = (uint64_t *)(smem + L::BAR_OFFSET);
+    uint64_t *empty_bar = full_bar + STAGES;
+    uint64_t *tmem_full = empty_bar + STAGES;
+    uint64_t *tmem_empty = tmem_full + ACC_STAGES;
+    uint32_t *tmem_base_slot = (uint32_t *)(tmem_empty + ACC_STAGES);
+    volatile int *abort_flag = (volatile int *)(tmem_base_slot + 1);
+
+    const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+    const int num_tiles = tp.num_m_tiles * tp.num_n_tiles;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            ptx::mbar_init(&full_bar[s], 1);
+            ptx::mbar_init(&empty_bar[s], 1);
+        }
+        for (int s = 0; s < ACC_STAGES; ++s) {
+            ptx::mbar_init(&tmem_full[s], 1);
+            ptx::mbar_init(&tmem_empty[s], NUM_EPI_WARPS); // one arrival per epilogue warp
+        }
+        *abort_flag = 0;
+        ptx::fence_barrier_init();
+        ptx::prefetch_tensormap(&tmA);
+        ptx::prefetch_tensormap(&tmB);
+    }
+    if (warp == 1) ptx::tmem_alloc(tmem_base_slot, TMEM_COLS);
+    ptx::tc_fence_before_sync();
+    __syncthreads();
+    ptx::tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_base_slot;
+
+    if (warp == 0) {
+        // ------------------------------------------------ TMA producer
+        if (lane == 0) {
+            uint32_t it = 0;
+            for (int tile = blockIdx.x; tile < num_tiles && !*abort_flag; tile += gridDim.x) {
+                const int m0 = (tile % tp.num_m_tiles) * BM;
+                const int n0 = (tile / tp.num_m_tiles) * BN;
+                for (int kb = 0; kb < tp.num_k_blocks; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    const uint32_t ph = (it / STAGES) & 1;
+                    if (!ptx::mbar_wait(&empty_bar[s], ph ^ 1)) { *abort_flag = 1; atomicExch(a.status, 5); break; }
+                    uint8_t *sa = smem + s * L::STAGE_BYTES, *sb = sa + L::A_BYTES;
+                    ptx::mbar_arrive_expect_tx(&full_bar[s], L::STAGE_BYTES);
+                    ptx::tma_load_2d(sa, &tmA, &full_bar[s], kb * BKB, m0);
+                    if (tp.b_kmajor) {
+                        ptx::tma_load_2d(sb, &tmB, &full_bar[s], kb * BKB, n0);
+                    } else {
+                        for (int j = 0; j < BN / 128; ++j)
+                            ptx::tma_load_2d(sb + j * 128 * BKB, &tmB, &full_bar[s], n0 + j * 128, kb * BKB);
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            uint32_t it = 0, acc_it = 0;
+            for (int tile = blockIdx.x; tile < num_tiles && !*abort_flag; tile += gridDim.x, ++acc_it) {
+                const int as = acc_it % ACC_STAGES;
+                const uint32_t aph = (acc_it / ACC_STAGES) & 1;
+                if (!ptx::mbar_wait(&tmem_empty[as], aph ^ 1)) { *abort_flag = 1; atomicExch(a.status, 5); break; }
+                ptx::tc_fence_after_sync();
+                const uint32_t tmem_d = tmem_base + as * BN;
+                bool failed = false;
+                for (int kb = 0; kb < tp.num_k_blocks; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    const uint32_t ph = (it / STAGES) & 1;
+                    if (!ptx::mbar_wait(&full_bar[s], ph)) { failed = true; break; }
+                    ptx::tc_fence_after_sync();
+                    const uint32_t sa = ptx::smem_u32(smem + s * L::STAGE_BYTES), sb = sa + L::A_BYTES;
+#pragma unroll
+                    for (int kk = 0; kk < BKB / UMMA_K; ++kk) {
+                        const uint64_t ad = ptx::smem_desc_sw128(sa + kk * UMMA_K, 0, 1024);
+                        const uint64_t bd = tp.b_kmajor
+                                ? ptx::smem_desc_sw128(sb + kk * UMMA_K, 0, 1024)
+                                : ptx::smem_desc_sw128(sb + kk * UMMA_K * 128, 128 * BKB, 1024);
+                        ptx::mma_ss<KIND>(tmem_d, ad, bd, tp.idesc, (kb | kk) != 0);
+                    }
+                    ptx::tc_commit(&empty_bar[s]); // stage reusable once these MMAs have read it
+                }
+                if (failed) { *abort_flag = 1; atomicExch(a.status, 5); break; }
+                ptx::tc_commit(&tmem_full[as]); // accumulator complete
+            }
+        }
+    } else {
+        // ------------------------------------------------ epilogue warps
+        const int lane_base = (warp % 4) * 32; // TMEM lanes this warp may access
+        constexpr int COLS_PER_WARP = BN / (NUM_EPI_WARPS / 4);
+        const int col_base = ((warp - 2) / 4) * COLS_PER_WARP; // its share of the tile's columns
+        const TensorTerms tt = load_tensor_terms(a, tp.int_path != 0);
+        uint32_t acc_it = 0;
+        for (int tile = blockIdx.x; tile < num_tiles && !*abort_flag; tile += gridDim.x, ++acc_it) {
+            const int as = acc_it % ACC_STAGES;
+            const uint32_t aph = (acc_it / ACC_STAGES) & 1;
+            const int64_t m_warp = (int64_t)(tile % tp.num_m_tiles) * BM + lane_base; // first row of this warp
+            const int64_t m = m_warp + lane; // row this lane reads from TMEM
+            const int64_t n0 = (int64_t)(tile / tp.num_m_tiles) * BN;
+            if (!ptx::mbar_wait(&tmem_full[as], aph)) { *abort_flag = 1; atomicExch(a.status, 5); break; }
+            ptx::tc_fence_after_sync();
+            if (tp.mainloop_only) { // profiling aid: results are not stored
+                ptx::tc_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) ptx::mbar_arrive(&tmem_empty[as]);
+                continue;
+            }
+            // per-row terms, held by the lane that owns the row
+            float ss = 1.f;
+            int rsum = 0;
+            if (m < a.M) {
+                if (a.src_scale.ptr) ss = load_float(a.src_scale.dt, a.src_scale.ptr, (a.src_scale.mask & 1) ? m : 0);
+                else if (a.src_scale.on_host) ss = a.src_scale.host_value;
+                if (tp.rowsum) rsum = tp.rowsum[m];
+            }
+            const int rows = (int)min((int64_t)32, a.M - m_warp); // <= 0: nothing to store
+            uint32_t *tile_buf = (uint32_t *)(smem + L::EPI_OFFSET) + (warp - 2) * 32 * L::EPI_PITCH;
+#pragma unroll 1
+            for (int c = 0; c < COLS_PER_WARP / 32; ++c) {
+                uint32_t r[32];
+                ptx::tmem_ld_32x32(tmem_base + ((uint32_t)lane_base << 16) + as * BN + col_base + c * 32, r);
+                ptx::tmem_ld_wait();
+                if (c == COLS_PER_WARP / 32 - 1) { // accumulator fully read: hand the buffer back
+                    ptx::tc_fence_before_sync();
+                    __syncwarp();
+                    if (lane == 0) ptx::mbar_arrive(&tmem_empty[as]);
+                }
+                // transpose through shared memory: afterwards lane = column, so
+                // per-column terms sit in registers and global accesses coalesce
+                __syncwarp();
+#pragma unroll
+                for (int j = 0; j < 32; ++j) tile_buf[lane * L::EPI_PITCH + j] = r[j];
+                __syncwarp();
+                const int64_t n = n0 + col_base + c * 32 + lane;
+                const ColTerms ct = load_col_terms(a, tp, n);
+                epilogue_rows_any<KIND == 1, CHAIN>(a, tt, ct, tile_buf + lane, L::EPI_PITCH, rows, m_warp, n, ss, rsum);
+            }
+        }
+    }
+
+    // ---------------------------------------------------- teardown
+    ptx::tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+        __syncwarp();
+        ptx::tc_fence_after_sync();
+        ptx::tmem_dealloc(tmem_base, TMEM_COLS);
+    }
+}
+
+// ---- zero-point compensation terms (int8 path) ----------------------------
+// colsum[n] = sum_k w[k][n]; one thread per column, coalesced over n for
+// N-contiguous weights.
+__global__ void colsum_kernel(const __grid_constant__ MatmulArgs a, int32_t *colsum) {
+    const int64_t n = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (n >= a.N) return;
+    int s = 0;
+    for (int64_t k = 0; k < a.K; ++k) s += load_int(a.wei_dt, a.wei, k * a.wei_sk + n * a.wei_sn);
+    colsum[n] = s;
+}
+// rowsum[m] = sum_k s[m][k]; one warp per row
+__global__ void rowsum_kernel(const __grid_constant__ MatmulArgs a, int32_t *rowsum) {
+    const int64_t m = (int64_t)blockIdx.x * (blockDim.x / 32) + threadIdx.x / 32;
+    if (m >= a.M) return;
+    int s = 0;
+    for (int64_t k = threadIdx.x % 32; k < a.K; k += 32) s += load_int(a.src_dt, a.src, m * a.src_sm + k * a.src_sk);
+    for (int o = 16; o; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    if (threadIdx.x % 32 == 0) rowsum[m] = s;
+}
+
+typedef CUresult (*encode_tiled_fn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+        const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+        CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+encode_tiled_fn get_encode() {
+    static encode_tiled_fn fn = nullptr;
+    if (!fn) {
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess
+                && q == cudaDriverEntryPointSuccess)
+            fn = (encode_tiled_fn)p;
+    }
+    return fn;
+}
+
+// 2D map over a byte matrix [rows, cols] with row pitch `pitch` bytes; box =
+// [box_rows, 128 bytes], 128-byte swizzle, out-of-bounds reads give zeros.
+bool make_map_2d(CUtensorMap *map, const void *base, uint64_t cols, uint64_t rows, uint64_t pitch, uint32_t box_rows) {
+    encode_tiled_fn enc = get_encode();
+    if (!enc) return false;
+    cuuint64_t dims[2] = {cols, rows};
+    cuuint64_t strides[1] = {pitch};
+    cuuint32_t box[2] = {128, box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    return enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void *>(base), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE)
+            == CUDA_SUCCESS;
+}
+
+template <int KIND, int BN, int STAGES, bool CHAIN>
+int launch_cfg(const CUtensorMap &ma, const CUtensorMap &mb, const MatmulArgs &a, TcParams tp, int sm_count,
+        cudaStream_t st) {
+    using L = SmemLayout<BN, STAGES>;
+    auto kern = gemm_tc_kernel<KIND, BN, STAGES, CHAIN>;
+    static bool configured = false;
+    if (!configured) {
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL) != cudaSuccess) return 5;
+        configured = true;
+    }
+    tp.num_n_tiles = (int)((a.N + BN - 1) / BN);
+    const int tiles = tp.num_m_tiles * tp.num_n_tiles;
+    const int grid = tiles < sm_count ? tiles : sm_count;
+    kern<<<grid, NUM_THREADS, L::TOTAL, st>>>(ma, mb, a, tp);
+    count_launch();
+    return cudaGetLastError() == cudaSuccess ? 0 : 5;
+}
+
+} // namespace
+
+size_t gemm_tc_scratch_bytes(int64_t M, int64_t N) { return (size_t)(M + N) * sizeof(int32_t) + 256; }
+
+bool gemm_tc_pointers_ok(const MatmulArgs &a) {
+    return ((uintptr_t)a.src % 16 == 0) && ((uintptr_t)a.wei % 16 == 0);
+}
+
+// `scratch`: gemm_tc_scratch_bytes(M, N) bytes of device memory, needed only
+// when zero-points are present.
+int launch_gemm_tc(const MatmulArgs &a, void *scratch, int sm_count, cudaStream_t st) {
+    if (a.M == 0 || a.N == 0) return 0;
+    const bool int_path = a.src_dt == DT_S8 || a.src_dt == DT_U8;
+    const bool b_kmajor = a.wei_sk == 1 && a.wei_sn != 1;
+    TcParams tp {};
+    tp.num_m_tiles = (int)((a.M + BM - 1) / BM);
+    tp.num_k_blocks = (int)((a.K + BKB - 1) / BKB);
+    tp.b_kmajor = b_kmajor;
+    tp.int_path = int_path;
+    static const bool mainloop_only = getenv("ONEDNN_CUDA_TC_MAINLOOP_ONLY") != nullptr;
+    tp.mainloop_only = mainloop_only;
+    if (a.K == 0) return 3;
+
+    int32_t *colsum = (int32_t *)scratch;
+    int32_t *rowsum = colsum ? colsum + ((a.N + 63) / 64) * 64 : nullptr;
+    if (int_path && a.src_zp.ptr) {
+        if (!scratch) return 5;
+        colsum_kernel<<<(unsigned)((a.N + 127) / 128), 128, 0, st>>>(a, colsum);
+        count_launch();
+        tp.colsum = colsum;
+    }
+    if (int_path && a.wei_zp.ptr) {
+        if (!scratch) return 5;
+        rowsum_kernel<<<(unsigned)((a.M + 3) / 4), 128, 0, st>>>(a, rowsum);
+        count_launch();
+        tp.rowsum = rowsum;
+    }
+
+    CUtensorMap ma, mb;
+    if (!make_map_2d(&ma, a.src, (uint64_t)a.K, (uint64_t)a.M, (uint64_t)a.src_sm, BM)) return 5;
+    // BN = 256 unless the problem is too narrow to fill the machine with it
+    const int64_t tiles256 = (int64_t)tp.num_m_tiles * ((a.N + 255) / 256);
+    const bool wide = a.N > 128 && tiles256 >= sm_count / 2;
+    const int BN = wide ? 256 : 128;
+    if (b_kmajor) {
+        if (!make_map_2d(&mb, a.wei, (uint64_t)a.K, (uint64_t)a.N, (uint64_t)a.wei_sn, BN)) return 5;
+    } else {
+        if (!make_map_2d(&mb, a.wei, (uint64_t)a.N, (uint64_t)a.K, (uint64_t)a.wei_sk, BKB)) return 5;
+    }
+    uint32_t afmt, bfmt, cfmt;
+    if (int_path) {
+        afmt = a.src_dt == DT_S8 ? ptx::FMT_S8 : ptx::FMT_U8;
+        bfmt = a.wei_dt == DT_S8 ? ptx::FMT_S8 : ptx::FMT_U8;
+        cfmt = ptx::CFMT_S32;
+    } else {
+        afmt = a.src_dt == DT_F8_E4M3 ? ptx::FMT_E4M3 : ptx::FMT_E5M2;
+        bfmt = a.wei_dt == DT_F8_E4M3 ? ptx::FMT_E4M3 : ptx::FMT_E5M2;
+        cfmt = ptx::CFMT_F32;
+    }
+    tp.idesc = ptx::make_idesc(cfmt, afmt, bfmt, false, !b_kmajor, BM, BN);
+    const bool chain = a.n_po > 0 || (a.bias && a.bias_sm != 0); // a bias varying along M rides the generic tail
+#define QMM_TC_LAUNCH(KIND) \
+    (wide ? (chain ? launch_cfg<KIND, 256, 4, true>(ma, mb, a, tp, sm_count, st) \
+                   : launch_cfg<KIND, 256, 4, false>(ma, mb, a, tp, sm_count, st)) \
+          : (chain ? launch_cfg<KIND, 128, 6, true>(ma, mb, a, tp, sm_count, st) \
+                   : launch_cfg<KIND, 128, 6, false>(ma, mb, a, tp, sm_count, st)))
+    return int_path ? QMM_TC_LAUNCH(1) : QMM_TC_LAUNCH(0);
+#undef QMM_TC_LAUNCH
+}
+
+} // namespace qmm

@@ -1,19 +1,31 @@
 // "cuda:tcgen05" GEMM for 8-bit operands: int8 (u8/s8 x u8/s8 -> s32
 // accumulate) and fp8 (e4m3/e5m2 -> f32 accumulate).
 //
-// One persistent CTA per SM walks output tiles of 128 x BN.  Three roles:
-//   warp 0     TMA producer: src tile [128 rows x 128 B of K] and weights tile
-//              ([128 k x BN] for N-contiguous `ab` weights, [BN x 128 B of K]
-//              for `ba`) into a ring of 128B-swizzled shared-memory stages
-//   warp 1     issues tcgen05.mma (M=128, N=BN, K=32 per instruction) into one
-//              of two TMEM accumulator buffers and commits to mbarriers
-//   warps 2-5  epilogue: TMEM -> registers, zero-point compensation, scales,
-//              bias, post-op chain, dst scale / zero-point, saturating store;
-//              runs while the next tile is being multiplied
-// Arithmetic of the epilogue follows the reference (ref_matmul_int8.cpp:
-// 241-304, ref_matmul.cpp:218-332): integer sums are exact, so int8 results
-// are the reference's bit for bit; fp8 differs only by f32 summation order.
+// The kernel computes dst^T tiles: the WEIGHTS are the A operand of
+// tcgen05.mma (128 dst columns = the 128 TMEM lanes) and the SRC rows are the
+// B operand (BT_M dst rows = TMEM columns).  An epilogue thread therefore owns
+// one dst column n and reads consecutive rows m from TMEM: the 32 lanes of a
+// warp hold 32 adjacent columns, so every global access of the epilogue (dst
+// stores, binary post-op operands) is coalesced without a shared-memory
+// transpose, and per-column terms (weight scales, bias, zero-point
+// compensation) live in registers for the whole tile.
+//
+// One persistent CTA per SM walks the tiles.  Roles:
+//   warp 0     TMA producer: weights tile ([128 k x 128 n] for N-contiguous
+//              `ab` weights, [128 n x 128 B of k] for `ba`) and src tile
+//              [BT_M rows x 128 B of k] into a ring of 128B-swizzled stages
+//   warp 1     issues tcgen05.mma (M=128, N=BT_M, K=32 per instruction) into
+//              one of two TMEM accumulator buffers, commits to mbarriers
+//   warps 2-9  epilogue (two warps per TMEM lane quarter, each half of the
+//              rows): zero-point compensation, scales, bias, post-op chain,
+//              dst scale / zero-point, saturating store; overlaps the next
+//              tile's multiplication
+// Epilogue arithmetic follows the reference (ref_matmul_int8.cpp:241-304,
+// ref_matmul.cpp:218-332): integer sums are exact, so int8 results equal the
+// reference's bit for bit; fp8 differs only by the f32 summation order.
 #include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
 
 #include "device_math.cuh"
 #include "launch.h"
@@ -23,43 +35,40 @@ namespace qmm {
 
 namespace {
 
-constexpr int BM = 128; // tile rows = TMEM lanes
+constexpr int BT_N = 128; // dst columns per tile = TMEM lanes = UMMA M
 constexpr int BKB = 128; // bytes (= 8-bit elements) of K per stage: one swizzle row
 constexpr int UMMA_K = 32; // K per tcgen05.mma for 8-bit operands
-constexpr int NUM_EPI_WARPS = 8; // two per TMEM lane quarter, each half of the tile's columns
+constexpr int NUM_EPI_WARPS = 8;
 constexpr int NUM_THREADS = 64 + 32 * NUM_EPI_WARPS;
 
 struct TcParams {
     int num_m_tiles, num_n_tiles, num_k_blocks;
     uint32_t idesc;
-    int b_kmajor; // weights are `ba` (K contiguous)
-    int int_path; // s32 accumulators
+    int w_kmajor; // weights are `ba` (K contiguous)
     int mainloop_only; // ONEDNN_CUDA_TC_MAINLOOP_ONLY=1: skip the epilogue (profiling aid)
     const int32_t *colsum; // sum_k w[k][n]       (src zero-point compensation)
     const int32_t *rowsum; // sum_k s[m][k]       (weights zero-point compensation)
 };
 
-template <int BN, int STAGES>
+template <int BT_M, int STAGES>
 struct SmemLayout {
-    static constexpr int A_BYTES = BM * BKB;
-    static constexpr int B_BYTES = BN * BKB;
-    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+    static constexpr int W_BYTES = BT_N * BKB;
+    static constexpr int S_BYTES = BT_M * BKB;
+    static constexpr int STAGE_BYTES = W_BYTES + S_BYTES;
     static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES;
-    static constexpr int EPI_OFFSET = BAR_OFFSET + 256; // after the barriers
-    static constexpr int EPI_PITCH = 33; // words per row of a warp's 32x32 transpose tile
-    static constexpr int EPI_BYTES = NUM_EPI_WARPS * 32 * EPI_PITCH * 4;
-    static constexpr int TOTAL = EPI_OFFSET + EPI_BYTES + 1024; // + alignment slack
+    static constexpr int TOTAL = BAR_OFFSET + 256 + 1024; // barriers + alignment slack
 };
 
-// Per-column terms of the epilogue, held by the lane that owns the column.
+// Per-column terms of the epilogue, in registers of the thread that owns the column.
 struct ColTerms {
     float wei_scale; // 1 when absent
-    float bias; // bias[n] when the bias is a row vector
+    float bias; // bias[n] when the bias is a row vector, else 0
     int zs_colsum; // src_zp * colsum[n] - K * src_zp * wei_zp[n]
     int wei_zp; // wei_zp[n]
     float dst_zp; // dst_zp[n] when per-N
 };
 
+template <bool INT>
 __device__ __forceinline__ ColTerms load_col_terms(const MatmulArgs &a, const TcParams &tp, int64_t n) {
     ColTerms c;
     c.wei_scale = 1.f;
@@ -72,7 +81,7 @@ __device__ __forceinline__ ColTerms load_col_terms(const MatmulArgs &a, const Tc
     if (a.wei_scale.ptr) c.wei_scale = load_float(a.wei_scale.dt, a.wei_scale.ptr, (a.wei_scale.mask & 2) ? n : 0);
     else if (a.wei_scale.on_host) c.wei_scale = a.wei_scale.host_value;
     if (a.bias && a.bias_sm == 0) c.bias = load_float(a.bias_dt, a.bias, n * a.bias_sn);
-    if (tp.int_path) {
+    if (INT) {
         if (a.wei_zp.ptr) c.wei_zp = load_int(a.wei_zp.dt, a.wei_zp.ptr, (a.wei_zp.mask & 2) ? n : 0);
         if (a.src_zp.ptr) {
             const int zs = ((const int *)a.src_zp.ptr)[0];
@@ -84,23 +93,30 @@ __device__ __forceinline__ ColTerms load_col_terms(const MatmulArgs &a, const Tc
 
 // Per-tensor terms of the epilogue, read once per thread.
 struct TensorTerms {
-    bool has_dst_scale, has_dst_zp, dst_zp_per_n;
-    float dst_scale, dst_zp;
+    bool has_dst_scale, has_dst_zp, dst_zp_per_n, row_scale, row_sum, bias_by_row;
+    float dst_scale, dst_zp, src_scale;
 };
 
-__device__ __forceinline__ TensorTerms load_tensor_terms(const MatmulArgs &a, bool int_path) {
+template <bool INT>
+__device__ __forceinline__ TensorTerms load_tensor_terms(const MatmulArgs &a, const TcParams &tp) {
     TensorTerms t;
     t.has_dst_scale = a.non_default_attr && (a.dst_scale.ptr || a.dst_scale.on_host);
     t.dst_scale = a.dst_scale.ptr ? load_float(a.dst_scale.dt, a.dst_scale.ptr, 0) : a.dst_scale.host_value;
     // the floating-point reference path has no dst zero-point
-    t.has_dst_zp = a.non_default_attr && int_path && a.dst_zp.ptr;
+    t.has_dst_zp = a.non_default_attr && INT && a.dst_zp.ptr;
     t.dst_zp_per_n = a.dst_zp.mask > 0;
     t.dst_zp = (t.has_dst_zp && !t.dst_zp_per_n) ? (float)((const int *)a.dst_zp.ptr)[0] : 0.f;
+    t.row_scale = a.src_scale.ptr && (a.src_scale.mask & 1);
+    t.src_scale = 1.f; // per-tensor src scale (1 when absent or per-row)
+    if (a.src_scale.ptr && !t.row_scale) t.src_scale = load_float(a.src_scale.dt, a.src_scale.ptr, 0);
+    else if (a.src_scale.on_host) t.src_scale = a.src_scale.host_value;
+    t.row_sum = INT && tp.rowsum != nullptr;
+    t.bias_by_row = a.bias && a.bias_sm != 0;
     return t;
 }
 
-// Typed stores of one f32 value, saturating / rounding as the reference does
-// (src/cpu/simple_q10n.hpp:41-81, src/common/bfloat16.cpp:22-47: f32
+// Typed store of one f32 value, saturating / rounding as the reference does
+// (src/cpu/simple_q10n.hpp:41-81; src/common/bfloat16.cpp:22-47: f32
 // subnormals flush to signed zero before the bf16 rounding).
 template <int DST>
 __device__ __forceinline__ void store_typed(void *p, float v) {
@@ -120,69 +136,102 @@ __device__ __forceinline__ void store_typed(void *p, float v) {
         *(unsigned char *)p = (unsigned char)__float2int_rn(fminf(fmaxf(v, 0.f), 255.f));
     }
 }
-template <int DST> struct dst_size { static constexpr int value = (DST == DT_F32 || DST == DT_S32) ? 4 : (DST == DT_BF16 || DST == DT_F16) ? 2 : 1; };
+template <int DST>
+struct dst_size {
+    static constexpr int value = (DST == DT_F32 || DST == DT_S32) ? 4 : (DST == DT_BF16 || DST == DT_F16) ? 2 : 1;
+};
 
-// The rows of one transposed 32x32 accumulator tile: lane = dst column n,
-// loop over the warp's rows.  Per element: zero-point compensation (INT),
-// src / weights scales, bias, post-op chain (CHAIN), dst scale and
-// zero-point, saturating store.  Absent scales are 1 and an absent bias is 0,
-// which leaves the value unchanged bit for bit.
+// 32 consecutive dst rows of column n, accumulators in r[0..31].  Absent
+// scales are 1 and an absent bias is 0, which leaves values unchanged.
 template <bool INT, bool CHAIN, int DST>
-__device__ __forceinline__ void epilogue_rows(const MatmulArgs &a, const TensorTerms &t, const ColTerms &c,
-        const uint32_t *tile_col, int pitch, int rows, int64_t m0, int64_t n, float ss, int rsum) {
-    const bool valid = n < a.N;
+__device__ __forceinline__ void epilogue_rows(const MatmulArgs &a, const TcParams &tp, const TensorTerms &t,
+        const ColTerms &c, const uint32_t (&r)[32], int64_t m0, int64_t n) {
+    if (n >= a.N) return;
     char *dptr = (char *)a.dst + (m0 * a.dst_sm + n * a.dst_sn) * dst_size<DST>::value;
     const int64_t dstep = a.dst_sm * dst_size<DST>::value;
-    const bool bias_by_row = a.bias && a.bias_sm != 0;
-#pragma unroll 8
-    for (int i = 0; i < rows; ++i) {
-        const uint32_t raw = tile_col[i * pitch];
-        const float ss_i = __shfl_sync(0xffffffffu, ss, i);
-        float d;
-        if constexpr (INT) {
-            const int rs_i = __shfl_sync(0xffffffffu, rsum, i);
-            d = (float)((int)raw - c.zs_colsum - c.wei_zp * rs_i);
+    const int rows = (int)min((int64_t)32, a.M - m0);
+    // Phases of straight-line code over the 32 rows (uniform conditions are
+    // tested once per phase, not per row), so the rows' dependency chains
+    // interleave; only the stores are predicated on the M tail.
+    float d[32];
+    if constexpr (INT) {
+        if (t.row_sum) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+                d[j] = (float)((int)r[j] - c.zs_colsum - c.wei_zp * __ldg(tp.rowsum + min(m0 + j, a.M - 1)));
         } else {
-            d = __uint_as_float(raw);
+#pragma unroll
+            for (int j = 0; j < 32; ++j) d[j] = (float)((int)r[j] - c.zs_colsum);
         }
-        d = __fmul_rn(__fmul_rn(d, ss_i), c.wei_scale);
-        d = __fadd_rn(d, c.bias);
-        if (valid) {
-            if constexpr (CHAIN) {
-                const int64_t m = m0 + i;
-                if (bias_by_row) d = __fadd_rn(d, load_float(a.bias_dt, a.bias, m * a.bias_sm + n * a.bias_sn));
+    } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) d[j] = __uint_as_float(r[j]);
+    }
+    if (t.row_scale) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+            d[j] = __fmul_rn(d[j], load_float(a.src_scale.dt, a.src_scale.ptr, min(m0 + j, a.M - 1)));
+    } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) d[j] = __fmul_rn(d[j], t.src_scale);
+    }
+#pragma unroll
+    for (int j = 0; j < 32; ++j) d[j] = __fadd_rn(__fmul_rn(d[j], c.wei_scale), c.bias);
+    if constexpr (CHAIN) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+            if (j < rows) {
+                const int64_t m = m0 + j;
+                float v = d[j];
+                if (t.bias_by_row) v = __fadd_rn(v, load_float(a.bias_dt, a.bias, m * a.bias_sm + n * a.bias_sn));
                 float old = 0.f;
                 if (has_sum(a)) old = load_float(a.sum_dt, a.dst, m * a.dst_sm + n * a.dst_sn);
-                d = apply_post_ops(a, d, old, m, n, 0);
+                d[j] = apply_post_ops(a, v, old, m, n, 0);
             }
-            if (t.has_dst_scale) d = __fdiv_rn(d, t.dst_scale); // the reference divides
-            if (t.has_dst_zp) d = __fadd_rn(d, t.dst_zp_per_n ? c.dst_zp : t.dst_zp);
-            store_typed<DST>(dptr, d);
         }
-        dptr += dstep;
     }
+    if (t.has_dst_scale) { // the reference divides
+#pragma unroll
+        for (int j = 0; j < 32; ++j) d[j] = __fdiv_rn(d[j], t.dst_scale);
+    }
+    if (t.has_dst_zp) {
+        const float z = t.dst_zp_per_n ? c.dst_zp : t.dst_zp;
+#pragma unroll
+        for (int j = 0; j < 32; ++j) d[j] = __fadd_rn(d[j], z);
+    }
+    if (tp.mainloop_only == 3) { // profiling aid: everything but the stores
+        float acc = 0.f;
+#pragma unroll
+        for (int j = 0; j < 32; ++j) acc += d[j];
+        if (acc == 123.456f) store_typed<DST>(dptr, acc);
+        return;
+    }
+#pragma unroll
+    for (int j = 0; j < 32; ++j)
+        if (j < rows) store_typed<DST>(dptr + j * dstep, d[j]);
 }
 
 template <bool INT, bool CHAIN>
-__device__ __forceinline__ void epilogue_rows_any(const MatmulArgs &a, const TensorTerms &t, const ColTerms &c,
-        const uint32_t *tile_col, int pitch, int rows, int64_t m0, int64_t n, float ss, int rsum) {
+__device__ __forceinline__ void epilogue_rows_any(const MatmulArgs &a, const TcParams &tp, const TensorTerms &t,
+        const ColTerms &c, const uint32_t (&r)[32], int64_t m0, int64_t n) {
     switch (a.dst_dt) {
-        case DT_BF16: epilogue_rows<INT, CHAIN, DT_BF16>(a, t, c, tile_col, pitch, rows, m0, n, ss, rsum); break;
-        case DT_F32: epilogue_rows<INT, CHAIN, DT_F32>(a, t, c, tile_col, pitch, rows, m0, n, ss, rsum); break;
-        case DT_S8: epilogue_rows<INT, CHAIN, DT_S8>(a, t, c, tile_col, pitch, rows, m0, n, ss, rsum); break;
-        case DT_S32: epilogue_rows<INT, CHAIN, DT_S32>(a, t, c, tile_col, pitch, rows, m0, n, ss, rsum); break;
-        case DT_F16: epilogue_rows<INT, CHAIN, DT_F16>(a, t, c, tile_col, pitch, rows, m0, n, ss, rsum); break;
-        default: epilogue_rows<INT, CHAIN, DT_U8>(a, t, c, tile_col, pitch, rows, m0, n, ss, rsum); break;
+        case DT_BF16: epilogue_rows<INT, CHAIN, DT_BF16>(a, tp, t, c, r, m0, n); break;
+        case DT_F32: epilogue_rows<INT, CHAIN, DT_F32>(a, tp, t, c, r, m0, n); break;
+        case DT_S8: epilogue_rows<INT, CHAIN, DT_S8>(a, tp, t, c, r, m0, n); break;
+        case DT_S32: epilogue_rows<INT, CHAIN, DT_S32>(a, tp, t, c, r, m0, n); break;
+        case DT_F16: epilogue_rows<INT, CHAIN, DT_F16>(a, tp, t, c, r, m0, n); break;
+        default: epilogue_rows<INT, CHAIN, DT_U8>(a, tp, t, c, r, m0, n); break;
     }
 }
 
-template <int KIND, int BN, int STAGES, bool CHAIN>
+template <int KIND, int BT_M, int STAGES, bool CHAIN>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
-gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmS,
         const __grid_constant__ MatmulArgs a, const __grid_constant__ TcParams tp) {
-    using L = SmemLayout<BN, STAGES>;
+    using L = SmemLayout<BT_M, STAGES>;
+    constexpr bool INT = KIND == 1;
     constexpr int ACC_STAGES = 2;
-    constexpr uint32_t TMEM_COLS = ACC_STAGES * BN; // 256 or 512, a power of two
+    constexpr uint32_t TMEM_COLS = ACC_STAGES * BT_M; // 256 or 512, a power of two
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint64_t *full_bar = (uint64_t *)(smem + L::BAR_OFFSET);
@@ -206,8 +255,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         }
         *abort_flag = 0;
         ptx::fence_barrier_init();
-        ptx::prefetch_tensormap(&tmA);
-        ptx::prefetch_tensormap(&tmB);
+        ptx::prefetch_tensormap(&tmW);
+        ptx::prefetch_tensormap(&tmS);
     }
     if (warp == 1) ptx::tmem_alloc(tmem_base_slot, TMEM_COLS);
     ptx::tc_fence_before_sync();
@@ -215,26 +264,24 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     ptx::tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_base_slot;
 
+    // Tile order: the m index runs fastest, so the CTAs working at any moment
+    // share a few weight column blocks and sweep the whole src once per block.
     if (warp == 0) {
         // ------------------------------------------------ TMA producer
         if (lane == 0) {
             uint32_t it = 0;
             for (int tile = blockIdx.x; tile < num_tiles && !*abort_flag; tile += gridDim.x) {
-                const int m0 = (tile % tp.num_m_tiles) * BM;
-                const int n0 = (tile / tp.num_m_tiles) * BN;
+                const int m0 = (tile % tp.num_m_tiles) * BT_M;
+                const int n0 = (tile / tp.num_m_tiles) * BT_N;
                 for (int kb = 0; kb < tp.num_k_blocks; ++kb, ++it) {
                     const int s = it % STAGES;
                     const uint32_t ph = (it / STAGES) & 1;
                     if (!ptx::mbar_wait(&empty_bar[s], ph ^ 1)) { *abort_flag = 1; atomicExch(a.status, 5); break; }
-                    uint8_t *sa = smem + s * L::STAGE_BYTES, *sb = sa + L::A_BYTES;
+                    uint8_t *sw = smem + s * L::STAGE_BYTES, *ss = sw + L::W_BYTES;
                     ptx::mbar_arrive_expect_tx(&full_bar[s], L::STAGE_BYTES);
-                    ptx::tma_load_2d(sa, &tmA, &full_bar[s], kb * BKB, m0);
-                    if (tp.b_kmajor) {
-                        ptx::tma_load_2d(sb, &tmB, &full_bar[s], kb * BKB, n0);
-                    } else {
-                        for (int j = 0; j < BN / 128; ++j)
-                            ptx::tma_load_2d(sb + j * 128 * BKB, &tmB, &full_bar[s], n0 + j * 128, kb * BKB);
-                    }
+                    if (tp.w_kmajor) ptx::tma_load_2d(sw, &tmW, &full_bar[s], kb * BKB, n0);
+                    else ptx::tma_load_2d(sw, &tmW, &full_bar[s], n0, kb * BKB);
+                    ptx::tma_load_2d(ss, &tmS, &full_bar[s], kb * BKB, m0);
                 }
             }
         }
@@ -247,21 +294,22 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                 const uint32_t aph = (acc_it / ACC_STAGES) & 1;
                 if (!ptx::mbar_wait(&tmem_empty[as], aph ^ 1)) { *abort_flag = 1; atomicExch(a.status, 5); break; }
                 ptx::tc_fence_after_sync();
-                const uint32_t tmem_d = tmem_base + as * BN;
+                const uint32_t tmem_d = tmem_base + as * BT_M;
                 bool failed = false;
                 for (int kb = 0; kb < tp.num_k_blocks; ++kb, ++it) {
                     const int s = it % STAGES;
                     const uint32_t ph = (it / STAGES) & 1;
                     if (!ptx::mbar_wait(&full_bar[s], ph)) { failed = true; break; }
                     ptx::tc_fence_after_sync();
-                    const uint32_t sa = ptx::smem_u32(smem + s * L::STAGE_BYTES), sb = sa + L::A_BYTES;
+                    const uint32_t sw = ptx::smem_u32(smem + s * L::STAGE_BYTES), ss = sw + L::W_BYTES;
 #pragma unroll
                     for (int kk = 0; kk < BKB / UMMA_K; ++kk) {
-                        const uint64_t ad = ptx::smem_desc_sw128(sa + kk * UMMA_K, 0, 1024);
-                        const uint64_t bd = tp.b_kmajor
-                                ? ptx::smem_desc_sw128(sb + kk * UMMA_K, 0, 1024)
-                                : ptx::smem_desc_sw128(sb + kk * UMMA_K * 128, 128 * BKB, 1024);
-                        ptx::mma_ss<KIND>(tmem_d, ad, bd, tp.idesc, (kb | kk) != 0);
+                        // weights: MN-major when N-contiguous (one 128-byte row per k),
+                        // K-major for `ba`; src rows: K-major
+                        const uint64_t wd = tp.w_kmajor ? ptx::smem_desc_sw128(sw + kk * UMMA_K, 0, 1024)
+                                                        : ptx::smem_desc_sw128(sw + kk * UMMA_K * 128, 128 * BKB, 1024);
+                        const uint64_t sd = ptx::smem_desc_sw128(ss + kk * UMMA_K, 0, 1024);
+                        ptx::mma_ss<KIND>(tmem_d, wd, sd, tp.idesc, (kb | kk) != 0);
                     }
                     ptx::tc_commit(&empty_bar[s]); // stage reusable once these MMAs have read it
                 }
@@ -271,54 +319,38 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         }
     } else {
         // ------------------------------------------------ epilogue warps
-        const int lane_base = (warp % 4) * 32; // TMEM lanes this warp may access
-        constexpr int COLS_PER_WARP = BN / (NUM_EPI_WARPS / 4);
-        const int col_base = ((warp - 2) / 4) * COLS_PER_WARP; // its share of the tile's columns
-        const TensorTerms tt = load_tensor_terms(a, tp.int_path != 0);
+        const int lane_base = (warp % 4) * 32; // TMEM lanes (dst columns) of this warp
+        constexpr int ROWS_PER_WARP = BT_M / (NUM_EPI_WARPS / 4);
+        const int row_base = ((warp - 2) / 4) * ROWS_PER_WARP; // its share of the tile's rows
+        const TensorTerms tt = load_tensor_terms<INT>(a, tp);
         uint32_t acc_it = 0;
         for (int tile = blockIdx.x; tile < num_tiles && !*abort_flag; tile += gridDim.x, ++acc_it) {
             const int as = acc_it % ACC_STAGES;
             const uint32_t aph = (acc_it / ACC_STAGES) & 1;
-            const int64_t m_warp = (int64_t)(tile % tp.num_m_tiles) * BM + lane_base; // first row of this warp
-            const int64_t m = m_warp + lane; // row this lane reads from TMEM
-            const int64_t n0 = (int64_t)(tile / tp.num_m_tiles) * BN;
+            const int64_t m_tile = (int64_t)(tile % tp.num_m_tiles) * BT_M + row_base;
+            const int64_t n = (int64_t)(tile / tp.num_m_tiles) * BT_N + lane_base + lane;
+            const ColTerms ct = load_col_terms<INT>(a, tp, n); // in flight while waiting for the MMAs
             if (!ptx::mbar_wait(&tmem_full[as], aph)) { *abort_flag = 1; atomicExch(a.status, 5); break; }
             ptx::tc_fence_after_sync();
-            if (tp.mainloop_only) { // profiling aid: results are not stored
+            if (tp.mainloop_only == 1) { // profiling aid: results are not stored
                 ptx::tc_fence_before_sync();
                 __syncwarp();
                 if (lane == 0) ptx::mbar_arrive(&tmem_empty[as]);
                 continue;
             }
-            // per-row terms, held by the lane that owns the row
-            float ss = 1.f;
-            int rsum = 0;
-            if (m < a.M) {
-                if (a.src_scale.ptr) ss = load_float(a.src_scale.dt, a.src_scale.ptr, (a.src_scale.mask & 1) ? m : 0);
-                else if (a.src_scale.on_host) ss = a.src_scale.host_value;
-                if (tp.rowsum) rsum = tp.rowsum[m];
-            }
-            const int rows = (int)min((int64_t)32, a.M - m_warp); // <= 0: nothing to store
-            uint32_t *tile_buf = (uint32_t *)(smem + L::EPI_OFFSET) + (warp - 2) * 32 * L::EPI_PITCH;
 #pragma unroll 1
-            for (int c = 0; c < COLS_PER_WARP / 32; ++c) {
+            for (int c = 0; c < ROWS_PER_WARP / 32; ++c) {
                 uint32_t r[32];
-                ptx::tmem_ld_32x32(tmem_base + ((uint32_t)lane_base << 16) + as * BN + col_base + c * 32, r);
+                ptx::tmem_ld_32x32(tmem_base + ((uint32_t)lane_base << 16) + as * BT_M + row_base + c * 32, r);
                 ptx::tmem_ld_wait();
-                if (c == COLS_PER_WARP / 32 - 1) { // accumulator fully read: hand the buffer back
+                if (c == ROWS_PER_WARP / 32 - 1) { // accumulator fully read: hand the buffer back
                     ptx::tc_fence_before_sync();
                     __syncwarp();
                     if (lane == 0) ptx::mbar_arrive(&tmem_empty[as]);
                 }
-                // transpose through shared memory: afterwards lane = column, so
-                // per-column terms sit in registers and global accesses coalesce
-                __syncwarp();
-#pragma unroll
-                for (int j = 0; j < 32; ++j) tile_buf[lane * L::EPI_PITCH + j] = r[j];
-                __syncwarp();
-                const int64_t n = n0 + col_base + c * 32 + lane;
-                const ColTerms ct = load_col_terms(a, tp, n);
-                epilogue_rows_any<KIND == 1, CHAIN>(a, tt, ct, tile_buf + lane, L::EPI_PITCH, rows, m_warp, n, ss, rsum);
+                const int64_t m0 = m_tile + c * 32;
+                if (tp.mainloop_only == 2) continue; // profiling aid: TMEM reads only
+                if (m0 < a.M) epilogue_rows_any<INT, CHAIN>(a, tp, tt, ct, r, m0, n);
             }
         }
     }
@@ -384,20 +416,19 @@ bool make_map_2d(CUtensorMap *map, const void *base, uint64_t cols, uint64_t row
             == CUDA_SUCCESS;
 }
 
-template <int KIND, int BN, int STAGES, bool CHAIN>
-int launch_cfg(const CUtensorMap &ma, const CUtensorMap &mb, const MatmulArgs &a, TcParams tp, int sm_count,
+template <int KIND, int BT_M, int STAGES, bool CHAIN>
+int launch_cfg(const CUtensorMap &mw, const CUtensorMap &ms, const MatmulArgs &a, TcParams tp, int sm_count,
         cudaStream_t st) {
-    using L = SmemLayout<BN, STAGES>;
-    auto kern = gemm_tc_kernel<KIND, BN, STAGES, CHAIN>;
+    using L = SmemLayout<BT_M, STAGES>;
+    auto kern = gemm_tc_kernel<KIND, BT_M, STAGES, CHAIN>;
     static bool configured = false;
     if (!configured) {
         if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL) != cudaSuccess) return 5;
         configured = true;
     }
-    tp.num_n_tiles = (int)((a.N + BN - 1) / BN);
     const int tiles = tp.num_m_tiles * tp.num_n_tiles;
     const int grid = tiles < sm_count ? tiles : sm_count;
-    kern<<<grid, NUM_THREADS, L::TOTAL, st>>>(ma, mb, a, tp);
+    kern<<<grid, NUM_THREADS, L::TOTAL, st>>>(mw, ms, a, tp);
     count_launch();
     return cudaGetLastError() == cudaSuccess ? 0 : 5;
 }
@@ -414,16 +445,16 @@ bool gemm_tc_pointers_ok(const MatmulArgs &a) {
 // when zero-points are present.
 int launch_gemm_tc(const MatmulArgs &a, void *scratch, int sm_count, cudaStream_t st) {
     if (a.M == 0 || a.N == 0) return 0;
-    const bool int_path = a.src_dt == DT_S8 || a.src_dt == DT_U8;
-    const bool b_kmajor = a.wei_sk == 1 && a.wei_sn != 1;
-    TcParams tp {};
-    tp.num_m_tiles = (int)((a.M + BM - 1) / BM);
-    tp.num_k_blocks = (int)((a.K + BKB - 1) / BKB);
-    tp.b_kmajor = b_kmajor;
-    tp.int_path = int_path;
-    static const bool mainloop_only = getenv("ONEDNN_CUDA_TC_MAINLOOP_ONLY") != nullptr;
-    tp.mainloop_only = mainloop_only;
     if (a.K == 0) return 3;
+    const bool int_path = a.src_dt == DT_S8 || a.src_dt == DT_U8;
+    const bool w_kmajor = a.wei_sk == 1 && a.wei_sn != 1;
+    TcParams tp {};
+    tp.num_n_tiles = (int)((a.N + BT_N - 1) / BT_N);
+    tp.num_k_blocks = (int)((a.K + BKB - 1) / BKB);
+    tp.w_kmajor = w_kmajor;
+    // profiling aid: 1 = no epilogue, 2 = TMEM reads only, 3 = everything but the stores
+    static const int mainloop_only = getenv("ONEDNN_CUDA_TC_MAINLOOP_ONLY") ? atoi(getenv("ONEDNN_CUDA_TC_MAINLOOP_ONLY")) : 0;
+    tp.mainloop_only = mainloop_only;
 
     int32_t *colsum = (int32_t *)scratch;
     int32_t *rowsum = colsum ? colsum + ((a.N + 63) / 64) * 64 : nullptr;
@@ -440,34 +471,37 @@ int launch_gemm_tc(const MatmulArgs &a, void *scratch, int sm_count, cudaStream_
         tp.rowsum = rowsum;
     }
 
-    CUtensorMap ma, mb;
-    if (!make_map_2d(&ma, a.src, (uint64_t)a.K, (uint64_t)a.M, (uint64_t)a.src_sm, BM)) return 5;
-    // BN = 256 unless the problem is too narrow to fill the machine with it
-    const int64_t tiles256 = (int64_t)tp.num_m_tiles * ((a.N + 255) / 256);
-    const bool wide = a.N > 128 && tiles256 >= sm_count / 2;
-    const int BN = wide ? 256 : 128;
-    if (b_kmajor) {
-        if (!make_map_2d(&mb, a.wei, (uint64_t)a.K, (uint64_t)a.N, (uint64_t)a.wei_sn, BN)) return 5;
+    // 256 dst rows per tile unless that leaves SMs without work
+    const int64_t tiles256 = (int64_t)tp.num_n_tiles * ((a.M + 255) / 256);
+    const bool tall = a.M > 128 && tiles256 >= sm_count / 2;
+    const int BT_M = tall ? 256 : 128;
+    tp.num_m_tiles = (int)((a.M + BT_M - 1) / BT_M);
+
+    CUtensorMap mw, ms;
+    if (!make_map_2d(&ms, a.src, (uint64_t)a.K, (uint64_t)a.M, (uint64_t)a.src_sm, BT_M)) return 5;
+    if (w_kmajor) {
+        if (!make_map_2d(&mw, a.wei, (uint64_t)a.K, (uint64_t)a.N, (uint64_t)a.wei_sn, BT_N)) return 5;
     } else {
-        if (!make_map_2d(&mb, a.wei, (uint64_t)a.N, (uint64_t)a.K, (uint64_t)a.wei_sk, BKB)) return 5;
+        if (!make_map_2d(&mw, a.wei, (uint64_t)a.N, (uint64_t)a.K, (uint64_t)a.wei_sk, BKB)) return 5;
     }
-    uint32_t afmt, bfmt, cfmt;
+    // operand A = weights, operand B = src
+    uint32_t wfmt, sfmt, cfmt;
     if (int_path) {
-        afmt = a.src_dt == DT_S8 ? ptx::FMT_S8 : ptx::FMT_U8;
-        bfmt = a.wei_dt == DT_S8 ? ptx::FMT_S8 : ptx::FMT_U8;
+        wfmt = a.wei_dt == DT_S8 ? ptx::FMT_S8 : ptx::FMT_U8;
+        sfmt = a.src_dt == DT_S8 ? ptx::FMT_S8 : ptx::FMT_U8;
         cfmt = ptx::CFMT_S32;
     } else {
-        afmt = a.src_dt == DT_F8_E4M3 ? ptx::FMT_E4M3 : ptx::FMT_E5M2;
-        bfmt = a.wei_dt == DT_F8_E4M3 ? ptx::FMT_E4M3 : ptx::FMT_E5M2;
+        wfmt = a.wei_dt == DT_F8_E4M3 ? ptx::FMT_E4M3 : ptx::FMT_E5M2;
+        sfmt = a.src_dt == DT_F8_E4M3 ? ptx::FMT_E4M3 : ptx::FMT_E5M2;
         cfmt = ptx::CFMT_F32;
     }
-    tp.idesc = ptx::make_idesc(cfmt, afmt, bfmt, false, !b_kmajor, BM, BN);
+    tp.idesc = ptx::make_idesc(cfmt, wfmt, sfmt, !w_kmajor, false, BT_N, BT_M);
     const bool chain = a.n_po > 0 || (a.bias && a.bias_sm != 0); // a bias varying along M rides the generic tail
 #define QMM_TC_LAUNCH(KIND) \
-    (wide ? (chain ? launch_cfg<KIND, 256, 4, true>(ma, mb, a, tp, sm_count, st) \
-                   : launch_cfg<KIND, 256, 4, false>(ma, mb, a, tp, sm_count, st)) \
-          : (chain ? launch_cfg<KIND, 128, 6, true>(ma, mb, a, tp, sm_count, st) \
-                   : launch_cfg<KIND, 128, 6, false>(ma, mb, a, tp, sm_count, st)))
+    (tall ? (chain ? launch_cfg<KIND, 256, 4, true>(mw, ms, a, tp, sm_count, st) \
+                   : launch_cfg<KIND, 256, 4, false>(mw, ms, a, tp, sm_count, st)) \
+          : (chain ? launch_cfg<KIND, 128, 6, true>(mw, ms, a, tp, sm_count, st) \
+                   : launch_cfg<KIND, 128, 6, false>(mw, ms, a, tp, sm_count, st)))
     return int_path ? QMM_TC_LAUNCH(1) : QMM_TC_LAUNCH(0);
 #undef QMM_TC_LAUNCH
 }
