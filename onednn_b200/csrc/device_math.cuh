@@ -197,6 +197,79 @@ __device__ __forceinline__ bool has_sum(const MatmulArgs &a) {
     return false;
 }
 
+// The same ordered chain applied to R values of one dst column n at rows
+// m0 .. m0+R-1 held in registers.  Every post-op is one phase of straight-line
+// code over the R values: its kind / algorithm / operand type is decided once
+// per phase instead of once per element, and the R dependency chains
+// interleave.  Rows at or beyond M (the tail of the last tile) read row M-1 of
+// binary operands and old dst; their results are never stored.
+template <int R>
+__device__ __forceinline__ void apply_post_ops_rows(const MatmulArgs &a, float (&d)[R], int64_t m0, int64_t n) {
+    for (int i = 0; i < a.n_po; ++i) {
+        const PostOpArg &e = a.po[i];
+        if (e.kind == PO_ELTWISE) {
+            const float al = e.alpha, be = e.beta, sc = e.scale;
+            switch (e.alg) {
+#define QMM_ELT_PHASE(ALG, EXPR) \
+    case ALG: \
+        _Pragma("unroll") for (int j = 0; j < R; ++j) { const float s = d[j]; d[j] = __fmul_rn((EXPR), sc); } \
+        break;
+                QMM_ELT_PHASE(0x20, s > 0 ? s : __fmul_rn(s, al)) // relu
+                QMM_ELT_PHASE(0x21, tanhf(s))
+                QMM_ELT_PHASE(0x26, __fadd_rn(__fmul_rn(al, s), be)) // linear
+                QMM_ELT_PHASE(0x29, logistic_f(s))
+                QMM_ELT_PHASE(0x2b, gelu_tanh_f(s))
+                QMM_ELT_PHASE(0x2c, __fmul_rn(s, logistic_f(__fmul_rn(al, s)))) // swish
+                QMM_ELT_PHASE(0x2e, ((s > al ? s : al) > be ? be : (s > al ? s : al))) // clip
+                QMM_ELT_PHASE(0x31,
+                        __fmul_rn(__fmul_rn(0.5f, s),
+                                __fadd_rn(1.f, erff(__fmul_rn(s, 0.707106769084930419921875f))))) // gelu_erf
+#undef QMM_ELT_PHASE
+                default:
+#pragma unroll
+                    for (int j = 0; j < R; ++j) d[j] = __fmul_rn(eltwise_fwd(e.alg, d[j], al, be), sc);
+            }
+        } else if (e.kind == PO_BINARY) {
+            float y[R];
+            const char *base = (const char *)e.src1;
+            const int64_t last = a.M - 1;
+            if (e.src1_dt == DT_F32) {
+#pragma unroll
+                for (int j = 0; j < R; ++j)
+                    y[j] = ((const float *)base)[min(m0 + j, last) * e.sm + n * e.sn];
+            } else if (e.src1_dt == DT_BF16) {
+#pragma unroll
+                for (int j = 0; j < R; ++j)
+                    y[j] = bf16_bits_to_f32(((const unsigned short *)base)[min(m0 + j, last) * e.sm + n * e.sn]);
+            } else {
+#pragma unroll
+                for (int j = 0; j < R; ++j)
+                    y[j] = load_float(e.src1_dt, base, min(m0 + j, last) * e.sm + n * e.sn);
+            }
+            switch (e.alg) {
+                case 0x1fff0:
+#pragma unroll
+                    for (int j = 0; j < R; ++j) d[j] = __fadd_rn(d[j], y[j]);
+                    break;
+                case 0x1fff1:
+#pragma unroll
+                    for (int j = 0; j < R; ++j) d[j] = __fmul_rn(d[j], y[j]);
+                    break;
+                default:
+#pragma unroll
+                    for (int j = 0; j < R; ++j) d[j] = binary_op(e.alg, d[j], y[j]);
+            }
+        } else if (e.kind == PO_SUM) {
+            const int64_t last = a.M - 1;
+#pragma unroll
+            for (int j = 0; j < R; ++j) {
+                const float old = load_float(a.sum_dt, a.dst, min(m0 + j, last) * a.dst_sm + n * a.dst_sn);
+                d[j] = __fadd_rn(d[j], __fmul_rn(e.scale, __fsub_rn(old, (float)e.zero_point)));
+            }
+        }
+    }
+}
+
 // Everything after the K reduction for a dense problem: bias was already
 // added by the caller.  Post-ops, dst scale (a division, as in the
 // reference), dst zero-point, saturating store.

@@ -143,84 +143,90 @@ struct dst_size {
 
 // 32 consecutive dst rows of column n, accumulators in r[0..31].  Absent
 // scales are 1 and an absent bias is 0, which leaves values unchanged.
-template <bool INT, bool CHAIN, int DST>
+template <bool INT, bool CHAIN, int DST, int R>
 __device__ __forceinline__ void epilogue_rows(const MatmulArgs &a, const TcParams &tp, const TensorTerms &t,
-        const ColTerms &c, const uint32_t (&r)[32], int64_t m0, int64_t n) {
+        const ColTerms &c, const uint32_t (&r)[R], int64_t m0, int64_t n) {
     if (n >= a.N) return;
     char *dptr = (char *)a.dst + (m0 * a.dst_sm + n * a.dst_sn) * dst_size<DST>::value;
     const int64_t dstep = a.dst_sm * dst_size<DST>::value;
-    const int rows = (int)min((int64_t)32, a.M - m0);
-    // Phases of straight-line code over the 32 rows (uniform conditions are
+    const int rows = (int)min((int64_t)R, a.M - m0);
+    // Phases of straight-line code over the R rows (uniform conditions are
     // tested once per phase, not per row), so the rows' dependency chains
     // interleave; only the stores are predicated on the M tail.
-    float d[32];
+    float d[R];
     if constexpr (INT) {
         if (t.row_sum) {
 #pragma unroll
-            for (int j = 0; j < 32; ++j)
+            for (int j = 0; j < R; ++j)
                 d[j] = (float)((int)r[j] - c.zs_colsum - c.wei_zp * __ldg(tp.rowsum + min(m0 + j, a.M - 1)));
         } else {
 #pragma unroll
-            for (int j = 0; j < 32; ++j) d[j] = (float)((int)r[j] - c.zs_colsum);
+            for (int j = 0; j < R; ++j) d[j] = (float)((int)r[j] - c.zs_colsum);
         }
     } else {
 #pragma unroll
-        for (int j = 0; j < 32; ++j) d[j] = __uint_as_float(r[j]);
+        for (int j = 0; j < R; ++j) d[j] = __uint_as_float(r[j]);
     }
     if (t.row_scale) {
 #pragma unroll
-        for (int j = 0; j < 32; ++j)
+        for (int j = 0; j < R; ++j)
             d[j] = __fmul_rn(d[j], load_float(a.src_scale.dt, a.src_scale.ptr, min(m0 + j, a.M - 1)));
     } else {
 #pragma unroll
-        for (int j = 0; j < 32; ++j) d[j] = __fmul_rn(d[j], t.src_scale);
+        for (int j = 0; j < R; ++j) d[j] = __fmul_rn(d[j], t.src_scale);
     }
 #pragma unroll
-    for (int j = 0; j < 32; ++j) d[j] = __fadd_rn(__fmul_rn(d[j], c.wei_scale), c.bias);
+    for (int j = 0; j < R; ++j) d[j] = __fadd_rn(__fmul_rn(d[j], c.wei_scale), c.bias);
     if constexpr (CHAIN) {
+        if (t.bias_by_row) {
 #pragma unroll
-        for (int j = 0; j < 32; ++j) {
-            if (j < rows) {
-                const int64_t m = m0 + j;
-                float v = d[j];
-                if (t.bias_by_row) v = __fadd_rn(v, load_float(a.bias_dt, a.bias, m * a.bias_sm + n * a.bias_sn));
-                float old = 0.f;
-                if (has_sum(a)) old = load_float(a.sum_dt, a.dst, m * a.dst_sm + n * a.dst_sn);
-                d[j] = apply_post_ops(a, v, old, m, n, 0);
-            }
+            for (int j = 0; j < R; ++j)
+                d[j] = __fadd_rn(d[j],
+                        load_float(a.bias_dt, a.bias, min(m0 + j, a.M - 1) * a.bias_sm + n * a.bias_sn));
         }
+        apply_post_ops_rows<R>(a, d, m0, n);
     }
     if (t.has_dst_scale) { // the reference divides
 #pragma unroll
-        for (int j = 0; j < 32; ++j) d[j] = __fdiv_rn(d[j], t.dst_scale);
+        for (int j = 0; j < R; ++j) d[j] = __fdiv_rn(d[j], t.dst_scale);
     }
     if (t.has_dst_zp) {
         const float z = t.dst_zp_per_n ? c.dst_zp : t.dst_zp;
 #pragma unroll
-        for (int j = 0; j < 32; ++j) d[j] = __fadd_rn(d[j], z);
+        for (int j = 0; j < R; ++j) d[j] = __fadd_rn(d[j], z);
     }
     if (tp.mainloop_only == 3) { // profiling aid: everything but the stores
         float acc = 0.f;
 #pragma unroll
-        for (int j = 0; j < 32; ++j) acc += d[j];
+        for (int j = 0; j < R; ++j) acc += d[j];
         if (acc == 123.456f) store_typed<DST>(dptr, acc);
         return;
     }
 #pragma unroll
-    for (int j = 0; j < 32; ++j)
+    for (int j = 0; j < R; ++j)
         if (j < rows) store_typed<DST>(dptr + j * dstep, d[j]);
+}
+
+template <bool INT, bool CHAIN, int DST>
+__device__ __forceinline__ void epilogue_rows_typed(const MatmulArgs &a, const TcParams &tp, const TensorTerms &t,
+        const ColTerms &c, const uint32_t (&r)[32], int64_t m0, int64_t n) {
+    if constexpr (CHAIN) {
+        epilogue_rows<INT, CHAIN, DST, 32>(a, tp, t, c, r, m0, n);
+    } else {
+        epilogue_rows<INT, CHAIN, DST, 32>(a, tp, t, c, r, m0, n);
+    }
 }
 
 template <bool INT, bool CHAIN>
 __device__ __forceinline__ void epilogue_rows_any(const MatmulArgs &a, const TcParams &tp, const TensorTerms &t,
         const ColTerms &c, const uint32_t (&r)[32], int64_t m0, int64_t n) {
     switch (a.dst_dt) {
-        case DT_BF16: epilogue_rows<INT, CHAIN, DT_BF16>(a, tp, t, c, r, m0, n); break;
-        case DT_F32: epilogue_rows<INT, CHAIN, DT_F32>(a, tp, t, c, r, m0, n); break;
-        case DT_S8: epilogue_rows<INT, CHAIN, DT_S8>(a, tp, t, c, r, m0, n); break;
-        case DT_S32: epilogue_rows<INT, CHAIN, DT_S32>(a, tp, t, c, r, m0, n); break;
-        case DT_F16: epilogue_rows<INT, CHAIN, DT_F16>(a, tp, t, c, r, m0, n); break;
-        default: epilogue_rows<INT, CHAIN, DT_U8>(a, tp, t, c, r, m0, n); break;
+        case DT_BF16: epilogue_rows_typed<INT, CHAIN, DT_BF16>(a, tp, t, c, r, m0, n); break;
+        case DT_F32: epilogue_rows_typed<INT, CHAIN, DT_F32>(a, tp, t, c, r, m0, n); break;
+        case DT_S8: epilogue_rows_typed<INT, CHAIN, DT_S8>(a, tp, t, c, r, m0, n); break;
+        case DT_S32: epilogue_rows_typed<INT, CHAIN, DT_S32>(a, tp, t, c, r, m0, n); break;
+        case DT_F16: epilogue_rows_typed<INT, CHAIN, DT_F16>(a, tp, t, c, r, m0, n); break;
+        default: epilogue_rows_typed<INT, CHAIN, DT_U8>(a, tp, t, c, r, m0, n); break;
     }
 }
 
