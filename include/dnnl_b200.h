@@ -467,6 +467,32 @@ uint64_t dnnl_cuda_interop_launch_count(void);
 /* Human-readable text of the last CUDA error seen by the calling thread. */
 const char *dnnl_cuda_interop_last_error(void);
 
+/* dst[M,N] (s32) = (src[M,K] (u8) - src_zero_point) x weights[K,N] (s8), all
+ * row-major device buffers, enqueued on `cuda_stream` (a cudaStream_t).
+ *
+ * This entry point has no counterpart in the reference.  It exists for
+ * callers that must not trigger a device allocation: code running while a
+ * CUDA graph is being assembled by someone else, real-time or embedded hosts
+ * with a fixed memory plan, plugins whose host forbids cudaMalloc after
+ * start-up.  The regular path (dnnl_primitive_create) allocates a scratch
+ * buffer for the zero-point compensation sums; this one keeps that scratch in
+ * a fixed array inside the library image instead, so it never calls
+ * cudaMalloc / cudaFree or any allocating routine.
+ *
+ * Limits and rules:
+ *  - N <= 131072 (the array holds one s32 per weight column, 512 KB per GPU,
+ *    resident on every GPU that loads the library); larger N is rejected with
+ *    dnnl_invalid_arguments.  K and N multiples of 16, src and weights
+ *    16-byte aligned, else dnnl_unimplemented.
+ *  - The first call on each device looks up the array's device address; make
+ *    that first call outside any stream capture.
+ *  - All calls share the one array: two calls that overlap on the GPU (other
+ *    streams, other threads) race.  Serialize them on one stream.
+ * The results equal those of the dnnl_matmul primitive with a per-tensor s32
+ * src zero-point, bit for bit. */
+dnnl_status_t dnnl_cuda_interop_matmul_u8s8s32_zp_static(void *cuda_stream, int64_t M, int64_t N, int64_t K,
+        const uint8_t *src, const int8_t *weights, int32_t src_zero_point, int32_t *dst);
+
 #ifdef __cplusplus
 }
 #endif

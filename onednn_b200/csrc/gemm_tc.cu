@@ -27,8 +27,11 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
+#include <string>
+
 #include "device_math.cuh"
 #include "launch.h"
+#include "objects.hpp"
 #include "sm100_ptx.cuh"
 
 namespace qmm {
@@ -512,4 +515,74 @@ int launch_gemm_tc(const MatmulArgs &a, void *scratch, int sm_count, cudaStream_
 #undef QMM_TC_LAUNCH
 }
 
+// ---- allocation-free variant ----------------------------------------------
+// Scratch of dnnl_cuda_interop_matmul_u8s8s32_zp_static: the column sums of
+// the weights (zero-point compensation), preceded by a small header (the
+// zero-point value and the kernel status word).  It is part of the library
+// image: every GPU that loads the library holds these bytes until exit.
+constexpr int64_t STATIC_MAX_N = 131072;
+constexpr int STATIC_HEADER_WORDS = 64;
+static __device__ __align__(256) int32_t g_static_scratch[STATIC_HEADER_WORDS + STATIC_MAX_N];
+
+__global__ void static_scratch_header_kernel(int32_t *hdr, int32_t zero_point) {
+    hdr[0] = zero_point; // read by the GEMM epilogue as the src zero-point
+    hdr[1] = 0; // status word: must start at zero for every call
+}
+
 } // namespace qmm
+
+// Host side of the static scratch: the array's NAME is only a host-side
+// stand-in here; kernels need its device address, looked up once per device
+// (with that device current) by cudaGetSymbolAddress.
+extern "C" dnnl_status_t dnnl_cuda_interop_matmul_u8s8s32_zp_static(void *cuda_stream, int64_t M, int64_t N,
+        int64_t K, const uint8_t *src, const int8_t *weights, int32_t src_zero_point, int32_t *dst) {
+    using namespace qmm;
+    if (M < 0 || N < 0 || K < 0 || ((M && K) && !src) || ((K && N) && !weights) || ((M && N) && !dst))
+        return (dnnl_status_t)2; // invalid_arguments
+    if (N > STATIC_MAX_N) {
+        set_last_error("dnnl_cuda_interop_matmul_u8s8s32_zp_static: N exceeds the static scratch (131072 columns)");
+        return (dnnl_status_t)2;
+    }
+    if (M == 0 || N == 0 || K == 0) return (dnnl_status_t)0; // nothing to compute, as the primitive does
+    if (K % 16 || N % 16 || (uintptr_t)src % 16 || (uintptr_t)weights % 16 || M >= (1LL << 31)
+            || K >= (1LL << 31)) {
+        set_last_error("dnnl_cuda_interop_matmul_u8s8s32_zp_static: K and N must be multiples of 16 and the "
+                       "src / weights pointers 16-byte aligned");
+        return (dnnl_status_t)3; // unimplemented
+    }
+    int dev = 0;
+    if (!cuda_ok(cudaGetDevice(&dev), "cudaGetDevice")) return (dnnl_status_t)5;
+    constexpr int MAX_DEVICES = 64;
+    static int32_t *scratch_of[MAX_DEVICES] = {};
+    static int sm_count_of[MAX_DEVICES] = {};
+    if (dev < 0 || dev >= MAX_DEVICES) return (dnnl_status_t)3;
+    if (!scratch_of[dev]) { // set-up, once per device; not to be done under stream capture
+        void *p = nullptr;
+        if (!cuda_ok(cudaGetSymbolAddress(&p, g_static_scratch), "cudaGetSymbolAddress")) return (dnnl_status_t)5;
+        int sms = 0;
+        if (!cuda_ok(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev), "cudaDeviceGetAttribute"))
+            return (dnnl_status_t)5;
+        sm_count_of[dev] = sms;
+        scratch_of[dev] = (int32_t *)p;
+    }
+    int32_t *hdr = scratch_of[dev];
+    cudaStream_t st = (cudaStream_t)cuda_stream;
+    static_scratch_header_kernel<<<1, 1, 0, st>>>(hdr, src_zero_point);
+    count_launch();
+
+    MatmulArgs a {};
+    a.M = M; a.N = N; a.K = K;
+    a.src = src; a.src_dt = DT_U8; a.src_sm = K; a.src_sk = 1;
+    a.wei = weights; a.wei_dt = DT_S8; a.wei_sk = N; a.wei_sn = 1;
+    a.dst = dst; a.dst_dt = DT_S32; a.dst_sm = N; a.dst_sn = 1;
+    for (QParam *q : {&a.src_scale, &a.wei_scale, &a.dst_scale, &a.src_zp, &a.wei_zp, &a.dst_zp, &a.src_pr})
+        q->g0 = q->g1 = 1;
+    a.src_zp.ptr = hdr; // word 0 of the header
+    a.src_zp.dt = DT_S32;
+    a.non_default_attr = 1;
+    a.sum_dt = DT_S32;
+    a.status = hdr + 1;
+    const int rc = launch_gemm_tc(a, hdr + STATIC_HEADER_WORDS, sm_count_of[dev], st);
+    if (rc == 5) set_last_error(std::string("kernel launch: ") + cudaGetErrorString(cudaGetLastError()));
+    return (dnnl_status_t)rc;
+}
