@@ -380,8 +380,43 @@ dnnl_status_t tc_accepts(const dnnl_primitive_desc &pd) {
     return dnnl_success;
 }
 
+// Skinny weight-decompression GEMM: few src rows (decode), bf16/f16 src,
+// s4/u4 `ab` weights, weight scales per N or per (K-group, N), optional
+// zero-points with the same grouping (or per tensor).
+dnnl_status_t woq_accepts(const dnnl_primitive_desc &pd) {
+    if (ref_dense_accepts(pd) != dnnl_success) return dnnl_unimplemented;
+    const auto s = pd.src.data_type, w = pd.wei.data_type;
+    const auto &attr = pd.attr;
+    UNIMPL_IF(!(s == dnnl_bf16 || s == dnnl_f16) || !(w == dnnl_s4 || w == dnnl_u4));
+    const dnnl_dim_t M = pd.M(), N = pd.N(), K = pd.K();
+    UNIMPL_IF(M < 1 || M > 32 || N % 32 != 0 || K % 16 != 0 || K < 16);
+    UNIMPL_IF(N >= (1LL << 31) || K >= (1LL << 31));
+    UNIMPL_IF(pd.src.strides[1] != 1 || pd.src.strides[0] % 2 != 0);
+    UNIMPL_IF(pd.wei.strides[1] != 1 || pd.wei.strides[0] % 32 != 0 || pd.wei.strides[0] < N);
+    const auto &ws = attr.scale(DNNL_ARG_WEIGHTS), &ss = attr.scale(DNNL_ARG_SRC);
+    UNIMPL_IF(!ws.set || ws.on_host);
+    dnnl_dim_t group = K;
+    if (ws.mask == 3) {
+        UNIMPL_IF(!ws.group_ndims || ws.groups[1] != 1 || ws.groups[0] % 16 != 0);
+        group = ws.groups[0];
+    } else UNIMPL_IF(ws.mask != 2 || ws.group_ndims);
+    if (ss.set) UNIMPL_IF(ss.mask != 0 || ss.group_ndims);
+    const auto &wz = attr.zp(DNNL_ARG_WEIGHTS);
+    if (wz.set) {
+        UNIMPL_IF(wz.on_host);
+        if (wz.mask == 3) {
+            UNIMPL_IF(!wz.group_ndims || wz.groups[1] != 1 || wz.groups[0] != group);
+        } else UNIMPL_IF(wz.mask != 0);
+    }
+    return dnnl_success;
+}
+
 dnnl_status_t impl_accepts(const dnnl_primitive_desc &pd, int impl, std::string &name) {
     switch (impl) {
+        case IMPL_WOQ_GEMV:
+            if (pd.grouped) return dnnl_unimplemented;
+            name = "cuda:woq:skinny";
+            return woq_accepts(pd);
         case IMPL_TCGEN05_GEMM:
             if (pd.grouped) return dnnl_unimplemented;
             name = is_int8(pd.src.data_type) ? "cuda:tcgen05:int8" : "cuda:tcgen05:fp8";
@@ -404,6 +439,10 @@ dnnl_status_t select_impl(dnnl_primitive_desc &pd, int first) {
             pd.scratch_bytes = 0;
             if (i == IMPL_TCGEN05_GEMM && (pd.attr.zp(DNNL_ARG_SRC).set || pd.attr.zp(DNNL_ARG_WEIGHTS).set))
                 pd.scratch_bytes = gemm_tc_scratch_bytes(pd.M(), pd.N());
+            // the skinny GEMM keeps split-K partial sums and arrival counters there
+            if (i == IMPL_WOQ_GEMV)
+                pd.scratch_bytes = woq_skinny_scratch_bytes(
+                        pd.N(), pd.K(), pd.engine->sm_count > 0 ? pd.engine->sm_count : 148);
             pd.scratchpad = dnnl_memory_desc();
             if (pd.scratch_bytes && pd.attr.scratchpad_mode == dnnl_scratchpad_mode_user) {
                 pd.scratchpad.ndims = 1;
@@ -596,6 +635,7 @@ dnnl_status_t dnnl_primitive_create(dnnl_primitive_t *primitive, const_dnnl_prim
                 delete p;
                 return dnnl_out_of_memory;
             }
+            cudaMemset(p->scratch, 0, pd->scratch_bytes); // arrival counters start at zero
         }
     }
     *primitive = p;
@@ -788,6 +828,16 @@ extern "C" dnnl_status_t dnnl_primitive_execute(const_dnnl_primitive_t primitive
     int rc;
     switch (pd.impl) {
         case IMPL_REF: rc = launch_ref(a, stream->stream); break;
+        case IMPL_WOQ_GEMV:
+            if ((uintptr_t)a.wei % 16 || (uintptr_t)a.src % 4 || (uintptr_t)a.wei_scale.ptr % 4
+                    || (a.wei_zp.ptr && (uintptr_t)a.wei_zp.ptr % 16)) {
+                rc = launch_ref(a, stream->stream); // misaligned user pointers: generic kernel
+            } else {
+                if (pd.attr.scratchpad_mode == dnnl_scratchpad_mode_user) // counters of a user buffer
+                    cudaMemsetAsync(scratch, 0, ((pd.N() + 255) / 256) * sizeof(int), stream->stream);
+                rc = launch_woq_skinny(a, scratch, pd.engine->sm_count, stream->stream);
+            }
+            break;
         case IMPL_TCGEN05_GEMM:
             // TMA needs 16-byte aligned base pointers; a misaligned user
             // pointer is served by the generic kernel instead

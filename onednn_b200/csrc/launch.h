@@ -21,4 +21,10 @@ int launch_gemm_tc(const MatmulArgs &a, void *scratch, int sm_count, cudaStream_
 size_t gemm_tc_scratch_bytes(int64_t M, int64_t N);
 bool gemm_tc_pointers_ok(const MatmulArgs &a);
 
+// int4 weight-decompression skinny GEMM (woq_skinny.cu).  `scratch`:
+// woq_skinny_scratch_bytes(...) bytes, zero-initialised once (split-K partial
+// sums and per-column-block arrival counters).
+int launch_woq_skinny(const MatmulArgs &a, void *scratch, int sm_count, cudaStream_t st);
+size_t woq_skinny_scratch_bytes(int64_t N, int64_t K, int sm_count);
+
 } // namespace qmm

@@ -1,0 +1,374 @@
+// "cuda:woq:skinny": weight-decompression matmul for few rows (decode):
+// dst[M,N] = src[M,K] (bf16/f16) x dequant(weights[K,N] s4/u4), M <= 8 per
+// pass, K-grouped scales and zero-points (fpmath apply_to_int).
+//
+// The problem is bound by the HBM stream of the packed weights (half a byte
+// per element), and at B200 bandwidth a CUDA-core FMA per weight plus its
+// int4->float conversion would already exceed the instruction budget (about
+// 2 lane-operations per weight).  So the multiply-accumulate runs on the
+// tensor cores (mma.sync m16n8k16, weights as the 16-row operand, the src rows
+// as the 8-column operand) and the lanes only rebuild the operand registers:
+//   * a nibble u becomes the bf16 value 128+u (f16: 1024+u) by OR-ing it into
+//     the mantissa of a constant - one LOP3 per two weights, exact;
+//   * the offset and the zero-point are removed after the K-group is summed:
+//     sum_k s_k (w_k - zp) scale = scale * (sum_k s_k w'_k - (off + zp) sum_k s_k)
+//     with f32 accumulators, so no bf16 rounding of scaled weights is involved
+//     (the reference multiplies each weight by its scale in f32,
+//     src/cpu/matmul/ref_matmul.cpp:193-214; results differ from it only by
+//     f32 summation order).
+// Data movement: every warp owns a ring of TMA stages (16 k-rows x 128 bytes =
+// 256 columns, 128B swizzle, so the 16-byte reads of a quarter-warp hit 8
+// distinct bank groups); the packed layout of the API (N contiguous, two
+// columns per byte) is consumed as it is.  K is split over the warps of a CTA
+// and over `splits` CTAs; partial sums meet in shared memory, then in a global
+// scratch where the last CTA of a column block adds them in a fixed order
+// (deterministic) and runs the epilogue.
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include "device_math.cuh"
+#include "launch.h"
+#include "sm100_ptx.cuh"
+
+namespace qmm {
+
+namespace {
+
+constexpr int WARPS = 8;
+constexpr int STAGES = 8; // per warp
+constexpr int STAGE_BYTES = 16 * 128; // 16 k-rows of 256 packed columns
+constexpr int NB = 256; // dst columns per CTA
+constexpr int MB = 8; // src rows per pass (the MMA's n extent)
+constexpr int SMEM_BYTES = WARPS * STAGES * STAGE_BYTES + WARPS * STAGES * 8 + 64 + 1024;
+
+struct WoqParams {
+    int M; // rows of this pass (<= 8)
+    int64_t m_base; // first src/dst row of this pass
+    int ksteps; // K / 16
+    int group_steps; // k-steps per quantization group (group / 16); ksteps when not grouped along K
+    int splits;
+    int sgn4; // weights are s4 (else u4)
+    int zp_mode; // 0 none, 1 per (group, n), 2 per tensor
+    float *partial; // [nblk][splits][8][256]
+    int *counters; // [nblk]
+};
+
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile(
+            "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+            : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+            : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void mma_f16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile(
+            "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+            : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+            : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+// (x & 0x000F000F) ^ magic : two nibbles -> two 16-bit floats
+__device__ __forceinline__ uint32_t nib2(uint32_t x, uint32_t magic) {
+    uint32_t r;
+    asm("lop3.b32 %0, %1, 0x000F000F, %2, 0x6a;" : "=r"(r) : "r"(x), "r"(magic));
+    return r;
+}
+__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
+    uint32_t r;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(sel));
+    return r;
+}
+
+template <bool F16>
+__device__ __forceinline__ float pair_sum(uint32_t v) {
+    if (F16) {
+        const __half2 h = *reinterpret_cast<const __half2 *>(&v);
+        return __low2float(h) + __high2float(h);
+    }
+    return __uint_as_float(v << 16) + __uint_as_float(v & 0xffff0000u);
+}
+
+template <bool F16>
+__global__ void __launch_bounds__(WARPS * 32, 1)
+woq_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ MatmulArgs a,
+        const __grid_constant__ WoqParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint64_t *bars = (uint64_t *)(smem + WARPS * STAGES * STAGE_BYTES);
+    int *flag = (int *)(bars + WARPS * STAGES);
+
+    const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+    const int g = lane >> 2, tig = lane & 3;
+    const int nblk = blockIdx.x, split = blockIdx.y;
+    const int64_t n0 = (int64_t)nblk * NB + g * 32; // this thread's 32 columns
+    const bool cols_ok = n0 < a.N;
+
+    // k-steps of this CTA, then of this warp (contiguous ranges)
+    const int cs0 = (int)((int64_t)p.ksteps * split / p.splits), cs1 = (int)((int64_t)p.ksteps * (split + 1) / p.splits);
+    const int ws0 = cs0 + (int)((int64_t)(cs1 - cs0) * warp / WARPS), ws1 = cs0 + (int)((int64_t)(cs1 - cs0) * (warp + 1) / WARPS);
+    const int nsteps = ws1 - ws0;
+
+    uint8_t *ring = smem + warp * STAGES * STAGE_BYTES;
+    uint64_t *full = bars + warp * STAGES;
+    if (lane == 0) {
+        for (int s = 0; s < STAGES; ++s) ptx::mbar_init(&full[s], 1);
+        ptx::fence_barrier_init();
+    }
+    if (threadIdx.x == 0) *flag = 0;
+    __syncwarp();
+    if (lane == 0) {
+        ptx::prefetch_tensormap(&tmW);
+        for (int i = 0; i < STAGES && i < nsteps; ++i) {
+            ptx::mbar_arrive_expect_tx(&full[i], STAGE_BYTES);
+            ptx::tma_load_2d(ring + i * STAGE_BYTES, &tmW, &full[i], nblk * (NB / 2), (ws0 + i) * 16);
+        }
+    }
+
+    // bf16: nibble u -> 128+u (0x4300 | u).  f16: u alone is the subnormal u * 2^-24, exact in the MMA,
+    // so only the s4 bias of 8 remains as offset and the group sum is rescaled by 2^24.
+    const uint32_t magic = F16 ? (p.sgn4 ? 0x00080008u : 0u) : (p.sgn4 ? 0x43084308u : 0x43004300u);
+    const float off = (F16 ? 0.f : 128.f) + (p.sgn4 ? 8.f : 0.f);
+    const float acc_scale = F16 ? 16777216.f : 1.f;
+    float acc[16][4], tot[16][4];
+#pragma unroll
+    for (int t = 0; t < 16; ++t)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) acc[t][i] = tot[t][i] = 0.f;
+    float sp = 0.f; // running sum of this lane's src values (row g) in the current group
+
+    const char *src_row = (const char *)a.src + ((p.m_base + g) * a.src_sm) * 2;
+    const bool row_ok = g < p.M;
+    bool ok = true;
+
+    for (int it = 0; it < nsteps; ++it) {
+        const int s = it % STAGES;
+        const int kstep = ws0 + it;
+        if (!ptx::mbar_wait(&full[s], (it / STAGES) & 1)) { ok = false; break; }
+        // rows 2tig, 2tig+1, 2tig+8, 2tig+9 of the stage; column chunk g, swizzled by (row & 7)
+        const uint8_t *st = ring + s * STAGE_BYTES;
+        uint4 R[4];
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+            const int row = 2 * tig + (r & 1) + (r >> 1) * 8;
+            R[r] = *reinterpret_cast<const uint4 *>(st + row * 128 + ((g ^ (row & 7)) << 4));
+        }
+        __syncwarp();
+        if (lane == 0 && it + STAGES < nsteps) { // stage consumed by every lane: refill it
+            ptx::mbar_arrive_expect_tx(&full[s], STAGE_BYTES);
+            ptx::tma_load_2d(ring + s * STAGE_BYTES, &tmW, &full[s], nblk * (NB / 2), (kstep + STAGES) * 16);
+        }
+        // src operand: row g, k = 16*kstep + {2tig, 2tig+1} and {2tig+8, 2tig+9}
+        uint32_t b0 = 0, b1 = 0;
+        if (row_ok) {
+            const char *sp_ = src_row + ((int64_t)kstep * 16 + 2 * tig) * 2;
+            b0 = __ldg(reinterpret_cast<const uint32_t *>(sp_));
+            b1 = __ldg(reinterpret_cast<const uint32_t *>(sp_ + 16));
+            sp += pair_sum<F16>(b0) + pair_sum<F16>(b1);
+        }
+        const uint32_t *w0 = reinterpret_cast<const uint32_t *>(&R[0]), *w1 = reinterpret_cast<const uint32_t *>(&R[1]);
+        const uint32_t *w2 = reinterpret_cast<const uint32_t *>(&R[2]), *w3 = reinterpret_cast<const uint32_t *>(&R[3]);
+#pragma unroll
+        for (int t = 0; t < 16; ++t) {
+            // byte t of the four rows: low nibble = column 2t, high nibble = column 2t+1
+            const uint32_t sel = ((4 + (t & 3)) << 12) | ((4 + (t & 3)) << 8) | ((t & 3) << 4) | (t & 3);
+            const uint32_t x01 = prmt(w0[t >> 2], w1[t >> 2], sel);
+            const uint32_t x23 = prmt(w2[t >> 2], w3[t >> 2], sel);
+            uint32_t af[4];
+            af[0] = nib2(x01, magic); // column 2t,   k pair (2tig, 2tig+1)
+            af[1] = nib2(x01 >> 4, magic); // column 2t+1
+            af[2] = nib2(x23, magic); // column 2t,   k pair (2tig+8, 2tig+9)
+            af[3] = nib2(x23 >> 4, magic); // column 2t+1
+            if (F16) mma_f16(acc[t], af, b0, b1);
+            else mma_bf16(acc[t], af, b0, b1);
+        }
+        // end of a quantization group (or of this warp's range): fold the group into the totals
+        const bool group_end = ((kstep + 1) % p.group_steps) == 0;
+        if (group_end || it == nsteps - 1) {
+            const int gi = kstep / p.group_steps;
+            sp += __shfl_xor_sync(0xffffffffu, sp, 1);
+            sp += __shfl_xor_sync(0xffffffffu, sp, 2);
+            const float S0 = __shfl_sync(0xffffffffu, sp, (2 * tig) * 4);
+            const float S1 = __shfl_sync(0xffffffffu, sp, (2 * tig + 1) * 4);
+            sp = 0.f;
+            if (cols_ok) {
+                const int64_t qbase = (a.wei_scale.mask & 1) ? (int64_t)gi * a.wei_scale.ld : 0;
+                uint4 zq = make_uint4(0, 0, 0, 0);
+                const bool zp4 = p.zp_mode == 1 && (a.wei_zp.dt == DT_U4 || a.wei_zp.dt == DT_S4);
+                if (zp4) zq = __ldg(reinterpret_cast<const uint4 *>((const char *)a.wei_zp.ptr + ((int64_t)gi * a.wei_zp.ld + n0) / 2));
+                float zt = 0.f;
+                if (p.zp_mode == 2) zt = (float)load_int(a.wei_zp.dt, a.wei_zp.ptr, 0);
+#pragma unroll
+                for (int t = 0; t < 16; ++t) {
+                    float sc_lo, sc_hi;
+                    if (a.wei_scale.dt == DT_BF16) {
+                        const uint32_t w = __ldg(reinterpret_cast<const uint32_t *>(
+                                (const char *)a.wei_scale.ptr + (qbase + n0 + 2 * t) * 2));
+                        sc_lo = __uint_as_float(w << 16);
+                        sc_hi = __uint_as_float(w & 0xffff0000u);
+                    } else {
+                        sc_lo = load_float(a.wei_scale.dt, a.wei_scale.ptr, qbase + n0 + 2 * t);
+                        sc_hi = load_float(a.wei_scale.dt, a.wei_scale.ptr, qbase + n0 + 2 * t + 1);
+                    }
+                    float z_lo = zt, z_hi = zt;
+                    if (zp4) {
+                        const uint32_t byte = (reinterpret_cast<const uint32_t *>(&zq)[t >> 2] >> ((t & 3) * 8)) & 0xffu;
+                        int lo = byte & 0xf, hi = byte >> 4;
+                        if (a.wei_zp.dt == DT_S4) { lo = (lo ^ 8) - 8; hi = (hi ^ 8) - 8; }
+                        z_lo = (float)lo; z_hi = (float)hi;
+                    } else if (p.zp_mode == 1) {
+                        z_lo = (float)load_int(a.wei_zp.dt, a.wei_zp.ptr, (int64_t)gi * a.wei_zp.ld + n0 + 2 * t);
+                        z_hi = (float)load_int(a.wei_zp.dt, a.wei_zp.ptr, (int64_t)gi * a.wei_zp.ld + n0 + 2 * t + 1);
+                    }
+                    const float oz_lo = off + z_lo, oz_hi = off + z_hi;
+                    tot[t][0] = fmaf(sc_lo, acc[t][0] * acc_scale - oz_lo * S0, tot[t][0]);
+                    tot[t][1] = fmaf(sc_lo, acc[t][1] * acc_scale - oz_lo * S1, tot[t][1]);
+                    tot[t][2] = fmaf(sc_hi, acc[t][2] * acc_scale - oz_hi * S0, tot[t][2]);
+                    tot[t][3] = fmaf(sc_hi, acc[t][3] * acc_scale - oz_hi * S1, tot[t][3]);
+                    acc[t][0] = acc[t][1] = acc[t][2] = acc[t][3] = 0.f;
+                }
+            }
+        }
+    }
+    if (!ok) atomicExch(a.status, 5);
+
+    // ---- reduce the warps' totals through shared memory: red[warp][m][256]
+    __syncthreads();
+    float *red = reinterpret_cast<float *>(smem);
+#pragma unroll
+    for (int t = 0; t < 16; ++t) {
+        const int nl = g * 32 + 2 * t;
+        red[(warp * MB + 2 * tig) * NB + nl] = tot[t][0];
+        red[(warp * MB + 2 * tig + 1) * NB + nl] = tot[t][1];
+        red[(warp * MB + 2 * tig) * NB + nl + 1] = tot[t][2];
+        red[(warp * MB + 2 * tig + 1) * NB + nl + 1] = tot[t][3];
+    }
+    __syncthreads();
+    const int i = threadIdx.x; // column of the block
+    const int64_t n = (int64_t)nblk * NB + i;
+    float v[MB];
+#pragma unroll
+    for (int m = 0; m < MB; ++m) {
+        float s = 0.f;
+#pragma unroll
+        for (int w = 0; w < WARPS; ++w) s += red[(w * MB + m) * NB + i];
+        v[m] = s;
+    }
+    if (p.splits > 1) {
+        float *mine = p.partial + ((int64_t)(nblk * p.splits + split) * MB) * NB;
+#pragma unroll
+        for (int m = 0; m < MB; ++m) mine[m * NB + i] = v[m];
+        __threadfence();
+        __syncthreads();
+        if (threadIdx.x == 0) *flag = atomicAdd(&p.counters[nblk], 1) == p.splits - 1;
+        __syncthreads();
+        if (!*flag) return;
+        __threadfence();
+        // last CTA of the column block: add the partial sums in split order
+#pragma unroll
+        for (int m = 0; m < MB; ++m) v[m] = 0.f;
+        for (int sidx = 0; sidx < p.splits; ++sidx) {
+            const float *q = p.partial + ((int64_t)(nblk * p.splits + sidx) * MB) * NB;
+#pragma unroll
+            for (int m = 0; m < MB; ++m) v[m] += __ldcg(q + m * NB + i);
+        }
+        if (threadIdx.x == 0) p.counters[nblk] = 0; // ready for the next launch
+    }
+    if (n >= a.N) return;
+    float ss = 1.f;
+    if (a.src_scale.ptr) ss = load_float(a.src_scale.dt, a.src_scale.ptr, 0);
+    else if (a.src_scale.on_host) ss = a.src_scale.host_value;
+#pragma unroll
+    for (int m = 0; m < MB; ++m) {
+        if (m < p.M) {
+            const int64_t mm = p.m_base + m;
+            float d = v[m] * ss;
+            if (a.bias) d = __fadd_rn(d, load_float(a.bias_dt, a.bias, mm * a.bias_sm + n * a.bias_sn));
+            finish_store(a, d, mm, n, false);
+        }
+    }
+}
+
+typedef CUresult (*encode_tiled_fn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+        const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+        CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+encode_tiled_fn woq_get_encode() {
+    static encode_tiled_fn fn = nullptr;
+    if (!fn) {
+        void *ptr = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess
+                && q == cudaDriverEntryPointSuccess)
+            fn = (encode_tiled_fn)ptr;
+    }
+    return fn;
+}
+
+// K splits: fill whole waves of one CTA per SM, keep >= 8 k-steps per warp
+int woq_splits(int64_t N, int64_t K, int sm_count) {
+    const int64_t nblk = (N + NB - 1) / NB, ksteps = K / 16;
+    int best = 1;
+    double best_eff = 0;
+    for (int s = 1; s <= 16; ++s) {
+        if (s > 1 && ksteps / s < 8 * WARPS) break;
+        const int64_t ctas = nblk * s, waves = (ctas + sm_count - 1) / sm_count;
+        const double eff = (double)ctas / (double)(waves * sm_count);
+        if (eff > best_eff + 0.02) { best_eff = eff; best = s; }
+    }
+    return best;
+}
+
+} // namespace
+
+size_t woq_skinny_scratch_bytes(int64_t N, int64_t K, int sm_count) {
+    const int64_t nblk = (N + NB - 1) / NB;
+    const int splits = woq_splits(N, K, sm_count);
+    return (size_t)(nblk * splits * MB * NB) * sizeof(float) + (size_t)nblk * sizeof(int) + 256;
+}
+
+// `scratch`: woq_skinny_scratch_bytes(N, K, sm_count) bytes whose counters
+// (the first nblk ints) are zero before the first launch; the kernel leaves
+// them zero.
+int launch_woq_skinny(const MatmulArgs &a, void *scratch, int sm_count, cudaStream_t st) {
+    if (a.M == 0 || a.N == 0) return 0;
+    encode_tiled_fn enc = woq_get_encode();
+    if (!enc || !scratch) return 5;
+    const int64_t nblk = (a.N + NB - 1) / NB;
+    CUtensorMap tm;
+    cuuint64_t dims[2] = {(cuuint64_t)(a.N / 2), (cuuint64_t)a.K};
+    cuuint64_t strides[1] = {(cuuint64_t)(a.wei_sk / 2)};
+    cuuint32_t box[2] = {128, 16};
+    cuuint32_t estr[2] = {1, 1};
+    if (enc(&tm, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void *>(a.wei), dims, strides, box, estr,
+                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE)
+            != CUDA_SUCCESS)
+        return 5;
+    WoqParams p {};
+    p.ksteps = (int)(a.K / 16);
+    const int64_t group = (a.wei_scale.ptr && (a.wei_scale.mask & 1)) ? a.wei_scale.g0
+            : (a.wei_zp.ptr && (a.wei_zp.mask & 1))                    ? a.wei_zp.g0
+                                                                       : a.K;
+    p.group_steps = (int)(group / 16);
+    p.splits = woq_splits(a.N, a.K, sm_count);
+    p.sgn4 = a.wei_dt == DT_S4;
+    p.zp_mode = !a.wei_zp.ptr ? 0 : (a.wei_zp.mask ? 1 : 2);
+    p.counters = (int *)scratch;
+    p.partial = (float *)((char *)scratch + ((nblk * sizeof(int) + 255) / 256) * 256);
+    const bool f16 = a.src_dt == DT_F16;
+    auto kern = f16 ? woq_skinny_kernel<true> : woq_skinny_kernel<false>;
+    static bool configured[2] = {false, false};
+    if (!configured[f16]) {
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess) return 5;
+        configured[f16] = true;
+    }
+    dim3 grid((unsigned)nblk, (unsigned)p.splits);
+    for (int64_t m0 = 0; m0 < a.M; m0 += MB) { // more than 8 rows: one pass over the weights per 8 rows
+        p.m_base = m0;
+        p.M = (int)((a.M - m0) < MB ? (a.M - m0) : MB);
+        kern<<<grid, WARPS * 32, SMEM_BYTES, st>>>(tm, a, p);
+        count_launch();
+    }
+    return cudaGetLastError() == cudaSuccess ? 0 : 5;
+}
+
+} // namespace qmm

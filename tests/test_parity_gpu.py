@@ -99,6 +99,51 @@ def test_tcgen05_gemm_matches_oracle(gpu, name):
     assert_parity(got, want, p.dst_dt, name, slack_for(p, impl))
 
 
+def _per_n_scale(p):
+    r = np.random.Generator(np.random.PCG64(8))
+    p.quant["wei_scale"] = W.Quant(W.f32_to_bf16(r.uniform(0.005, 0.02, (1, p.N)).astype(np.float32)), W.BF16, 2)
+    p.quant.pop("wei_zp", None)
+    return p
+
+
+def _with_bias_relu(p):
+    r = np.random.Generator(np.random.PCG64(9))
+    p.bias = W.QTensor(W.f32_to_bf16(r.standard_normal((1, p.N), dtype=np.float32)), W.BF16, (1, p.N))
+    p.post_ops.append(W.PostOp(W.PO_ELTWISE, W.ELTWISE["relu"], 0.0, 0.0, 1.0))
+    return p
+
+
+WOQ_CASES = {
+    "m1": lambda: W.int4_decode(1, 2048, 1024),
+    "m8": lambda: W.int4_decode(8, 2048, 1024),
+    "m3_tail_cols": lambda: W.int4_decode(3, 1024, 288),
+    "m17_two_passes": lambda: W.int4_decode(17, 512, 512),
+    "m32": lambda: W.int4_decode(32, 1024, 256),
+    "long_k_splits": lambda: W.int4_decode(4, 8192, 512),
+    "group32": lambda: W.int4_decode(5, 512, 256, group=32),
+    "u4_u8zp": lambda: W.int4_decode(2, 1024, 256, wei_dt=W.U4, zp_dt=W.U8),
+    "s4_s4zp": lambda: W.int4_decode(2, 1024, 256, zp_dt=W.S4),
+    "no_zp": lambda: W.int4_decode(6, 1024, 256, with_zp=False),
+    "per_n_scale": lambda: _per_n_scale(W.int4_decode(4, 1024, 256)),
+    "f16_src": lambda: W.int4_decode(4, 1024, 256, src_dt=W.F16, dst_dt=W.F16),
+    "bias_relu": lambda: _with_bias_relu(W.int4_decode(7, 1024, 512)),
+    "f32_dst": lambda: W.int4_decode(2, 512, 256, dst_dt=W.F32),
+}
+
+
+@pytest.mark.parametrize("name", sorted(WOQ_CASES))
+def test_woq_skinny_matches_oracle(gpu, name):
+    eng, strm = gpu
+    p = WOQ_CASES[name]()
+    want = O.run_port(p)
+    got, impl = run_problem(p, eng, strm, impl="woq")
+    assert impl == "cuda:woq:skinny"
+    assert_parity(got, want, p.dst_dt, name, slack_for(p, impl))
+    # the arrival counters are left at zero: a second execution gives the same bits
+    got2, _ = run_problem(p, eng, strm, impl="woq")
+    assert np.array_equal(got, got2)
+
+
 def test_grouped_bad_offsets_reports_invalid_arguments(gpu):
     """Non-monotone offsets: the reference returns invalid_arguments
     (ref_grouped_gemm.cpp:164-213); here the status surfaces at wait()."""
