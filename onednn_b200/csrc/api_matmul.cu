@@ -829,7 +829,7 @@ extern "C" dnnl_status_t dnnl_primitive_execute(const_dnnl_primitive_t primitive
     switch (pd.impl) {
         case IMPL_REF: rc = launch_ref(a, stream->stream); break;
         case IMPL_WOQ_GEMV:
-            if ((uintptr_t)a.wei % 16 || (uintptr_t)a.src % 4 || (uintptr_t)a.wei_scale.ptr % 4
+            if ((uintptr_t)a.wei % 16 || (uintptr_t)a.src % 4 || (uintptr_t)a.wei_scale.ptr % 16
                     || (a.wei_zp.ptr && (uintptr_t)a.wei_zp.ptr % 16)) {
                 rc = launch_ref(a, stream->stream); // misaligned user pointers: generic kernel
             } else {

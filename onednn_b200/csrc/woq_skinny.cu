@@ -1,28 +1,30 @@
 // "cuda:woq:skinny": weight-decompression matmul for few rows (decode):
-// dst[M,N] = src[M,K] (bf16/f16) x dequant(weights[K,N] s4/u4), M <= 8 per
-// pass, K-grouped scales and zero-points (fpmath apply_to_int).
+// dst[M,N] = src[M,K] (bf16/f16) x dequant(weights[K,N] s4/u4), 8 rows per
+// pass, scales per column or per (K-group, column), optional zero-points
+// (fpmath apply_to_int).
 //
 // The problem is bound by the HBM stream of the packed weights (half a byte
 // per element), and at B200 bandwidth a CUDA-core FMA per weight plus its
-// int4->float conversion would already exceed the instruction budget (about
-// 2 lane-operations per weight).  So the multiply-accumulate runs on the
-// tensor cores (mma.sync m16n8k16, weights as the 16-row operand, the src rows
-// as the 8-column operand) and the lanes only rebuild the operand registers:
-//   * a nibble u becomes the bf16 value 128+u (f16: 1024+u) by OR-ing it into
-//     the mantissa of a constant - one LOP3 per two weights, exact;
-//   * the offset and the zero-point are removed after the K-group is summed:
+// int4->float conversion would exceed the instruction budget (about 2
+// lane-operations per weight).  So the multiply-accumulate runs on the tensor
+// cores (mma.sync m16n8k16: weights as the 16-row operand, src rows as the
+// 8-column operand) and the lanes only rebuild operand registers:
+//   * bf16: a nibble u becomes 128+u by OR-ing it into the mantissa of 0x4300;
+//     f16: u itself is the subnormal u*2^-24.  One LOP3 per two weights, exact.
+//   * the offset and the zero-point leave after the K-group has been summed:
 //     sum_k s_k (w_k - zp) scale = scale * (sum_k s_k w'_k - (off + zp) sum_k s_k)
-//     with f32 accumulators, so no bf16 rounding of scaled weights is involved
-//     (the reference multiplies each weight by its scale in f32,
-//     src/cpu/matmul/ref_matmul.cpp:193-214; results differ from it only by
-//     f32 summation order).
-// Data movement: every warp owns a ring of TMA stages (16 k-rows x 128 bytes =
-// 256 columns, 128B swizzle, so the 16-byte reads of a quarter-warp hit 8
-// distinct bank groups); the packed layout of the API (N contiguous, two
-// columns per byte) is consumed as it is.  K is split over the warps of a CTA
-// and over `splits` CTAs; partial sums meet in shared memory, then in a global
-// scratch where the last CTA of a column block adds them in a fixed order
-// (deterministic) and runs the epilogue.
+//     in f32, so no rounding of scaled weights is involved (the reference
+//     scales each weight in f32, src/cpu/matmul/ref_matmul.cpp:193-214;
+//     results differ from it only by f32 summation order).
+// Work decomposition ("stream-K"): the (column block, k-step) space is cut
+// into one contiguous, equally long range per CTA, one CTA per SM, so every
+// SM streams the same number of bytes; a CTA touches at most two column
+// blocks.  Inside a range the 8 warps take consecutive k sub-ranges and each
+// warp feeds itself through its own ring of TMA stages (16 k-rows x 128 bytes
+// = 256 columns, 128B swizzle: the 16-byte reads of a quarter-warp hit 8
+// distinct bank groups).  Warp totals meet in shared memory; where several
+// CTAs share a column block their partial sums go to a global scratch and the
+// last arriver adds them in CTA order (deterministic) and runs the epilogue.
 #include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
@@ -38,19 +40,24 @@ namespace {
 constexpr int WARPS = 8;
 constexpr int STAGES = 8; // per warp
 constexpr int STAGE_BYTES = 16 * 128; // 16 k-rows of 256 packed columns
-constexpr int NB = 256; // dst columns per CTA
+constexpr int NB = 256; // dst columns per column block
 constexpr int MB = 8; // src rows per pass (the MMA's n extent)
-constexpr int SMEM_BYTES = WARPS * STAGES * STAGE_BYTES + WARPS * STAGES * 8 + 64 + 1024;
+constexpr int RED_PITCH = 276; // words per row of the reduction tile: 256 + 8 x 2 pads, = 4 mod 16
+constexpr int RING_BYTES = WARPS * STAGES * STAGE_BYTES;
+constexpr int RED_BYTES = WARPS * MB * RED_PITCH * 4;
+constexpr int SMEM_BYTES = RING_BYTES + RED_BYTES + WARPS * STAGES * 8 + 64 + 1024;
 
 struct WoqParams {
     int M; // rows of this pass (<= 8)
     int64_t m_base; // first src/dst row of this pass
     int ksteps; // K / 16
-    int group_steps; // k-steps per quantization group (group / 16); ksteps when not grouped along K
-    int splits;
+    int group_steps; // k-steps per quantization group; ksteps when not grouped along K
+    int nblk; // column blocks
+    int per; // (column block, k-step) pairs per CTA
+    int max_slots; // partial-sum slots per column block
     int sgn4; // weights are s4 (else u4)
     int zp_mode; // 0 none, 1 per (group, n), 2 per tensor
-    float *partial; // [nblk][splits][8][256]
+    float *partial; // [nblk][max_slots][8][256]
     int *counters; // [nblk]
 };
 
@@ -77,7 +84,6 @@ __device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
     asm("prmt.b32 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(sel));
     return r;
 }
-
 template <bool F16>
 __device__ __forceinline__ float pair_sum(uint32_t v) {
     if (F16) {
@@ -86,6 +92,10 @@ __device__ __forceinline__ float pair_sum(uint32_t v) {
     }
     return __uint_as_float(v << 16) + __uint_as_float(v & 0xffff0000u);
 }
+// position of column c in a row of the reduction tile: two pad words per 32
+// columns keep the float2 stores of a half-warp (4 rows x 4 column groups) on
+// 16 distinct bank pairs and 8-byte aligned
+__device__ __forceinline__ int red_pos(int c) { return c + 2 * (c >> 5); }
 
 template <bool F16>
 __global__ void __launch_bounds__(WARPS * 32, 1)
@@ -93,198 +103,237 @@ woq_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
         const __grid_constant__ WoqParams p) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-    uint64_t *bars = (uint64_t *)(smem + WARPS * STAGES * STAGE_BYTES);
+    float *red = reinterpret_cast<float *>(smem + RING_BYTES);
+    uint64_t *bars = (uint64_t *)(smem + RING_BYTES + RED_BYTES);
     int *flag = (int *)(bars + WARPS * STAGES);
 
     const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
     const int g = lane >> 2, tig = lane & 3;
-    const int nblk = blockIdx.x, split = blockIdx.y;
-    const int64_t n0 = (int64_t)nblk * NB + g * 32; // this thread's 32 columns
-    const bool cols_ok = n0 < a.N;
-
-    // k-steps of this CTA, then of this warp (contiguous ranges)
-    const int cs0 = (int)((int64_t)p.ksteps * split / p.splits), cs1 = (int)((int64_t)p.ksteps * (split + 1) / p.splits);
-    const int ws0 = cs0 + (int)((int64_t)(cs1 - cs0) * warp / WARPS), ws1 = cs0 + (int)((int64_t)(cs1 - cs0) * (warp + 1) / WARPS);
-    const int nsteps = ws1 - ws0;
-
     uint8_t *ring = smem + warp * STAGES * STAGE_BYTES;
     uint64_t *full = bars + warp * STAGES;
     if (lane == 0) {
         for (int s = 0; s < STAGES; ++s) ptx::mbar_init(&full[s], 1);
         ptx::fence_barrier_init();
-    }
-    if (threadIdx.x == 0) *flag = 0;
-    __syncwarp();
-    if (lane == 0) {
         ptx::prefetch_tensormap(&tmW);
-        for (int i = 0; i < STAGES && i < nsteps; ++i) {
-            ptx::mbar_arrive_expect_tx(&full[i], STAGE_BYTES);
-            ptx::tma_load_2d(ring + i * STAGE_BYTES, &tmW, &full[i], nblk * (NB / 2), (ws0 + i) * 16);
-        }
     }
+    __syncwarp();
 
-    // bf16: nibble u -> 128+u (0x4300 | u).  f16: u alone is the subnormal u * 2^-24, exact in the MMA,
-    // so only the s4 bias of 8 remains as offset and the group sum is rescaled by 2^24.
+    // bf16: nibble u -> 128+u.  f16: u alone is the subnormal u * 2^-24 (exact in the MMA), so only the
+    // s4 bias of 8 remains as offset and the group sum is rescaled by 2^24.
     const uint32_t magic = F16 ? (p.sgn4 ? 0x00080008u : 0u) : (p.sgn4 ? 0x43084308u : 0x43004300u);
     const float off = (F16 ? 0.f : 128.f) + (p.sgn4 ? 8.f : 0.f);
     const float acc_scale = F16 ? 16777216.f : 1.f;
-    float acc[16][4], tot[16][4];
-#pragma unroll
-    for (int t = 0; t < 16; ++t)
-#pragma unroll
-        for (int i = 0; i < 4; ++i) acc[t][i] = tot[t][i] = 0.f;
-    float sp = 0.f; // running sum of this lane's src values (row g) in the current group
-
+    const bool sc_bf16 = a.wei_scale.dt == DT_BF16;
+    const bool zp4 = p.zp_mode == 1 && (a.wei_zp.dt == DT_U4 || a.wei_zp.dt == DT_S4);
+    const float zt = p.zp_mode == 2 ? (float)load_int(a.wei_zp.dt, a.wei_zp.ptr, 0) : 0.f;
     const char *src_row = (const char *)a.src + ((p.m_base + g) * a.src_sm) * 2;
     const bool row_ok = g < p.M;
+
+    const int64_t total = (int64_t)p.nblk * p.ksteps;
+    int64_t L = (int64_t)blockIdx.x * p.per;
+    const int64_t L1 = min(total, L + p.per);
+    // byte offsets inside a stage of this lane's 16-byte chunks in k-rows 2tig and 2tig+1 (128B swizzle)
+    const int lds0 = (2 * tig) * 128 + ((g ^ ((2 * tig) & 7)) << 4);
+    const int lds1 = (2 * tig + 1) * 128 + ((g ^ ((2 * tig + 1) & 7)) << 4);
+    uint32_t git = 0; // stages consumed so far by this warp (ring position and phase)
     bool ok = true;
 
-    for (int it = 0; it < nsteps; ++it) {
-        const int s = it % STAGES;
-        const int kstep = ws0 + it;
-        if (!ptx::mbar_wait(&full[s], (it / STAGES) & 1)) { ok = false; break; }
-        // rows 2tig, 2tig+1, 2tig+8, 2tig+9 of the stage; column chunk g, swizzled by (row & 7)
-        const uint8_t *st = ring + s * STAGE_BYTES;
-        uint4 R[4];
+    while (L < L1) {
+        const int nblk = (int)(L / p.ksteps), kb = (int)(L % p.ksteps);
+        const int ke = (int)min((int64_t)p.ksteps, kb + (L1 - L));
+        const int seg = ke - kb;
+        const int ws0 = kb + (int)((int64_t)seg * warp / WARPS), ws1 = kb + (int)((int64_t)seg * (warp + 1) / WARPS);
+        const int nsteps = ok ? ws1 - ws0 : 0; // after an expired wait the warp only takes part in the barriers
+        const int64_t n0 = (int64_t)nblk * NB + g * 32; // this thread's 32 columns
+        const bool cols_ok = n0 < a.N;
+
+        if (lane == 0) {
+            for (int i = 0; i < STAGES && i < nsteps; ++i) {
+                const int s = (git + i) % STAGES;
+                ptx::mbar_arrive_expect_tx(&full[s], STAGE_BYTES);
+                ptx::tma_load_2d(ring + s * STAGE_BYTES, &tmW, &full[s], nblk * (NB / 2), (ws0 + i) * 16);
+            }
+        }
+        float acc[16][4], tot[16][4];
 #pragma unroll
-        for (int r = 0; r < 4; ++r) {
-            const int row = 2 * tig + (r & 1) + (r >> 1) * 8;
-            R[r] = *reinterpret_cast<const uint4 *>(st + row * 128 + ((g ^ (row & 7)) << 4));
+        for (int t = 0; t < 16; ++t)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) acc[t][i] = tot[t][i] = 0.f;
+        float sp = 0.f; // running sum of this lane's src values (row g) in the current group
+        uint32_t scw[16]; // bf16 scale pairs (columns 2t, 2t+1) of the current group
+        uint4 zq = make_uint4(0, 0, 0, 0); // 4-bit zero-points of the current group
+        uint32_t nb0 = 0, nb1 = 0; // src operand of the next k-step
+        // this lane's src words of k-step ws0 (k = 16 ws0 + 2 tig, +1 and +8, +9); 8 words per k-step
+        const uint32_t *sq = reinterpret_cast<const uint32_t *>(src_row + ((int64_t)ws0 * 16 + 2 * tig) * 2);
+        if (row_ok && nsteps > 0) {
+            nb0 = __ldg(sq);
+            nb1 = __ldg(sq + 4);
         }
-        __syncwarp();
-        if (lane == 0 && it + STAGES < nsteps) { // stage consumed by every lane: refill it
-            ptx::mbar_arrive_expect_tx(&full[s], STAGE_BYTES);
-            ptx::tma_load_2d(ring + s * STAGE_BYTES, &tmW, &full[s], nblk * (NB / 2), (kstep + STAGES) * 16);
-        }
-        // src operand: row g, k = 16*kstep + {2tig, 2tig+1} and {2tig+8, 2tig+9}
-        uint32_t b0 = 0, b1 = 0;
-        if (row_ok) {
-            const char *sp_ = src_row + ((int64_t)kstep * 16 + 2 * tig) * 2;
-            b0 = __ldg(reinterpret_cast<const uint32_t *>(sp_));
-            b1 = __ldg(reinterpret_cast<const uint32_t *>(sp_ + 16));
+        // all loop-carried positions advance by increments: no division in the loop
+        int gi = ws0 / p.group_steps, gpos = ws0 - gi * p.group_steps; // group and k-step inside it
+        int s = git % STAGES;
+        uint32_t phase = (git / STAGES) & 1;
+        git += nsteps;
+
+        for (int it = 0; it < nsteps; ++it) {
+            const int kstep = ws0 + it;
+            // quantization parameters of a new group: requested now, used when the group ends
+            if ((it == 0 || gpos == 0) && cols_ok) {
+                if (sc_bf16) {
+                    const int64_t qb = ((a.wei_scale.mask & 1) ? (int64_t)gi * a.wei_scale.ld : 0) + n0;
+                    const uint4 *q = reinterpret_cast<const uint4 *>((const char *)a.wei_scale.ptr + qb * 2);
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const uint4 v = __ldg(q + j);
+                        scw[4 * j] = v.x; scw[4 * j + 1] = v.y; scw[4 * j + 2] = v.z; scw[4 * j + 3] = v.w;
+                    }
+                }
+                if (zp4)
+                    zq = __ldg(reinterpret_cast<const uint4 *>(
+                            (const char *)a.wei_zp.ptr + ((int64_t)gi * a.wei_zp.ld + n0) / 2));
+            }
+            if (!ptx::mbar_wait(&full[s], phase)) { ok = false; break; }
+            // rows 2tig, 2tig+1 (and 8 rows further down) of the stage; column chunk g, swizzled by (row & 7)
+            const uint8_t *st = ring + s * STAGE_BYTES;
+            uint4 R[4];
+            R[0] = *reinterpret_cast<const uint4 *>(st + lds0);
+            R[1] = *reinterpret_cast<const uint4 *>(st + lds1);
+            R[2] = *reinterpret_cast<const uint4 *>(st + lds0 + 1024);
+            R[3] = *reinterpret_cast<const uint4 *>(st + lds1 + 1024);
+            // src operand (row g; k = 16*kstep + {2tig, 2tig+1}, {2tig+8, 2tig+9}): loaded one step ahead
+            const uint32_t b0 = nb0, b1 = nb1;
+            sq += 8;
+            if (row_ok && it + 1 < nsteps) {
+                nb0 = __ldg(sq);
+                nb1 = __ldg(sq + 4);
+            }
             sp += pair_sum<F16>(b0) + pair_sum<F16>(b1);
+            const uint32_t *w0 = reinterpret_cast<const uint32_t *>(&R[0]), *w1 = reinterpret_cast<const uint32_t *>(&R[1]);
+            const uint32_t *w2 = reinterpret_cast<const uint32_t *>(&R[2]), *w3 = reinterpret_cast<const uint32_t *>(&R[3]);
+#pragma unroll
+            for (int t = 0; t < 16; ++t) {
+                // byte t of the four rows: low nibble = column 2t, high nibble = column 2t+1
+                const uint32_t sel = ((4 + (t & 3)) << 12) | ((4 + (t & 3)) << 8) | ((t & 3) << 4) | (t & 3);
+                const uint32_t x01 = prmt(w0[t >> 2], w1[t >> 2], sel);
+                const uint32_t x23 = prmt(w2[t >> 2], w3[t >> 2], sel);
+                uint32_t af[4];
+                af[0] = nib2(x01, magic); // column 2t,   k pair (2tig, 2tig+1)
+                af[1] = nib2(x01 >> 4, magic); // column 2t+1
+                af[2] = nib2(x23, magic); // column 2t,   k pair (2tig+8, 2tig+9)
+                af[3] = nib2(x23 >> 4, magic); // column 2t+1
+                if (F16) mma_f16(acc[t], af, b0, b1);
+                else mma_bf16(acc[t], af, b0, b1);
+            }
+            // the MMAs have consumed R, so every lane's reads of the stage are complete: refill it
+            __syncwarp();
+            if (lane == 0 && it + STAGES < nsteps) {
+                ptx::mbar_arrive_expect_tx(&full[s], STAGE_BYTES);
+                ptx::tma_load_2d(ring + s * STAGE_BYTES, &tmW, &full[s], nblk * (NB / 2), (kstep + STAGES) * 16);
+            }
+            if (++s == STAGES) { s = 0; phase ^= 1; }
+            // end of a quantization group (or of this warp's range): fold the group into the totals
+            const bool group_end = ++gpos == p.group_steps;
+            if (group_end || it == nsteps - 1) {
+                sp += __shfl_xor_sync(0xffffffffu, sp, 1);
+                sp += __shfl_xor_sync(0xffffffffu, sp, 2);
+                const float S0 = __shfl_sync(0xffffffffu, sp, (2 * tig) * 4);
+                const float S1 = __shfl_sync(0xffffffffu, sp, (2 * tig + 1) * 4);
+                sp = 0.f;
+                if (cols_ok) {
+                    const int64_t qbase = ((a.wei_scale.mask & 1) ? (int64_t)gi * a.wei_scale.ld : 0) + n0;
+#pragma unroll
+                    for (int t = 0; t < 16; ++t) {
+                        float sc_lo, sc_hi;
+                        if (sc_bf16) {
+                            sc_lo = __uint_as_float(scw[t] << 16);
+                            sc_hi = __uint_as_float(scw[t] & 0xffff0000u);
+                        } else {
+                            sc_lo = load_float(a.wei_scale.dt, a.wei_scale.ptr, qbase + 2 * t);
+                            sc_hi = load_float(a.wei_scale.dt, a.wei_scale.ptr, qbase + 2 * t + 1);
+                        }
+                        float z_lo = zt, z_hi = zt;
+                        if (zp4) {
+                            const uint32_t byte = (reinterpret_cast<const uint32_t *>(&zq)[t >> 2] >> ((t & 3) * 8)) & 0xffu;
+                            int lo = byte & 0xf, hi = byte >> 4;
+                            if (a.wei_zp.dt == DT_S4) { lo = (lo ^ 8) - 8; hi = (hi ^ 8) - 8; }
+                            z_lo = (float)lo; z_hi = (float)hi;
+                        } else if (p.zp_mode == 1) {
+                            const int64_t zb = (int64_t)gi * a.wei_zp.ld + n0 + 2 * t;
+                            z_lo = (float)load_int(a.wei_zp.dt, a.wei_zp.ptr, zb);
+                            z_hi = (float)load_int(a.wei_zp.dt, a.wei_zp.ptr, zb + 1);
+                        }
+                        const float oz_lo = off + z_lo, oz_hi = off + z_hi;
+                        tot[t][0] = fmaf(sc_lo, acc[t][0] * acc_scale - oz_lo * S0, tot[t][0]);
+                        tot[t][1] = fmaf(sc_lo, acc[t][1] * acc_scale - oz_lo * S1, tot[t][1]);
+                        tot[t][2] = fmaf(sc_hi, acc[t][2] * acc_scale - oz_hi * S0, tot[t][2]);
+                        tot[t][3] = fmaf(sc_hi, acc[t][3] * acc_scale - oz_hi * S1, tot[t][3]);
+                        acc[t][0] = acc[t][1] = acc[t][2] = acc[t][3] = 0.f;
+                    }
+                }
+                if (group_end) { gpos = 0; ++gi; }
+            }
         }
-        const uint32_t *w0 = reinterpret_cast<const uint32_t *>(&R[0]), *w1 = reinterpret_cast<const uint32_t *>(&R[1]);
-        const uint32_t *w2 = reinterpret_cast<const uint32_t *>(&R[2]), *w3 = reinterpret_cast<const uint32_t *>(&R[3]);
+
+        // ---- the warps' totals meet in shared memory: red[warp][m][column]
 #pragma unroll
         for (int t = 0; t < 16; ++t) {
-            // byte t of the four rows: low nibble = column 2t, high nibble = column 2t+1
-            const uint32_t sel = ((4 + (t & 3)) << 12) | ((4 + (t & 3)) << 8) | ((t & 3) << 4) | (t & 3);
-            const uint32_t x01 = prmt(w0[t >> 2], w1[t >> 2], sel);
-            const uint32_t x23 = prmt(w2[t >> 2], w3[t >> 2], sel);
-            uint32_t af[4];
-            af[0] = nib2(x01, magic); // column 2t,   k pair (2tig, 2tig+1)
-            af[1] = nib2(x01 >> 4, magic); // column 2t+1
-            af[2] = nib2(x23, magic); // column 2t,   k pair (2tig+8, 2tig+9)
-            af[3] = nib2(x23 >> 4, magic); // column 2t+1
-            if (F16) mma_f16(acc[t], af, b0, b1);
-            else mma_bf16(acc[t], af, b0, b1);
+            const int c = red_pos(g * 32 + 2 * t); // columns 2t and 2t+1 are adjacent: no pad between them
+            *reinterpret_cast<float2 *>(&red[(warp * MB + 2 * tig) * RED_PITCH + c]) = make_float2(tot[t][0], tot[t][2]);
+            *reinterpret_cast<float2 *>(&red[(warp * MB + 2 * tig + 1) * RED_PITCH + c]) = make_float2(tot[t][1], tot[t][3]);
         }
-        // end of a quantization group (or of this warp's range): fold the group into the totals
-        const bool group_end = ((kstep + 1) % p.group_steps) == 0;
-        if (group_end || it == nsteps - 1) {
-            const int gi = kstep / p.group_steps;
-            sp += __shfl_xor_sync(0xffffffffu, sp, 1);
-            sp += __shfl_xor_sync(0xffffffffu, sp, 2);
-            const float S0 = __shfl_sync(0xffffffffu, sp, (2 * tig) * 4);
-            const float S1 = __shfl_sync(0xffffffffu, sp, (2 * tig + 1) * 4);
-            sp = 0.f;
-            if (cols_ok) {
-                const int64_t qbase = (a.wei_scale.mask & 1) ? (int64_t)gi * a.wei_scale.ld : 0;
-                uint4 zq = make_uint4(0, 0, 0, 0);
-                const bool zp4 = p.zp_mode == 1 && (a.wei_zp.dt == DT_U4 || a.wei_zp.dt == DT_S4);
-                if (zp4) zq = __ldg(reinterpret_cast<const uint4 *>((const char *)a.wei_zp.ptr + ((int64_t)gi * a.wei_zp.ld + n0) / 2));
-                float zt = 0.f;
-                if (p.zp_mode == 2) zt = (float)load_int(a.wei_zp.dt, a.wei_zp.ptr, 0);
+        __syncthreads();
+        const int i = threadIdx.x; // column of the block
+        const int64_t n = (int64_t)nblk * NB + i;
+        float v[MB];
 #pragma unroll
-                for (int t = 0; t < 16; ++t) {
-                    float sc_lo, sc_hi;
-                    if (a.wei_scale.dt == DT_BF16) {
-                        const uint32_t w = __ldg(reinterpret_cast<const uint32_t *>(
-                                (const char *)a.wei_scale.ptr + (qbase + n0 + 2 * t) * 2));
-                        sc_lo = __uint_as_float(w << 16);
-                        sc_hi = __uint_as_float(w & 0xffff0000u);
-                    } else {
-                        sc_lo = load_float(a.wei_scale.dt, a.wei_scale.ptr, qbase + n0 + 2 * t);
-                        sc_hi = load_float(a.wei_scale.dt, a.wei_scale.ptr, qbase + n0 + 2 * t + 1);
-                    }
-                    float z_lo = zt, z_hi = zt;
-                    if (zp4) {
-                        const uint32_t byte = (reinterpret_cast<const uint32_t *>(&zq)[t >> 2] >> ((t & 3) * 8)) & 0xffu;
-                        int lo = byte & 0xf, hi = byte >> 4;
-                        if (a.wei_zp.dt == DT_S4) { lo = (lo ^ 8) - 8; hi = (hi ^ 8) - 8; }
-                        z_lo = (float)lo; z_hi = (float)hi;
-                    } else if (p.zp_mode == 1) {
-                        z_lo = (float)load_int(a.wei_zp.dt, a.wei_zp.ptr, (int64_t)gi * a.wei_zp.ld + n0 + 2 * t);
-                        z_hi = (float)load_int(a.wei_zp.dt, a.wei_zp.ptr, (int64_t)gi * a.wei_zp.ld + n0 + 2 * t + 1);
-                    }
-                    const float oz_lo = off + z_lo, oz_hi = off + z_hi;
-                    tot[t][0] = fmaf(sc_lo, acc[t][0] * acc_scale - oz_lo * S0, tot[t][0]);
-                    tot[t][1] = fmaf(sc_lo, acc[t][1] * acc_scale - oz_lo * S1, tot[t][1]);
-                    tot[t][2] = fmaf(sc_hi, acc[t][2] * acc_scale - oz_hi * S0, tot[t][2]);
-                    tot[t][3] = fmaf(sc_hi, acc[t][3] * acc_scale - oz_hi * S1, tot[t][3]);
-                    acc[t][0] = acc[t][1] = acc[t][2] = acc[t][3] = 0.f;
+        for (int m = 0; m < MB; ++m) {
+            float sacc = 0.f;
+#pragma unroll
+            for (int w = 0; w < WARPS; ++w) sacc += red[(w * MB + m) * RED_PITCH + red_pos(i)];
+            v[m] = sacc;
+        }
+        // CTAs sharing this column block, in k order
+        const int first = (int)(((int64_t)nblk * p.ksteps) / p.per);
+        const int last = (int)((((int64_t)nblk + 1) * p.ksteps - 1) / p.per);
+        bool finalize = true;
+        if (last > first) {
+            const int count = last - first + 1, slot = (int)blockIdx.x - first;
+            float *base = p.partial + ((int64_t)nblk * p.max_slots) * (MB * NB);
+#pragma unroll
+            for (int m = 0; m < MB; ++m) base[(slot * MB + m) * NB + i] = v[m];
+            __threadfence();
+            __syncthreads();
+            if (threadIdx.x == 0) *flag = atomicAdd(&p.counters[nblk], 1) == count - 1;
+            __syncthreads();
+            finalize = *flag != 0;
+            if (finalize) {
+                __threadfence();
+#pragma unroll
+                for (int m = 0; m < MB; ++m) v[m] = 0.f;
+                for (int sl = 0; sl < count; ++sl)
+#pragma unroll
+                    for (int m = 0; m < MB; ++m) v[m] += __ldcg(base + (sl * MB + m) * NB + i);
+                if (threadIdx.x == 0) p.counters[nblk] = 0; // ready for the next launch
+            }
+        }
+        if (finalize && n < a.N) {
+            float ss = 1.f;
+            if (a.src_scale.ptr) ss = load_float(a.src_scale.dt, a.src_scale.ptr, 0);
+            else if (a.src_scale.on_host) ss = a.src_scale.host_value;
+#pragma unroll
+            for (int m = 0; m < MB; ++m) {
+                if (m < p.M) {
+                    const int64_t mm = p.m_base + m;
+                    float d = v[m] * ss;
+                    if (a.bias) d = __fadd_rn(d, load_float(a.bias_dt, a.bias, mm * a.bias_sm + n * a.bias_sn));
+                    finish_store(a, d, mm, n, false);
                 }
             }
         }
+        __syncthreads(); // red and flag are reused by the next segment
+        L += seg;
     }
     if (!ok) atomicExch(a.status, 5);
-
-    // ---- reduce the warps' totals through shared memory: red[warp][m][256]
-    __syncthreads();
-    float *red = reinterpret_cast<float *>(smem);
-#pragma unroll
-    for (int t = 0; t < 16; ++t) {
-        const int nl = g * 32 + 2 * t;
-        red[(warp * MB + 2 * tig) * NB + nl] = tot[t][0];
-        red[(warp * MB + 2 * tig + 1) * NB + nl] = tot[t][1];
-        red[(warp * MB + 2 * tig) * NB + nl + 1] = tot[t][2];
-        red[(warp * MB + 2 * tig + 1) * NB + nl + 1] = tot[t][3];
-    }
-    __syncthreads();
-    const int i = threadIdx.x; // column of the block
-    const int64_t n = (int64_t)nblk * NB + i;
-    float v[MB];
-#pragma unroll
-    for (int m = 0; m < MB; ++m) {
-        float s = 0.f;
-#pragma unroll
-        for (int w = 0; w < WARPS; ++w) s += red[(w * MB + m) * NB + i];
-        v[m] = s;
-    }
-    if (p.splits > 1) {
-        float *mine = p.partial + ((int64_t)(nblk * p.splits + split) * MB) * NB;
-#pragma unroll
-        for (int m = 0; m < MB; ++m) mine[m * NB + i] = v[m];
-        __threadfence();
-        __syncthreads();
-        if (threadIdx.x == 0) *flag = atomicAdd(&p.counters[nblk], 1) == p.splits - 1;
-        __syncthreads();
-        if (!*flag) return;
-        __threadfence();
-        // last CTA of the column block: add the partial sums in split order
-#pragma unroll
-        for (int m = 0; m < MB; ++m) v[m] = 0.f;
-        for (int sidx = 0; sidx < p.splits; ++sidx) {
-            const float *q = p.partial + ((int64_t)(nblk * p.splits + sidx) * MB) * NB;
-#pragma unroll
-            for (int m = 0; m < MB; ++m) v[m] += __ldcg(q + m * NB + i);
-        }
-        if (threadIdx.x == 0) p.counters[nblk] = 0; // ready for the next launch
-    }
-    if (n >= a.N) return;
-    float ss = 1.f;
-    if (a.src_scale.ptr) ss = load_float(a.src_scale.dt, a.src_scale.ptr, 0);
-    else if (a.src_scale.on_host) ss = a.src_scale.host_value;
-#pragma unroll
-    for (int m = 0; m < MB; ++m) {
-        if (m < p.M) {
-            const int64_t mm = p.m_base + m;
-            float d = v[m] * ss;
-            if (a.bias) d = __fadd_rn(d, load_float(a.bias_dt, a.bias, mm * a.bias_sm + n * a.bias_sn));
-            finish_store(a, d, mm, n, false);
-        }
-    }
 }
 
 typedef CUresult (*encode_tiled_fn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
@@ -303,36 +352,43 @@ encode_tiled_fn woq_get_encode() {
     return fn;
 }
 
-// K splits: fill whole waves of one CTA per SM, keep >= 8 k-steps per warp
-int woq_splits(int64_t N, int64_t K, int sm_count) {
-    const int64_t nblk = (N + NB - 1) / NB, ksteps = K / 16;
-    int best = 1;
-    double best_eff = 0;
-    for (int s = 1; s <= 16; ++s) {
-        if (s > 1 && ksteps / s < 8 * WARPS) break;
-        const int64_t ctas = nblk * s, waves = (ctas + sm_count - 1) / sm_count;
-        const double eff = (double)ctas / (double)(waves * sm_count);
-        if (eff > best_eff + 0.02) { best_eff = eff; best = s; }
-    }
-    return best;
+// The cut of the (column block, k-step) space: `per` pairs per CTA (a multiple
+// of 8 so the warps get equal shares, at least 32 so a CTA is worth its
+// launch), `grid` CTAs, at most `max_slots` CTAs on one column block.
+struct WoqPlan {
+    int nblk, ksteps, per, grid, max_slots;
+};
+WoqPlan woq_plan(int64_t N, int64_t K, int sm_count) {
+    WoqPlan pl;
+    pl.nblk = (int)((N + NB - 1) / NB);
+    pl.ksteps = (int)(K / 16);
+    const int64_t total = (int64_t)pl.nblk * pl.ksteps;
+    if (sm_count < 1) sm_count = 148;
+    int64_t per = (total + sm_count - 1) / sm_count;
+    per = (per + 7) / 8 * 8;
+    if (per < 32) per = 32;
+    pl.per = (int)per;
+    pl.grid = (int)((total + per - 1) / per);
+    pl.max_slots = (int)((pl.ksteps + per - 1) / per) + 1;
+    return pl;
 }
 
 } // namespace
 
 size_t woq_skinny_scratch_bytes(int64_t N, int64_t K, int sm_count) {
-    const int64_t nblk = (N + NB - 1) / NB;
-    const int splits = woq_splits(N, K, sm_count);
-    return (size_t)(nblk * splits * MB * NB) * sizeof(float) + (size_t)nblk * sizeof(int) + 256;
+    const WoqPlan pl = woq_plan(N, K, sm_count);
+    return ((size_t)pl.nblk * sizeof(int) + 255) / 256 * 256
+            + (size_t)pl.nblk * pl.max_slots * MB * NB * sizeof(float);
 }
 
 // `scratch`: woq_skinny_scratch_bytes(N, K, sm_count) bytes whose counters
-// (the first nblk ints) are zero before the first launch; the kernel leaves
-// them zero.
+// (the first ceil(N/256) ints) are zero before the first launch; the kernel
+// leaves them zero.
 int launch_woq_skinny(const MatmulArgs &a, void *scratch, int sm_count, cudaStream_t st) {
     if (a.M == 0 || a.N == 0) return 0;
     encode_tiled_fn enc = woq_get_encode();
     if (!enc || !scratch) return 5;
-    const int64_t nblk = (a.N + NB - 1) / NB;
+    const WoqPlan pl = woq_plan(a.N, a.K, sm_count);
     CUtensorMap tm;
     cuuint64_t dims[2] = {(cuuint64_t)(a.N / 2), (cuuint64_t)a.K};
     cuuint64_t strides[1] = {(cuuint64_t)(a.wei_sk / 2)};
@@ -344,16 +400,18 @@ int launch_woq_skinny(const MatmulArgs &a, void *scratch, int sm_count, cudaStre
             != CUDA_SUCCESS)
         return 5;
     WoqParams p {};
-    p.ksteps = (int)(a.K / 16);
+    p.ksteps = pl.ksteps;
     const int64_t group = (a.wei_scale.ptr && (a.wei_scale.mask & 1)) ? a.wei_scale.g0
             : (a.wei_zp.ptr && (a.wei_zp.mask & 1))                    ? a.wei_zp.g0
                                                                        : a.K;
     p.group_steps = (int)(group / 16);
-    p.splits = woq_splits(a.N, a.K, sm_count);
+    p.nblk = pl.nblk;
+    p.per = pl.per;
+    p.max_slots = pl.max_slots;
     p.sgn4 = a.wei_dt == DT_S4;
     p.zp_mode = !a.wei_zp.ptr ? 0 : (a.wei_zp.mask ? 1 : 2);
     p.counters = (int *)scratch;
-    p.partial = (float *)((char *)scratch + ((nblk * sizeof(int) + 255) / 256) * 256);
+    p.partial = (float *)((char *)scratch + ((size_t)pl.nblk * sizeof(int) + 255) / 256 * 256);
     const bool f16 = a.src_dt == DT_F16;
     auto kern = f16 ? woq_skinny_kernel<true> : woq_skinny_kernel<false>;
     static bool configured[2] = {false, false};
@@ -361,11 +419,10 @@ int launch_woq_skinny(const MatmulArgs &a, void *scratch, int sm_count, cudaStre
         if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess) return 5;
         configured[f16] = true;
     }
-    dim3 grid((unsigned)nblk, (unsigned)p.splits);
     for (int64_t m0 = 0; m0 < a.M; m0 += MB) { // more than 8 rows: one pass over the weights per 8 rows
         p.m_base = m0;
         p.M = (int)((a.M - m0) < MB ? (a.M - m0) : MB);
-        kern<<<grid, WARPS * 32, SMEM_BYTES, st>>>(tm, a, p);
+        kern<<<pl.grid, WARPS * 32, SMEM_BYTES, st>>>(tm, a, p);
         count_launch();
     }
     return cudaGetLastError() == cudaSuccess ? 0 : 5;

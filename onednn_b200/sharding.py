@@ -102,8 +102,9 @@ def gather_columns(local, N, world, dist=None, group=None):
     widths = [column_range(N, r, world)[1] - column_range(N, r, world)[0] for r in range(world)]
     wmax = max(widths)
     send = local if local.shape[1] == wmax else torch.nn.functional.pad(local, (0, wmax - local.shape[1]))
-    out = torch.empty((world, M, wmax), dtype=local.dtype, device=local.device)
-    dist.all_gather_into_tensor(out, send.contiguous(), group=group)
+    flat = torch.empty((world * M, wmax), dtype=local.dtype, device=local.device)
+    dist.all_gather_into_tensor(flat, send.contiguous(), group=group)
+    out = flat.view(world, M, wmax)
     return torch.cat([out[r, :, :widths[r]] for r in range(world)], dim=1)
 
 
@@ -116,6 +117,7 @@ def gather_rows(local, rows_per_rank, dist=None, group=None):
     dist = dist or torch.distributed
     mmax = max(rows_per_rank)
     send = local if local.shape[0] == mmax else torch.nn.functional.pad(local, (0, 0, 0, mmax - local.shape[0]))
-    out = torch.empty((world, mmax, local.shape[1]), dtype=local.dtype, device=local.device)
-    dist.all_gather_into_tensor(out, send.contiguous(), group=group)
+    flat = torch.empty((world * mmax, local.shape[1]), dtype=local.dtype, device=local.device)
+    dist.all_gather_into_tensor(flat, send.contiguous(), group=group)
+    out = flat.view(world, mmax, local.shape[1])
     return torch.cat([out[r, :rows_per_rank[r]] for r in range(world)], dim=0)

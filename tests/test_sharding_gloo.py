@@ -1,0 +1,99 @@
+"""N>1 host logic on CPU: two `gloo` ranks shard a problem the way the GPU
+ranks do (columns for dense problems, experts for grouped ones), compute
+their shard with the CPU oracle, all-gather, and the assembled result must
+equal the unsharded oracle result bit for bit."""
+import os
+import socket
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+ROOT = os.path.dirname(HERE)
+
+WORKER = r"""
+import os, sys
+import numpy as np
+import torch
+import torch.distributed as dist
+sys.path.insert(0, sys.argv[1])
+from onednn_b200 import workloads as W, sharding as S
+from oracle import oracle as O
+
+rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+dist.init_process_group("gloo", rank=rank, world_size=world)
+
+def as_f32(p, out):
+    return torch.from_numpy(np.ascontiguousarray(W.to_f32(out, p.dst_dt).reshape(p.M, p.N)))
+
+problems = [W.int8_zp(24, 64, 96, per_n_scales=True), W.int8_postops(16, 64, 80), W.fp8_prefill(8, 64, 48),
+            W.int4_decode(3, 128, 64), W.moe_grouped(40, 64, 32, 5, sizes=[7, 0, 13, 20, 0])]
+for p in problems:
+    local = S.shard(p, rank, world)
+    got_local = as_f32(local, O.run_port(local))
+    if p.offsets is None:
+        full = S.gather_columns(got_local, p.N, world)
+    else:
+        rows = [S.shard(p, r, world).M for r in range(world)]
+        full = S.gather_rows(got_local, rows)
+    want = as_f32(p, O.run_port(p))
+    assert full.shape == want.shape, (p.name, full.shape, want.shape)
+    assert torch.equal(full, want), "%s: sharded result differs on rank %d" % (p.name, rank)
+dist.barrier()
+dist.destroy_process_group()
+print("rank %d ok" % rank)
+"""
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    return port
+
+
+def test_two_gloo_ranks_assemble_the_unsharded_result(tmp_path):
+    script = tmp_path / "worker.py"
+    script.write_text(WORKER)
+    port = _free_port()
+    procs = []
+    for rank in range(2):
+        env = dict(os.environ, RANK=str(rank), WORLD_SIZE="2", MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+        procs.append(subprocess.Popen([sys.executable, str(script), ROOT], env=env, stdout=subprocess.PIPE,
+                                      stderr=subprocess.STDOUT, text=True))
+    outs = []
+    for pr in procs:
+        try:
+            out, _ = pr.communicate(timeout=240)
+        except subprocess.TimeoutExpired:
+            pr.kill()
+            out, _ = pr.communicate()
+        outs.append(out)
+    for rank, (pr, out) in enumerate(zip(procs, outs)):
+        assert pr.returncode == 0, "rank %d failed:\n%s" % (rank, out[-3000:])
+        assert "rank %d ok" % rank in out
+
+
+@pytest.mark.parametrize("world", [2, 3, 4, 8])
+def test_column_ranges_partition_n(world):
+    from onednn_b200.sharding import column_range
+    for N in (16, 48, 4096, 28672, 16 * 13):
+        edges = [column_range(N, r, world) for r in range(world)]
+        assert edges[0][0] == 0 and edges[-1][1] == N
+        for (lo, hi), (lo2, _) in zip(edges, edges[1:]):
+            assert hi == lo2 and lo % 16 == 0 and hi >= lo
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_expert_shards_cover_all_rows(world):
+    from onednn_b200 import workloads as W
+    from onednn_b200.sharding import shard
+    p = W.moe_grouped(64, 32, 16, 8)
+    shards = [shard(p, r, world) for r in range(world)]
+    assert sum(s.M for s in shards) == p.M
+    assert sum(s.groups for s in shards) == p.groups
+    src = np.concatenate([s.src.data.reshape(s.M, s.K) for s in shards], axis=0)
+    assert np.array_equal(src, p.src.data.reshape(p.M, p.K))
