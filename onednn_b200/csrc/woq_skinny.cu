@@ -29,6 +29,8 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
+#include <cstring>
+
 #include "device_math.cuh"
 #include "launch.h"
 #include "sm100_ptx.cuh"
@@ -59,6 +61,10 @@ struct WoqParams {
     int zp_mode; // 0 none, 1 per (group, n), 2 per tensor
     float *partial; // [nblk][max_slots][8][256]
     int *counters; // [nblk]
+    // zero-point correction through the tensor cores (ZPMMA kernels)
+    uint32_t magic_z; // turns a zero-point nibble pair into bf16 (128 [+ 8] + z)
+    uint32_t az_const; // bf16 pair of the offset when there are no per-group zero-points
+    uint32_t az_diff; // bf16 pair of (weight offset - zero-point offset): 0, 8 or -8
 };
 
 __device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
@@ -92,12 +98,26 @@ __device__ __forceinline__ float pair_sum(uint32_t v) {
     }
     return __uint_as_float(v << 16) + __uint_as_float(v & 0xffff0000u);
 }
+// 16-byte read-only load that stays where it is written (issued groups ahead of its use; a plain
+// load may be moved down to the use and then stalls the warp there)
+__device__ __forceinline__ uint4 ldg_v4_here(const void *ptr) {
+    uint4 v;
+    asm volatile("ld.global.nc.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(ptr));
+    return v;
+}
+__device__ __forceinline__ uint32_t ldg_u32_here(const void *ptr) {
+    uint32_t v;
+    asm volatile("ld.global.nc.u32 %0, [%1];" : "=r"(v) : "l"(ptr));
+    return v;
+}
 // position of column c in a row of the reduction tile: two pad words per 32
 // columns keep the float2 stores of a half-warp (4 rows x 4 column groups) on
 // 16 distinct bank pairs and 8-byte aligned
 __device__ __forceinline__ int red_pos(int c) { return c + 2 * (c >> 5); }
 
-template <bool F16>
+// ZPMMA (bf16 src; no, per-tensor-free or 4-bit per-group zero-points): the zero-point correction
+// runs on the tensor cores; otherwise it is applied with FMAs when a group ends.
+template <bool F16, bool ZPMMA>
 __global__ void __launch_bounds__(WARPS * 32, 1)
 woq_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ MatmulArgs a,
         const __grid_constant__ WoqParams p) {
@@ -161,13 +181,15 @@ woq_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
             for (int i = 0; i < 4; ++i) acc[t][i] = tot[t][i] = 0.f;
         float sp = 0.f; // running sum of this lane's src values (row g) in the current group
         uint32_t scw[16]; // bf16 scale pairs (columns 2t, 2t+1) of the current group
+#pragma unroll
+        for (int t = 0; t < 16; ++t) scw[t] = 0u; // lanes whose columns lie beyond N keep zeros
         uint4 zq = make_uint4(0, 0, 0, 0); // 4-bit zero-points of the current group
         uint32_t nb0 = 0, nb1 = 0; // src operand of the next k-step
         // this lane's src words of k-step ws0 (k = 16 ws0 + 2 tig, +1 and +8, +9); 8 words per k-step
         const uint32_t *sq = reinterpret_cast<const uint32_t *>(src_row + ((int64_t)ws0 * 16 + 2 * tig) * 2);
         if (row_ok && nsteps > 0) {
-            nb0 = __ldg(sq);
-            nb1 = __ldg(sq + 4);
+            nb0 = ldg_u32_here(sq);
+            nb1 = ldg_u32_here(sq + 4);
         }
         // all loop-carried positions advance by increments: no division in the loop
         int gi = ws0 / p.group_steps, gpos = ws0 - gi * p.group_steps; // group and k-step inside it
@@ -181,18 +203,17 @@ woq_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
             if ((it == 0 || gpos == 0) && cols_ok) {
                 if (sc_bf16) {
                     const int64_t qb = ((a.wei_scale.mask & 1) ? (int64_t)gi * a.wei_scale.ld : 0) + n0;
-                    const uint4 *q = reinterpret_cast<const uint4 *>((const char *)a.wei_scale.ptr + qb * 2);
+                    const char *q = (const char *)a.wei_scale.ptr + qb * 2;
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
-                        const uint4 v = __ldg(q + j);
+                        const uint4 v = ldg_v4_here(q + 16 * j);
                         scw[4 * j] = v.x; scw[4 * j + 1] = v.y; scw[4 * j + 2] = v.z; scw[4 * j + 3] = v.w;
                     }
                 }
-                if (zp4)
-                    zq = __ldg(reinterpret_cast<const uint4 *>(
-                            (const char *)a.wei_zp.ptr + ((int64_t)gi * a.wei_zp.ld + n0) / 2));
+                if (zp4) zq = ldg_v4_here((const char *)a.wei_zp.ptr + ((int64_t)gi * a.wei_zp.ld + n0) / 2);
             }
-            if (!ptx::mbar_wait(&full[s], phase)) { ok = false; break; }
+            // every lane waits (it reads the stage), and the warp leaves the loop as a whole
+            if (!__all_sync(0xffffffffu, ptx::mbar_wait(&full[s], phase))) { ok = false; break; }
             // rows 2tig, 2tig+1 (and 8 rows further down) of the stage; column chunk g, swizzled by (row & 7)
             const uint8_t *st = ring + s * STAGE_BYTES;
             uint4 R[4];
@@ -204,8 +225,8 @@ woq_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
             const uint32_t b0 = nb0, b1 = nb1;
             sq += 8;
             if (row_ok && it + 1 < nsteps) {
-                nb0 = __ldg(sq);
-                nb1 = __ldg(sq + 4);
+                nb0 = ldg_u32_here(sq);
+                nb1 = ldg_u32_here(sq + 4);
             }
             sp += pair_sum<F16>(b0) + pair_sum<F16>(b1);
             const uint32_t *w0 = reinterpret_cast<const uint32_t *>(&R[0]), *w1 = reinterpret_cast<const uint32_t *>(&R[1]);
@@ -233,7 +254,55 @@ woq_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
             if (++s == STAGES) { s = 0; phase ^= 1; }
             // end of a quantization group (or of this warp's range): fold the group into the totals
             const bool group_end = ++gpos == p.group_steps;
-            if (group_end || it == nsteps - 1) {
+            if (ZPMMA && (group_end || it == nsteps - 1)) {
+                // The correction -(offset + zp) * S leaves through one more MMA per 16 columns: its first
+                // k slots pair (128 [+8] + zp), rebuilt from the zero-point nibble like a weight, with -S
+                // cut into three bf16 pieces (8 + 8 + 8 significant bits: exact), and slots 8..11 pair the
+                // remaining constant offset with the same pieces.
+                sp += __shfl_xor_sync(0xffffffffu, sp, 1);
+                sp += __shfl_xor_sync(0xffffffffu, sp, 2); // every lane: S of src row g
+                const float ns = -sp;
+                sp = 0.f;
+                const uint32_t ph = __float_as_uint(ns) & 0xffff0000u;
+                const float r1 = ns - __uint_as_float(ph);
+                const uint32_t pm = __float_as_uint(r1) & 0xffff0000u;
+                const uint32_t pl = __float_as_uint(r1 - __uint_as_float(pm));
+                const uint32_t cb0 = tig == 0 ? ((ph >> 16) | pm) : (tig == 1 ? (pl >> 16) : 0u);
+                const uint32_t cb1 = p.az_diff ? cb0 : 0u;
+                { // every lane takes part in the MMAs, also those whose columns lie beyond N
+#pragma unroll
+                    for (int t = 0; t < 16; ++t) {
+                        uint32_t za[4];
+                        if (p.zp_mode == 1) {
+                            // byte t of the lane's 16 zero-point bytes -> [b, 0, b, 0]
+                            const uint32_t sel = (4u << 12) | ((t & 3) << 8) | (4u << 4) | (t & 3);
+                            const uint32_t x = prmt(reinterpret_cast<const uint32_t *>(&zq)[t >> 2], 0u, sel);
+                            za[0] = nib2(x, p.magic_z);
+                            za[1] = nib2(x >> 4, p.magic_z);
+                        } else {
+                            za[0] = za[1] = p.az_const;
+                        }
+                        za[2] = za[3] = p.az_diff;
+                        mma_bf16(acc[t], za, cb0, cb1);
+                        float sc_lo, sc_hi;
+                        if (sc_bf16) {
+                            sc_lo = __uint_as_float(scw[t] << 16);
+                            sc_hi = __uint_as_float(scw[t] & 0xffff0000u);
+                        } else {
+                            const int64_t qbase = ((a.wei_scale.mask & 1) ? (int64_t)gi * a.wei_scale.ld : 0) + n0;
+                            sc_lo = cols_ok ? load_float(a.wei_scale.dt, a.wei_scale.ptr, qbase + 2 * t) : 0.f;
+                            sc_hi = cols_ok ? load_float(a.wei_scale.dt, a.wei_scale.ptr, qbase + 2 * t + 1) : 0.f;
+                        }
+                        tot[t][0] = fmaf(sc_lo, acc[t][0], tot[t][0]);
+                        tot[t][1] = fmaf(sc_lo, acc[t][1], tot[t][1]);
+                        tot[t][2] = fmaf(sc_hi, acc[t][2], tot[t][2]);
+                        tot[t][3] = fmaf(sc_hi, acc[t][3], tot[t][3]);
+                        acc[t][0] = acc[t][1] = acc[t][2] = acc[t][3] = 0.f;
+                    }
+                }
+                if (group_end) { gpos = 0; ++gi; }
+            }
+            if (!ZPMMA && (group_end || it == nsteps - 1)) {
                 sp += __shfl_xor_sync(0xffffffffu, sp, 1);
                 sp += __shfl_xor_sync(0xffffffffu, sp, 2);
                 const float S0 = __shfl_sync(0xffffffffu, sp, (2 * tig) * 4);
@@ -413,11 +482,29 @@ int launch_woq_skinny(const MatmulArgs &a, void *scratch, int sm_count, cudaStre
     p.counters = (int *)scratch;
     p.partial = (float *)((char *)scratch + ((size_t)pl.nblk * sizeof(int) + 255) / 256 * 256);
     const bool f16 = a.src_dt == DT_F16;
-    auto kern = f16 ? woq_skinny_kernel<true> : woq_skinny_kernel<false>;
-    static bool configured[2] = {false, false};
-    if (!configured[f16]) {
+    // tensor-core zero-point correction: bf16 src and either no zero-points or 4-bit ones per group
+    const bool zp4 = p.zp_mode == 1 && (a.wei_zp.dt == DT_U4 || a.wei_zp.dt == DT_S4);
+    const bool zpmma = !f16 && (p.zp_mode == 0 || zp4);
+    if (zpmma) {
+        const int off_w = p.sgn4 ? 136 : 128; // a weight nibble becomes off_w + w
+        const int off_z = (zp4 && a.wei_zp.dt == DT_S4) ? 136 : 128; // a zero-point nibble becomes off_z + zp
+        auto bf16_pair = [](int v) { // small integers are exact in bf16
+            const float f = (float)v;
+            uint32_t u;
+            memcpy(&u, &f, 4);
+            return (u >> 16) | (u & 0xffff0000u);
+        };
+        p.magic_z = off_z == 136 ? 0x43084308u : 0x43004300u;
+        p.az_const = bf16_pair(off_w);
+        p.az_diff = zp4 ? (off_w == off_z ? 0u : bf16_pair(off_w - off_z)) : 0u;
+    }
+    const int variant = f16 ? 2 : (zpmma ? 1 : 0);
+    auto kern = f16 ? woq_skinny_kernel<true, false>
+                    : (zpmma ? woq_skinny_kernel<false, true> : woq_skinny_kernel<false, false>);
+    static bool configured[3] = {false, false, false};
+    if (!configured[variant]) {
         if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess) return 5;
-        configured[f16] = true;
+        configured[variant] = true;
     }
     for (int64_t m0 = 0; m0 < a.M; m0 += MB) { // more than 8 rows: one pass over the weights per 8 rows
         p.m_base = m0;
