@@ -18,13 +18,15 @@
 //     results differ from it only by f32 summation order).
 // Work decomposition ("stream-K"): the (column block, k-step) space is cut
 // into one contiguous, equally long range per CTA, one CTA per SM, so every
-// SM streams the same number of bytes; a CTA touches at most two column
-// blocks.  Inside a range the 8 warps take consecutive k sub-ranges and each
-// warp feeds itself through its own ring of TMA stages (16 k-rows x 128 bytes
-// = 256 columns, 128B swizzle: the 16-byte reads of a quarter-warp hit 8
-// distinct bank groups).  Warp totals meet in shared memory; where several
-// CTAs share a column block their partial sums go to a global scratch and the
-// last arriver adds them in CTA order (deterministic) and runs the epilogue.
+// SM streams the same number of bytes.  A column block is 256 columns; inside
+// a range the 16 warps form 8 pairs that take consecutive k sub-ranges, the
+// two warps of a pair side by side on 128 columns each.  Every warp feeds
+// itself through its own ring of TMA stages (32 k-rows x 64 bytes, 64B
+// swizzle) and keeps only the running group sums in registers: the scaled
+// totals live in shared memory, which keeps the kernel under 128 registers
+// so that 16 warps hide each other's latencies.  Where several CTAs share a
+// column block their partial sums go to a global scratch and the last arriver
+// adds them in CTA order (deterministic) and runs the epilogue.
 #include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
@@ -39,15 +41,15 @@ namespace qmm {
 
 namespace {
 
-constexpr int WARPS = 8;
-constexpr int STAGES = 8; // per warp
-constexpr int STAGE_BYTES = 16 * 128; // 16 k-rows of 256 packed columns
+constexpr int WARPS = 16;
+constexpr int PAIRS = WARPS / 2;
+constexpr int STAGES = 4; // per warp
+constexpr int STAGE_BYTES = 32 * 64; // 32 k-rows (two MMA k-steps) of 128 packed columns
 constexpr int NB = 256; // dst columns per column block
 constexpr int MB = 8; // src rows per pass (the MMA's n extent)
-constexpr int RED_PITCH = 276; // words per row of the reduction tile: 256 + 8 x 2 pads, = 4 mod 16
 constexpr int RING_BYTES = WARPS * STAGES * STAGE_BYTES;
-constexpr int RED_BYTES = WARPS * MB * RED_PITCH * 4;
-constexpr int SMEM_BYTES = RING_BYTES + RED_BYTES + WARPS * STAGES * 8 + 64 + 1024;
+constexpr int TOT_BYTES = WARPS * 8 * 32 * 16; // per warp: [8 column pairs][32 lanes] float4
+constexpr int SMEM_BYTES = RING_BYTES + TOT_BYTES + WARPS * STAGES * 8 + 64 + 1024;
 
 struct WoqParams {
     int M; // rows of this pass (<= 8)
@@ -59,7 +61,7 @@ struct WoqParams {
     int max_slots; // partial-sum slots per column block
     int sgn4; // weights are s4 (else u4)
     int zp_mode; // 0 none, 1 per (group, n), 2 per tensor
-    float *partial; // [nblk][max_slots][8][256]
+    float4 *partial; // [nblk][max_slots][512]
     int *counters; // [nblk]
     // zero-point correction through the tensor cores (ZPMMA kernels)
     uint32_t magic_z; // turns a zero-point nibble pair into bf16 (128 [+ 8] + z)
@@ -98,11 +100,16 @@ __device__ __forceinline__ float pair_sum(uint32_t v) {
     }
     return __uint_as_float(v << 16) + __uint_as_float(v & 0xffff0000u);
 }
-// 16-byte read-only load that stays where it is written (issued groups ahead of its use; a plain
-// load may be moved down to the use and then stalls the warp there)
+// Read-only loads that stay where they are written (issued well ahead of
+// their use; a plain load may be moved down to the use and stalls the warp there)
 __device__ __forceinline__ uint4 ldg_v4_here(const void *ptr) {
     uint4 v;
     asm volatile("ld.global.nc.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(ptr));
+    return v;
+}
+__device__ __forceinline__ uint2 ldg_v2_here(const void *ptr) {
+    uint2 v;
+    asm volatile("ld.global.nc.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(ptr));
     return v;
 }
 __device__ __forceinline__ uint32_t ldg_u32_here(const void *ptr) {
@@ -110,27 +117,25 @@ __device__ __forceinline__ uint32_t ldg_u32_here(const void *ptr) {
     asm volatile("ld.global.nc.u32 %0, [%1];" : "=r"(v) : "l"(ptr));
     return v;
 }
-// position of column c in a row of the reduction tile: two pad words per 32
-// columns keep the float2 stores of a half-warp (4 rows x 4 column groups) on
-// 16 distinct bank pairs and 8-byte aligned
-__device__ __forceinline__ int red_pos(int c) { return c + 2 * (c >> 5); }
 
-// ZPMMA (bf16 src; no, per-tensor-free or 4-bit per-group zero-points): the zero-point correction
-// runs on the tensor cores; otherwise it is applied with FMAs when a group ends.
+// ZPMMA (bf16 src; no zero-points or 4-bit ones per group): the zero-point
+// correction runs on the tensor cores; otherwise FMAs apply it when a group ends.
 template <bool F16, bool ZPMMA>
 __global__ void __launch_bounds__(WARPS * 32, 1)
 woq_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ MatmulArgs a,
         const __grid_constant__ WoqParams p) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-    float *red = reinterpret_cast<float *>(smem + RING_BYTES);
-    uint64_t *bars = (uint64_t *)(smem + RING_BYTES + RED_BYTES);
+    float4 *tot_all = reinterpret_cast<float4 *>(smem + RING_BYTES);
+    uint64_t *bars = (uint64_t *)(smem + RING_BYTES + TOT_BYTES);
     int *flag = (int *)(bars + WARPS * STAGES);
 
     const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
     const int g = lane >> 2, tig = lane & 3;
+    const int pair = warp >> 1, half = warp & 1;
     uint8_t *ring = smem + warp * STAGES * STAGE_BYTES;
     uint64_t *full = bars + warp * STAGES;
+    float4 *tot_s = tot_all + warp * 256 + lane; // element t at tot_s[32 t]
     if (lane == 0) {
         for (int s = 0; s < STAGES; ++s) ptx::mbar_init(&full[s], 1);
         ptx::fence_barrier_init();
@@ -152,9 +157,10 @@ woq_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
     const int64_t total = (int64_t)p.nblk * p.ksteps;
     int64_t L = (int64_t)blockIdx.x * p.per;
     const int64_t L1 = min(total, L + p.per);
-    // byte offsets inside a stage of this lane's 16-byte chunks in k-rows 2tig and 2tig+1 (128B swizzle)
-    const int lds0 = (2 * tig) * 128 + ((g ^ ((2 * tig) & 7)) << 4);
-    const int lds1 = (2 * tig + 1) * 128 + ((g ^ ((2 * tig + 1) & 7)) << 4);
+    // Byte offset inside a 16-row half stage of this lane's 8 bytes (16 columns) in k-row 2tig; row
+    // 2tig+1 lies 64 bytes further, rows +8 another 512.  64B swizzle: the 16-byte chunk index is
+    // XORed with (row >> 1) & 3, which is tig for all four rows.
+    const int lds0 = (2 * tig) * 64 + ((((g >> 1) ^ tig) & 3) << 4) + (g & 1) * 8;
     uint32_t git = 0; // stages consumed so far by this warp (ring position and phase)
     bool ok = true;
 
@@ -162,28 +168,31 @@ woq_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
         const int nblk = (int)(L / p.ksteps), kb = (int)(L % p.ksteps);
         const int ke = (int)min((int64_t)p.ksteps, kb + (L1 - L));
         const int seg = ke - kb;
-        const int ws0 = kb + (int)((int64_t)seg * warp / WARPS), ws1 = kb + (int)((int64_t)seg * (warp + 1) / WARPS);
+        const int ws0 = kb + (int)((int64_t)seg * pair / PAIRS), ws1 = kb + (int)((int64_t)seg * (pair + 1) / PAIRS);
         const int nsteps = ok ? ws1 - ws0 : 0; // after an expired wait the warp only takes part in the barriers
-        const int64_t n0 = (int64_t)nblk * NB + g * 32; // this thread's 32 columns
+        const int nstages = (nsteps + 1) >> 1;
+        const int64_t n0 = (int64_t)nblk * NB + half * 128 + g * 16; // this lane's 16 columns
         const bool cols_ok = n0 < a.N;
+        const int xbyte = nblk * (NB / 2) + half * 64;
 
         if (lane == 0) {
-            for (int i = 0; i < STAGES && i < nsteps; ++i) {
+            for (int i = 0; i < STAGES && i < nstages; ++i) {
                 const int s = (git + i) % STAGES;
                 ptx::mbar_arrive_expect_tx(&full[s], STAGE_BYTES);
-                ptx::tma_load_2d(ring + s * STAGE_BYTES, &tmW, &full[s], nblk * (NB / 2), (ws0 + i) * 16);
+                ptx::tma_load_2d(ring + s * STAGE_BYTES, &tmW, &full[s], xbyte, (ws0 + 2 * i) * 16);
             }
         }
-        float acc[16][4], tot[16][4];
+        float acc[8][4];
 #pragma unroll
-        for (int t = 0; t < 16; ++t)
-#pragma unroll
-            for (int i = 0; i < 4; ++i) acc[t][i] = tot[t][i] = 0.f;
+        for (int t = 0; t < 8; ++t) {
+            acc[t][0] = acc[t][1] = acc[t][2] = acc[t][3] = 0.f;
+            tot_s[32 * t] = make_float4(0.f, 0.f, 0.f, 0.f);
+        }
         float sp = 0.f; // running sum of this lane's src values (row g) in the current group
-        uint32_t scw[16]; // bf16 scale pairs (columns 2t, 2t+1) of the current group
+        uint32_t scw[8]; // bf16 scale pairs (columns 2t, 2t+1) of the current group
 #pragma unroll
-        for (int t = 0; t < 16; ++t) scw[t] = 0u; // lanes whose columns lie beyond N keep zeros
-        uint4 zq = make_uint4(0, 0, 0, 0); // 4-bit zero-points of the current group
+        for (int t = 0; t < 8; ++t) scw[t] = 0u; // lanes whose columns lie beyond N keep zeros
+        uint2 zq = make_uint2(0, 0); // 4-bit zero-points of the current group
         uint32_t nb0 = 0, nb1 = 0; // src operand of the next k-step
         // this lane's src words of k-step ws0 (k = 16 ws0 + 2 tig, +1 and +8, +9); 8 words per k-step
         const uint32_t *sq = reinterpret_cast<const uint32_t *>(src_row + ((int64_t)ws0 * 16 + 2 * tig) * 2);
@@ -195,32 +204,29 @@ woq_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
         int gi = ws0 / p.group_steps, gpos = ws0 - gi * p.group_steps; // group and k-step inside it
         int s = git % STAGES;
         uint32_t phase = (git / STAGES) & 1;
-        git += nsteps;
+        git += nstages;
 
         for (int it = 0; it < nsteps; ++it) {
             const int kstep = ws0 + it;
+            const int hs = it & 1; // which 16-row half of the stage
             // quantization parameters of a new group: requested now, used when the group ends
             if ((it == 0 || gpos == 0) && cols_ok) {
                 if (sc_bf16) {
                     const int64_t qb = ((a.wei_scale.mask & 1) ? (int64_t)gi * a.wei_scale.ld : 0) + n0;
                     const char *q = (const char *)a.wei_scale.ptr + qb * 2;
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        const uint4 v = ldg_v4_here(q + 16 * j);
-                        scw[4 * j] = v.x; scw[4 * j + 1] = v.y; scw[4 * j + 2] = v.z; scw[4 * j + 3] = v.w;
-                    }
+                    const uint4 v0 = ldg_v4_here(q), v1 = ldg_v4_here(q + 16);
+                    scw[0] = v0.x; scw[1] = v0.y; scw[2] = v0.z; scw[3] = v0.w;
+                    scw[4] = v1.x; scw[5] = v1.y; scw[6] = v1.z; scw[7] = v1.w;
                 }
-                if (zp4) zq = ldg_v4_here((const char *)a.wei_zp.ptr + ((int64_t)gi * a.wei_zp.ld + n0) / 2);
+                if (zp4) zq = ldg_v2_here((const char *)a.wei_zp.ptr + ((int64_t)gi * a.wei_zp.ld + n0) / 2);
             }
-            // every lane waits (it reads the stage), and the warp leaves the loop as a whole
-            if (!__all_sync(0xffffffffu, ptx::mbar_wait(&full[s], phase))) { ok = false; break; }
-            // rows 2tig, 2tig+1 (and 8 rows further down) of the stage; column chunk g, swizzled by (row & 7)
-            const uint8_t *st = ring + s * STAGE_BYTES;
-            uint4 R[4];
-            R[0] = *reinterpret_cast<const uint4 *>(st + lds0);
-            R[1] = *reinterpret_cast<const uint4 *>(st + lds1);
-            R[2] = *reinterpret_cast<const uint4 *>(st + lds0 + 1024);
-            R[3] = *reinterpret_cast<const uint4 *>(st + lds1 + 1024);
+            // a new stage: every lane waits (it reads the stage), and the warp leaves the loop as a whole
+            if (!hs && !__all_sync(0xffffffffu, ptx::mbar_wait(&full[s], phase))) { ok = false; break; }
+            const uint8_t *st = ring + s * STAGE_BYTES + hs * 1024 + lds0;
+            const uint2 R0 = *reinterpret_cast<const uint2 *>(st); // k-row 2tig
+            const uint2 R1 = *reinterpret_cast<const uint2 *>(st + 64); // 2tig+1
+            const uint2 R2 = *reinterpret_cast<const uint2 *>(st + 512); // 2tig+8
+            const uint2 R3 = *reinterpret_cast<const uint2 *>(st + 576); // 2tig+9
             // src operand (row g; k = 16*kstep + {2tig, 2tig+1}, {2tig+8, 2tig+9}): loaded one step ahead
             const uint32_t b0 = nb0, b1 = nb1;
             sq += 8;
@@ -229,14 +235,12 @@ woq_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
                 nb1 = ldg_u32_here(sq + 4);
             }
             sp += pair_sum<F16>(b0) + pair_sum<F16>(b1);
-            const uint32_t *w0 = reinterpret_cast<const uint32_t *>(&R[0]), *w1 = reinterpret_cast<const uint32_t *>(&R[1]);
-            const uint32_t *w2 = reinterpret_cast<const uint32_t *>(&R[2]), *w3 = reinterpret_cast<const uint32_t *>(&R[3]);
 #pragma unroll
-            for (int t = 0; t < 16; ++t) {
+            for (int t = 0; t < 8; ++t) {
                 // byte t of the four rows: low nibble = column 2t, high nibble = column 2t+1
                 const uint32_t sel = ((4 + (t & 3)) << 12) | ((4 + (t & 3)) << 8) | ((t & 3) << 4) | (t & 3);
-                const uint32_t x01 = prmt(w0[t >> 2], w1[t >> 2], sel);
-                const uint32_t x23 = prmt(w2[t >> 2], w3[t >> 2], sel);
+                const uint32_t x01 = prmt(t < 4 ? R0.x : R0.y, t < 4 ? R1.x : R1.y, sel);
+                const uint32_t x23 = prmt(t < 4 ? R2.x : R2.y, t < 4 ? R3.x : R3.y, sel);
                 uint32_t af[4];
                 af[0] = nib2(x01, magic); // column 2t,   k pair (2tig, 2tig+1)
                 af[1] = nib2(x01 >> 4, magic); // column 2t+1
@@ -245,13 +249,17 @@ woq_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
                 if (F16) mma_f16(acc[t], af, b0, b1);
                 else mma_bf16(acc[t], af, b0, b1);
             }
-            // the MMAs have consumed R, so every lane's reads of the stage are complete: refill it
-            __syncwarp();
-            if (lane == 0 && it + STAGES < nsteps) {
-                ptx::mbar_arrive_expect_tx(&full[s], STAGE_BYTES);
-                ptx::tma_load_2d(ring + s * STAGE_BYTES, &tmW, &full[s], nblk * (NB / 2), (kstep + STAGES) * 16);
+            // The MMAs have consumed the registers read from the stage, so every lane's reads are
+            // complete: after its second half (or the range's last step) the stage is refilled.
+            if (hs || it == nsteps - 1) {
+                __syncwarp();
+                const int next = (it >> 1) + STAGES;
+                if (lane == 0 && next < nstages) {
+                    ptx::mbar_arrive_expect_tx(&full[s], STAGE_BYTES);
+                    ptx::tma_load_2d(ring + s * STAGE_BYTES, &tmW, &full[s], xbyte, (ws0 + 2 * next) * 16);
+                }
+                if (++s == STAGES) { s = 0; phase ^= 1; }
             }
-            if (++s == STAGES) { s = 0; phase ^= 1; }
             // end of a quantization group (or of this warp's range): fold the group into the totals
             const bool group_end = ++gpos == p.group_steps;
             if (ZPMMA && (group_end || it == nsteps - 1)) {
@@ -269,36 +277,37 @@ woq_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
                 const uint32_t pl = __float_as_uint(r1 - __uint_as_float(pm));
                 const uint32_t cb0 = tig == 0 ? ((ph >> 16) | pm) : (tig == 1 ? (pl >> 16) : 0u);
                 const uint32_t cb1 = p.az_diff ? cb0 : 0u;
-                { // every lane takes part in the MMAs, also those whose columns lie beyond N
+                // every lane takes part in the MMAs, also those whose columns lie beyond N
 #pragma unroll
-                    for (int t = 0; t < 16; ++t) {
-                        uint32_t za[4];
-                        if (p.zp_mode == 1) {
-                            // byte t of the lane's 16 zero-point bytes -> [b, 0, b, 0]
-                            const uint32_t sel = (4u << 12) | ((t & 3) << 8) | (4u << 4) | (t & 3);
-                            const uint32_t x = prmt(reinterpret_cast<const uint32_t *>(&zq)[t >> 2], 0u, sel);
-                            za[0] = nib2(x, p.magic_z);
-                            za[1] = nib2(x >> 4, p.magic_z);
-                        } else {
-                            za[0] = za[1] = p.az_const;
-                        }
-                        za[2] = za[3] = p.az_diff;
-                        mma_bf16(acc[t], za, cb0, cb1);
-                        float sc_lo, sc_hi;
-                        if (sc_bf16) {
-                            sc_lo = __uint_as_float(scw[t] << 16);
-                            sc_hi = __uint_as_float(scw[t] & 0xffff0000u);
-                        } else {
-                            const int64_t qbase = ((a.wei_scale.mask & 1) ? (int64_t)gi * a.wei_scale.ld : 0) + n0;
-                            sc_lo = cols_ok ? load_float(a.wei_scale.dt, a.wei_scale.ptr, qbase + 2 * t) : 0.f;
-                            sc_hi = cols_ok ? load_float(a.wei_scale.dt, a.wei_scale.ptr, qbase + 2 * t + 1) : 0.f;
-                        }
-                        tot[t][0] = fmaf(sc_lo, acc[t][0], tot[t][0]);
-                        tot[t][1] = fmaf(sc_lo, acc[t][1], tot[t][1]);
-                        tot[t][2] = fmaf(sc_hi, acc[t][2], tot[t][2]);
-                        tot[t][3] = fmaf(sc_hi, acc[t][3], tot[t][3]);
-                        acc[t][0] = acc[t][1] = acc[t][2] = acc[t][3] = 0.f;
+                for (int t = 0; t < 8; ++t) {
+                    uint32_t za[4];
+                    if (p.zp_mode == 1) {
+                        // byte t of the lane's 8 zero-point bytes -> [b, 0, b, 0]
+                        const uint32_t sel = (4u << 12) | ((t & 3) << 8) | (4u << 4) | (t & 3);
+                        const uint32_t x = prmt(t < 4 ? zq.x : zq.y, 0u, sel);
+                        za[0] = nib2(x, p.magic_z);
+                        za[1] = nib2(x >> 4, p.magic_z);
+                    } else {
+                        za[0] = za[1] = p.az_const;
                     }
+                    za[2] = za[3] = p.az_diff;
+                    mma_bf16(acc[t], za, cb0, cb1);
+                    float sc_lo, sc_hi;
+                    if (sc_bf16) {
+                        sc_lo = __uint_as_float(scw[t] << 16);
+                        sc_hi = __uint_as_float(scw[t] & 0xffff0000u);
+                    } else {
+                        const int64_t qbase = ((a.wei_scale.mask & 1) ? (int64_t)gi * a.wei_scale.ld : 0) + n0;
+                        sc_lo = cols_ok ? load_float(a.wei_scale.dt, a.wei_scale.ptr, qbase + 2 * t) : 0.f;
+                        sc_hi = cols_ok ? load_float(a.wei_scale.dt, a.wei_scale.ptr, qbase + 2 * t + 1) : 0.f;
+                    }
+                    float4 v = tot_s[32 * t];
+                    v.x = fmaf(sc_lo, acc[t][0], v.x);
+                    v.y = fmaf(sc_lo, acc[t][1], v.y);
+                    v.z = fmaf(sc_hi, acc[t][2], v.z);
+                    v.w = fmaf(sc_hi, acc[t][3], v.w);
+                    tot_s[32 * t] = v;
+                    acc[t][0] = acc[t][1] = acc[t][2] = acc[t][3] = 0.f;
                 }
                 if (group_end) { gpos = 0; ++gi; }
             }
@@ -311,7 +320,7 @@ woq_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
                 if (cols_ok) {
                     const int64_t qbase = ((a.wei_scale.mask & 1) ? (int64_t)gi * a.wei_scale.ld : 0) + n0;
 #pragma unroll
-                    for (int t = 0; t < 16; ++t) {
+                    for (int t = 0; t < 8; ++t) {
                         float sc_lo, sc_hi;
                         if (sc_bf16) {
                             sc_lo = __uint_as_float(scw[t] << 16);
@@ -322,7 +331,7 @@ woq_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
                         }
                         float z_lo = zt, z_hi = zt;
                         if (zp4) {
-                            const uint32_t byte = (reinterpret_cast<const uint32_t *>(&zq)[t >> 2] >> ((t & 3) * 8)) & 0xffu;
+                            const uint32_t byte = ((t < 4 ? zq.x : zq.y) >> ((t & 3) * 8)) & 0xffu;
                             int lo = byte & 0xf, hi = byte >> 4;
                             if (a.wei_zp.dt == DT_S4) { lo = (lo ^ 8) - 8; hi = (hi ^ 8) - 8; }
                             z_lo = (float)lo; z_hi = (float)hi;
@@ -332,34 +341,28 @@ woq_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
                             z_hi = (float)load_int(a.wei_zp.dt, a.wei_zp.ptr, zb + 1);
                         }
                         const float oz_lo = off + z_lo, oz_hi = off + z_hi;
-                        tot[t][0] = fmaf(sc_lo, acc[t][0] * acc_scale - oz_lo * S0, tot[t][0]);
-                        tot[t][1] = fmaf(sc_lo, acc[t][1] * acc_scale - oz_lo * S1, tot[t][1]);
-                        tot[t][2] = fmaf(sc_hi, acc[t][2] * acc_scale - oz_hi * S0, tot[t][2]);
-                        tot[t][3] = fmaf(sc_hi, acc[t][3] * acc_scale - oz_hi * S1, tot[t][3]);
-                        acc[t][0] = acc[t][1] = acc[t][2] = acc[t][3] = 0.f;
+                        float4 v = tot_s[32 * t];
+                        v.x = fmaf(sc_lo, acc[t][0] * acc_scale - oz_lo * S0, v.x);
+                        v.y = fmaf(sc_lo, acc[t][1] * acc_scale - oz_lo * S1, v.y);
+                        v.z = fmaf(sc_hi, acc[t][2] * acc_scale - oz_hi * S0, v.z);
+                        v.w = fmaf(sc_hi, acc[t][3] * acc_scale - oz_hi * S1, v.w);
+                        tot_s[32 * t] = v;
                     }
                 }
+#pragma unroll
+                for (int t = 0; t < 8; ++t) acc[t][0] = acc[t][1] = acc[t][2] = acc[t][3] = 0.f;
                 if (group_end) { gpos = 0; ++gi; }
             }
         }
 
-        // ---- the warps' totals meet in shared memory: red[warp][m][column]
-#pragma unroll
-        for (int t = 0; t < 16; ++t) {
-            const int c = red_pos(g * 32 + 2 * t); // columns 2t and 2t+1 are adjacent: no pad between them
-            *reinterpret_cast<float2 *>(&red[(warp * MB + 2 * tig) * RED_PITCH + c]) = make_float2(tot[t][0], tot[t][2]);
-            *reinterpret_cast<float2 *>(&red[(warp * MB + 2 * tig + 1) * RED_PITCH + c]) = make_float2(tot[t][1], tot[t][3]);
-        }
+        // ---- the pairs' totals meet: thread i adds the 8 pairs' float4 of (half, t, lane) = i
         __syncthreads();
-        const int i = threadIdx.x; // column of the block
-        const int64_t n = (int64_t)nblk * NB + i;
-        float v[MB];
+        const int i = threadIdx.x;
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
-        for (int m = 0; m < MB; ++m) {
-            float sacc = 0.f;
-#pragma unroll
-            for (int w = 0; w < WARPS; ++w) sacc += red[(w * MB + m) * RED_PITCH + red_pos(i)];
-            v[m] = sacc;
+        for (int pr = 0; pr < PAIRS; ++pr) {
+            const float4 w = tot_all[(2 * pr + (i >> 8)) * 256 + (i & 255)];
+            v.x += w.x; v.y += w.y; v.z += w.z; v.w += w.w;
         }
         // CTAs sharing this column block, in k order
         const int first = (int)(((int64_t)nblk * p.ksteps) / p.per);
@@ -367,9 +370,8 @@ woq_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
         bool finalize = true;
         if (last > first) {
             const int count = last - first + 1, slot = (int)blockIdx.x - first;
-            float *base = p.partial + ((int64_t)nblk * p.max_slots) * (MB * NB);
-#pragma unroll
-            for (int m = 0; m < MB; ++m) base[(slot * MB + m) * NB + i] = v[m];
+            float4 *base = p.partial + ((int64_t)nblk * p.max_slots) * 512;
+            base[slot * 512 + i] = v;
             __threadfence();
             __syncthreads();
             if (threadIdx.x == 0) *flag = atomicAdd(&p.counters[nblk], 1) == count - 1;
@@ -377,29 +379,34 @@ woq_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
             finalize = *flag != 0;
             if (finalize) {
                 __threadfence();
-#pragma unroll
-                for (int m = 0; m < MB; ++m) v[m] = 0.f;
-                for (int sl = 0; sl < count; ++sl)
-#pragma unroll
-                    for (int m = 0; m < MB; ++m) v[m] += __ldcg(base + (sl * MB + m) * NB + i);
+                v = make_float4(0.f, 0.f, 0.f, 0.f);
+                for (int sl = 0; sl < count; ++sl) {
+                    const float4 w = __ldcg(base + sl * 512 + i);
+                    v.x += w.x; v.y += w.y; v.z += w.z; v.w += w.w;
+                }
                 if (threadIdx.x == 0) p.counters[nblk] = 0; // ready for the next launch
             }
         }
-        if (finalize && n < a.N) {
+        // v: columns c0 (x, y) and c0 + 1 (z, w), src rows 2tig (x, z) and 2tig + 1 (y, w)
+        const int64_t c0 = (int64_t)nblk * NB + (i >> 8) * 128 + g * 16 + 2 * ((i >> 5) & 7);
+        if (finalize && c0 < a.N) {
             float ss = 1.f;
             if (a.src_scale.ptr) ss = load_float(a.src_scale.dt, a.src_scale.ptr, 0);
             else if (a.src_scale.on_host) ss = a.src_scale.host_value;
+            const float vals[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
-            for (int m = 0; m < MB; ++m) {
+            for (int e = 0; e < 4; ++e) {
+                const int m = 2 * tig + (e & 1);
+                const int64_t n = c0 + (e >> 1);
                 if (m < p.M) {
                     const int64_t mm = p.m_base + m;
-                    float d = v[m] * ss;
+                    float d = vals[e] * ss;
                     if (a.bias) d = __fadd_rn(d, load_float(a.bias_dt, a.bias, mm * a.bias_sm + n * a.bias_sn));
                     finish_store(a, d, mm, n, false);
                 }
             }
         }
-        __syncthreads(); // red and flag are reused by the next segment
+        __syncthreads(); // the totals and the flag are reused by the next segment
         L += seg;
     }
     if (!ok) atomicExch(a.status, 5);
@@ -422,8 +429,9 @@ encode_tiled_fn woq_get_encode() {
 }
 
 // The cut of the (column block, k-step) space: `per` pairs per CTA (a multiple
-// of 8 so the warps get equal shares, at least 32 so a CTA is worth its
-// launch), `grid` CTAs, at most `max_slots` CTAs on one column block.
+// of 16 so the warp pairs get equal shares of whole stages, at least 32 so a
+// CTA is worth its launch), `grid` CTAs, at most `max_slots` CTAs on one
+// column block.
 struct WoqPlan {
     int nblk, ksteps, per, grid, max_slots;
 };
@@ -434,7 +442,7 @@ WoqPlan woq_plan(int64_t N, int64_t K, int sm_count) {
     const int64_t total = (int64_t)pl.nblk * pl.ksteps;
     if (sm_count < 1) sm_count = 148;
     int64_t per = (total + sm_count - 1) / sm_count;
-    per = (per + 7) / 8 * 8;
+    per = (per + 15) / 16 * 16;
     if (per < 32) per = 32;
     pl.per = (int)per;
     pl.grid = (int)((total + per - 1) / per);
@@ -461,10 +469,10 @@ int launch_woq_skinny(const MatmulArgs &a, void *scratch, int sm_count, cudaStre
     CUtensorMap tm;
     cuuint64_t dims[2] = {(cuuint64_t)(a.N / 2), (cuuint64_t)a.K};
     cuuint64_t strides[1] = {(cuuint64_t)(a.wei_sk / 2)};
-    cuuint32_t box[2] = {128, 16};
+    cuuint32_t box[2] = {64, 32};
     cuuint32_t estr[2] = {1, 1};
     if (enc(&tm, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void *>(a.wei), dims, strides, box, estr,
-                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE)
             != CUDA_SUCCESS)
         return 5;
@@ -480,7 +488,7 @@ int launch_woq_skinny(const MatmulArgs &a, void *scratch, int sm_count, cudaStre
     p.sgn4 = a.wei_dt == DT_S4;
     p.zp_mode = !a.wei_zp.ptr ? 0 : (a.wei_zp.mask ? 1 : 2);
     p.counters = (int *)scratch;
-    p.partial = (float *)((char *)scratch + ((size_t)pl.nblk * sizeof(int) + 255) / 256 * 256);
+    p.partial = (float4 *)((char *)scratch + ((size_t)pl.nblk * sizeof(int) + 255) / 256 * 256);
     const bool f16 = a.src_dt == DT_F16;
     // tensor-core zero-point correction: bf16 src and either no zero-points or 4-bit ones per group
     const bool zp4 = p.zp_mode == 1 && (a.wei_zp.dt == DT_U4 || a.wei_zp.dt == DT_S4);
