@@ -37,6 +37,13 @@
 #include "launch.h"
 #include "sm100_ptx.cuh"
 
+// Profiling aid: -DWOQ_ABLATE=<bits> compiles parts of the kernel out (1 dequantization and MMAs,
+// 2 group-end arithmetic, 4 src loads, 8 shared-memory reads, 16 reduction and epilogue) so that
+// instruction counts and times of the rest can be measured.  Results are wrong unless it is 0.
+#ifndef WOQ_ABLATE
+#define WOQ_ABLATE 0
+#endif
+
 namespace qmm {
 
 namespace {
@@ -196,7 +203,7 @@ woq_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
         uint32_t nb0 = 0, nb1 = 0; // src operand of the next k-step
         // this lane's src words of k-step ws0 (k = 16 ws0 + 2 tig, +1 and +8, +9); 8 words per k-step
         const uint32_t *sq = reinterpret_cast<const uint32_t *>(src_row + ((int64_t)ws0 * 16 + 2 * tig) * 2);
-        if (row_ok && nsteps > 0) {
+        if (!(WOQ_ABLATE & 4) && row_ok && nsteps > 0) {
             nb0 = ldg_u32_here(sq);
             nb1 = ldg_u32_here(sq + 4);
         }
@@ -223,20 +230,21 @@ woq_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
             // a new stage: every lane waits (it reads the stage), and the warp leaves the loop as a whole
             if (!hs && !__all_sync(0xffffffffu, ptx::mbar_wait(&full[s], phase))) { ok = false; break; }
             const uint8_t *st = ring + s * STAGE_BYTES + hs * 1024 + lds0;
-            const uint2 R0 = *reinterpret_cast<const uint2 *>(st); // k-row 2tig
-            const uint2 R1 = *reinterpret_cast<const uint2 *>(st + 64); // 2tig+1
-            const uint2 R2 = *reinterpret_cast<const uint2 *>(st + 512); // 2tig+8
-            const uint2 R3 = *reinterpret_cast<const uint2 *>(st + 576); // 2tig+9
+            const bool lds = !(WOQ_ABLATE & 8);
+            const uint2 R0 = lds ? *reinterpret_cast<const uint2 *>(st) : make_uint2(it, lane); // k-row 2tig
+            const uint2 R1 = lds ? *reinterpret_cast<const uint2 *>(st + 64) : make_uint2(s, it); // 2tig+1
+            const uint2 R2 = lds ? *reinterpret_cast<const uint2 *>(st + 512) : make_uint2(lane, s); // 2tig+8
+            const uint2 R3 = lds ? *reinterpret_cast<const uint2 *>(st + 576) : make_uint2(kstep, kstep); // 2tig+9
             // src operand (row g; k = 16*kstep + {2tig, 2tig+1}, {2tig+8, 2tig+9}): loaded one step ahead
             const uint32_t b0 = nb0, b1 = nb1;
             sq += 8;
-            if (row_ok && it + 1 < nsteps) {
+            if (!(WOQ_ABLATE & 4) && row_ok && it + 1 < nsteps) {
                 nb0 = ldg_u32_here(sq);
                 nb1 = ldg_u32_here(sq + 4);
             }
             sp += pair_sum<F16>(b0) + pair_sum<F16>(b1);
 #pragma unroll
-            for (int t = 0; t < 8; ++t) {
+            for (int t = 0; t < ((WOQ_ABLATE & 1) ? 0 : 8); ++t) {
                 // byte t of the four rows: low nibble = column 2t, high nibble = column 2t+1
                 const uint32_t sel = ((4 + (t & 3)) << 12) | ((4 + (t & 3)) << 8) | ((t & 3) << 4) | (t & 3);
                 const uint32_t x01 = prmt(t < 4 ? R0.x : R0.y, t < 4 ? R1.x : R1.y, sel);
@@ -279,7 +287,7 @@ woq_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
                 const uint32_t cb1 = p.az_diff ? cb0 : 0u;
                 // every lane takes part in the MMAs, also those whose columns lie beyond N
 #pragma unroll
-                for (int t = 0; t < 8; ++t) {
+                for (int t = 0; t < ((WOQ_ABLATE & 2) ? 0 : 8); ++t) {
                     uint32_t za[4];
                     if (p.zp_mode == 1) {
                         // byte t of the lane's 8 zero-point bytes -> [b, 0, b, 0]
@@ -355,6 +363,7 @@ woq_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
             }
         }
 
+        if (WOQ_ABLATE & 16) { L += seg; continue; }
         // ---- the pairs' totals meet: thread i adds the 8 pairs' float4 of (half, t, lane) = i
         __syncthreads();
         const int i = threadIdx.x;
