@@ -136,6 +136,16 @@ def peaks():
     return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
 
 
+def dram_traffic(workload_key, world):
+    """DRAM bytes of one launch of the dominant kernel, from the committed ncu
+    capture of this exact workload (single GPU); None when there is none."""
+    path = os.path.join(ROOT, "profiles", "dram_traffic.json")
+    if world != 1 or not os.path.exists(path):
+        return None
+    entry = json.load(open(path)).get(workload_key)
+    return entry["bytes"] if entry else None
+
+
 # ------------------------------------------------------------------ GPU arm
 def device_buffers(p, torch, dev):
     """Uploads every tensor of the problem once; returns (ptr dict, keepalive)."""
@@ -246,8 +256,21 @@ def run_gpu(args):
     e1.record()
     barrier()
     launches = api.launch_count() - launches0
-    clocks = sampler.stop() if sampler else None
     total_ms = e0.elapsed_time(e1)
+    # The timed region lasts milliseconds, less than one nvidia-smi sampling period: the same
+    # step is repeated (untimed) for about 1.5 s so that the sampler sees the clocks under this load.
+    if sampler:
+        t_end = time.time() + 1.5
+        i = 0
+        while time.time() < t_end:
+            for _ in range(50):
+                preps[i % len(preps)].execute(strm)
+                i += 1
+            torch.cuda.synchronize()
+    barrier()
+    clocks = sampler.stop() if sampler else None
+    if clocks is not None:
+        clocks["sampled"] = "over the timed region and a 1.5 s untimed repeat of the same step"
     kernel_ms = float(np.mean([a.elapsed_time(b) for a, b in k_ev]))
 
     # ---- end-to-end: src from pinned host memory, dst back to the host, every step
@@ -291,17 +314,20 @@ def run_gpu(args):
             peak, runit = mult * pk["bf16_tflops"], "TFLOP/s"
         value = work_full / (ms_per_step * per)
         achieved = work_launch / (kernel_ms * per)
+        wkey = "%s M=%d K=%d N=%d" % (name, full.M, full.K, full.N)
         line = {
             "metric": metric, "value": value, "unit": unit, "n_gpus": world, "steps": args.steps,
             "warmup": max(3, args.warmup), "ms_per_step": ms_per_step, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": dtype, "data": "synthetic",
-            "config": {"workload": "%s M=%d K=%d N=%d" % (name, full.M, full.K, full.N),
+            "config": {"workload": wkey,
                        "kernel": prep.impl, "parallelism": "n-shard x%d + all-gather" % world if world > 1 else "single",
                        "l2": "weight copies rotated (3 x %.0f MB)" % (p.wei.data.nbytes / 1e6) if rotate
                              else "working set %.0f MB > 126 MB L2" % (p.algorithmic_bytes() / 1e6),
                        "e2e": "src H2D from pinned memory and dst D2H every step; weights resident"},
             "roofline": {"bound": bound, "achieved": achieved, "peak": peak, "unit": runit,
-                         "frac": achieved / peak, "traffic": None, "peak_source": pk["source"],
+                         "frac": achieved / peak, "traffic": dram_traffic(wkey, world),
+                         "traffic_unit": "bytes per launch (ncu, profiles/dram_traffic.json)",
+                         "algorithmic_bytes": int(p.algorithmic_bytes()), "peak_source": pk["source"],
                          "kernel_ms": kernel_ms},
             "e2e": {"value": work_full / (e2e_ms * per), "unit": unit,
                     "h2d_bytes_per_step": int(src_host.numel()), "d2h_bytes_per_step": int(out_bytes),
