@@ -27,4 +27,10 @@ bool gemm_tc_pointers_ok(const MatmulArgs &a);
 int launch_woq_skinny(const MatmulArgs &a, void *scratch, int sm_count, cudaStream_t st);
 size_t woq_skinny_scratch_bytes(int64_t N, int64_t K, int sm_count);
 
+// tcgen05 grouped (MoE) GEMM, bf16 src x s8 weights (grouped_tc.cu).
+// `scratch`: grouped_tc_scratch_bytes(group_count) bytes, no initialisation.
+int launch_grouped_tc(const MatmulArgs &a, void *scratch, int sm_count, cudaStream_t st);
+size_t grouped_tc_scratch_bytes(int groups);
+bool grouped_tc_pointers_ok(const MatmulArgs &a);
+
 } // namespace qmm

@@ -6,15 +6,15 @@ import pytest
 from onednn_b200 import workloads as W
 from onednn_b200.runner import run_problem
 from oracle import oracle as O
-from util import assert_parity, summation_slack
+from util import assert_parity, summation_slack, summation_slack_grouped
 
 
 def slack_for(p, impl):
     """Summation slack only for floating-point sums taken in another order
     than the reference's (every implementation but the cuda:ref kernels)."""
-    if impl.startswith("cuda:ref") or p.src.dt in (W.S8, W.U8) or p.offsets is not None:
+    if impl.startswith("cuda:ref") or p.src.dt in (W.S8, W.U8):
         return None
-    return summation_slack(p)
+    return summation_slack_grouped(p) if p.offsets is not None else summation_slack(p)
 
 pytestmark = pytest.mark.gpu
 
@@ -142,6 +142,26 @@ def test_woq_skinny_matches_oracle(gpu, name):
     # the arrival counters are left at zero: a second execution gives the same bits
     got2, _ = run_problem(p, eng, strm, impl="woq")
     assert np.array_equal(got, got2)
+
+
+GROUPED_TC_CASES = {
+    "small": lambda: W.moe_grouped(96, 256, 128, 8),
+    "empty_groups": lambda: W.moe_grouped(40, 128, 64, 6, sizes=[0, 17, 0, 3, 20, 0]),
+    "all_in_one": lambda: W.moe_grouped(70, 192, 256, 4, sizes=[0, 0, 70, 0]),
+    "several_row_blocks": lambda: W.moe_grouped(700, 128, 256, 3, sizes=[513, 1, 186]),
+    "tails_n_k": lambda: W.moe_grouped(50, 200, 176, 3, sizes=[16, 33, 1]),
+    "zipf": lambda: W.moe_grouped(1024, 512, 384, 16),
+}
+
+
+@pytest.mark.parametrize("name", sorted(GROUPED_TC_CASES))
+def test_tcgen05_grouped_matches_oracle(gpu, name):
+    eng, strm = gpu
+    p = GROUPED_TC_CASES[name]()
+    want = O.run_port(p)
+    got, impl = run_problem(p, eng, strm, impl="tcgen05:grouped")
+    assert impl == "cuda:tcgen05:grouped"
+    assert_parity(got, want, p.dst_dt, name, summation_slack_grouped(p))
 
 
 def test_grouped_bad_offsets_reports_invalid_arguments(gpu):

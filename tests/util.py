@@ -64,6 +64,23 @@ def summation_slack(p: W.Problem) -> np.ndarray:
     return 4.0 * 2.0 ** -24 * mag
 
 
+def summation_slack_grouped(p: W.Problem) -> np.ndarray:
+    """The same allowance for a grouped problem: every expert's rows against
+    that expert's weights and per-(expert, column) scales."""
+    s = np.abs(W.to_f32(p.src.data.reshape(p.M, p.K), p.src.dt)).astype(np.float64)
+    w = np.abs(W.to_f32(p.wei.data.reshape(p.groups, p.K, p.N), p.wei.dt).astype(np.float64))
+    q = p.quant.get("wei_scale")
+    sc = np.abs(W.to_f32(q.data, q.dt).astype(np.float64)).reshape(p.groups, -1, p.N).max(axis=1) if q is not None \
+        else np.ones((p.groups, p.N))
+    mag = np.zeros((p.M, p.N))
+    begin = 0
+    for g, end in enumerate(p.offsets.astype(np.int64)):
+        if end > begin:
+            mag[begin:end] = (s[begin:end] @ w[g]) * sc[g][None, :]
+        begin = int(end)
+    return 4.0 * 2.0 ** -24 * mag
+
+
 def compare(got: np.ndarray, want: np.ndarray, dt: int, slack=None):
     """Returns (ok, message).  `slack`: per-element absolute allowance in real
     units (see the module docstring), or None for the plain rules."""
