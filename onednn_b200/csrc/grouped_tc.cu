@@ -8,7 +8,7 @@
 //
 // The tensor cores take 16-bit operands from shared memory, so the int8
 // weights are widened on the way: TMA brings a raw [64 k x 128 n] s8 tile,
-// four converter warps rewrite it as bf16 (exact: 8 significant bits) in the
+// converter warps rewrite it as bf16 (exact: 8 significant bits) in the
 // MN-major 128B-swizzled layout the MMA reads, and `tcgen05.mma kind::f16`
 // multiplies it with the src rows (K-major, straight from TMA).  As in the
 // 8-bit GEMM the kernel computes dst^T: weights are the A operand (128 dst
@@ -21,9 +21,11 @@
 // so CTAs running together share weight tiles through L2.  A small planning
 // kernel turns the offsets (cumulative END rows, validated like
 // ref_grouped_gemm.cpp:164-213) into per-expert tile ranges on the device:
-// no host synchronisation.  One persistent CTA per SM: warp 0 TMA producer,
-// warp 1 MMA issuer, warps 2-5 converters, warps 6-9 epilogue; two TMEM
-// accumulator buffers.  Every mbarrier wait is bounded.
+// no host synchronisation.  One persistent CTA per SM: warp 0 streams the raw
+// weight tiles (ring of 8: they come from HBM), the last warp the src rows
+// (ring of 4: they come from L2), warps 2-9 convert into a ring of 2 bf16
+// tiles, warp 1 issues the MMAs, the next four warps run the epilogue; two
+// TMEM accumulator buffers.  Every mbarrier wait is bounded.
 #include <cuda.h>
 
 #include "device_math.cuh"
@@ -37,16 +39,19 @@ namespace {
 constexpr int GT_N = 128; // dst columns per tile = TMEM lanes = UMMA M
 constexpr int GT_M = 256; // most src rows per tile = UMMA N
 constexpr int GK = 64; // k per stage: one 128-byte swizzle row of bf16 src
-constexpr int G_STAGES = 3;
+// Three rings, one per kind of tile, because their needs differ: the raw weights come from HBM
+// (deep ring of small tiles to cover its latency), the src rows from L2, and the bf16 copy is
+// produced and consumed on the SM (two slots: one being written, one being multiplied).
+constexpr int RAW_STAGES = 8, A_STAGES = 2, B_STAGES = 4;
 constexpr int RAW_BYTES = GK * GT_N; // s8 weights as loaded
 constexpr int A_BYTES = GK * GT_N * 2; // the same tile as bf16: two 64-column blocks of [64 k][128 B]
 constexpr int B_BYTES = GT_M * GK * 2; // src rows, K-major
-constexpr int G_STAGE_BYTES = RAW_BYTES + A_BYTES + B_BYTES;
-constexpr int CONV_WARPS = 4, EPI_WARPS = 4;
-constexpr int G_THREADS = 32 * (2 + CONV_WARPS + EPI_WARPS);
+constexpr int CONV_WARPS = 8, EPI_WARPS = 4;
+constexpr int G_THREADS = 32 * (3 + CONV_WARPS + EPI_WARPS);
 constexpr int ACC_STAGES = 2;
-constexpr int G_BAR_OFFSET = G_STAGES * G_STAGE_BYTES;
-constexpr int G_SMEM_BYTES = G_BAR_OFFSET + 256 + 1024;
+constexpr int A_OFFSET = 0, B_OFFSET = A_STAGES * A_BYTES, RAW_OFFSET = B_OFFSET + B_STAGES * B_BYTES;
+constexpr int G_BAR_OFFSET = RAW_OFFSET + RAW_STAGES * RAW_BYTES;
+constexpr int G_SMEM_BYTES = G_BAR_OFFSET + 512 + 1024;
 
 // plan[0] = {total tiles, groups, 0, 0}; plan[1 + g] = {first src row, first dst row, rows, first tile}
 struct Tile {
@@ -90,21 +95,23 @@ __global__ void grouped_plan_kernel(const __grid_constant__ MatmulArgs a, int4 *
     plan[0] = make_int4(tiles, a.group_count, 0, 0);
 }
 
-// four s8 -> four bf16: 0x4B0000uu is 2^23 + u, u = x + 128; minus (2^23 + 128) leaves x, whose
-// upper 16 bits are its bf16 (|x| <= 128 has at most 8 significant bits)
+// four s8 -> four bf16 without a conversion instruction: with xx = x & 0x7f the bf16 0x43xx is
+// 128 + (x & 127), with xx = x & 0x80 it is 128 or 256; their difference is x, exactly
 __device__ __forceinline__ uint32_t prmt_(uint32_t a, uint32_t b, uint32_t sel) {
     uint32_t r;
     asm("prmt.b32 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(sel));
     return r;
 }
+__device__ __forceinline__ uint32_t bf16x2_sub(uint32_t a, uint32_t b) {
+    uint32_t d;
+    asm("sub.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+    return d;
+}
 __device__ __forceinline__ void s8x4_to_bf16x4(uint32_t w, uint32_t &o0, uint32_t &o1) {
-    const uint32_t x = w ^ 0x80808080u;
-    const float f0 = __uint_as_float(prmt_(x, 0x4B000000u, 0x7540)) - 8388736.f;
-    const float f1 = __uint_as_float(prmt_(x, 0x4B000000u, 0x7541)) - 8388736.f;
-    const float f2 = __uint_as_float(prmt_(x, 0x4B000000u, 0x7542)) - 8388736.f;
-    const float f3 = __uint_as_float(prmt_(x, 0x4B000000u, 0x7543)) - 8388736.f;
-    o0 = prmt_(__float_as_uint(f0), __float_as_uint(f1), 0x7632);
-    o1 = prmt_(__float_as_uint(f2), __float_as_uint(f3), 0x7632);
+    const uint32_t p0 = prmt_(w, 0x43434343u, 0x4140); // [x0, 0x43, x1, 0x43]
+    const uint32_t p1 = prmt_(w, 0x43434343u, 0x4342); // [x2, 0x43, x3, 0x43]
+    o0 = bf16x2_sub(p0 & 0xff7fff7fu, p0 & 0xff80ff80u);
+    o1 = bf16x2_sub(p1 & 0xff7fff7fu, p1 & 0xff80ff80u);
 }
 
 __global__ void __launch_bounds__(G_THREADS, 1)
@@ -113,20 +120,30 @@ grouped_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
     constexpr uint32_t TMEM_COLS = ACC_STAGES * GT_M;
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-    uint64_t *raw_full = (uint64_t *)(smem + G_BAR_OFFSET); // TMA bytes of a stage have landed
-    uint64_t *a_full = raw_full + G_STAGES; // the stage's weights are rewritten as bf16
-    uint64_t *empty_bar = a_full + G_STAGES; // the MMAs have read the stage
-    uint64_t *tmem_full = empty_bar + G_STAGES;
+    uint64_t *raw_full = (uint64_t *)(smem + G_BAR_OFFSET); // raw weight tile has landed
+    uint64_t *raw_empty = raw_full + RAW_STAGES; // the converters have read it
+    uint64_t *b_full = raw_empty + RAW_STAGES; // src rows have landed
+    uint64_t *b_empty = b_full + B_STAGES; // the MMAs have read them
+    uint64_t *a_full = b_empty + B_STAGES; // the weights are rewritten as bf16
+    uint64_t *a_empty = a_full + A_STAGES; // the MMAs have read them
+    uint64_t *tmem_full = a_empty + A_STAGES;
     uint64_t *tmem_empty = tmem_full + ACC_STAGES;
     uint32_t *tmem_base_slot = (uint32_t *)(tmem_empty + ACC_STAGES);
     volatile int *abort_flag = (volatile int *)(tmem_base_slot + 1);
 
     const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
     if (threadIdx.x == 0) {
-        for (int s = 0; s < G_STAGES; ++s) {
+        for (int s = 0; s < RAW_STAGES; ++s) {
             ptx::mbar_init(&raw_full[s], 1);
+            ptx::mbar_init(&raw_empty[s], CONV_WARPS);
+        }
+        for (int s = 0; s < B_STAGES; ++s) {
+            ptx::mbar_init(&b_full[s], 1);
+            ptx::mbar_init(&b_empty[s], 1);
+        }
+        for (int s = 0; s < A_STAGES; ++s) {
             ptx::mbar_init(&a_full[s], CONV_WARPS);
-            ptx::mbar_init(&empty_bar[s], 1);
+            ptx::mbar_init(&a_empty[s], 1);
         }
         for (int s = 0; s < ACC_STAGES; ++s) {
             ptx::mbar_init(&tmem_full[s], 1);
@@ -146,22 +163,35 @@ grouped_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
     const int num_tiles = head.x, groups = head.y;
 
     if (warp == 0) {
-        // ------------------------------------------------ TMA producer
+        // ------------------------------------------------ TMA producer of the raw weight tiles
+        if (lane == 0) {
+            uint32_t it = 0;
+            for (int t = blockIdx.x; t < num_tiles && !*abort_flag; t += gridDim.x) {
+                const Tile tl = decode_tile(plan, groups, num_n_tiles, t);
+                for (int kb = 0; kb < num_k_blocks; ++kb, ++it) {
+                    const int s = it % RAW_STAGES;
+                    const uint32_t ph = (it / RAW_STAGES) & 1;
+                    if (!ptx::mbar_wait(&raw_empty[s], ph ^ 1)) { *abort_flag = 1; atomicExch(a.status, 5); break; }
+                    ptx::mbar_arrive_expect_tx(&raw_full[s], RAW_BYTES);
+                    ptx::tma_load_3d(smem + RAW_OFFSET + s * RAW_BYTES, &tmW, &raw_full[s], tl.n0, kb * GK, tl.g);
+                }
+            }
+        }
+    } else if (warp == 2 + CONV_WARPS + EPI_WARPS) {
+        // ------------------------------------------------ TMA producer of the src rows
         if (lane == 0) {
             uint32_t it = 0;
             for (int t = blockIdx.x; t < num_tiles && !*abort_flag; t += gridDim.x) {
                 const Tile tl = decode_tile(plan, groups, num_n_tiles, t);
                 const int nbox = (tl.rows + 63) / 64; // src boxes of 64 rows
                 for (int kb = 0; kb < num_k_blocks; ++kb, ++it) {
-                    const int s = it % G_STAGES;
-                    const uint32_t ph = (it / G_STAGES) & 1;
-                    if (!ptx::mbar_wait(&empty_bar[s], ph ^ 1)) { *abort_flag = 1; atomicExch(a.status, 5); break; }
-                    uint8_t *st = smem + s * G_STAGE_BYTES;
-                    ptx::mbar_arrive_expect_tx(&raw_full[s], RAW_BYTES + nbox * 64 * GK * 2);
-                    ptx::tma_load_3d(st, &tmW, &raw_full[s], tl.n0, kb * GK, tl.g);
+                    const int s = it % B_STAGES;
+                    const uint32_t ph = (it / B_STAGES) & 1;
+                    if (!ptx::mbar_wait(&b_empty[s], ph ^ 1)) { *abort_flag = 1; atomicExch(a.status, 5); break; }
+                    uint8_t *bt = smem + B_OFFSET + s * B_BYTES;
+                    ptx::mbar_arrive_expect_tx(&b_full[s], nbox * 64 * GK * 2);
                     for (int j = 0; j < nbox; ++j)
-                        ptx::tma_load_2d(st + RAW_BYTES + A_BYTES + j * 64 * GK * 2, &tmS, &raw_full[s], kb * GK,
-                                tl.src_row + 64 * j);
+                        ptx::tma_load_2d(bt + j * 64 * GK * 2, &tmS, &b_full[s], kb * GK, tl.src_row + 64 * j);
                 }
             }
         }
@@ -181,11 +211,15 @@ grouped_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
                 const uint32_t tmem_d = tmem_base + as * GT_M;
                 bool failed = false;
                 for (int kb = 0; kb < num_k_blocks; ++kb, ++it) {
-                    const int s = it % G_STAGES;
-                    const uint32_t ph = (it / G_STAGES) & 1;
-                    if (!ptx::mbar_wait(&raw_full[s], ph) || !ptx::mbar_wait(&a_full[s], ph)) { failed = true; break; }
+                    const int sa_i = it % A_STAGES, sb_i = it % B_STAGES;
+                    if (!ptx::mbar_wait(&a_full[sa_i], (it / A_STAGES) & 1)
+                            || !ptx::mbar_wait(&b_full[sb_i], (it / B_STAGES) & 1)) {
+                        failed = true;
+                        break;
+                    }
                     ptx::tc_fence_after_sync();
-                    const uint32_t sa = ptx::smem_u32(smem + s * G_STAGE_BYTES + RAW_BYTES), sb = sa + A_BYTES;
+                    const uint32_t sa = ptx::smem_u32(smem + A_OFFSET + sa_i * A_BYTES);
+                    const uint32_t sb = ptx::smem_u32(smem + B_OFFSET + sb_i * B_BYTES);
 #pragma unroll
                     for (int kk = 0; kk < GK / 16; ++kk) {
                         // weights MN-major: 16 k-rows of 128 bytes per MMA, 64-column blocks 8 KB apart;
@@ -194,7 +228,9 @@ grouped_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
                         const uint64_t sd = ptx::smem_desc_sw128(sb + kk * 32, 0, 1024);
                         ptx::mma_ss<2>(tmem_d, wd, sd, idesc, (kb | kk) != 0);
                     }
-                    ptx::tc_commit(&empty_bar[s]); // stage reusable once these MMAs have read it
+                    // both tiles are reusable once these MMAs have read them
+                    ptx::tc_commit(&a_empty[sa_i]);
+                    ptx::tc_commit(&b_empty[sb_i]);
                 }
                 if (failed) { *abort_flag = 1; atomicExch(a.status, 5); break; }
                 ptx::tc_commit(&tmem_full[as]); // accumulator complete
@@ -202,21 +238,30 @@ grouped_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
         }
     } else if (warp < 2 + CONV_WARPS) {
         // ------------------------------------------------ converters: s8 tile -> bf16 MMA operand
-        const int ct = threadIdx.x - 64; // 0..127
+        const int ct = threadIdx.x - 64; // 0 .. 32 CONV_WARPS - 1
         const int c = ct & 7; // 16-byte chunk of the raw row: columns 16c .. 16c+15
         const int blk = c >> 2, q = 2 * (c & 3); // 64-column block and 16-byte chunk pair of the bf16 row
+        // A 16-byte store is served a quarter-warp (8 lanes, here one k-row) at a time: the lanes of
+        // block 0 store their even chunk first and those of block 1 their odd one, so that the eight
+        // stores of a quarter-warp fall on eight different 16-byte bank groups.
+        const int q_first = q + blk, q_second = q + 1 - blk;
         uint32_t it = 0;
         bool ok = true;
         for (int t = blockIdx.x; t < num_tiles && ok && !*abort_flag; t += gridDim.x) {
             for (int kb = 0; kb < num_k_blocks; ++kb, ++it) {
-                const int s = it % G_STAGES;
-                const uint32_t ph = (it / G_STAGES) & 1;
-                if (!__all_sync(0xffffffffu, ptx::mbar_wait(&raw_full[s], ph))) { ok = false; break; }
-                const uint8_t *raw = smem + s * G_STAGE_BYTES;
-                uint8_t *at = smem + s * G_STAGE_BYTES + RAW_BYTES + blk * (GK * 128);
+                const int sr = it % RAW_STAGES, sa_i = it % A_STAGES;
+                // the raw tile has landed, and the MMAs have finished with the bf16 slot to overwrite
+                if (!__all_sync(0xffffffffu,
+                            ptx::mbar_wait(&raw_full[sr], (it / RAW_STAGES) & 1)
+                                    && ptx::mbar_wait(&a_empty[sa_i], ((it / A_STAGES) & 1) ^ 1))) {
+                    ok = false;
+                    break;
+                }
+                const uint8_t *raw = smem + RAW_OFFSET + sr * RAW_BYTES;
+                uint8_t *at = smem + A_OFFSET + sa_i * A_BYTES + blk * (GK * 128);
 #pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    const int r = (ct >> 3) + 16 * i; // k-row
+                for (int i = 0; i < 16 / CONV_WARPS; ++i) {
+                    const int r = (ct >> 3) + 4 * CONV_WARPS * i; // k-row
                     const uint4 w = *reinterpret_cast<const uint4 *>(raw + r * 128 + c * 16);
                     uint4 lo, hi;
                     s8x4_to_bf16x4(w.x, lo.x, lo.y);
@@ -224,12 +269,15 @@ grouped_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
                     s8x4_to_bf16x4(w.z, hi.x, hi.y);
                     s8x4_to_bf16x4(w.w, hi.z, hi.w);
                     uint8_t *row = at + r * 128;
-                    *reinterpret_cast<uint4 *>(row + ((q ^ (r & 7)) << 4)) = lo;
-                    *reinterpret_cast<uint4 *>(row + (((q + 1) ^ (r & 7)) << 4)) = hi;
+                    *reinterpret_cast<uint4 *>(row + ((q_first ^ (r & 7)) << 4)) = blk ? hi : lo;
+                    *reinterpret_cast<uint4 *>(row + ((q_second ^ (r & 7)) << 4)) = blk ? lo : hi;
                 }
                 ptx::fence_proxy_async(); // the MMA reads these bytes through the async proxy
                 __syncwarp();
-                if (lane == 0) ptx::mbar_arrive(&a_full[s]);
+                if (lane == 0) {
+                    ptx::mbar_arrive(&a_full[sa_i]);
+                    ptx::mbar_arrive(&raw_empty[sr]);
+                }
             }
         }
         if (!ok) { *abort_flag = 1; atomicExch(a.status, 5); }
