@@ -224,9 +224,11 @@ def run_gpu(args):
         if world == 1:
             return None
         local = dst_t.view(elem).view(p.M, p.N)
+        # the gathered result stays in the collective's blocked layout ([rank][M][N/g] column
+        # slices, [rank][rows][N] expert blocks): no interleaving copy inside the step
         if rows_per_rank is not None:
-            return sharding.gather_rows(local, rows_per_rank)
-        return sharding.gather_columns(local, full.N, world)
+            return sharding.gather_rows_blocked(local, rows_per_rank)
+        return sharding.gather_columns_blocked(local, full.N, world)
 
     def step(i):
         preps[i % len(preps)].execute(strm)
@@ -275,14 +277,15 @@ def run_gpu(args):
 
     # ---- end-to-end: src from pinned host memory, dst back to the host, every step
     src_host = torch.from_numpy(p.src.data.view(np.uint8).reshape(-1).copy()).pin_memory()
-    out_bytes = W.nbytes(full.dst_dt, full.M * full.N) if world > 1 else dst_t.numel()
+    g0 = gather()
+    out_bytes = int(g0.numel() * g0.element_size()) if g0 is not None else dst_t.numel()
     dst_host = torch.empty(out_bytes, dtype=torch.uint8).pin_memory()
     e2e_steps = max(3, min(args.steps, 10))
 
     def e2e_step(i):
         keep["src"].copy_(src_host, non_blocking=True)
         g = step(i)
-        res = dst_t if g is None else g.view(torch.uint8).view(-1)
+        res = dst_t if g is None else g.reshape(-1).view(torch.uint8)
         dst_host[:res.numel()].copy_(res, non_blocking=True)
 
     e2e_step(0)
@@ -320,7 +323,9 @@ def run_gpu(args):
             "warmup": max(3, args.warmup), "ms_per_step": ms_per_step, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": dtype, "data": "synthetic",
             "config": {"workload": wkey,
-                       "kernel": prep.impl, "parallelism": "n-shard x%d + all-gather" % world if world > 1 else "single",
+                       "kernel": prep.impl, "parallelism": ("%s x%d + NCCL all-gather into [rank][M][N/g] blocks"
+                                       % ("expert-shard" if full.offsets is not None else "n-shard", world))
+                       if world > 1 else "single",
                        "l2": "weight copies rotated (3 x %.0f MB)" % (p.wei.data.nbytes / 1e6) if rotate
                              else "working set %.0f MB > 126 MB L2" % (p.algorithmic_bytes() / 1e6),
                        "e2e": "src H2D from pinned memory and dst D2H every step; weights resident"},

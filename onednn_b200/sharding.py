@@ -108,6 +108,37 @@ def gather_columns(local, N, world, dist=None, group=None):
     return torch.cat([out[r, :, :widths[r]] for r in range(world)], dim=1)
 
 
+def gather_columns_blocked(local, N, world, dist=None, group=None):
+    """All-gathers column slices [M, n_r] into the blocked layout [world, M, n_max]
+    (slice r in block r, padded to the widest slice): the collective's own
+    output, without the copy that would interleave the slices into [M, N]."""
+    import torch
+    if world == 1:
+        return local.unsqueeze(0)
+    dist = dist or torch.distributed
+    M = local.shape[0]
+    wmax = max(column_range(N, r, world)[1] - column_range(N, r, world)[0] for r in range(world))
+    send = local if local.shape[1] == wmax else torch.nn.functional.pad(local, (0, wmax - local.shape[1]))
+    flat = torch.empty((world * M, wmax), dtype=local.dtype, device=local.device)
+    dist.all_gather_into_tensor(flat, send.contiguous(), group=group)
+    return flat.view(world, M, wmax)
+
+
+def gather_rows_blocked(local, rows_per_rank, dist=None, group=None):
+    """All-gathers row blocks [m_r, N] into [world, m_max, N] (block r holds
+    rank r's rows, padded to the tallest block)."""
+    import torch
+    world = len(rows_per_rank)
+    if world == 1:
+        return local.unsqueeze(0)
+    dist = dist or torch.distributed
+    mmax = max(rows_per_rank)
+    send = local if local.shape[0] == mmax else torch.nn.functional.pad(local, (0, 0, 0, mmax - local.shape[0]))
+    flat = torch.empty((world * mmax, local.shape[1]), dtype=local.dtype, device=local.device)
+    dist.all_gather_into_tensor(flat, send.contiguous(), group=group)
+    return flat.view(world, mmax, local.shape[1])
+
+
 def gather_rows(local, rows_per_rank, dist=None, group=None):
     """All-gathers row blocks [m_r, N] of different heights into [sum m_r, N]."""
     import torch

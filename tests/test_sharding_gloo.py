@@ -35,9 +35,14 @@ for p in problems:
     got_local = as_f32(local, O.run_port(local))
     if p.offsets is None:
         full = S.gather_columns(got_local, p.N, world)
+        blocks = S.gather_columns_blocked(got_local, p.N, world)  # [rank][M][widest slice]
+        widths = [S.column_range(p.N, r, world)[1] - S.column_range(p.N, r, world)[0] for r in range(world)]
+        assert torch.equal(torch.cat([blocks[r, :, :widths[r]] for r in range(world)], dim=1), full)
     else:
         rows = [S.shard(p, r, world).M for r in range(world)]
         full = S.gather_rows(got_local, rows)
+        blocks = S.gather_rows_blocked(got_local, rows)  # [rank][tallest block][N]
+        assert torch.equal(torch.cat([blocks[r, :rows[r]] for r in range(world)], dim=0), full)
     want = as_f32(p, O.run_port(p))
     assert full.shape == want.shape, (p.name, full.shape, want.shape)
     assert torch.equal(full, want), "%s: sharded result differs on rank %d" % (p.name, rank)
