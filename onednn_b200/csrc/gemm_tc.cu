@@ -41,8 +41,10 @@ namespace {
 constexpr int BT_N = 128; // dst columns per tile = TMEM lanes = UMMA M
 constexpr int BKB = 128; // bytes (= 8-bit elements) of K per stage: one swizzle row
 constexpr int UMMA_K = 32; // K per tcgen05.mma for 8-bit operands
-constexpr int NUM_EPI_WARPS = 8;
-constexpr int NUM_THREADS = 64 + 32 * NUM_EPI_WARPS;
+// Epilogue warps: 8 keep up with the MMAs when the epilogue is scale + bias + store; a post-op chain
+// is latency-bound per element, and 16 warps (at 96 registers) hide a third more of it.
+constexpr int epi_warps(bool chain) { return chain ? 16 : 8; }
+constexpr int num_threads(bool chain) { return 64 + 32 * epi_warps(chain); }
 
 struct TcParams {
     int num_m_tiles, num_n_tiles, num_k_blocks;
@@ -210,31 +212,21 @@ __device__ __forceinline__ void epilogue_rows(const MatmulArgs &a, const TcParam
         if (j < rows) store_typed<DST>(dptr + j * dstep, d[j]);
 }
 
-template <bool INT, bool CHAIN, int DST>
-__device__ __forceinline__ void epilogue_rows_typed(const MatmulArgs &a, const TcParams &tp, const TensorTerms &t,
-        const ColTerms &c, const uint32_t (&r)[32], int64_t m0, int64_t n) {
-    if constexpr (CHAIN) {
-        epilogue_rows<INT, CHAIN, DST, 32>(a, tp, t, c, r, m0, n);
-    } else {
-        epilogue_rows<INT, CHAIN, DST, 32>(a, tp, t, c, r, m0, n);
-    }
-}
-
-template <bool INT, bool CHAIN>
+template <bool INT, bool CHAIN, int R>
 __device__ __forceinline__ void epilogue_rows_any(const MatmulArgs &a, const TcParams &tp, const TensorTerms &t,
-        const ColTerms &c, const uint32_t (&r)[32], int64_t m0, int64_t n) {
+        const ColTerms &c, const uint32_t (&r)[R], int64_t m0, int64_t n) {
     switch (a.dst_dt) {
-        case DT_BF16: epilogue_rows_typed<INT, CHAIN, DT_BF16>(a, tp, t, c, r, m0, n); break;
-        case DT_F32: epilogue_rows_typed<INT, CHAIN, DT_F32>(a, tp, t, c, r, m0, n); break;
-        case DT_S8: epilogue_rows_typed<INT, CHAIN, DT_S8>(a, tp, t, c, r, m0, n); break;
-        case DT_S32: epilogue_rows_typed<INT, CHAIN, DT_S32>(a, tp, t, c, r, m0, n); break;
-        case DT_F16: epilogue_rows_typed<INT, CHAIN, DT_F16>(a, tp, t, c, r, m0, n); break;
-        default: epilogue_rows_typed<INT, CHAIN, DT_U8>(a, tp, t, c, r, m0, n); break;
+        case DT_BF16: epilogue_rows<INT, CHAIN, DT_BF16, R>(a, tp, t, c, r, m0, n); break;
+        case DT_F32: epilogue_rows<INT, CHAIN, DT_F32, R>(a, tp, t, c, r, m0, n); break;
+        case DT_S8: epilogue_rows<INT, CHAIN, DT_S8, R>(a, tp, t, c, r, m0, n); break;
+        case DT_S32: epilogue_rows<INT, CHAIN, DT_S32, R>(a, tp, t, c, r, m0, n); break;
+        case DT_F16: epilogue_rows<INT, CHAIN, DT_F16, R>(a, tp, t, c, r, m0, n); break;
+        default: epilogue_rows<INT, CHAIN, DT_U8, R>(a, tp, t, c, r, m0, n); break;
     }
 }
 
 template <int KIND, int BT_M, int STAGES, bool CHAIN>
-__global__ void __launch_bounds__(NUM_THREADS, 1)
+__global__ void __launch_bounds__(num_threads(CHAIN), 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmS,
         const __grid_constant__ MatmulArgs a, const __grid_constant__ TcParams tp) {
     using L = SmemLayout<BT_M, STAGES>;
@@ -260,7 +252,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
         }
         for (int s = 0; s < ACC_STAGES; ++s) {
             ptx::mbar_init(&tmem_full[s], 1);
-            ptx::mbar_init(&tmem_empty[s], NUM_EPI_WARPS); // one arrival per epilogue warp
+            ptx::mbar_init(&tmem_empty[s], epi_warps(CHAIN)); // one arrival per epilogue warp
         }
         *abort_flag = 0;
         ptx::fence_barrier_init();
@@ -329,7 +321,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
     } else {
         // ------------------------------------------------ epilogue warps
         const int lane_base = (warp % 4) * 32; // TMEM lanes (dst columns) of this warp
-        constexpr int ROWS_PER_WARP = BT_M / (NUM_EPI_WARPS / 4);
+        constexpr int ROWS_PER_WARP = BT_M / (epi_warps(CHAIN) / 4);
         const int row_base = ((warp - 2) / 4) * ROWS_PER_WARP; // its share of the tile's rows
         const TensorTerms tt = load_tensor_terms<INT>(a, tp);
         uint32_t acc_it = 0;
@@ -347,19 +339,38 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
                 if (lane == 0) ptx::mbar_arrive(&tmem_empty[as]);
                 continue;
             }
+            if constexpr (CHAIN) {
+                // With a post-op chain the code of 32 unrolled rows exceeds the instruction cache, so the
+                // rows go through a rolled loop of 8-row pieces (8 independent dependency chains each).
 #pragma unroll 1
-            for (int c = 0; c < ROWS_PER_WARP / 32; ++c) {
-                uint32_t r[32];
-                ptx::tmem_ld_32x32(tmem_base + ((uint32_t)lane_base << 16) + as * BT_M + row_base + c * 32, r);
-                ptx::tmem_ld_wait();
-                if (c == ROWS_PER_WARP / 32 - 1) { // accumulator fully read: hand the buffer back
-                    ptx::tc_fence_before_sync();
-                    __syncwarp();
-                    if (lane == 0) ptx::mbar_arrive(&tmem_empty[as]);
+                for (int c = 0; c < ROWS_PER_WARP / 8; ++c) {
+                    uint32_t r[8];
+                    ptx::tmem_ld_32x8(tmem_base + ((uint32_t)lane_base << 16) + as * BT_M + row_base + c * 8, r);
+                    ptx::tmem_ld_wait();
+                    if (c == ROWS_PER_WARP / 8 - 1) { // accumulator fully read: hand the buffer back
+                        ptx::tc_fence_before_sync();
+                        __syncwarp();
+                        if (lane == 0) ptx::mbar_arrive(&tmem_empty[as]);
+                    }
+                    const int64_t m0 = m_tile + c * 8;
+                    if (tp.mainloop_only == 2) continue; // profiling aid: TMEM reads only
+                    if (m0 < a.M) epilogue_rows_any<INT, CHAIN, 8>(a, tp, tt, ct, r, m0, n);
                 }
-                const int64_t m0 = m_tile + c * 32;
-                if (tp.mainloop_only == 2) continue; // profiling aid: TMEM reads only
-                if (m0 < a.M) epilogue_rows_any<INT, CHAIN>(a, tp, tt, ct, r, m0, n);
+            } else {
+#pragma unroll 1
+                for (int c = 0; c < ROWS_PER_WARP / 32; ++c) {
+                    uint32_t r[32];
+                    ptx::tmem_ld_32x32(tmem_base + ((uint32_t)lane_base << 16) + as * BT_M + row_base + c * 32, r);
+                    ptx::tmem_ld_wait();
+                    if (c == ROWS_PER_WARP / 32 - 1) { // accumulator fully read: hand the buffer back
+                        ptx::tc_fence_before_sync();
+                        __syncwarp();
+                        if (lane == 0) ptx::mbar_arrive(&tmem_empty[as]);
+                    }
+                    const int64_t m0 = m_tile + c * 32;
+                    if (tp.mainloop_only == 2) continue; // profiling aid: TMEM reads only
+                    if (m0 < a.M) epilogue_rows_any<INT, CHAIN, 32>(a, tp, tt, ct, r, m0, n);
+                }
             }
         }
     }
@@ -437,7 +448,7 @@ int launch_cfg(const CUtensorMap &mw, const CUtensorMap &ms, const MatmulArgs &a
     }
     const int tiles = tp.num_m_tiles * tp.num_n_tiles;
     const int grid = tiles < sm_count ? tiles : sm_count;
-    kern<<<grid, NUM_THREADS, L::TOTAL, st>>>(mw, ms, a, tp);
+    kern<<<grid, num_threads(CHAIN), L::TOTAL, st>>>(mw, ms, a, tp);
     count_launch();
     return cudaGetLastError() == cudaSuccess ? 0 : 5;
 }
