@@ -170,6 +170,23 @@ woq_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
     const int lds0 = (2 * tig) * 64 + ((((g >> 1) ^ tig) & 3) << 4) + (g & 1) * 8;
     uint32_t git = 0; // stages consumed so far by this warp (ring position and phase)
     bool ok = true;
+    // Lane 0 requests the first stages of this warp's k sub-range of the segment that starts at
+    // position Ls.  Called before the first segment, and for the following one as soon as the k
+    // loop of a segment ends, so that the loads run under the reduction and the epilogue.
+    auto prefetch_segment = [&](int64_t Ls) {
+        if (lane != 0 || Ls >= L1 || !ok) return;
+        const int nb = (int)(Ls / p.ksteps), kb = (int)(Ls % p.ksteps);
+        const int ke = (int)min((int64_t)p.ksteps, kb + (L1 - Ls));
+        const int sg = ke - kb;
+        const int w0 = kb + (int)((int64_t)sg * pair / PAIRS), w1 = kb + (int)((int64_t)sg * (pair + 1) / PAIRS);
+        const int nst = (w1 - w0 + 1) >> 1;
+        for (int i = 0; i < STAGES && i < nst; ++i) {
+            const int s = (git + i) % STAGES;
+            ptx::mbar_arrive_expect_tx(&full[s], STAGE_BYTES);
+            ptx::tma_load_2d(ring + s * STAGE_BYTES, &tmW, &full[s], nb * (NB / 2) + half * 64, (w0 + 2 * i) * 16);
+        }
+    };
+    prefetch_segment(L);
 
     while (L < L1) {
         const int nblk = (int)(L / p.ksteps), kb = (int)(L % p.ksteps);
@@ -182,13 +199,6 @@ woq_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
         const bool cols_ok = n0 < a.N;
         const int xbyte = nblk * (NB / 2) + half * 64;
 
-        if (lane == 0) {
-            for (int i = 0; i < STAGES && i < nstages; ++i) {
-                const int s = (git + i) % STAGES;
-                ptx::mbar_arrive_expect_tx(&full[s], STAGE_BYTES);
-                ptx::tma_load_2d(ring + s * STAGE_BYTES, &tmW, &full[s], xbyte, (ws0 + 2 * i) * 16);
-            }
-        }
         float acc[8][4];
 #pragma unroll
         for (int t = 0; t < 8; ++t) {
@@ -363,6 +373,8 @@ woq_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
             }
         }
 
+        __syncwarp(); // every lane has read the ring's last stage
+        prefetch_segment(L + seg);
         if (WOQ_ABLATE & 16) { L += seg; continue; }
         // ---- the pairs' totals meet: thread i adds the 8 pairs' float4 of (half, t, lane) = i
         __syncthreads();
