@@ -62,5 +62,16 @@ int main() {
         matmul::primitive_desc pd(eng, src, wei, bias, dst, attr);
         std::cout << "int8_postops " << pd.impl_info_str() << "\n";
     }
+    { // grouped (MoE): bf16 rows of 8 experts concatenated, s8 weights [G, K, N], one scale per (expert, column)
+        const memory::dim G = 8, M = 512, K = 256, N = 384;
+        memory::desc src = memory::desc::grouped({M, K}, dt::bf16, 0, G);
+        memory::desc dst = memory::desc::grouped({M, N}, dt::bf16, 0, G);
+        memory::desc wei({G, K, N}, dt::s8, tag::abc);
+        primitive_attr attr;
+        attr.set_fpmath_mode(fpmath_mode::bf16, true);
+        attr.set_scales_mask(DNNL_ARG_WEIGHTS, (1 << 0) | (1 << 2));
+        matmul::primitive_desc pd(eng, src, wei, dst, attr);
+        std::cout << "grouped " << pd.impl_info_str() << "\n";
+    }
     return 0;
 }

@@ -36,3 +36,4 @@ def test_unchanged_dnnl_hpp_program_builds_and_dispatches(tmp_path):
     assert out["int4"] == "cuda:woq:skinny"
     assert out["int4_last"] == "cuda:ref:any"
     assert out["int8_postops"] == "cuda:tcgen05:int8"
+    assert out["grouped"] == "cuda:tcgen05:grouped"
