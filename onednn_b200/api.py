@@ -21,6 +21,7 @@ _STATUS_NAME = ["success", "out_of_memory", "invalid_arguments", "unimplemented"
 
 # exec-arg ids (dnnl_types.h:2542-2786)
 ARG_SRC, ARG_SRC_1, ARG_DST, ARG_WEIGHTS, ARG_BIAS, ARG_SCRATCHPAD = 1, 2, 17, 33, 41, 80
+SCRATCHPAD_MODE_LIBRARY, SCRATCHPAD_MODE_USER = 0, 1  # dnnl_scratchpad_mode_t
 ARG_ATTR_SCALES, ARG_ATTR_ZERO_POINTS, ARG_ATTR_PRECOMPUTED_REDUCTIONS = 4096, 8192, 512
 
 

@@ -17,8 +17,9 @@ def _md(t: W.QTensor):
 
 
 class Prepared:
-    def __init__(self, p: W.Problem, eng, impl=None):
+    def __init__(self, p: W.Problem, eng, impl=None, user_scratchpad=False):
         self.p, self.eng = p, eng
+        self.user_scratchpad = user_scratchpad
         grouped = p.offsets is not None
         if grouped:
             self.src_md = api.memory.desc.grouped((p.M, p.K), p.src.dt, 0, p.groups)
@@ -59,6 +60,8 @@ class Prepared:
                 self.binary_args[api.ARG_ATTR_MULTIPLE_POST_OP(i) | api.ARG_SRC_1] = e.src1
         if p.post_ops:
             attr.set_post_ops(po)
+        if user_scratchpad:
+            attr.set_scratchpad_mode(api.SCRATCHPAD_MODE_USER)
         self.attr = attr
         self.pd = api.matmul.primitive_desc(eng, self.src_md, self.wei_md, self.dst_md, self.bias_md, attr)
         if impl is not None:
@@ -95,7 +98,21 @@ class Prepared:
             self.args[key] = put(md, [q.data])
         for key, t in self.binary_args.items():
             self.args[key] = put(_md(t), [t.data])
+        self._bind_scratchpad()
         return self
+
+    def _bind_scratchpad(self):
+        """scratchpad_mode::user: the caller provides the buffer the descriptor asks for
+        (a zero-size request needs none); it is filled with a pattern, the library must not
+        rely on its contents."""
+        if not self.user_scratchpad:
+            return
+        md = self.pd.query_md(api.QUERY_EXEC_ARG_MD, api.ARG_SCRATCHPAD)
+        size = md.get_size(0)
+        if size:
+            m = api.memory(md, self.eng)
+            m.write(np.full(size, 0xA5, np.uint8), 0)
+            self.args[api.ARG_SCRATCHPAD] = m
 
     # ---- buffers owned by the caller (device pointers)
     def bind_device(self, ptrs):
@@ -136,9 +153,9 @@ class Prepared:
         return raw.view(W.NP_STORAGE[dt]).reshape(self.p.M, self.p.N)
 
 
-def run_problem(p: W.Problem, eng, strm, impl=None):
+def run_problem(p: W.Problem, eng, strm, impl=None, user_scratchpad=False):
     """Uploads, executes, waits, downloads.  Returns (dst, implementation)."""
-    r = Prepared(p, eng, impl).upload()
+    r = Prepared(p, eng, impl, user_scratchpad).upload()
     r.execute(strm)
     strm.wait()
     return r.download(), r.impl

@@ -214,3 +214,21 @@ def test_deviceless_engine_executes_nothing(host_engine):
     with pytest.raises(api.error) as ei:
         r.upload()
     assert ei.value.status == api.runtime_error
+
+
+def test_user_scratchpad_descriptor(host_engine):
+    """scratchpad_mode::user: the primitive descriptor says how many bytes the caller
+    has to bring; library mode (the default) asks for nothing."""
+    from onednn_b200 import workloads as W
+    from onednn_b200.runner import Prepared
+
+    def size(p, user):
+        r = Prepared(p, host_engine, user_scratchpad=user)
+        return r.pd.query_md(api.QUERY_EXEC_ARG_MD, api.ARG_SCRATCHPAD).get_size(0)
+
+    int4 = W.int4_decode(1, 1024, 512)
+    assert size(int4, False) == 0
+    assert size(int4, True) > 0
+    assert size(W.moe_grouped(40, 128, 64, 4), True) >= 16 * 5  # one int4 record per expert and a header
+    assert size(W.int8_zp(64, 128, 64), True) >= 4 * (64 + 64)  # column and row sums
+    assert size(W.fp8_prefill(64, 128, 64), True) == 0

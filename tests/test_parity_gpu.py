@@ -164,6 +164,30 @@ def test_tcgen05_grouped_matches_oracle(gpu, name):
     assert_parity(got, want, p.dst_dt, name, summation_slack_grouped(p))
 
 
+SCRATCHPAD_CASES = {
+    "int8_zero_points": lambda: _wei_zp(W.int8_zp(200, 272, 176), True),  # column and row sums
+    "int4_split_k": lambda: W.int4_decode(3, 4096, 512),  # partial sums and arrival counters
+    "moe_plan": lambda: W.moe_grouped(96, 256, 128, 8),  # per-expert tile ranges
+    "fp8_none": lambda: W.fp8_prefill(64, 256, 128),  # asks for no scratchpad
+}
+
+
+@pytest.mark.parametrize("name", sorted(SCRATCHPAD_CASES))
+def test_user_scratchpad_gives_the_same_bits(gpu, name):
+    """scratchpad_mode::user (the buffer comes from the caller through DNNL_ARG_SCRATCHPAD,
+    with arbitrary contents) against the default library-owned scratchpad, twice in a row."""
+    from onednn_b200.runner import Prepared
+    eng, strm = gpu
+    p = SCRATCHPAD_CASES[name]()
+    want, impl = run_problem(p, eng, strm)
+    r = Prepared(p, eng, user_scratchpad=True).upload()
+    assert r.impl == impl
+    for _ in range(2):
+        r.execute(strm)
+        strm.wait()
+        assert np.array_equal(r.download(), want), name
+
+
 def test_grouped_bad_offsets_reports_invalid_arguments(gpu):
     """Non-monotone offsets: the reference returns invalid_arguments
     (ref_grouped_gemm.cpp:164-213); here the status surfaces at wait()."""
