@@ -432,10 +432,33 @@ dnnl_status_t grouped_tc_accepts(const dnnl_primitive_desc &pd) {
     return dnnl_success;
 }
 
+// Dense weight decompression on the tensor cores (prefill-sized M): bf16 src x
+// s8 `ab` weights with one scale per tensor or per column; nothing else attached.
+dnnl_status_t dense_woq8_accepts(const dnnl_primitive_desc &pd) {
+    if (ref_dense_accepts(pd) != dnnl_success) return dnnl_unimplemented;
+    const auto &attr = pd.attr;
+    UNIMPL_IF(pd.src.ndims != 2);
+    UNIMPL_IF(pd.src.data_type != dnnl_bf16 || pd.wei.data_type != dnnl_s8);
+    UNIMPL_IF(!one_of(pd.dst.data_type, {dnnl_bf16, dnnl_f16, dnnl_f32}));
+    UNIMPL_IF(!attr.apply_to_int || pd.bias.ndims != 0 || !attr.post_ops.entries.empty());
+    const auto &ws = attr.scale(DNNL_ARG_WEIGHTS);
+    UNIMPL_IF(!ws.set || ws.on_host || (ws.mask != 0 && ws.mask != 2) || ws.group_ndims);
+    UNIMPL_IF(attr.scale(DNNL_ARG_SRC).set || attr.scale(DNNL_ARG_DST).set);
+    UNIMPL_IF(attr.zp(DNNL_ARG_SRC).set || attr.zp(DNNL_ARG_WEIGHTS).set || attr.zp(DNNL_ARG_DST).set);
+    const dnnl_dim_t N = pd.N(), K = pd.K();
+    UNIMPL_IF(N >= (1LL << 31) || K >= (1LL << 31) || pd.M() >= (1LL << 31) || pd.M() < 1);
+    UNIMPL_IF(pd.wei.strides[1] != 1 || pd.wei.strides[0] % 16 != 0 || pd.wei.strides[0] < N);
+    UNIMPL_IF(pd.src.strides[1] != 1 || pd.src.strides[0] % 8 != 0 || pd.dst.strides[1] != 1);
+    return dnnl_success;
+}
+
 dnnl_status_t impl_accepts(const dnnl_primitive_desc &pd, int impl, std::string &name) {
     switch (impl) {
         case IMPL_GROUPED_TC:
-            if (!pd.grouped) return dnnl_unimplemented;
+            if (!pd.grouped) { // the same kernel with the dense problem as its only group
+                name = "cuda:tcgen05:woq8";
+                return dense_woq8_accepts(pd);
+            }
             name = "cuda:tcgen05:grouped";
             return grouped_tc_accepts(pd);
         case IMPL_WOQ_GEMV:
@@ -469,7 +492,8 @@ dnnl_status_t select_impl(dnnl_primitive_desc &pd, int first) {
                 pd.scratch_bytes = woq_skinny_scratch_bytes(
                         pd.N(), pd.K(), pd.engine->sm_count > 0 ? pd.engine->sm_count : 148);
             // the grouped GEMM keeps its per-expert tile ranges there
-            if (i == IMPL_GROUPED_TC) pd.scratch_bytes = grouped_tc_scratch_bytes((int)pd.src.group_count);
+            if (i == IMPL_GROUPED_TC)
+                pd.scratch_bytes = grouped_tc_scratch_bytes(pd.grouped ? (int)pd.src.group_count : 1);
             pd.scratchpad = dnnl_memory_desc();
             if (pd.scratch_bytes && pd.attr.scratchpad_mode == dnnl_scratchpad_mode_user) {
                 pd.scratchpad.ndims = 1;

@@ -78,6 +78,11 @@ __device__ __forceinline__ Tile decode_tile(const int4 *plan, int groups, int nu
 
 __global__ void grouped_plan_kernel(const __grid_constant__ MatmulArgs a, int4 *plan, int num_n_tiles) {
     if (threadIdx.x != 0 || blockIdx.x != 0) return;
+    if (a.group_count == 0) { // a dense problem: one group that owns every row
+        plan[1] = make_int4(0, 0, (int)a.M, 0);
+        plan[0] = make_int4((int)((a.M + GT_M - 1) / GT_M) * num_n_tiles, 1, 0, 0);
+        return;
+    }
     bool bad = false;
     int tiles = 0;
     for (int g = 0; g < a.group_count; ++g) {
@@ -292,7 +297,8 @@ grouped_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
             const int64_t n = tl.n0 + lane_base + lane;
             float scale = 1.f;
             if (a.wei_scale.ptr && n < a.N)
-                scale = load_float(a.wei_scale.dt, a.wei_scale.ptr, (int64_t)tl.g * a.wei_scale.gstride + n);
+                scale = load_float(a.wei_scale.dt, a.wei_scale.ptr,
+                        (int64_t)tl.g * a.wei_scale.gstride + ((a.wei_scale.mask & 2) ? n : 0));
             if (!ptx::mbar_wait(&tmem_full[as], aph)) { *abort_flag = 1; atomicExch(a.status, 5); break; }
             ptx::tc_fence_after_sync();
             const int chunks = (tl.rows + 31) / 32;
@@ -362,13 +368,15 @@ bool grouped_tc_pointers_ok(const MatmulArgs &a) {
 // bf16 src [M, K] (rows of all experts concatenated), s8 weights [G, K, N] with N contiguous, per-(expert, column)
 // weight scales, bf16 / f16 / f32 dst.  `scratch`: grouped_tc_scratch_bytes(group_count) bytes.
 int launch_grouped_tc(const MatmulArgs &a, void *scratch, int sm_count, cudaStream_t st) {
-    if (a.M == 0 || a.N == 0 || a.group_count == 0) return 0;
+    if (a.M == 0 || a.N == 0) return 0;
     encode_tiled_fn enc = grouped_get_encode();
     if (!enc || !scratch) return 5;
     CUtensorMap tw, ts;
-    { // weights as bytes [G][K][N]: raw tile of 64 k x 128 n
-        cuuint64_t dims[3] = {(cuuint64_t)a.N, (cuuint64_t)a.K, (cuuint64_t)a.group_count};
-        cuuint64_t strides[2] = {(cuuint64_t)a.wei_sk, (cuuint64_t)a.wei_sg};
+    { // weights as bytes [G][K][N]: raw tile of 64 k x 128 n; a dense [K][N] matrix is one group
+        const int64_t groups = a.group_count > 0 ? a.group_count : 1;
+        const int64_t group_pitch = a.group_count > 0 ? a.wei_sg : a.K * a.wei_sk;
+        cuuint64_t dims[3] = {(cuuint64_t)a.N, (cuuint64_t)a.K, (cuuint64_t)groups};
+        cuuint64_t strides[2] = {(cuuint64_t)a.wei_sk, (cuuint64_t)group_pitch};
         cuuint32_t box[3] = {GT_N, GK, 1};
         cuuint32_t estr[3] = {1, 1, 1};
         if (enc(&tw, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void *>(a.wei), dims, strides, box, estr,

@@ -164,6 +164,35 @@ def test_tcgen05_grouped_matches_oracle(gpu, name):
     assert_parity(got, want, p.dst_dt, name, summation_slack_grouped(p))
 
 
+def _woq8(M, K, N, per_n=True, dst_dt=W.BF16, seed=31):
+    """bf16 src x s8 weights, one weight scale per column (or per tensor), nothing else."""
+    r = np.random.Generator(np.random.PCG64(seed))
+    sc = r.uniform(0.001, 0.01, (1, N) if per_n else (1,)).astype(np.float32)
+    q = {"wei_scale": W.Quant(sc, W.F32, 2 if per_n else 0)}
+    return W.Problem("woq8", M, N, K, W.QTensor(W.f32_to_bf16(r.standard_normal((M, K), dtype=np.float32)), W.BF16, (M, K)),
+                     W.QTensor(r.integers(-127, 128, (K, N), dtype=np.int8), W.S8, (K, N)), dst_dt, quant=q,
+                     apply_to_int=True, fpmath=1)
+
+
+WOQ8_CASES = {
+    "prefill": lambda: _woq8(300, 512, 384),
+    "tails": lambda: _woq8(77, 200, 176),
+    "one_row": lambda: _woq8(1, 256, 128),
+    "common_scale_f32": lambda: _woq8(130, 128, 256, per_n=False, dst_dt=W.F32),
+}
+
+
+@pytest.mark.parametrize("name", sorted(WOQ8_CASES))
+def test_tcgen05_dense_woq8_matches_oracle(gpu, name):
+    """Dense weight decompression with s8 weights runs the grouped kernel with one group."""
+    eng, strm = gpu
+    p = WOQ8_CASES[name]()
+    want = O.run_port(p)
+    got, impl = run_problem(p, eng, strm)
+    assert impl == "cuda:tcgen05:woq8"
+    assert_parity(got, want, p.dst_dt, name, summation_slack(p))
+
+
 SCRATCHPAD_CASES = {
     "int8_zero_points": lambda: _wei_zp(W.int8_zp(200, 272, 176), True),  # column and row sums
     "int4_split_k": lambda: W.int4_decode(3, 4096, 512),  # partial sums and arrival counters
