@@ -412,13 +412,15 @@ dnnl_status_t woq_accepts(const dnnl_primitive_desc &pd) {
 }
 
 // tcgen05 grouped GEMM: bf16 src rows x s8 weights [G, K, N] (N contiguous)
-// with one weight scale per (expert, column); nothing else attached.
+// with one weight scale per (expert, column); optional bias [G, N] and
+// eltwise / binary post-ops.
 dnnl_status_t grouped_tc_accepts(const dnnl_primitive_desc &pd) {
     if (ref_grouped_accepts(pd) != dnnl_success) return dnnl_unimplemented;
     const auto &attr = pd.attr;
     UNIMPL_IF(pd.src.data_type != dnnl_bf16 || pd.wei.data_type != dnnl_s8);
     UNIMPL_IF(!one_of(pd.dst.data_type, {dnnl_bf16, dnnl_f16, dnnl_f32}));
-    UNIMPL_IF(!attr.apply_to_int || pd.bias.ndims != 0 || !attr.post_ops.entries.empty());
+    UNIMPL_IF(!attr.apply_to_int);
+    for (const auto &e : attr.post_ops.entries) UNIMPL_IF(e.kind != dnnl_eltwise && e.kind != dnnl_binary); // no sum
     const auto &ws = attr.scale(DNNL_ARG_WEIGHTS);
     UNIMPL_IF(!ws.set || ws.on_host || ws.mask != 0b101 || ws.group_ndims);
     UNIMPL_IF(attr.scale(DNNL_ARG_SRC).set || attr.scale(DNNL_ARG_DST).set);
@@ -433,14 +435,16 @@ dnnl_status_t grouped_tc_accepts(const dnnl_primitive_desc &pd) {
 }
 
 // Dense weight decompression on the tensor cores (prefill-sized M): bf16 src x
-// s8 `ab` weights with one scale per tensor or per column; nothing else attached.
+// s8 `ab` weights with one scale per tensor or per column; optional bias and
+// eltwise / binary post-ops.
 dnnl_status_t dense_woq8_accepts(const dnnl_primitive_desc &pd) {
     if (ref_dense_accepts(pd) != dnnl_success) return dnnl_unimplemented;
     const auto &attr = pd.attr;
     UNIMPL_IF(pd.src.ndims != 2);
     UNIMPL_IF(pd.src.data_type != dnnl_bf16 || pd.wei.data_type != dnnl_s8);
     UNIMPL_IF(!one_of(pd.dst.data_type, {dnnl_bf16, dnnl_f16, dnnl_f32}));
-    UNIMPL_IF(!attr.apply_to_int || pd.bias.ndims != 0 || !attr.post_ops.entries.empty());
+    UNIMPL_IF(!attr.apply_to_int);
+    for (const auto &e : attr.post_ops.entries) UNIMPL_IF(e.kind != dnnl_eltwise && e.kind != dnnl_binary); // no sum
     const auto &ws = attr.scale(DNNL_ARG_WEIGHTS);
     UNIMPL_IF(!ws.set || ws.on_host || (ws.mask != 0 && ws.mask != 2) || ws.group_ndims);
     UNIMPL_IF(attr.scale(DNNL_ARG_SRC).set || attr.scale(DNNL_ARG_DST).set);

@@ -315,7 +315,23 @@ grouped_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
                 if (n < a.N) {
                     const int m_hi = min(32, tl.rows - cidx * 32);
                     const int64_t row0 = (int64_t)tl.dst_row + cidx * 32;
-                    if (a.dst_dt == DT_BF16) {
+                    if (a.bias || a.n_po) {
+                        // bias (one row per expert, or the dense problem's own broadcast) and the post-op
+                        // chain, in the reference's order: scale, bias, post-ops, store
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) {
+                            if (j >= m_hi) continue;
+                            const int64_t m = row0 + j;
+                            float d = __fmul_rn(__uint_as_float(r[j]), scale);
+                            if (a.bias)
+                                d = __fadd_rn(d,
+                                        load_float(a.bias_dt, a.bias,
+                                                a.group_count > 0 ? (int64_t)tl.g * a.bias_sg + n
+                                                                  : m * a.bias_sm + n * a.bias_sn));
+                            d = apply_post_ops(a, d, 0.f, m, n, tl.g);
+                            store_float(a.dst_dt, d, a.dst, m * a.dst_sm + n);
+                        }
+                    } else if (a.dst_dt == DT_BF16) {
                         unsigned short *d = (unsigned short *)a.dst + row0 * a.dst_sm + n;
 #pragma unroll
                         for (int j = 0; j < 32; ++j)

@@ -174,7 +174,35 @@ def _woq8(M, K, N, per_n=True, dst_dt=W.BF16, seed=31):
                      apply_to_int=True, fpmath=1)
 
 
+def _woq8_bias_chain():
+    """... with a bf16 bias per column, relu and a multiplication by an f32 column vector (one value per row)."""
+    p = _with_bias_relu(_woq8(150, 256, 256))
+    r = np.random.Generator(np.random.PCG64(12))
+    p.post_ops.append(W.PostOp(W.PO_BINARY, W.BINARY["mul"],
+                               src1=W.QTensor(r.uniform(0.5, 1.5, (p.M, 1)).astype(np.float32), W.F32, (p.M, 1))))
+    return p
+
+
+def _moe_bias_gelu():
+    """Grouped problem with one f32 bias row per expert and gelu_erf."""
+    p = W.moe_grouped(120, 128, 128, 5, sizes=[40, 0, 33, 46, 1])
+    r = np.random.Generator(np.random.PCG64(13))
+    p.bias = W.QTensor(r.standard_normal((5, p.N)).astype(np.float32), W.F32, (5, p.N))
+    p.post_ops.append(W.PostOp(W.PO_ELTWISE, W.ELTWISE["gelu_erf"], 0.0, 0.0, 1.0))
+    return p
+
+
+def test_tcgen05_grouped_bias_and_eltwise(gpu):
+    eng, strm = gpu
+    p = _moe_bias_gelu()
+    want = O.run_port(p)
+    got, impl = run_problem(p, eng, strm)
+    assert impl == "cuda:tcgen05:grouped"
+    assert_parity(got, want, p.dst_dt, p.name, summation_slack_grouped(p))
+
+
 WOQ8_CASES = {
+    "bias_relu_mul": _woq8_bias_chain,
     "prefill": lambda: _woq8(300, 512, 384),
     "tails": lambda: _woq8(77, 200, 176),
     "one_row": lambda: _woq8(1, 256, 128),
