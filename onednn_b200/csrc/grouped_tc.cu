@@ -119,6 +119,7 @@ __device__ __forceinline__ void s8x4_to_bf16x4(uint32_t w, uint32_t &o0, uint32_
     o1 = bf16x2_sub(p1 & 0xff7fff7fu, p1 & 0xff80ff80u);
 }
 
+template <bool EPI_CHAIN>
 __global__ void __launch_bounds__(G_THREADS, 1)
 grouped_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmS,
         const __grid_constant__ MatmulArgs a, const int4 *plan, int num_n_tiles, int num_k_blocks) {
@@ -315,7 +316,7 @@ grouped_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
                 if (n < a.N) {
                     const int m_hi = min(32, tl.rows - cidx * 32);
                     const int64_t row0 = (int64_t)tl.dst_row + cidx * 32;
-                    if (a.bias || a.n_po) {
+                    if constexpr (EPI_CHAIN) {
                         // bias (one row per expert, or the dense problem's own broadcast) and the post-op
                         // chain, in the reference's order: scale, bias, post-ops, store
 #pragma unroll
@@ -417,15 +418,15 @@ int launch_grouped_tc(const MatmulArgs &a, void *scratch, int sm_count, cudaStre
     int4 *plan = (int4 *)scratch;
     grouped_plan_kernel<<<1, 32, 0, st>>>(a, plan, num_n_tiles);
     count_launch();
-    static bool configured = false;
-    if (!configured) {
-        if (cudaFuncSetAttribute(grouped_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, G_SMEM_BYTES)
-                != cudaSuccess)
+    const bool chain = a.bias != nullptr || a.n_po > 0; // epilogue with bias / post-ops: its own instantiation
+    auto kern = chain ? grouped_tc_kernel<true> : grouped_tc_kernel<false>;
+    static bool configured[2] = {false, false};
+    if (!configured[chain]) {
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, G_SMEM_BYTES) != cudaSuccess)
             return 5;
-        configured = true;
+        configured[chain] = true;
     }
-    grouped_tc_kernel<<<sm_count > 0 ? sm_count : 148, G_THREADS, G_SMEM_BYTES, st>>>(
-            tw, ts, a, plan, num_n_tiles, num_k_blocks);
+    kern<<<sm_count > 0 ? sm_count : 148, G_THREADS, G_SMEM_BYTES, st>>>(tw, ts, a, plan, num_n_tiles, num_k_blocks);
     count_launch();
     return cudaGetLastError() == cudaSuccess ? 0 : 5;
 }
