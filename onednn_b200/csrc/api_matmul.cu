@@ -411,6 +411,15 @@ dnnl_status_t woq_accepts(const dnnl_primitive_desc &pd) {
     return dnnl_success;
 }
 
+// weight zero-points the s8-decompression tensor-core kernel handles: one per
+// (expert, column) for grouped problems, one per tensor or per column otherwise
+bool woq_tc_wei_zp_ok(const dnnl_primitive_desc &pd) {
+    const auto &wz = pd.attr.zp(DNNL_ARG_WEIGHTS);
+    if (!wz.set) return true;
+    if (wz.on_host || wz.group_ndims || !one_of(wz.dt, {dnnl_s8, dnnl_u8, dnnl_s32})) return false;
+    return pd.grouped ? wz.mask == 0b101 : (wz.mask == 0 || wz.mask == 2);
+}
+
 // tcgen05 grouped GEMM: bf16 src rows x s8 weights [G, K, N] (N contiguous)
 // with one weight scale per (expert, column); optional bias [G, N] and
 // eltwise / binary post-ops.
@@ -424,7 +433,7 @@ dnnl_status_t grouped_tc_accepts(const dnnl_primitive_desc &pd) {
     const auto &ws = attr.scale(DNNL_ARG_WEIGHTS);
     UNIMPL_IF(!ws.set || ws.on_host || ws.mask != 0b101 || ws.group_ndims);
     UNIMPL_IF(attr.scale(DNNL_ARG_SRC).set || attr.scale(DNNL_ARG_DST).set);
-    UNIMPL_IF(attr.zp(DNNL_ARG_SRC).set || attr.zp(DNNL_ARG_WEIGHTS).set || attr.zp(DNNL_ARG_DST).set);
+    UNIMPL_IF(attr.zp(DNNL_ARG_SRC).set || attr.zp(DNNL_ARG_DST).set || !woq_tc_wei_zp_ok(pd));
     const dnnl_dim_t N = pd.N(), K = pd.K();
     UNIMPL_IF(N >= (1LL << 31) || K >= (1LL << 31) || pd.M() >= (1LL << 31) || pd.src.group_count < 1);
     // TMA: unit inner strides, 16-byte multiples for the others
@@ -448,7 +457,7 @@ dnnl_status_t dense_woq8_accepts(const dnnl_primitive_desc &pd) {
     const auto &ws = attr.scale(DNNL_ARG_WEIGHTS);
     UNIMPL_IF(!ws.set || ws.on_host || (ws.mask != 0 && ws.mask != 2) || ws.group_ndims);
     UNIMPL_IF(attr.scale(DNNL_ARG_SRC).set || attr.scale(DNNL_ARG_DST).set);
-    UNIMPL_IF(attr.zp(DNNL_ARG_SRC).set || attr.zp(DNNL_ARG_WEIGHTS).set || attr.zp(DNNL_ARG_DST).set);
+    UNIMPL_IF(attr.zp(DNNL_ARG_SRC).set || attr.zp(DNNL_ARG_DST).set || !woq_tc_wei_zp_ok(pd));
     const dnnl_dim_t N = pd.N(), K = pd.K();
     UNIMPL_IF(N >= (1LL << 31) || K >= (1LL << 31) || pd.M() >= (1LL << 31) || pd.M() < 1);
     UNIMPL_IF(pd.wei.strides[1] != 1 || pd.wei.strides[0] % 16 != 0 || pd.wei.strides[0] < N);
@@ -497,7 +506,7 @@ dnnl_status_t select_impl(dnnl_primitive_desc &pd, int first) {
                         pd.N(), pd.K(), pd.engine->sm_count > 0 ? pd.engine->sm_count : 148);
             // the grouped GEMM keeps its per-expert tile ranges there
             if (i == IMPL_GROUPED_TC)
-                pd.scratch_bytes = grouped_tc_scratch_bytes(pd.grouped ? (int)pd.src.group_count : 1);
+                pd.scratch_bytes = grouped_tc_scratch_bytes(pd.grouped ? (int)pd.src.group_count : 1, pd.M());
             pd.scratchpad = dnnl_memory_desc();
             if (pd.scratch_bytes && pd.attr.scratchpad_mode == dnnl_scratchpad_mode_user) {
                 pd.scratchpad.ndims = 1;

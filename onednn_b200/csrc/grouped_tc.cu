@@ -119,10 +119,23 @@ __device__ __forceinline__ void s8x4_to_bf16x4(uint32_t w, uint32_t &o0, uint32_
     o1 = bf16x2_sub(p1 & 0xff7fff7fu, p1 & 0xff80ff80u);
 }
 
+// Sum over k of every src row (bf16), one warp per row: the factor of a weight zero-point,
+// sum_k s (w - z) = sum_k s w - z sum_k s.
+__global__ void grouped_rowsum_kernel(const __grid_constant__ MatmulArgs a, float *rowsum) {
+    const int64_t m = (int64_t)blockIdx.x * (blockDim.x / 32) + threadIdx.x / 32;
+    if (m >= a.M) return;
+    const unsigned short *row = (const unsigned short *)a.src + m * a.src_sm;
+    float s = 0.f;
+    for (int64_t k = threadIdx.x % 32; k < a.K; k += 32) s += bf16_bits_to_f32(row[k]);
+    for (int o = 16; o; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    if (threadIdx.x % 32 == 0) rowsum[m] = s;
+}
+
 template <bool EPI_CHAIN>
 __global__ void __launch_bounds__(G_THREADS, 1)
 grouped_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmS,
-        const __grid_constant__ MatmulArgs a, const int4 *plan, int num_n_tiles, int num_k_blocks) {
+        const __grid_constant__ MatmulArgs a, const int4 *plan, const float *rowsum, int num_n_tiles,
+        int num_k_blocks) {
     constexpr uint32_t TMEM_COLS = ACC_STAGES * GT_M;
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -300,6 +313,10 @@ grouped_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
             if (a.wei_scale.ptr && n < a.N)
                 scale = load_float(a.wei_scale.dt, a.wei_scale.ptr,
                         (int64_t)tl.g * a.wei_scale.gstride + ((a.wei_scale.mask & 2) ? n : 0));
+            float zp = 0.f; // weight zero-point of this column (chain epilogue only)
+            if (EPI_CHAIN && a.wei_zp.ptr && n < a.N)
+                zp = (float)load_int(a.wei_zp.dt, a.wei_zp.ptr,
+                        (int64_t)tl.g * a.wei_zp.gstride + ((a.wei_zp.mask & 2) ? n : 0));
             if (!ptx::mbar_wait(&tmem_full[as], aph)) { *abort_flag = 1; atomicExch(a.status, 5); break; }
             ptx::tc_fence_after_sync();
             const int chunks = (tl.rows + 31) / 32;
@@ -323,7 +340,9 @@ grouped_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
                         for (int j = 0; j < 32; ++j) {
                             if (j >= m_hi) continue;
                             const int64_t m = row0 + j;
-                            float d = __fmul_rn(__uint_as_float(r[j]), scale);
+                            float acc = __uint_as_float(r[j]);
+                            if (a.wei_zp.ptr) acc = fmaf(-zp, __ldg(rowsum + tl.src_row + cidx * 32 + j), acc);
+                            float d = __fmul_rn(acc, scale);
                             if (a.bias)
                                 d = __fadd_rn(d,
                                         load_float(a.bias_dt, a.bias,
@@ -376,7 +395,9 @@ encode_tiled_fn grouped_get_encode() {
 
 } // namespace
 
-size_t grouped_tc_scratch_bytes(int groups) { return (size_t)(1 + groups) * sizeof(int4); }
+// plan records, then (256-byte aligned) one f32 row sum per src row
+static size_t plan_bytes(int groups) { return ((size_t)(1 + groups) * sizeof(int4) + 255) / 256 * 256; }
+size_t grouped_tc_scratch_bytes(int groups, int64_t M) { return plan_bytes(groups) + (size_t)M * sizeof(float); }
 
 bool grouped_tc_pointers_ok(const MatmulArgs &a) {
     return (uintptr_t)a.wei % 16 == 0 && (uintptr_t)a.src % 16 == 0 && (uintptr_t)a.dst % 2 == 0;
@@ -418,7 +439,13 @@ int launch_grouped_tc(const MatmulArgs &a, void *scratch, int sm_count, cudaStre
     int4 *plan = (int4 *)scratch;
     grouped_plan_kernel<<<1, 32, 0, st>>>(a, plan, num_n_tiles);
     count_launch();
-    const bool chain = a.bias != nullptr || a.n_po > 0; // epilogue with bias / post-ops: its own instantiation
+    float *rowsum = (float *)((char *)scratch + plan_bytes(a.group_count > 0 ? a.group_count : 1));
+    if (a.wei_zp.ptr) {
+        grouped_rowsum_kernel<<<(unsigned)((a.M + 7) / 8), 256, 0, st>>>(a, rowsum);
+        count_launch();
+    }
+    // epilogue with zero-points / bias / post-ops: its own instantiation
+    const bool chain = a.bias != nullptr || a.n_po > 0 || a.wei_zp.ptr != nullptr;
     auto kern = chain ? grouped_tc_kernel<true> : grouped_tc_kernel<false>;
     static bool configured[2] = {false, false};
     if (!configured[chain]) {
@@ -426,7 +453,7 @@ int launch_grouped_tc(const MatmulArgs &a, void *scratch, int sm_count, cudaStre
             return 5;
         configured[chain] = true;
     }
-    kern<<<sm_count > 0 ? sm_count : 148, G_THREADS, G_SMEM_BYTES, st>>>(tw, ts, a, plan, num_n_tiles, num_k_blocks);
+    kern<<<sm_count > 0 ? sm_count : 148, G_THREADS, G_SMEM_BYTES, st>>>(tw, ts, a, plan, rowsum, num_n_tiles, num_k_blocks);
     count_launch();
     return cudaGetLastError() == cudaSuccess ? 0 : 5;
 }

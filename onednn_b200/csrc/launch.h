@@ -28,9 +28,10 @@ int launch_woq_skinny(const MatmulArgs &a, void *scratch, int sm_count, cudaStre
 size_t woq_skinny_scratch_bytes(int64_t N, int64_t K, int sm_count);
 
 // tcgen05 grouped (MoE) GEMM, bf16 src x s8 weights (grouped_tc.cu).
-// `scratch`: grouped_tc_scratch_bytes(group_count) bytes, no initialisation.
+// `scratch`: grouped_tc_scratch_bytes(group_count, M) bytes, no initialisation
+// (tile ranges per group, and the src row sums that weight zero-points need).
 int launch_grouped_tc(const MatmulArgs &a, void *scratch, int sm_count, cudaStream_t st);
-size_t grouped_tc_scratch_bytes(int groups);
+size_t grouped_tc_scratch_bytes(int groups, int64_t M);
 bool grouped_tc_pointers_ok(const MatmulArgs &a);
 
 } // namespace qmm

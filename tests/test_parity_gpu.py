@@ -192,9 +192,39 @@ def _moe_bias_gelu():
     return p
 
 
-def test_tcgen05_grouped_bias_and_eltwise(gpu):
+def _moe_zero_points(zp_dt=W.S8):
+    """Grouped problem with one weight zero-point per (expert, column), several row blocks in one expert."""
+    p = W.moe_grouped(400, 192, 176, 4, sizes=[150, 0, 249, 1])
+    r = np.random.Generator(np.random.PCG64(14))
+    lo, hi = (0, 9) if zp_dt == W.U8 else (-8, 9)
+    z = r.integers(lo, hi, (p.groups, 1, p.N)).astype({W.S8: np.int8, W.U8: np.uint8, W.S32: np.int32}[zp_dt])
+    p.quant["wei_zp"] = W.Quant(z, zp_dt, 0b101)
+    return p
+
+
+def _woq8_zp(per_n, zp_dt=W.S8):
+    """Dense s8 decompression with a weight zero-point per column (or one for the tensor)."""
+    p = _woq8(200, 320, 208, per_n=per_n)
+    r = np.random.Generator(np.random.PCG64(15))
+    z = r.integers(-8, 9, (1, p.N) if per_n else (1,)).astype({W.S8: np.int8, W.S32: np.int32}[zp_dt])
+    p.quant["wei_zp"] = W.Quant(z, zp_dt, 2 if per_n else 0)
+    return p
+
+
+GROUPED_TC_CHAIN_CASES = {
+    "bias_gelu": _moe_bias_gelu,
+    "zero_points_s8": _moe_zero_points,
+    "zero_points_u8": lambda: _moe_zero_points(W.U8),
+    "zero_points_s32": lambda: _moe_zero_points(W.S32),
+}
+
+
+@pytest.mark.parametrize("name", sorted(GROUPED_TC_CHAIN_CASES))
+def test_tcgen05_grouped_bias_and_eltwise(gpu, name):
+    """Attributes the grouped kernel folds into its epilogue: bias, eltwise, weight zero-points
+    (sum_k s (w - z) = sum_k s w - z sum_k s, the row sums from a pre-kernel)."""
     eng, strm = gpu
-    p = _moe_bias_gelu()
+    p = GROUPED_TC_CHAIN_CASES[name]()
     want = O.run_port(p)
     got, impl = run_problem(p, eng, strm)
     assert impl == "cuda:tcgen05:grouped"
@@ -203,6 +233,8 @@ def test_tcgen05_grouped_bias_and_eltwise(gpu):
 
 WOQ8_CASES = {
     "bias_relu_mul": _woq8_bias_chain,
+    "zero_point_per_column": lambda: _woq8_zp(True),
+    "zero_point_common_s32": lambda: _woq8_zp(False, W.S32),
     "prefill": lambda: _woq8(300, 512, 384),
     "tails": lambda: _woq8(77, 200, 176),
     "one_row": lambda: _woq8(1, 256, 128),

@@ -46,8 +46,9 @@ def summation_slack(p: W.Problem) -> np.ndarray:
     else:
         w = W.to_f32(wraw.reshape(p.K, -1), wdt)
     w = np.abs(w.astype(np.float64))
-    if "wei_zp" in p.quant:
-        w = w + 16.0  # magnitude bound with any 4/8-bit zero-point folded in
+    if "wei_zp" in p.quant:  # magnitude bound with the largest zero-point folded in
+        zq = p.quant["wei_zp"]
+        w = w + max(16.0, float(np.abs(W.to_f32(zq.data, zq.dt)).max(initial=0)))
     mag = s @ w
     for name in ("src_scale", "wei_scale"):
         q = p.quant.get(name)
@@ -72,6 +73,9 @@ def summation_slack_grouped(p: W.Problem) -> np.ndarray:
     q = p.quant.get("wei_scale")
     sc = np.abs(W.to_f32(q.data, q.dt).astype(np.float64)).reshape(p.groups, -1, p.N).max(axis=1) if q is not None \
         else np.ones((p.groups, p.N))
+    zq = p.quant.get("wei_zp")
+    if zq is not None:  # per-(expert, column) zero-points join the magnitude of every term
+        w = w + np.abs(W.to_f32(zq.data, zq.dt).astype(np.float64)).reshape(p.groups, 1, -1)
     mag = np.zeros((p.M, p.N))
     begin = 0
     for g, end in enumerate(p.offsets.astype(np.int64)):
