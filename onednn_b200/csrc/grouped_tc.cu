@@ -4,7 +4,10 @@
 // with f32 accumulation in tensor memory.  The scale multiplies the finished
 // sum, as the reference's grouped implementation does
 // (src/cpu/matmul/ref_grouped_gemm.cpp:312-339); results differ from it only
-// by f32 summation order.
+// by f32 summation order.  A second instantiation of the kernel adds, in the
+// epilogue, the bias, the eltwise / binary post-op chain and weight
+// zero-points: sum_k s (w - z) = sum_k s w - z sum_k s, with the src row sums
+// from a small pre-kernel.
 //
 // The tensor cores take 16-bit operands from shared memory, so the int8
 // weights are widened on the way: TMA brings a raw [64 k x 128 n] s8 tile,
