@@ -225,6 +225,8 @@ typedef enum {
 #define DNNL_ARG_SRC_1 2
 #define DNNL_ARG_SRC_2 3
 #define DNNL_ARG_DST 17
+#define DNNL_ARG_FROM DNNL_ARG_SRC_0
+#define DNNL_ARG_TO DNNL_ARG_DST
 #define DNNL_ARG_WEIGHTS 33
 #define DNNL_ARG_BIAS 41
 #define DNNL_ARG_SCRATCHPAD 80
@@ -418,6 +420,14 @@ dnnl_status_t DNNL_API dnnl_matmul_primitive_desc_create(dnnl_primitive_desc_t *
         dnnl_engine_t engine, const_dnnl_memory_desc_t src_desc, const_dnnl_memory_desc_t weights_desc,
         const_dnnl_memory_desc_t bias_desc, const_dnnl_memory_desc_t dst_desc,
         const_dnnl_primitive_attr_t attr);
+/* dnnl.h:1727 (src/common/reorder.cpp:153-237): both engines must be the same
+ * CUDA engine; plain strided layouts; src / dst scales, src zero-points, a
+ * common dst zero-point and one sum post-op, as the reference's
+ * simple_reorder reference implementations take them
+ * (src/cpu/reorder/simple_reorder.hpp:2168-2679) */
+dnnl_status_t DNNL_API dnnl_reorder_primitive_desc_create(dnnl_primitive_desc_t *reorder_primitive_desc,
+        const_dnnl_memory_desc_t src_desc, dnnl_engine_t src_engine, const_dnnl_memory_desc_t dst_desc,
+        dnnl_engine_t dst_engine, const_dnnl_primitive_attr_t attr);
 dnnl_status_t DNNL_API dnnl_primitive_desc_next_impl(dnnl_primitive_desc_t primitive_desc);
 dnnl_status_t DNNL_API dnnl_primitive_desc_clone(dnnl_primitive_desc_t *primitive_desc,
         const_dnnl_primitive_desc_t existing_primitive_desc);

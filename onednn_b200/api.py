@@ -21,6 +21,7 @@ _STATUS_NAME = ["success", "out_of_memory", "invalid_arguments", "unimplemented"
 
 # exec-arg ids (dnnl_types.h:2542-2786)
 ARG_SRC, ARG_SRC_1, ARG_DST, ARG_WEIGHTS, ARG_BIAS, ARG_SCRATCHPAD = 1, 2, 17, 33, 41, 80
+ARG_FROM, ARG_TO = ARG_SRC, ARG_DST
 SCRATCHPAD_MODE_LIBRARY, SCRATCHPAD_MODE_USER = 0, 1  # dnnl_scratchpad_mode_t
 ARG_ATTR_SCALES, ARG_ATTR_ZERO_POINTS, ARG_ATTR_PRECOMPUTED_REDUCTIONS = 4096, 8192, 512
 
@@ -411,6 +412,20 @@ class matmul:
     def __del__(self):
         if getattr(self, "_h", None) and _lib is not None:
             _lib.dnnl_primitive_destroy(self._h)
+
+
+class reorder(matmul):
+    """dnnl::reorder: ``reorder(reorder.primitive_desc(eng, src_md, eng, dst_md, attr)).execute(strm,
+    {ARG_FROM: src, ARG_TO: dst, ...})``.  Creation, execution and destruction are the primitive's own."""
+
+    class primitive_desc(matmul.primitive_desc):
+        def __init__(self, src_eng, src_md, dst_eng, dst_md, attr=None):
+            self._h = C.c_void_p()
+            self._eng = src_eng
+            _check(lib().dnnl_reorder_primitive_desc_create(
+                C.byref(self._h), src_md._h, src_eng._h, dst_md._h, dst_eng._h,
+                attr._h if attr is not None else None),
+                "could not create a primitive descriptor for a reorder primitive")
 
 
 def launch_count():

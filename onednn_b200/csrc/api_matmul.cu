@@ -605,6 +605,7 @@ dnnl_status_t dnnl_matmul_primitive_desc_create(dnnl_primitive_desc_t *primitive
 
 dnnl_status_t dnnl_primitive_desc_next_impl(dnnl_primitive_desc_t pd) {
     if (!pd) return dnnl_invalid_arguments;
+    if (pd->kind != dnnl_matmul) return dnnl_last_impl_reached; // one reorder implementation
     dnnl_primitive_desc tmp = *pd;
     dnnl_status_t st = select_impl(tmp, pd->impl + 1);
     if (st != dnnl_success) return dnnl_last_impl_reached;
@@ -664,8 +665,10 @@ dnnl_status_t dnnl_primitive_desc_query(const_dnnl_primitive_desc_t pd, dnnl_que
     switch ((int)what) {
         case dnnl_query_engine:
         case dnnl_query_scratchpad_engine: *(dnnl_engine_t *)result = pd->engine; break;
-        case dnnl_query_primitive_kind: *(dnnl_primitive_kind_t *)result = dnnl_matmul; break;
-        case dnnl_query_num_of_inputs_s32: *(int *)result = 2 + (pd->bias.ndims != 0) + n_binary; break;
+        case dnnl_query_primitive_kind: *(dnnl_primitive_kind_t *)result = pd->kind; break;
+        case dnnl_query_num_of_inputs_s32:
+            *(int *)result = pd->kind == dnnl_reorder ? 1 : 2 + (pd->bias.ndims != 0) + n_binary;
+            break;
         case dnnl_query_num_of_outputs_s32: *(int *)result = 1; break;
         case dnnl_query_time_estimate_f64: *(double *)result = 0.0; break;
         case dnnl_query_memory_consumption_s64: *(dnnl_dim_t *)result = 0; break;
@@ -777,6 +780,7 @@ extern "C" dnnl_status_t dnnl_primitive_execute(const_dnnl_primitive_t primitive
     if (stream->engine != pd.engine && stream->engine->device != pd.engine->device) return dnnl_invalid_arguments;
     for (int i = 0; i < nargs; ++i)
         if (!args[i].memory) return dnnl_invalid_arguments;
+    if (pd.kind == dnnl_reorder) return execute_reorder(pd, stream, nargs, args);
     arg_map_t am {args, nargs};
     const auto &attr = pd.attr;
 

@@ -131,6 +131,7 @@ enum impl_id_t : int {
 };
 
 struct dnnl_primitive_desc {
+    dnnl_primitive_kind_t kind = dnnl_matmul; // dnnl_reorder: only src, dst and attr are used
     dnnl_engine_t engine = nullptr;
     dnnl_memory_desc src, wei, bias, dst, scratchpad;
     dnnl_primitive_attr attr;
@@ -158,4 +159,7 @@ bool cuda_ok(cudaError_t e, const char *what);
 int verbose_level();
 size_t dt_bits(dnnl_data_type_t dt);
 size_t md_bytes(const dnnl_memory_desc &md, int index);
+// reorder.cu: enqueues the reorder described by pd on the stream
+dnnl_status_t execute_reorder(const dnnl_primitive_desc &pd, dnnl_stream_t stream, int nargs,
+        const dnnl_exec_arg_t *args);
 } // namespace qmm

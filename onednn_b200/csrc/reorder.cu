@@ -1,0 +1,325 @@
+// dnnl::reorder on the CUDA engine ("cuda:ref:reorder"): a quantizing /
+// dequantizing copy between two plain strided layouts of one logical tensor,
+//   dst = cvt((src_scale * (src - src_zp) [+ beta * dst]) / dst_scale + dst_zp)
+// in the reference's operation order
+// (src/cpu/reorder/simple_reorder.hpp:2621-2676; 4-bit sources :2391-2421,
+// 4-bit targets :2256-2277), so results equal the reference's bit for bit.
+// Descriptor checks follow src/common/reorder.cpp:67-150.
+//
+// One thread per element (per byte for 4-bit targets).  Threads walk the
+// tensor in the order of the dst strides, smallest first, so the stores of a
+// warp are contiguous whatever the src layout is; the work is a single pass
+// over both tensors, bound by HBM for same-order layouts.
+#include <cstdio>
+
+#include "device_math.cuh"
+#include "launch.h"
+#include "objects.hpp"
+
+using namespace qmm;
+
+namespace {
+
+constexpr int RMAX = 6; // tensor dims the kernel handles
+
+struct RQuant {
+    const void *ptr;
+    int dt;
+    int64_t grp[RMAX]; // group size per dim (1 except, possibly, the last two)
+    int64_t str[RMAX]; // stride of the parameter tensor per dim, 0 where the mask bit is clear
+};
+
+struct ReorderArgs {
+    int ndims;
+    int order[RMAX]; // dims from the fastest varying thread index to the slowest
+    int64_t dims[RMAX], sstr[RMAX], dstr[RMAX];
+    int64_t work; // elements, or element pairs for 4-bit targets
+    const void *src;
+    void *dst;
+    int src_dt, dst_dt;
+    RQuant src_scale, dst_scale, src_zp;
+    const int *dst_zp;
+    float beta;
+};
+
+__device__ __forceinline__ int64_t rq_off(const RQuant &q, const int64_t *idx, int ndims) {
+    int64_t off = 0;
+    for (int d = 0; d < ndims; ++d) off += (idx[d] / q.grp[d]) * q.str[d];
+    return off;
+}
+
+__device__ __forceinline__ bool dt_is_int(int dt) { return dt == DT_S32 || dt == DT_S8 || dt == DT_U8; }
+
+__device__ __forceinline__ unsigned quantize_nibble(float v, bool sgn) {
+    v = fminf(fmaxf(v, sgn ? -8.f : 0.f), sgn ? 7.f : 15.f);
+    return (unsigned)__float2int_rn(v) & 0xFu;
+}
+
+__global__ void __launch_bounds__(256) reorder_kernel(const __grid_constant__ ReorderArgs a) {
+    const bool dst4 = a.dst_dt == DT_S4 || a.dst_dt == DT_U4;
+    const bool src4 = a.src_dt == DT_S4 || a.src_dt == DT_U4;
+    const int dst_zp = a.dst_zp ? __ldg(a.dst_zp) : 0;
+    for (int64_t l = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; l < a.work;
+            l += (int64_t)gridDim.x * blockDim.x) {
+        int64_t idx[RMAX], rem = l, i_off = 0, o_off = 0;
+#pragma unroll
+        for (int k = 0; k < RMAX; ++k) {
+            if (k >= a.ndims) break;
+            const int d = a.order[k];
+            int64_t extent = a.dims[d];
+            if (dst4 && k == 0) extent >>= 1; // a thread owns elements (2j, 2j+1) of the innermost dim
+            int64_t i = rem % extent;
+            rem /= extent;
+            if (dst4 && k == 0) i *= 2;
+            idx[d] = i;
+            i_off += i * a.sstr[d];
+            o_off += i * a.dstr[d];
+        }
+        if (dst4) {
+            const int64_t s1 = a.sstr[a.order[0]];
+            const float v0 = ((const float *)a.src)[i_off], v1 = ((const float *)a.src)[i_off + s1];
+            const bool sgn = a.dst_dt == DT_S4;
+            ((unsigned char *)a.dst)[o_off >> 1] = (unsigned char)(quantize_nibble(v0, sgn) | (quantize_nibble(v1, sgn) << 4));
+            continue;
+        }
+        float src_scale = 1.f, dst_scale = 1.f;
+        if (a.src_scale.ptr) src_scale = load_float(a.src_scale.dt, a.src_scale.ptr, rq_off(a.src_scale, idx, a.ndims));
+        if (a.dst_scale.ptr) dst_scale = __ldg((const float *)a.dst_scale.ptr + rq_off(a.dst_scale, idx, a.ndims));
+        int zp = 0;
+        if (a.src_zp.ptr) zp = (int)load_float(a.src_zp.dt, a.src_zp.ptr, rq_off(a.src_zp, idx, a.ndims));
+        // integer sources subtract in integer arithmetic, the others (and 4-bit ones, which the
+        // reference widens to the floating-point dst type first) in float
+        float diff;
+        if (dt_is_int(a.src_dt)) diff = (float)(load_int(a.src_dt, a.src, i_off) - zp);
+        else diff = __fsub_rn(load_float(a.src_dt, a.src, i_off), (float)zp);
+        float d = __fmul_rn(src_scale, diff);
+        if (!src4) {
+            if (a.beta != 0.f) d = __fadd_rn(d, __fmul_rn(a.beta, load_float(a.dst_dt, a.dst, o_off)));
+            d = __fadd_rn(__fdiv_rn(d, dst_scale), (float)dst_zp);
+        }
+        store_float(a.dst_dt, d, a.dst, o_off);
+    }
+}
+
+bool one_of_dt(dnnl_data_type_t v, std::initializer_list<dnnl_data_type_t> l) {
+    for (auto x : l)
+        if (v == x) return true;
+    return false;
+}
+
+bool is_integral(dnnl_data_type_t dt) { return one_of_dt(dt, {dnnl_s32, dnnl_s8, dnnl_u8, dnnl_s4, dnnl_u4}); }
+
+// memory descriptor of a scale / zero-point buffer: the tensor's dims under the mask, the
+// last two divided by the groups, dense row-major (quant_entry_t::get_md,
+// src/common/primitive_attr_quant.hpp:116-140)
+dnnl_memory_desc quant_md(const quant_entry_t &e, const dnnl_memory_desc &t) {
+    dnnl_memory_desc md;
+    md.ndims = t.ndims;
+    md.data_type = e.dt;
+    md.format_kind = dnnl_blocked;
+    for (int d = 0; d < t.ndims; ++d) {
+        dnnl_dim_t g = 1;
+        if (e.group_ndims && t.ndims >= 2 && d == t.ndims - 1) g = e.groups[1];
+        if (e.group_ndims && t.ndims >= 2 && d == t.ndims - 2) g = e.groups[0];
+        md.dims[d] = ((e.mask >> d) & 1) ? t.dims[d] / g : 1;
+    }
+    dnnl_dim_t acc = 1;
+    for (int d = t.ndims - 1; d >= 0; --d) {
+        md.strides[d] = acc;
+        acc *= md.dims[d];
+    }
+    return md;
+}
+
+dnnl_status_t bind_rquant(RQuant &q, const quant_entry_t &e, const dnnl_memory_desc &t, dnnl_memory_t mem) {
+    q = RQuant {};
+    for (int d = 0; d < RMAX; ++d) q.grp[d] = 1;
+    if (!e.set) return dnnl_success;
+    if (!mem || mem->is_host_scalar || !mem->handles[0]) return dnnl_invalid_arguments;
+    const dnnl_memory_desc md = quant_md(e, t);
+    q.ptr = mem->handles[0];
+    q.dt = e.dt;
+    for (int d = 0; d < t.ndims; ++d) {
+        if (e.group_ndims && t.ndims >= 2 && d == t.ndims - 1) q.grp[d] = e.groups[1];
+        if (e.group_ndims && t.ndims >= 2 && d == t.ndims - 2) q.grp[d] = e.groups[0];
+        q.str[d] = ((e.mask >> d) & 1) ? md.strides[d] : 0;
+    }
+    return dnnl_success;
+}
+
+bool plain(const dnnl_memory_desc &md) { return md.format_kind == dnnl_blocked; }
+
+} // namespace
+
+extern "C" dnnl_status_t dnnl_reorder_primitive_desc_create(dnnl_primitive_desc_t *reorder_primitive_desc,
+        const_dnnl_memory_desc_t src_desc, dnnl_engine_t src_engine, const_dnnl_memory_desc_t dst_desc,
+        dnnl_engine_t dst_engine, const_dnnl_primitive_attr_t attr) {
+    if (!reorder_primitive_desc || !src_desc || !src_engine || !dst_desc || !dst_engine) return dnnl_invalid_arguments;
+    // one engine kind here, so a cross-engine reorder can only be between two devices: not provided
+    if (src_engine != dst_engine && src_engine->device != dst_engine->device) return dnnl_unimplemented;
+    if (!plain(*src_desc) || !plain(*dst_desc)) {
+        // format_any is an error, sparse / grouped encodings have no reorder on a GPU engine
+        const bool any = src_desc->format_kind == dnnl_format_kind_any || dst_desc->format_kind == dnnl_format_kind_any;
+        return any ? dnnl_invalid_arguments : dnnl_unimplemented;
+    }
+    const int nd = src_desc->ndims;
+    if (nd != dst_desc->ndims || nd < 1) return dnnl_invalid_arguments;
+    for (int d = 0; d < nd; ++d)
+        if (src_desc->dims[d] != dst_desc->dims[d]) return dnnl_invalid_arguments;
+
+    auto pd = new dnnl_primitive_desc;
+    pd->kind = dnnl_reorder;
+    pd->engine = src_engine;
+    pd->src = *src_desc;
+    pd->dst = *dst_desc;
+    if (attr) pd->attr = *attr;
+    const auto &at = pd->attr;
+    const dnnl_data_type_t si = src_desc->data_type, di = dst_desc->data_type;
+
+    auto fail = [&](dnnl_status_t st) {
+        delete pd;
+        return st;
+    };
+    // src/common/reorder.cpp:95-147
+    if (!is_integral(si) && at.zp(DNNL_ARG_SRC).set) return fail(dnnl_invalid_arguments);
+    if (!is_integral(di) && at.zp(DNNL_ARG_DST).set) return fail(dnnl_invalid_arguments);
+    for (const auto &kv : at.scales)
+        if (kv.first != DNNL_ARG_SRC && kv.first != DNNL_ARG_DST) return fail(dnnl_unimplemented);
+    const quant_entry_t &ss = at.scale(DNNL_ARG_SRC), &ds = at.scale(DNNL_ARG_DST);
+    const quant_entry_t &sz = at.zp(DNNL_ARG_SRC), &dz = at.zp(DNNL_ARG_DST);
+    const bool src4 = si == dnnl_s4 || si == dnnl_u4, dst4 = di == dnnl_s4 || di == dnnl_u4;
+    if (src4 && ss.set && ss.mask == 0) return fail(dnnl_invalid_arguments);
+    for (const quant_entry_t *q : {&ss, &sz}) {
+        if (!q->set || !q->group_ndims) continue;
+        if (nd < 2) return fail(dnnl_invalid_arguments);
+        if ((q->groups[0] > 1 && src_desc->dims[nd - 2] % q->groups[0])
+                || (q->groups[1] > 1 && src_desc->dims[nd - 1] % q->groups[1]))
+            return fail(dnnl_invalid_arguments);
+        if (!((q->mask >> (nd - 1)) & 1) || !((q->mask >> (nd - 2)) & 1)) return fail(dnnl_invalid_arguments);
+    }
+    if (ds.set && ds.group_ndims) return fail(dnnl_invalid_arguments);
+
+    // what the kernel covers (the reference's simple_reorder reference implementations)
+    const std::initializer_list<dnnl_data_type_t> in_types
+            = {dnnl_f32, dnnl_bf16, dnnl_f16, dnnl_s32, dnnl_s8, dnnl_u8, dnnl_f8_e4m3, dnnl_f8_e5m2, dnnl_s4, dnnl_u4};
+    const std::initializer_list<dnnl_data_type_t> out_types
+            = {dnnl_f32, dnnl_bf16, dnnl_f16, dnnl_s32, dnnl_s8, dnnl_u8, dnnl_s4, dnnl_u4};
+    if (nd > RMAX || !one_of_dt(si, in_types) || !one_of_dt(di, out_types)) return fail(dnnl_unimplemented);
+    if (src_desc->offset0 || dst_desc->offset0) return fail(dnnl_unimplemented);
+    for (const quant_entry_t *q : {&ss, &ds, &sz, &dz})
+        if (q->set && q->on_host) return fail(dnnl_unimplemented);
+    if (at.fpmath != dnnl_fpmath_mode_strict || at.apply_to_int || !at.reductions.empty() || !at.rounding.empty())
+        return fail(dnnl_unimplemented);
+    if (ss.set && !one_of_dt(ss.dt, {dnnl_f32, dnnl_bf16, dnnl_f16})) return fail(dnnl_unimplemented);
+    if (ds.set && ds.dt != dnnl_f32) return fail(dnnl_unimplemented);
+    if (sz.set && !is_integral(sz.dt)) return fail(dnnl_unimplemented);
+    if (dz.set && (dz.mask != 0 || dz.dt != dnnl_s32 || dz.group_ndims)) return fail(dnnl_unimplemented);
+    const auto &po = at.post_ops.entries;
+    if (po.size() > 1 || (po.size() == 1 && (po[0].kind != dnnl_sum || po[0].zero_point != 0)))
+        return fail(dnnl_unimplemented);
+    const bool has_sum = po.size() == 1;
+    if (has_sum && po[0].sum_dt != dnnl_data_type_undef && po[0].sum_dt != di) return fail(dnnl_unimplemented);
+    if (dst4) {
+        // plain conversion of f32 into a buffer whose innermost dim is dense and even, so that two
+        // neighbours share a byte no other thread touches
+        if (si != dnnl_f32 || ss.set || ds.set || sz.set || dz.set || has_sum) return fail(dnnl_unimplemented);
+        if (dst_desc->strides[nd - 1] != 1 || dst_desc->dims[nd - 1] % 2) return fail(dnnl_unimplemented);
+        for (int d = 0; d < nd - 1; ++d)
+            if (dst_desc->strides[d] % 2) return fail(dnnl_unimplemented);
+    }
+    if (src4) {
+        if (!one_of_dt(di, {dnnl_f32, dnnl_bf16, dnnl_f16}) || ds.set || dz.set || has_sum) return fail(dnnl_unimplemented);
+    }
+
+    pd->impl = IMPL_REF;
+    pd->impl_name = "cuda:ref:reorder";
+    if (ss.set) pd->quant_mds[DNNL_ARG_ATTR_SCALES | DNNL_ARG_SRC] = quant_md(ss, pd->src);
+    if (ds.set) pd->quant_mds[DNNL_ARG_ATTR_SCALES | DNNL_ARG_DST] = quant_md(ds, pd->src);
+    if (sz.set) pd->quant_mds[DNNL_ARG_ATTR_ZERO_POINTS | DNNL_ARG_SRC] = quant_md(sz, pd->src);
+    if (dz.set) pd->quant_mds[DNNL_ARG_ATTR_ZERO_POINTS | DNNL_ARG_DST] = quant_md(dz, pd->src);
+    *reorder_primitive_desc = pd;
+    return dnnl_success;
+}
+
+dnnl_status_t qmm::execute_reorder(const dnnl_primitive_desc &pd, dnnl_stream_t stream, int nargs,
+        const dnnl_exec_arg_t *args) {
+    auto find = [&](int key) -> dnnl_memory_t {
+        for (int i = 0; i < nargs; ++i)
+            if (args[i].arg == key) return args[i].memory;
+        return nullptr;
+    };
+    dnnl_memory_t src = find(DNNL_ARG_FROM), dst = find(DNNL_ARG_TO);
+    if (!src || !dst) return dnnl_invalid_arguments;
+    const auto &at = pd.attr;
+    ReorderArgs a {};
+    a.ndims = pd.src.ndims;
+    int64_t nelems = 1;
+    for (int d = 0; d < a.ndims; ++d) {
+        a.dims[d] = pd.src.dims[d];
+        a.sstr[d] = pd.src.strides[d];
+        a.dstr[d] = pd.dst.strides[d];
+        a.order[d] = d;
+        nelems *= a.dims[d];
+    }
+    // dims by increasing dst stride (insertion sort; ties keep the later dim first, as row-major does)
+    for (int i = 0; i < a.ndims; ++i) a.order[i] = a.ndims - 1 - i;
+    for (int i = 1; i < a.ndims; ++i)
+        for (int j = i; j > 0 && a.dstr[a.order[j]] < a.dstr[a.order[j - 1]]; --j) {
+            const int t = a.order[j];
+            a.order[j] = a.order[j - 1];
+            a.order[j - 1] = t;
+        }
+    a.src = src->handles[0];
+    a.dst = dst->handles[0];
+    a.src_dt = pd.src.data_type;
+    a.dst_dt = pd.dst.data_type;
+    const bool dst4 = a.dst_dt == DT_S4 || a.dst_dt == DT_U4;
+    a.work = dst4 ? nelems / 2 : nelems;
+    if (nelems == 0) return dnnl_success;
+    if (!a.src || !a.dst) return dnnl_invalid_arguments;
+    dnnl_status_t st;
+    st = bind_rquant(a.src_scale, at.scale(DNNL_ARG_SRC), pd.src, find(DNNL_ARG_ATTR_SCALES | DNNL_ARG_SRC));
+    if (st != dnnl_success) return st;
+    st = bind_rquant(a.dst_scale, at.scale(DNNL_ARG_DST), pd.src, find(DNNL_ARG_ATTR_SCALES | DNNL_ARG_DST));
+    if (st != dnnl_success) return st;
+    st = bind_rquant(a.src_zp, at.zp(DNNL_ARG_SRC), pd.src, find(DNNL_ARG_ATTR_ZERO_POINTS | DNNL_ARG_SRC));
+    if (st != dnnl_success) return st;
+    if (at.zp(DNNL_ARG_DST).set) {
+        dnnl_memory_t m = find(DNNL_ARG_ATTR_ZERO_POINTS | DNNL_ARG_DST);
+        if (!m || m->is_host_scalar || !m->handles[0]) return dnnl_invalid_arguments;
+        a.dst_zp = (const int *)m->handles[0];
+    }
+    if (!at.post_ops.entries.empty()) a.beta = at.post_ops.entries[0].scale;
+    if (pd.engine->device < 0) {
+        set_last_error("a device-less engine cannot execute primitives");
+        return dnnl_runtime_error;
+    }
+    cudaSetDevice(pd.engine->device);
+    const int sms = pd.engine->sm_count > 0 ? pd.engine->sm_count : 148;
+    int64_t blocks = (a.work + 255) / 256;
+    if (blocks > (int64_t)sms * 32) blocks = (int64_t)sms * 32; // grid-stride beyond 32 CTAs per SM
+    cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+    const bool verbose = verbose_level() >= 1;
+    if (verbose) {
+        cudaEventCreate(&ev0); cudaEventCreate(&ev1);
+        cudaEventRecord(ev0, stream->stream);
+    }
+    reorder_kernel<<<(unsigned)blocks, 256, 0, stream->stream>>>(a);
+    count_launch();
+    const bool ok = cudaGetLastError() == cudaSuccess;
+    if (verbose) {
+        cudaEventRecord(ev1, stream->stream);
+        cudaEventSynchronize(ev1);
+        float ms = 0;
+        cudaEventElapsedTime(&ms, ev0, ev1);
+        cudaEventDestroy(ev0); cudaEventDestroy(ev1);
+        printf("onednn_verbose,v1,primitive,exec,gpu,reorder,%s,undef,src:%d dst:%d,,,%lld,%g\n", pd.impl_name.c_str(),
+                a.src_dt, a.dst_dt, (long long)nelems, ms);
+        fflush(stdout);
+    }
+    if (!ok) {
+        set_last_error("kernel launch: reorder");
+        return dnnl_runtime_error;
+    }
+    return dnnl_success;
+}

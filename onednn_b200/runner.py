@@ -153,6 +153,48 @@ class Prepared:
         return raw.view(W.NP_STORAGE[dt]).reshape(self.p.M, self.p.N)
 
 
+def run_reorder(r: W.Reorder, eng, strm):
+    """Runs a :class:`workloads.Reorder` through ``dnnl::reorder``; returns (dst storage, flat and
+    spanning the dst strides, implementation name)."""
+    src_md = _md(r.src)
+    dst_md = api.memory.desc(r.src.dims, r.dst_dt, tuple(r.dst_strides))
+    attr = api.primitive_attr()
+    arg_of = {"src": api.ARG_SRC, "dst": api.ARG_DST}
+    quant_args = {}
+    for name, q in r.quant.items():
+        arg = arg_of[name[:3]]
+        groups = tuple(q.groups) if tuple(q.groups) != (1, 1) else ()
+        if name.endswith("scale"):
+            attr.set_scales(arg, q.mask, groups, q.dt)
+            quant_args[api.ARG_ATTR_SCALES | arg] = q
+        else:
+            attr.set_zero_points(arg, q.mask, groups, q.dt)
+            quant_args[api.ARG_ATTR_ZERO_POINTS | arg] = q
+    if r.beta:
+        po = api.post_ops()
+        po.append_sum(r.beta, 0, 0)
+        attr.set_post_ops(po)
+    pd = api.reorder.primitive_desc(eng, src_md, eng, dst_md, attr)
+
+    def put(md, a):
+        m = api.memory(md, eng)
+        if a.nbytes:
+            m.write(np.ascontiguousarray(a), 0)
+        return m
+
+    args = {api.ARG_FROM: put(src_md, r.src.data)}
+    init = r.dst_init if r.dst_init is not None else np.zeros(dst_md.get_size(0), np.uint8)
+    args[api.ARG_TO] = put(dst_md, init)
+    for key, q in quant_args.items():
+        args[key] = put(pd.query_md(api.QUERY_EXEC_ARG_MD, key), q.data)
+    prim = api.reorder(pd)
+    prim.execute(strm, args)
+    strm.wait()
+    raw = args[api.ARG_TO].read(np.uint8, 0)
+    out = raw if r.dst_dt in (W.S4, W.U4) else raw.view(W.NP_STORAGE[r.dst_dt])
+    return out, pd.impl_info_str()
+
+
 def run_problem(p: W.Problem, eng, strm, impl=None, user_scratchpad=False):
     """Uploads, executes, waits, downloads.  Returns (dst, implementation)."""
     r = Prepared(p, eng, impl, user_scratchpad).upload()

@@ -147,6 +147,28 @@ class Quant:
 
 
 @dataclass
+class Reorder:
+    """One ``dnnl::reorder`` call between two plain (strided) layouts of the
+    same logical tensor: ``src`` carries data, dims and strides; the result has
+    data type ``dst_dt`` and strides ``dst_strides`` (None = row-major)."""
+    name: str
+    src: QTensor
+    dst_dt: int
+    dst_strides: Optional[Tuple[int, ...]] = None
+    quant: Dict[str, Quant] = field(default_factory=dict)  # src_scale, dst_scale, src_zp, dst_zp
+    beta: float = 0.0  # scale of a sum post-op (0 = none)
+    dst_init: Optional[np.ndarray] = None  # dst storage before the call (sum)
+
+    def __post_init__(self):
+        if self.dst_strides is None:
+            self.dst_strides = QTensor(self.src.data, self.src.dt, self.src.dims).strides
+
+    def dst_nelems(self) -> int:
+        """Elements the dst buffer spans (largest offset + 1)."""
+        return 1 + sum((d - 1) * s for d, s in zip(self.src.dims, self.dst_strides))
+
+
+@dataclass
 class PostOp:
     kind: int
     alg: int = 0

@@ -48,6 +48,19 @@ class _Problem(C.Structure):
                 ("wei_sg", C.c_int64), ("bias_sg", C.c_int64), ("fpmath_mode", C.c_int32)]
 
 
+class _RQuant(C.Structure):
+    _fields_ = [("ptr", C.c_void_p), ("dt", C.c_int32), ("mask", C.c_int32),
+                ("g0", C.c_int64), ("g1", C.c_int64)]
+
+
+class _Reorder(C.Structure):
+    _fields_ = [("ndims", C.c_int32), ("dims", C.c_int64 * 6),
+                ("src", C.c_void_p), ("src_dt", C.c_int32), ("src_strides", C.c_int64 * 6),
+                ("dst", C.c_void_p), ("dst_dt", C.c_int32), ("dst_strides", C.c_int64 * 6),
+                ("src_scale", _RQuant), ("dst_scale", _RQuant), ("src_zp", _RQuant), ("dst_zp", _RQuant),
+                ("beta", C.c_float)]
+
+
 _port = None
 _ref = None
 
@@ -60,6 +73,8 @@ def _load_port():
         for f in (_port.qmm_oracle_int8, _port.qmm_oracle_fp, _port.qmm_oracle_grouped):
             f.argtypes = [C.POINTER(_Problem)]
             f.restype = C.c_int
+        _port.qmm_oracle_reorder.argtypes = [C.POINTER(_Reorder)]
+        _port.qmm_oracle_reorder.restype = C.c_int
     return _port
 
 
@@ -74,6 +89,8 @@ def _load_ref():
         _ref.ref_runner_run.argtypes = [C.POINTER(_Problem), C.c_int, C.c_int,
                                         C.POINTER(C.c_double), C.c_char_p, C.c_int]
         _ref.ref_runner_run.restype = C.c_int
+        _ref.ref_runner_reorder.argtypes = [C.POINTER(_Reorder), C.c_char_p, C.c_int]
+        _ref.ref_runner_reorder.restype = C.c_int
     return _ref
 
 
@@ -175,3 +192,55 @@ def run_ref(p: W.Problem, pin_ref=True, iters=0):
     if rc != 0:
         raise RuntimeError("reference status %d: %s" % (rc, name.value.decode()))
     return _view(dst, p), name.value.decode(), (ms.value if iters > 0 else None)
+
+
+def _marshal_reorder(r: W.Reorder):
+    s = _Reorder()
+    nd = len(r.src.dims)
+    s.ndims = nd
+    for i in range(nd):
+        s.dims[i] = r.src.dims[i]
+        s.src_strides[i] = r.src.strides[i]
+        s.dst_strides[i] = r.dst_strides[i]
+    s.src, s.src_dt = _ptr(r.src.data), r.src.dt
+    dst = np.zeros(W.nbytes(r.dst_dt, r.dst_nelems()), np.uint8)
+    if r.dst_init is not None:
+        dst[:] = r.dst_init.view(np.uint8).reshape(-1)
+    s.dst, s.dst_dt = _ptr(dst), r.dst_dt
+    for name in ("src_scale", "dst_scale", "src_zp", "dst_zp"):
+        q = r.quant.get(name)
+        if q is None:
+            continue
+        cq = getattr(s, name)
+        cq.ptr, cq.dt, cq.mask = _ptr(q.data), q.dt, q.mask
+        cq.g0, cq.g1 = q.groups
+    for name in ("src_scale", "dst_scale", "src_zp", "dst_zp"):
+        if r.quant.get(name) is None:
+            getattr(s, name).g0 = getattr(s, name).g1 = 1
+    s.beta = r.beta
+    return s, dst
+
+
+def _view_reorder(dst: np.ndarray, r: W.Reorder):
+    return dst if r.dst_dt in (W.S4, W.U4) else dst.view(W.NP_STORAGE[r.dst_dt])
+
+
+def run_port_reorder(r: W.Reorder) -> np.ndarray:
+    """dst storage (flat, spanning the dst strides) of the C restatement of the reorder."""
+    lib = _load_port()
+    s, dst = _marshal_reorder(r)
+    rc = lib.qmm_oracle_reorder(C.byref(s))
+    if rc != 0:
+        raise RuntimeError("oracle status %d" % rc)
+    return _view_reorder(dst, r)
+
+
+def run_ref_reorder(r: W.Reorder):
+    """(dst storage, implementation name) from the reference library."""
+    lib = _load_ref()
+    s, dst = _marshal_reorder(r)
+    name = C.create_string_buffer(256)
+    rc = lib.ref_runner_reorder(C.byref(s), name, 256)
+    if rc != 0:
+        raise RuntimeError("reference status %d: %s" % (rc, name.value.decode()))
+    return _view_reorder(dst, r), name.value.decode()

@@ -539,3 +539,100 @@ int qmm_oracle_grouped(const qmm_problem_t *p) {
     }
     return 0;
 }
+
+/* ---- reorder -------------------------------------------------------------- */
+
+/* get_quant_off, simple_reorder.hpp:184-201: the parameter tensor has the
+ * data tensor's dims where the mask bit is set and 1 elsewhere, the last two
+ * divided by the groups, dense row-major; a grouped index is idx / group. */
+static int64_t rquant_off(const qmm_rquant_t *q, const qmm_reorder_t *r,
+        const int64_t *idx) {
+    int64_t off = 0;
+    for (int d = 0; d < r->ndims; ++d) {
+        int64_t g = 1;
+        if (r->ndims >= 2 && d == r->ndims - 1) g = q->g1;
+        if (r->ndims >= 2 && d == r->ndims - 2) g = q->g0;
+        int64_t extent = (q->mask >> d) & 1 ? r->dims[d] / g : 1;
+        int64_t i = (q->mask >> d) & 1 ? idx[d] / g : 0;
+        off = off * extent + i;
+    }
+    return off;
+}
+
+static int is_int_dt(int32_t dt) {
+    return dt == QMM_S32 || dt == QMM_S8 || dt == QMM_U8 || dt == QMM_S4
+            || dt == QMM_U4;
+}
+
+static void store_nibble(void *p, int64_t i, float v, int is_signed) {
+    /* saturate_and_round to the 4-bit range, nibble.hpp packing: even element
+     * in the low half of byte i/2 */
+    float lo = is_signed ? -8.f : 0.f, hi = is_signed ? 7.f : 15.f;
+    if (v < lo) v = lo;
+    if (v > hi) v = hi;
+    int q = (int)nearbyintf(v) & 0xF;
+    uint8_t *b = (uint8_t *)p + i / 2;
+    *b = (i % 2) ? (uint8_t)((*b & 0x0F) | (q << 4)) : (uint8_t)((*b & 0xF0) | q);
+}
+
+int qmm_oracle_reorder(const qmm_reorder_t *r) {
+    const int src4 = r->src_dt == QMM_S4 || r->src_dt == QMM_U4;
+    const int dst4 = r->dst_dt == QMM_S4 || r->dst_dt == QMM_U4;
+    if (r->ndims < 1 || r->ndims > QMM_MAX_DIMS) return 2;
+    /* the reference's implementation lists: 4-bit targets only from f32 and
+     * without arithmetic, 4-bit sources only to floating-point types and
+     * without dst scales, dst zero-points or a sum */
+    if (dst4
+            && (r->src_dt != QMM_F32 || r->src_scale.ptr || r->dst_scale.ptr
+                    || r->src_zp.ptr || r->dst_zp.ptr || r->beta != 0.f))
+        return 3;
+    if (src4
+            && ((r->dst_dt != QMM_F32 && r->dst_dt != QMM_BF16
+                        && r->dst_dt != QMM_F16)
+                    || r->dst_scale.ptr || r->dst_zp.ptr || r->beta != 0.f))
+        return 3;
+    int64_t nelems = 1;
+    for (int d = 0; d < r->ndims; ++d) nelems *= r->dims[d];
+    const int32_t dst_zp
+            = r->dst_zp.ptr ? ((const int32_t *)r->dst_zp.ptr)[0] : 0;
+    for (int64_t l = 0; l < nelems; ++l) {
+        int64_t idx[QMM_MAX_DIMS], rem = l, i_off = 0, o_off = 0;
+        for (int d = r->ndims - 1; d >= 0; --d) {
+            idx[d] = rem % r->dims[d];
+            rem /= r->dims[d];
+            i_off += idx[d] * r->src_strides[d];
+            o_off += idx[d] * r->dst_strides[d];
+        }
+        if (dst4) {
+            store_nibble(r->dst, o_off, ((const float *)r->src)[i_off],
+                    r->dst_dt == QMM_S4);
+            continue;
+        }
+        float src_scale = 1.f, dst_scale = 1.f;
+        if (r->src_scale.ptr)
+            src_scale = qmm_load_float(r->src_scale.dt, r->src_scale.ptr,
+                    rquant_off(&r->src_scale, r, idx));
+        if (r->dst_scale.ptr)
+            dst_scale = ((const float *)r->dst_scale.ptr)[rquant_off(
+                    &r->dst_scale, r, idx)];
+        int zp = 0;
+        if (r->src_zp.ptr)
+            zp = (int)qmm_load_float(
+                    r->src_zp.dt, r->src_zp.ptr, rquant_off(&r->src_zp, r, idx));
+        /* input[i_off] - src_zp_val: integer arithmetic for integer sources,
+         * float otherwise (the 4-bit path converts to the float type first) */
+        float diff;
+        if (is_int_dt(r->src_dt) && !src4)
+            diff = (float)(qmm_load_int(r->src_dt, r->src, i_off) - zp);
+        else
+            diff = qmm_load_float(r->src_dt, r->src, i_off) - (float)zp;
+        float d = src_scale * diff;
+        if (!src4) {
+            if (r->beta != 0.f)
+                d += r->beta * qmm_load_float(r->dst_dt, r->dst, o_off);
+            d = d / dst_scale + (float)dst_zp;
+        }
+        qmm_store_float(r->dst_dt, d, r->dst, o_off);
+    }
+    return 0;
+}

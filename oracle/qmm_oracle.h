@@ -106,6 +106,33 @@ int qmm_oracle_fp(const qmm_problem_t *p);
  * arguments) when the offsets are not monotone or exceed M */
 int qmm_oracle_grouped(const qmm_problem_t *p);
 
+/* ---- reorder (quantizing / dequantizing copy between plain layouts) ------- */
+#define QMM_MAX_DIMS 6
+typedef struct {
+    const void *ptr; /* NULL = attribute not set */
+    int32_t dt;
+    int32_t mask; /* bit d set: one value per index of dim d */
+    int64_t g0, g1; /* group sizes along the last two dims (1 = none) */
+} qmm_rquant_t;
+
+typedef struct {
+    int32_t ndims;
+    int64_t dims[QMM_MAX_DIMS];
+    const void *src;
+    int32_t src_dt;
+    int64_t src_strides[QMM_MAX_DIMS]; /* elements */
+    void *dst;
+    int32_t dst_dt;
+    int64_t dst_strides[QMM_MAX_DIMS];
+    qmm_rquant_t src_scale, dst_scale, src_zp, dst_zp;
+    float beta; /* scale of the sum post-op; 0 = no post-op */
+} qmm_reorder_t;
+
+/* simple_reorder.hpp reference implementations (:2168-2281 f32 -> 4-bit,
+ * :2283-2425 4-bit -> float, :2527-2679 everything else).  Returns 3
+ * (unimplemented) for combinations the reference has no implementation of. */
+int qmm_oracle_reorder(const qmm_reorder_t *r);
+
 /* scalar helpers exported for unit tests */
 float qmm_load_float(int32_t dt, const void *ptr, int64_t idx);
 int qmm_load_int(int32_t dt, const void *ptr, int64_t idx);

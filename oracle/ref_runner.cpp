@@ -200,4 +200,61 @@ int ref_runner_run(const qmm_problem_t *p, int pin_ref, int iters,
     }
 }
 
+// Runs a reorder on the reference CPU engine (whatever implementation the
+// library dispatches; the reorder primitive descriptor has no iterator).
+int ref_runner_reorder(const qmm_reorder_t *r, char *impl_name, int impl_len) {
+    try {
+        engine eng(engine::kind::cpu, 0);
+        stream s(eng);
+        dims d(r->dims, r->dims + r->ndims);
+        memory::desc src_md(d, to_dt(r->src_dt), dims(r->src_strides, r->src_strides + r->ndims));
+        memory::desc dst_md(d, to_dt(r->dst_dt), dims(r->dst_strides, r->dst_strides + r->ndims));
+        primitive_attr attr;
+        std::unordered_map<int, memory> args;
+        auto quant = [&](const qmm_rquant_t &q, int arg, bool zp) {
+            if (!q.ptr) return;
+            const bool grouped = q.g0 > 1 || q.g1 > 1;
+            dims groups = grouped ? dims {q.g0, q.g1} : dims {};
+            if (zp) attr.set_zero_points(arg, q.mask, groups, to_dt(q.dt));
+            else attr.set_scales(arg, q.mask, groups, to_dt(q.dt));
+            dims qd(r->ndims, 1);
+            for (int i = 0; i < r->ndims; ++i)
+                if ((q.mask >> i) & 1) qd[i] = r->dims[i];
+            if (r->ndims >= 2) {
+                qd[r->ndims - 1] /= ((q.mask >> (r->ndims - 1)) & 1) ? q.g1 : 1;
+                qd[r->ndims - 2] /= ((q.mask >> (r->ndims - 2)) & 1) ? q.g0 : 1;
+            }
+            dims qs(r->ndims, 1);
+            for (int i = r->ndims - 2; i >= 0; --i) qs[i] = qs[i + 1] * qd[i + 1];
+            memory::desc md(qd, to_dt(q.dt), qs);
+            args.emplace((zp ? DNNL_ARG_ATTR_ZERO_POINTS : DNNL_ARG_ATTR_SCALES) | arg, make_mem(md, eng, q.ptr));
+        };
+        quant(r->src_scale, DNNL_ARG_SRC, false);
+        quant(r->dst_scale, DNNL_ARG_DST, false);
+        quant(r->src_zp, DNNL_ARG_SRC, true);
+        quant(r->dst_zp, DNNL_ARG_DST, true);
+        if (r->beta != 0.f) {
+            post_ops po;
+            po.append_sum(r->beta);
+            attr.set_post_ops(po);
+        }
+        reorder::primitive_desc pd(eng, src_md, eng, dst_md, attr);
+        if (impl_name && impl_len > 0) {
+            std::strncpy(impl_name, pd.impl_info_str(), impl_len - 1);
+            impl_name[impl_len - 1] = 0;
+        }
+        args.emplace(DNNL_ARG_FROM, make_mem(src_md, eng, r->src));
+        args.emplace(DNNL_ARG_TO, make_mem(dst_md, eng, r->dst));
+        reorder(pd).execute(s, args);
+        s.wait();
+        return 0;
+    } catch (const error &e) {
+        if (impl_name && impl_len > 0) {
+            std::strncpy(impl_name, e.message, impl_len - 1);
+            impl_name[impl_len - 1] = 0;
+        }
+        return e.status ? (int)e.status : -1;
+    }
+}
+
 } // extern "C"

@@ -105,5 +105,34 @@ int main() {
         std::printf("f32 %s %s (%d beyond 1e-5)\n", pd.impl_info_str(), wrong ? "FAILED" : "ok", wrong);
         bad += wrong;
     }
+    { // dnnl::reorder: f32 weights -> s8 with one dst scale per column, then back to f32 column-major
+        std::vector<float> wf(K * N);
+        for (auto &x : wf) x = (float)((int)(rng() % 2001) - 1000) / 400.f;
+        memory::desc f_md({K, N}, dt::f32, tag::ab), q_md({K, N}, dt::s8, tag::ab), t_md({K, N}, dt::f32, tag::ba);
+        memory f_m(f_md, eng), q_m(q_md, eng), t_m(t_md, eng), sc_m(memory::desc({N}, dt::f32, tag::x), eng);
+        write_to(f_m, wf);
+        write_to(sc_m, scales);
+        primitive_attr qattr, dattr;
+        qattr.set_scales_mask(DNNL_ARG_DST, 1 << 1);
+        dattr.set_scales_mask(DNNL_ARG_SRC, 1 << 1);
+        reorder::primitive_desc qpd(eng, f_md, eng, q_md, qattr);
+        reorder(qpd).execute(strm, {{DNNL_ARG_FROM, f_m}, {DNNL_ARG_TO, q_m}, {DNNL_ARG_ATTR_SCALES | DNNL_ARG_DST, sc_m}});
+        reorder(reorder::primitive_desc(q_m, t_m, dattr))
+                .execute(strm, {{DNNL_ARG_FROM, q_m}, {DNNL_ARG_TO, t_m}, {DNNL_ARG_ATTR_SCALES | DNNL_ARG_SRC, sc_m}});
+        strm.wait();
+        auto q = read_from<int8_t>(q_m, K * N);
+        auto t = read_from<float>(t_m, K * N);
+        int wrong = 0;
+        for (memory::dim k = 0; k < K; ++k)
+            for (memory::dim n = 0; n < N; ++n) {
+                float d = wf[k * N + n] / scales[n];
+                d = d < -128.f ? -128.f : (d > 127.f ? 127.f : d);
+                const int8_t want = (int8_t)std::nearbyintf(d);
+                wrong += q[k * N + n] != want;
+                wrong += t[n * K + k] != scales[n] * (float)want;
+            }
+        std::printf("reorder %s %s (%d mismatches)\n", qpd.impl_info_str(), wrong ? "FAILED" : "ok", wrong);
+        bad += wrong;
+    }
     return bad ? 1 : 0;
 }

@@ -52,3 +52,4 @@ def test_dnnl_hpp_program_executes_on_the_gpu():
     r = subprocess.run([exe], capture_output=True, text=True, timeout=120)
     assert r.returncode == 0, (r.stdout, r.stderr)
     assert "s32 cuda:tcgen05:int8 ok" in r.stdout and "f32 cuda:tcgen05:int8 ok" in r.stdout, r.stdout
+    assert "reorder cuda:ref:reorder ok" in r.stdout, r.stdout

@@ -1,0 +1,89 @@
+"""dnnl::reorder between plain layouts (tests/reorder_cases.py).
+
+CPU: the C restatement reproduces, bit for bit, the fixtures the reference
+library produced (tests/golden/reorder.npz, made by make_golden_reorder.py)
+and, where that library is built, its live output.  GPU: the CUDA library
+reproduces the restatement bit for bit (element-wise work, one rounding
+sequence: no tolerance)."""
+import os
+
+import numpy as np
+import pytest
+
+from onednn_b200 import workloads as W
+from oracle import oracle as O
+from reorder_cases import CASES
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+GOLDEN = np.load(os.path.join(HERE, "golden", "reorder.npz"))
+
+
+@pytest.mark.parametrize("name", sorted(CASES))
+def test_restatement_matches_the_fixture(name):
+    got = O.run_port_reorder(CASES[name]())
+    assert np.array_equal(got.view(np.uint8).reshape(-1), GOLDEN[name]), \
+        "%s differs from %s" % (name, bytes(GOLDEN[name + "__impl"]).decode())
+
+
+@pytest.mark.parametrize("name", sorted(CASES))
+def test_restatement_matches_the_live_reference(name):
+    if not O.ref_available():
+        pytest.skip("reference library not built")
+    r = CASES[name]()
+    want, impl = O.run_ref_reorder(r)
+    got = O.run_port_reorder(r)
+    assert np.array_equal(got.view(np.uint8), want.view(np.uint8)), "%s: differs from %s" % (name, impl)
+
+
+def test_restatement_rejects_what_the_reference_has_no_implementation_of():
+    r = CASES["compress_f32_to_s4"]()
+    r.quant["dst_scale"] = W.Quant(np.array([0.5], np.float32), W.F32, 0)
+    with pytest.raises(RuntimeError):
+        O.run_port_reorder(r)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("name", sorted(CASES))
+def test_cuda_reorder_matches_oracle(gpu, name):
+    from onednn_b200.runner import run_reorder
+    eng, strm = gpu
+    r = CASES[name]()
+    want = O.run_port_reorder(r)
+    got, impl = run_reorder(r, eng, strm)
+    assert impl == "cuda:ref:reorder"
+    n = want.view(np.uint8).size
+    assert np.array_equal(got.view(np.uint8).reshape(-1)[:n], want.view(np.uint8).reshape(-1)), name
+
+
+@pytest.mark.gpu
+def test_cuda_reorder_feeds_the_matmul(gpu):
+    """The canonical flow: quantize f32 weights to s8 with per-column scales by a reorder, then
+    run the int8 matmul with the same scales; compared with the oracle run on the oracle's
+    own quantized weights."""
+    from onednn_b200.runner import run_problem, run_reorder
+    eng, strm = gpu
+    r = np.random.Generator(np.random.PCG64(77))
+    K, N, M = 256, 128, 64
+    wf = W.QTensor((r.standard_normal((K, N)) * 0.05).astype(np.float32), W.F32, (K, N))
+    sc = (np.abs(wf.data).max(axis=0, keepdims=True) / 127.0).astype(np.float32)
+    ro = W.Reorder("quantize", wf, W.S8, quant={"dst_scale": W.Quant(sc, W.F32, 2)})
+    wq, _ = run_reorder(ro, eng, strm)
+    assert np.array_equal(wq, O.run_port_reorder(ro))
+    p = W.int8_zp(M, K, N, dst_dt=W.F32)
+    p.wei = W.QTensor(wq.reshape(K, N).copy(), W.S8, (K, N))
+    p.quant = {"wei_scale": W.Quant(sc, W.F32, 2)}
+    got, impl = run_problem(p, eng, strm)
+    want = O.run_port(p)
+    assert impl.startswith("cuda:tcgen05:int8"), impl
+    assert np.allclose(got, want, rtol=1e-5, atol=0)
+
+
+def test_reorder_descriptor_checks():
+    """Checks that need no device: creation on a device-less engine is not possible, so only the
+    argument validation that precedes any engine use is exercised through the C ABI."""
+    import ctypes as C
+    from onednn_b200 import api
+    L = api.lib()
+    h = C.c_void_p()
+    # null descriptors / engines: invalid_arguments, as dnnl_reorder_primitive_desc_create returns
+    assert L.dnnl_reorder_primitive_desc_create(C.byref(h), None, None, None, None, None) == api.invalid_arguments
