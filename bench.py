@@ -49,7 +49,7 @@ def parse_args():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--workload", default="fp8_prefill", choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default="fp8_prefill", choices=sorted(WORKLOADS) + ["reorder_quantize"])
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--kernel", default=None, help="pin an implementation by name substring")
     ap.add_argument("--M", type=int, default=None, help="override M (decode: 1, 8 or 32)")
@@ -418,9 +418,154 @@ def run_reference(args):
     print(json.dumps(line), flush=True)
 
 
+# ------------------------------------------ reorder (weight quantization) arm
+def reorder_problem(K, N, seed=20266):
+    """f32 [K,N] -> s8 with one dst scale per column: the quantization of a weight matrix."""
+    r = np.random.Generator(np.random.PCG64(seed))
+    w = (r.standard_normal((K, N), dtype=np.float32) * 0.05)
+    sc = (np.abs(w).max(axis=0, keepdims=True) / 127.0).astype(np.float32)
+    return W.Reorder("reorder_quantize", W.QTensor(w, W.F32, (K, N)), W.S8, quant={"dst_scale": W.Quant(sc, W.F32, 2)})
+
+
+def reorder_cpu(K, N, seconds=10.0):
+    """The reference's CPU reorder on a sample of the rows (wall clock around one call of the
+    reference library through its C++ API, primitive creation included; best of 3)."""
+    from oracle import oracle as O
+    os.environ.setdefault("OMP_NUM_THREADS", str(os.cpu_count() or 1))
+    rows = K  # the whole tensor: a call takes milliseconds
+    r = reorder_problem(rows, N)
+    run = (lambda: O.run_ref_reorder(r)[1]) if O.ref_available() else (lambda: (O.run_port_reorder(r), "oracle port")[1])
+    best, impl, t_all = 1e30, "", time.perf_counter()
+    for _ in range(3):
+        t0 = time.perf_counter()
+        impl = run()
+        best = min(best, time.perf_counter() - t0)
+        if time.perf_counter() - t_all > seconds:
+            break
+    gb = rows * N * 5 / 1e9
+    return {"value": gb / best, "unit": "GB/s", "cores": int(os.environ["OMP_NUM_THREADS"]),
+            "kind": "reference" if O.ref_available() else "port", "impl": impl, "ms": best * 1e3,
+            "sample": "%d of %d rows, N=%d, %.1f ms per call incl. primitive creation" % (rows, K, N, best * 1e3)}
+
+
+def run_reorder_bench(args):
+    K, N = args.K or 4096, args.N or 14336
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    wkey = "reorder_quantize f32[%d,%d] -> s8, per-column dst scales" % (K, N)
+    if args.impl == "reference":
+        if rank == 0:
+            base = reorder_cpu(K, N)
+            print(json.dumps({"impl": "reference", "metric": "reorder_hbm_gbs", "value": base["value"], "unit": "GB/s",
+                              "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": base["ms"],
+                              "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
+                              "data": "synthetic", "config": {"workload": wkey, "sample": base["sample"]},
+                              "cpu_baseline": base,
+                              "e2e": {"value": base["value"], "unit": "GB/s", "h2d_bytes_per_step": 0,
+                                      "d2h_bytes_per_step": 0}}), flush=True)
+        return
+    import torch
+    import torch.distributed as dist
+    from onednn_b200 import api
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    Nl = N // world // 16 * 16 if world > 1 else N  # this rank's columns (a tensor of its own)
+    if world > 1 and rank == world - 1:
+        Nl = N - Nl * (world - 1)
+    eng = api.engine(api.engine.kind.gpu, local_rank)
+    strm = api.stream(eng, torch.cuda.current_stream().cuda_stream)
+    g = torch.Generator(device=dev).manual_seed(20266 + rank)
+    src = torch.randn((K, Nl), generator=g, device=dev, dtype=torch.float32) * 0.05
+    sc = (src.abs().amax(dim=0, keepdim=True) / 127.0).contiguous()
+    dst = torch.zeros((K, Nl), device=dev, dtype=torch.int8)
+    src_md, dst_md = api.memory.desc((K, Nl), W.F32, api.tag.ab), api.memory.desc((K, Nl), W.S8, api.tag.ab)
+    attr = api.primitive_attr()
+    attr.set_scales(api.ARG_DST, 2, (), W.F32)
+    pd = api.reorder.primitive_desc(eng, src_md, eng, dst_md, attr)
+    prim = api.reorder(pd)
+    key = api.ARG_ATTR_SCALES | api.ARG_DST
+    ex_args = {api.ARG_FROM: api.memory(src_md, eng, src.data_ptr()), api.ARG_TO: api.memory(dst_md, eng, dst.data_ptr()),
+               key: api.memory(pd.query_md(api.QUERY_EXEC_ARG_MD, key), eng, sc.data_ptr())}
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(3, args.warmup)):
+        prim.execute(strm, ex_args)
+    barrier()
+    sampler = ClockSampler(local_rank).start() if rank == 0 else None
+    launches0 = api.launch_count()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for _ in range(args.steps):
+        prim.execute(strm, ex_args)
+    e1.record()
+    barrier()
+    launches = api.launch_count() - launches0
+    total_ms = e0.elapsed_time(e1)
+    if sampler:
+        t_end = time.time() + 1.5
+        while time.time() < t_end:
+            for _ in range(20):
+                prim.execute(strm, ex_args)
+            torch.cuda.synchronize()
+    barrier()
+    clocks = sampler.stop() if sampler else None
+    if clocks is not None:
+        clocks["sampled"] = "over the timed region and a 1.5 s untimed repeat of the same step"
+    # end to end: f32 weights from pinned host memory, s8 result back to the host
+    src_host = src.cpu().pin_memory()
+    dst_host = torch.empty((K, Nl), dtype=torch.int8).pin_memory()
+    e2e_steps = max(3, min(args.steps, 10))
+    f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    f0.record()
+    for _ in range(e2e_steps):
+        src.copy_(src_host, non_blocking=True)
+        prim.execute(strm, ex_args)
+        dst_host.copy_(dst, non_blocking=True)
+    f1.record()
+    barrier()
+    e2e_ms = f0.elapsed_time(f1) / e2e_steps
+    t = torch.tensor([total_ms, e2e_ms], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    total_ms, e2e_ms = [float(x) for x in t.tolist()]
+    if rank == 0:
+        pk = peaks()
+        ms = total_ms / args.steps
+        full_gb, launch_gb = (K * N * 5 + N * 4) / 1e9, (K * Nl * 5 + Nl * 4) / 1e9
+        line = {"metric": "reorder_hbm_gbs", "value": full_gb / (ms * 1e-3), "unit": "GB/s", "n_gpus": world,
+                "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms, "higher_is_better": True,
+                "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+                "config": {"workload": wkey, "kernel": pd.impl_info_str(),
+                           "parallelism": "column blocks, one tensor per rank, no collective" if world > 1 else "single",
+                           "l2": "working set %.0f MB > 126 MB L2" % (launch_gb * 1e3),
+                           "e2e": "f32 src H2D from pinned memory and s8 dst D2H every step"},
+                "roofline": {"bound": "hbm", "achieved": launch_gb / (ms * 1e-3), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                             "frac": launch_gb / (ms * 1e-3) / pk["hbm_gbs"], "traffic": dram_traffic(wkey, world),
+                             "algorithmic_bytes": int(launch_gb * 1e9), "peak_source": pk["source"], "kernel_ms": ms},
+                "e2e": {"value": full_gb / (e2e_ms * 1e-3), "unit": "GB/s", "h2d_bytes_per_step": int(K * Nl * 4),
+                        "d2h_bytes_per_step": int(K * Nl), "ms_per_step": e2e_ms},
+                "gpu_launches": int(launches), "clocks": clocks}
+        if world == 1 and not args.no_cpu_baseline:
+            line["cpu_baseline"] = reorder_cpu(K, N)
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
 if __name__ == "__main__":
     a = parse_args()
-    if a.impl == "reference":
+    if a.workload == "reorder_quantize":
+        run_reorder_bench(a)
+    elif a.impl == "reference":
         run_reference(a)
     else:
         run_gpu(a)

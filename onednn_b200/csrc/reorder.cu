@@ -9,7 +9,9 @@
 // One thread per element (per byte for 4-bit targets).  Threads walk the
 // tensor in the order of the dst strides, smallest first, so the stores of a
 // warp are contiguous whatever the src layout is; the work is a single pass
-// over both tensors, bound by HBM for same-order layouts.
+// over both tensors, bound by HBM.  When both tensors are dense in the same
+// dim order (the quantization of weights and activations before a matmul) a
+// thread takes four neighbours with 16-byte loads and one packed store.
 #include <cstdio>
 
 #include "device_math.cuh"
@@ -34,6 +36,7 @@ struct ReorderArgs {
     int order[RMAX]; // dims from the fastest varying thread index to the slowest
     int64_t dims[RMAX], sstr[RMAX], dstr[RMAX];
     int64_t work; // elements, or element pairs for 4-bit targets
+    int tx; // dense kernel: column chunks per CTA row
     const void *src;
     void *dst;
     int src_dt, dst_dt;
@@ -98,6 +101,215 @@ __global__ void __launch_bounds__(256) reorder_kernel(const __grid_constant__ Re
             d = __fadd_rn(__fdiv_rn(d, dst_scale), (float)dst_zp);
         }
         store_float(a.dst_dt, d, a.dst, o_off);
+    }
+}
+
+// ---- both tensors dense in the same dim order: four neighbours per thread, 16-byte accesses
+// elements off .. off+3 (off a multiple of 4) as floats, and as ints for integer types
+__device__ __forceinline__ void load4(int dt, const void *p, int64_t off, float (&f)[4], int (&iv)[4]) {
+    if (dt == DT_F32) {
+        const float4 v = __ldg((const float4 *)p + (off >> 2));
+        f[0] = v.x; f[1] = v.y; f[2] = v.z; f[3] = v.w;
+    } else if (dt == DT_S32) {
+        const int4 v = __ldg((const int4 *)p + (off >> 2));
+        iv[0] = v.x; iv[1] = v.y; iv[2] = v.z; iv[3] = v.w;
+    } else if (dt == DT_BF16 || dt == DT_F16) {
+        const uint2 v = __ldg((const uint2 *)p + (off >> 2));
+        const unsigned short h[4] = {(unsigned short)(v.x & 0xffffu), (unsigned short)(v.x >> 16),
+                (unsigned short)(v.y & 0xffffu), (unsigned short)(v.y >> 16)};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) f[e] = dt == DT_BF16 ? bf16_bits_to_f32(h[e]) : __half2float(__ushort_as_half(h[e]));
+    } else {
+        const unsigned v = __ldg((const unsigned *)p + (off >> 2));
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const unsigned b = (v >> (8 * e)) & 0xffu;
+            if (dt == DT_S8) iv[e] = (int)(signed char)b;
+            else if (dt == DT_U8) iv[e] = (int)b;
+            else f[e] = dt == DT_F8_E4M3 ? e4m3_to_f32((unsigned char)b) : e5m2_to_f32((unsigned char)b);
+        }
+    }
+}
+
+__device__ __forceinline__ void store4(int dt, const float (&d)[4], void *p, int64_t off) {
+    if (dt == DT_F32) {
+        ((float4 *)p)[off >> 2] = make_float4(d[0], d[1], d[2], d[3]);
+    } else if (dt == DT_S32) {
+        int q[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const float v = fminf(fmaxf(d[e], -2147483648.f), 2147483520.f);
+            q[e] = (v != v) ? (int)0x80000000 : __float2int_rn(v);
+        }
+        ((int4 *)p)[off >> 2] = make_int4(q[0], q[1], q[2], q[3]);
+    } else if (dt == DT_BF16 || dt == DT_F16) {
+        unsigned h[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e)
+            h[e] = dt == DT_BF16 ? (unsigned)f32_to_bf16_bits(d[e]) : (unsigned)__half_as_ushort(__float2half_rn(d[e]));
+        ((uint2 *)p)[off >> 2] = make_uint2(h[0] | (h[1] << 16), h[2] | (h[3] << 16));
+    } else {
+        unsigned w = 0;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const float v = dt == DT_S8 ? fminf(fmaxf(d[e], -128.f), 127.f) : fminf(fmaxf(d[e], 0.f), 255.f);
+            w |= ((unsigned)__float2int_rn(v) & 0xffu) << (8 * e);
+        }
+        ((unsigned *)p)[off >> 2] = w;
+    }
+}
+
+__global__ void __launch_bounds__(256) reorder_dense4_kernel(const __grid_constant__ ReorderArgs a) {
+    // A thread keeps its four columns (indices i0 .. i0+3 of the contiguous dim d0) and walks over
+    // the rows (all other dims collapsed): parameters that vary only along d0 -- per-column scales,
+    // the usual case -- are loaded once, and no index is decomposed inside the loop.
+    const int dst_zp = a.dst_zp ? __ldg(a.dst_zp) : 0;
+    const int d0 = a.order[0];
+    const int64_t cols = a.dims[d0], rows = a.work * 4 / cols;
+    // a CTA is tx column chunks wide and 256 / tx rows high (tx a power of two, narrow tensors get tall CTAs)
+    const int tx = a.tx, ty = 256 / tx;
+    const int64_t i0 = ((int64_t)blockIdx.x * tx + threadIdx.x % tx) * 4;
+    if (i0 >= cols) return;
+    int64_t c_ss[4], c_ds[4], c_sz[4]; // parameter offsets contributed by the column
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+        c_ss[e] = ((i0 + e) / a.src_scale.grp[d0]) * a.src_scale.str[d0];
+        c_ds[e] = ((i0 + e) / a.dst_scale.grp[d0]) * a.dst_scale.str[d0];
+        c_sz[e] = ((i0 + e) / a.src_zp.grp[d0]) * a.src_zp.str[d0];
+    }
+    bool outer = false; // does a parameter vary along another dim than d0?
+    for (int k = 1; k < a.ndims; ++k) {
+        const int d = a.order[k];
+        outer |= a.src_scale.str[d] != 0 || a.dst_scale.str[d] != 0 || a.src_zp.str[d] != 0;
+    }
+    float ss[4], ds[4];
+    int zps[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+        ss[e] = (a.src_scale.ptr && !outer) ? load_float(a.src_scale.dt, a.src_scale.ptr, c_ss[e]) : 1.f;
+        ds[e] = (a.dst_scale.ptr && !outer) ? __ldg((const float *)a.dst_scale.ptr + c_ds[e]) : 1.f;
+        zps[e] = (a.src_zp.ptr && !outer) ? (int)load_float(a.src_zp.dt, a.src_zp.ptr, c_sz[e]) : 0;
+    }
+#pragma unroll 2
+    for (int64_t r = (int64_t)blockIdx.y * ty + threadIdx.x / tx; r < rows; r += (int64_t)gridDim.y * ty) {
+        const int64_t off = r * cols + i0;
+        int64_t o_ss = 0, o_ds = 0, o_sz = 0; // parameter offsets contributed by the row
+        if (outer) {
+            int64_t rem = r;
+#pragma unroll
+            for (int k = 1; k < RMAX; ++k) {
+                if (k >= a.ndims) break;
+                const int d = a.order[k];
+                const int64_t i = rem % a.dims[d];
+                rem /= a.dims[d];
+                o_ss += (i / a.src_scale.grp[d]) * a.src_scale.str[d];
+                o_ds += (i / a.dst_scale.grp[d]) * a.dst_scale.str[d];
+                o_sz += (i / a.src_zp.grp[d]) * a.src_zp.str[d];
+            }
+        }
+        float f[4], old[4], out[4];
+        int iv[4], unused[4];
+        load4(a.src_dt, a.src, off, f, iv);
+        if (a.beta != 0.f) {
+            load4(a.dst_dt, a.dst, off, old, unused);
+            if (dt_is_int(a.dst_dt))
+#pragma unroll
+                for (int e = 0; e < 4; ++e) old[e] = (float)unused[e];
+        }
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            float src_scale = ss[e], dst_scale = ds[e];
+            int zp = zps[e];
+            if (outer) {
+                if (a.src_scale.ptr) src_scale = load_float(a.src_scale.dt, a.src_scale.ptr, o_ss + c_ss[e]);
+                if (a.dst_scale.ptr) dst_scale = __ldg((const float *)a.dst_scale.ptr + o_ds + c_ds[e]);
+                if (a.src_zp.ptr) zp = (int)load_float(a.src_zp.dt, a.src_zp.ptr, o_sz + c_sz[e]);
+            }
+            const float diff = dt_is_int(a.src_dt) ? (float)(iv[e] - zp) : __fsub_rn(f[e], (float)zp);
+            float d = __fmul_rn(src_scale, diff);
+            if (a.beta != 0.f) d = __fadd_rn(d, __fmul_rn(a.beta, old[e]));
+            if (a.dst_scale.ptr) d = __fdiv_rn(d, dst_scale); // x / 1 = x: skipped without dst scales
+            out[e] = __fadd_rn(d, (float)dst_zp);
+        }
+        store4(a.dst_dt, out, a.dst, off);
+    }
+}
+
+// The same walk with the data types known at compile time, for reorders whose parameters vary only
+// along the contiguous dim and that have no sum: four rows in flight per thread, conversions
+// without run-time type switches.  This is the quantization / dequantization of a weight or
+// activation matrix with per-tensor or per-column parameters.
+template <int SDT, int DDT>
+__global__ void __launch_bounds__(256) reorder_cols4_kernel(const __grid_constant__ ReorderArgs a) {
+    const int dst_zp = a.dst_zp ? __ldg(a.dst_zp) : 0;
+    const int d0 = a.order[0];
+    const int64_t cols = a.dims[d0], rows = a.work * 4 / cols;
+    const int tx = a.tx, ty = 256 / tx;
+    const int64_t i0 = ((int64_t)blockIdx.x * tx + threadIdx.x % tx) * 4;
+    if (i0 >= cols) return;
+    float ss[4], ds[4];
+    int zps[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+        ss[e] = a.src_scale.ptr ? load_float(a.src_scale.dt, a.src_scale.ptr,
+                                          ((i0 + e) / a.src_scale.grp[d0]) * a.src_scale.str[d0])
+                                : 1.f;
+        ds[e] = a.dst_scale.ptr ? __ldg((const float *)a.dst_scale.ptr + ((i0 + e) / a.dst_scale.grp[d0]) * a.dst_scale.str[d0])
+                                : 1.f;
+        zps[e] = a.src_zp.ptr ? (int)load_float(a.src_zp.dt, a.src_zp.ptr, ((i0 + e) / a.src_zp.grp[d0]) * a.src_zp.str[d0])
+                              : 0;
+    }
+    const bool has_ds = a.dst_scale.ptr != nullptr;
+    auto convert = [&](const float (&f)[4], const int (&iv)[4], int64_t off) {
+        float out[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const float diff = dt_is_int(SDT) ? (float)(iv[e] - zps[e]) : __fsub_rn(f[e], (float)zps[e]);
+            float d = __fmul_rn(ss[e], diff);
+            if (has_ds) d = __fdiv_rn(d, ds[e]);
+            out[e] = __fadd_rn(d, (float)dst_zp);
+        }
+        store4(DDT, out, a.dst, off);
+    };
+    const int64_t step = (int64_t)gridDim.y * ty;
+    int64_t r = (int64_t)blockIdx.y * ty + threadIdx.x / tx;
+    for (; r + 3 * step < rows; r += 4 * step) {
+        float f[4][4];
+        int iv[4][4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) load4(SDT, a.src, (r + u * step) * cols + i0, f[u], iv[u]);
+#pragma unroll
+        for (int u = 0; u < 4; ++u) convert(f[u], iv[u], (r + u * step) * cols + i0);
+    }
+    for (; r < rows; r += step) {
+        float f[4];
+        int iv[4];
+        load4(SDT, a.src, r * cols + i0, f, iv);
+        convert(f, iv, r * cols + i0);
+    }
+}
+
+typedef void (*reorder_kernel_fn)(const ReorderArgs);
+
+template <int SDT>
+reorder_kernel_fn cols4_for_dst(int ddt) {
+    switch (ddt) {
+        case DT_F32: return reorder_cols4_kernel<SDT, DT_F32>;
+        case DT_BF16: return reorder_cols4_kernel<SDT, DT_BF16>;
+        case DT_F16: return reorder_cols4_kernel<SDT, DT_F16>;
+        case DT_S8: return reorder_cols4_kernel<SDT, DT_S8>;
+        case DT_U8: return reorder_cols4_kernel<SDT, DT_U8>;
+        default: return nullptr;
+    }
+}
+reorder_kernel_fn cols4_kernel(int sdt, int ddt) {
+    switch (sdt) {
+        case DT_F32: return cols4_for_dst<DT_F32>(ddt);
+        case DT_BF16: return cols4_for_dst<DT_BF16>(ddt);
+        case DT_F16: return cols4_for_dst<DT_F16>(ddt);
+        case DT_S8: return cols4_for_dst<DT_S8>(ddt);
+        case DT_U8: return cols4_for_dst<DT_U8>(ddt);
+        default: return nullptr;
     }
 }
 
@@ -295,6 +507,19 @@ dnnl_status_t qmm::execute_reorder(const dnnl_primitive_desc &pd, dnnl_stream_t 
         return dnnl_runtime_error;
     }
     cudaSetDevice(pd.engine->device);
+    // Both tensors dense in the same dim order, the contiguous dim a multiple of four, buffers
+    // aligned for four elements: the kernel with 16-byte accesses.
+    const bool src4 = a.src_dt == DT_S4 || a.src_dt == DT_U4;
+    bool dense4 = !src4 && !dst4 && a.dims[a.order[0]] % 4 == 0;
+    int64_t expect = 1;
+    for (int k = 0; k < a.ndims && dense4; ++k) {
+        const int d = a.order[k];
+        if (a.dims[d] != 1 && (a.dstr[d] != expect || a.sstr[d] != expect)) dense4 = false;
+        expect *= a.dims[d];
+    }
+    auto width = [](int dt) { return (dt == DT_F32 || dt == DT_S32) ? 4 : (dt == DT_BF16 || dt == DT_F16) ? 2 : 1; };
+    if ((uintptr_t)a.src % (4 * width(a.src_dt)) || (uintptr_t)a.dst % (4 * width(a.dst_dt))) dense4 = false;
+    if (dense4) a.work = nelems / 4;
     const int sms = pd.engine->sm_count > 0 ? pd.engine->sm_count : 148;
     int64_t blocks = (a.work + 255) / 256;
     if (blocks > (int64_t)sms * 32) blocks = (int64_t)sms * 32; // grid-stride beyond 32 CTAs per SM
@@ -304,7 +529,28 @@ dnnl_status_t qmm::execute_reorder(const dnnl_primitive_desc &pd, dnnl_stream_t 
         cudaEventCreate(&ev0); cudaEventCreate(&ev1);
         cudaEventRecord(ev0, stream->stream);
     }
-    reorder_kernel<<<(unsigned)blocks, 256, 0, stream->stream>>>(a);
+    if (dense4) {
+        // x: the columns in chunks of four; y: as many row walkers as fill the SMs eight CTAs deep
+        const int64_t cols = a.dims[a.order[0]], rows = nelems / cols;
+        a.tx = 256;
+        while (a.tx > 1 && a.tx / 2 >= cols / 4) a.tx /= 2;
+        const int ty = 256 / a.tx;
+        const int64_t gx = (cols / 4 + a.tx - 1) / a.tx;
+        int64_t gy = ((int64_t)sms * 8 + gx - 1) / gx;
+        if (gy > (rows + ty - 1) / ty) gy = (rows + ty - 1) / ty;
+        if (gy > 65535) gy = 65535;
+        if (gx > 0x7fffffff) return dnnl_unimplemented;
+        bool outer = false; // a parameter that varies along another dim than the contiguous one
+        for (int k = 1; k < a.ndims; ++k) {
+            const int d = a.order[k];
+            outer |= a.src_scale.str[d] != 0 || a.dst_scale.str[d] != 0 || a.src_zp.str[d] != 0;
+        }
+        reorder_kernel_fn typed = (!outer && a.beta == 0.f) ? cols4_kernel(a.src_dt, a.dst_dt) : nullptr;
+        if (typed) typed<<<dim3((unsigned)gx, (unsigned)gy), 256, 0, stream->stream>>>(a);
+        else reorder_dense4_kernel<<<dim3((unsigned)gx, (unsigned)gy), 256, 0, stream->stream>>>(a);
+    } else {
+        reorder_kernel<<<(unsigned)blocks, 256, 0, stream->stream>>>(a);
+    }
     count_launch();
     const bool ok = cudaGetLastError() == cudaSuccess;
     if (verbose) {

@@ -33,6 +33,15 @@ def quantize_activations_u8():
     return W.Reorder("quantize_activations_u8", _f32(r, (33, 70), 3.0), W.U8, quant=q)
 
 
+def quantize_activations_per_row():
+    """bf16 [M,K] -> s8 with one dst scale per row (per-token quantization)."""
+    r = _r(215)
+    M, K = 21, 64
+    x = W.QTensor(W.f32_to_bf16(r.standard_normal((M, K)).astype(np.float32) * 2), W.BF16, (M, K))
+    q = {"dst_scale": W.Quant(r.uniform(0.01, 0.05, (M, 1)).astype(np.float32), W.F32, 1)}
+    return W.Reorder("quantize_activations_per_row", x, W.S8, quant=q)
+
+
 def transpose_f32_to_bf16():
     """f32 row-major -> bf16 column-major."""
     r = _r(203)
@@ -125,4 +134,4 @@ CASES = {f.__name__: f for f in (
     quantize_weights_per_column, quantize_activations_u8, transpose_f32_to_bf16, dequantize_s8_per_column,
     compress_f32_to_s4, compress_f32_to_u4, decompress_s4_grouped, decompress_u4_plain,
     quantize_experts_per_column, accumulate_with_sum, saturate_s32_to_s8, shift_u8_to_s8, widen_e4m3_to_f32,
-    narrow_bf16_to_f16_transposed)}
+    narrow_bf16_to_f16_transposed, quantize_activations_per_row)}
