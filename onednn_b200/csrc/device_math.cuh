@@ -77,12 +77,45 @@ __device__ __forceinline__ float load_float(int dt, const void *p, int64_t i) {
     }
 }
 
-// saturate + round-half-even for integer targets; RNE for bf16/f16
+// f32 -> f8 as the reference converts (src/common/float8.cpp:216-274, 47-117): through f16, then
+// round to nearest even.  e4m3: above 464 (and NaN / inf) the result is NaN S.1111.111, at or
+// below 2^-10 a signed zero.  e5m2: the upper byte of the rounded half, NaN with the quiet bit.
+__device__ __forceinline__ unsigned char f32_to_e4m3_bits(float f) {
+    const unsigned h = __half_as_ushort(__float2half_rn(f));
+    const unsigned s = (h & 0x8000u) >> 8, a = h & 0x7fffu;
+    if (a > 0x5f40u) return (unsigned char)(s | 0x7fu);
+    if (a <= 0x1400u) return (unsigned char)s;
+    const unsigned e16 = a >> 10, m = a & 0x3ffu;
+    unsigned v, rem, half;
+    if (e16 >= 9) { // normal target: three of the ten mantissa bits stay
+        v = ((e16 - 8) << 3) | (m >> 7);
+        rem = m & 0x7fu;
+        half = 0x40u;
+    } else { // subnormal target in units of 2^-9
+        const unsigned sig = 1024u + m, sh = 16u - e16;
+        v = sig >> sh;
+        rem = sig & ((1u << sh) - 1u);
+        half = 1u << (sh - 1u);
+    }
+    if (rem > half || (rem == half && (v & 1u))) ++v;
+    return (unsigned char)(s | v);
+}
+__device__ __forceinline__ unsigned char f32_to_e5m2_bits(float f) {
+    const unsigned h = __half_as_ushort(__float2half_rn(f));
+    const bool special = (h & 0x7c00u) == 0x7c00u;
+    if (special && (h & 0x03ffu)) return (unsigned char)((h >> 8) | 0x02u);
+    if (special) return (unsigned char)(h >> 8);
+    return (unsigned char)(((h + 0x007fu + ((h & 0x0100u) >> 8)) & 0xffffu) >> 8);
+}
+
+// saturate + round-half-even for integer targets; RNE for bf16/f16/f8
 __device__ __forceinline__ void store_float(int dt, float v, void *p, int64_t i) {
     switch (dt) {
         case DT_F32: ((float *)p)[i] = v; break;
         case DT_BF16: ((unsigned short *)p)[i] = f32_to_bf16_bits(v); break;
         case DT_F16: ((__half *)p)[i] = __float2half_rn(v); break;
+        case DT_F8_E4M3: ((unsigned char *)p)[i] = f32_to_e4m3_bits(v); break;
+        case DT_F8_E5M2: ((unsigned char *)p)[i] = f32_to_e5m2_bits(v); break;
         case DT_S32: {
             v = fmaxf(v, -2147483648.f);
             v = fminf(v, 2147483520.f);

@@ -98,7 +98,10 @@ __global__ void __launch_bounds__(256) reorder_kernel(const __grid_constant__ Re
         float d = __fmul_rn(src_scale, diff);
         if (!src4) {
             if (a.beta != 0.f) d = __fadd_rn(d, __fmul_rn(a.beta, load_float(a.dst_dt, a.dst, o_off)));
-            d = __fadd_rn(__fdiv_rn(d, dst_scale), (float)dst_zp);
+            d = __fdiv_rn(d, dst_scale);
+            // like the reference: its JIT reorders add a zero-point only when one is set (-0 stays
+            // -0), its scalar one, which serves reorders with a sum, always does
+            if (a.dst_zp || a.beta != 0.f) d = __fadd_rn(d, (float)dst_zp);
         }
         store_float(a.dst_dt, d, a.dst, o_off);
     }
@@ -152,8 +155,14 @@ __device__ __forceinline__ void store4(int dt, const float (&d)[4], void *p, int
         unsigned w = 0;
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
-            const float v = dt == DT_S8 ? fminf(fmaxf(d[e], -128.f), 127.f) : fminf(fmaxf(d[e], 0.f), 255.f);
-            w |= ((unsigned)__float2int_rn(v) & 0xffu) << (8 * e);
+            unsigned b;
+            if (dt == DT_F8_E4M3) b = f32_to_e4m3_bits(d[e]);
+            else if (dt == DT_F8_E5M2) b = f32_to_e5m2_bits(d[e]);
+            else {
+                const float v = dt == DT_S8 ? fminf(fmaxf(d[e], -128.f), 127.f) : fminf(fmaxf(d[e], 0.f), 255.f);
+                b = (unsigned)__float2int_rn(v) & 0xffu;
+            }
+            w |= b << (8 * e);
         }
         ((unsigned *)p)[off >> 2] = w;
     }
@@ -229,7 +238,7 @@ __global__ void __launch_bounds__(256) reorder_dense4_kernel(const __grid_consta
             float d = __fmul_rn(src_scale, diff);
             if (a.beta != 0.f) d = __fadd_rn(d, __fmul_rn(a.beta, old[e]));
             if (a.dst_scale.ptr) d = __fdiv_rn(d, dst_scale); // x / 1 = x: skipped without dst scales
-            out[e] = __fadd_rn(d, (float)dst_zp);
+            out[e] = (a.dst_zp || a.beta != 0.f) ? __fadd_rn(d, (float)dst_zp) : d;
         }
         store4(a.dst_dt, out, a.dst, off);
     }
@@ -259,7 +268,7 @@ __global__ void __launch_bounds__(256) reorder_cols4_kernel(const __grid_constan
         zps[e] = a.src_zp.ptr ? (int)load_float(a.src_zp.dt, a.src_zp.ptr, ((i0 + e) / a.src_zp.grp[d0]) * a.src_zp.str[d0])
                               : 0;
     }
-    const bool has_ds = a.dst_scale.ptr != nullptr;
+    const bool has_ds = a.dst_scale.ptr != nullptr, has_zp = a.dst_zp != nullptr;
     auto convert = [&](const float (&f)[4], const int (&iv)[4], int64_t off) {
         float out[4];
 #pragma unroll
@@ -267,7 +276,7 @@ __global__ void __launch_bounds__(256) reorder_cols4_kernel(const __grid_constan
             const float diff = dt_is_int(SDT) ? (float)(iv[e] - zps[e]) : __fsub_rn(f[e], (float)zps[e]);
             float d = __fmul_rn(ss[e], diff);
             if (has_ds) d = __fdiv_rn(d, ds[e]);
-            out[e] = __fadd_rn(d, (float)dst_zp);
+            out[e] = has_zp ? __fadd_rn(d, (float)dst_zp) : d;
         }
         store4(DDT, out, a.dst, off);
     };
@@ -299,6 +308,8 @@ reorder_kernel_fn cols4_for_dst(int ddt) {
         case DT_F16: return reorder_cols4_kernel<SDT, DT_F16>;
         case DT_S8: return reorder_cols4_kernel<SDT, DT_S8>;
         case DT_U8: return reorder_cols4_kernel<SDT, DT_U8>;
+        case DT_F8_E4M3: return reorder_cols4_kernel<SDT, DT_F8_E4M3>;
+        case DT_F8_E5M2: return reorder_cols4_kernel<SDT, DT_F8_E5M2>;
         default: return nullptr;
     }
 }
@@ -415,7 +426,7 @@ extern "C" dnnl_status_t dnnl_reorder_primitive_desc_create(dnnl_primitive_desc_
     const std::initializer_list<dnnl_data_type_t> in_types
             = {dnnl_f32, dnnl_bf16, dnnl_f16, dnnl_s32, dnnl_s8, dnnl_u8, dnnl_f8_e4m3, dnnl_f8_e5m2, dnnl_s4, dnnl_u4};
     const std::initializer_list<dnnl_data_type_t> out_types
-            = {dnnl_f32, dnnl_bf16, dnnl_f16, dnnl_s32, dnnl_s8, dnnl_u8, dnnl_s4, dnnl_u4};
+            = {dnnl_f32, dnnl_bf16, dnnl_f16, dnnl_s32, dnnl_s8, dnnl_u8, dnnl_f8_e4m3, dnnl_f8_e5m2, dnnl_s4, dnnl_u4};
     if (nd > RMAX || !one_of_dt(si, in_types) || !one_of_dt(di, out_types)) return fail(dnnl_unimplemented);
     if (src_desc->offset0 || dst_desc->offset0) return fail(dnnl_unimplemented);
     for (const quant_entry_t *q : {&ss, &ds, &sz, &dz})

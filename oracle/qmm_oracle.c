@@ -93,6 +93,39 @@ static float e4m3_to_f32(uint8_t b) {
 /* e5m2 is the upper byte of an IEEE half (src/common/float8.cpp:47-110) */
 static float e5m2_to_f32(uint8_t b) { return f16_to_f32((uint16_t)b << 8); }
 
+/* f16 -> e4m3, src/common/float8.cpp:216-267: round to nearest even; above
+ * 464 (and NaN / inf) the result is NaN S.1111.111, at or below 2^-10 a signed
+ * zero.  The reference rounds by adding and subtracting a shifter constant;
+ * the integer form below gives the same nearest-even result. */
+static uint8_t f16_to_e4m3(uint16_t h) {
+    uint8_t s = (uint8_t)((h & 0x8000) >> 8);
+    uint32_t a = h & 0x7fff;
+    if (a > 0x5f40) return s | 0x7f;
+    if (a <= 0x1400) return s;
+    uint32_t e16 = a >> 10, m = a & 0x3ff, v, rem, half;
+    if (e16 >= 9) { /* normal target: e8 = e16 - 8, three of ten mantissa bits stay */
+        v = ((e16 - 8) << 3) | (m >> 7);
+        rem = m & 0x7f;
+        half = 0x40;
+    } else { /* subnormal target, unit 2^-9: (1024 + m) * 2^(e16 - 16) units */
+        uint32_t sig = 1024 + m, sh = 16 - e16;
+        v = sig >> sh;
+        rem = sig & ((1u << sh) - 1);
+        half = 1u << (sh - 1);
+    }
+    if (rem > half || (rem == half && (v & 1))) v++;
+    return (uint8_t)(s | v);
+}
+/* f16 -> e5m2, src/common/float8.cpp:47-73: NaN keeps its sign and gets the
+ * quiet bit, infinity passes, everything else rounds to nearest even on the
+ * raw bits (an overflow carries into infinity) */
+static uint8_t f16_to_e5m2(uint16_t h) {
+    int special = (h & 0x7c00) == 0x7c00;
+    if (special && (h & 0x03ff)) return (uint8_t)((h >> 8) | 0x02);
+    if (special) return (uint8_t)(h >> 8);
+    return (uint8_t)((uint16_t)(h + 0x007f + ((h & 0x0100) >> 8)) >> 8);
+}
+
 /* ---- typed loads / stores (src/cpu/ref_io_helper.hpp:34-150) ------------ */
 
 /* src/common/nibble.hpp:28-65, int4.hpp:28-68: element i lives in byte i/2,
@@ -140,6 +173,9 @@ void qmm_store_float(int32_t dt, float v, void *p, int64_t i) {
         case QMM_F32: ((float *)p)[i] = v; break;
         case QMM_BF16: ((uint16_t *)p)[i] = f32_to_bf16(v); break;
         case QMM_F16: ((uint16_t *)p)[i] = f32_to_f16(v); break;
+        /* float -> f8 goes through f16 (float8.cpp:269-274, 112-117) */
+        case QMM_F8_E4M3: ((uint8_t *)p)[i] = f16_to_e4m3(f32_to_f16(v)); break;
+        case QMM_F8_E5M2: ((uint8_t *)p)[i] = f16_to_e5m2(f32_to_f16(v)); break;
         case QMM_S32: {
             if (v < -2147483648.f) v = -2147483648.f;
             if (v > 2147483520.f) v = 2147483520.f;
@@ -630,7 +666,12 @@ int qmm_oracle_reorder(const qmm_reorder_t *r) {
         if (!src4) {
             if (r->beta != 0.f)
                 d += r->beta * qmm_load_float(r->dst_dt, r->dst, o_off);
-            d = d / dst_scale + (float)dst_zp;
+            /* The scalar implementation adds the zero-point always (so a -0
+             * result becomes +0); the library dispatches it only for reorders
+             * with a sum.  Its JIT implementations, which serve the others,
+             * add a zero-point only when the attribute is set and keep -0. */
+            d = d / dst_scale;
+            if (r->dst_zp.ptr || r->beta != 0.f) d += (float)dst_zp;
         }
         qmm_store_float(r->dst_dt, d, r->dst, o_off);
     }

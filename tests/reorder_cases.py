@@ -42,6 +42,46 @@ def quantize_activations_per_row():
     return W.Reorder("quantize_activations_per_row", x, W.S8, quant=q)
 
 
+def _f8_edge_values(r, dims, top):
+    """Normal data plus the values where an 8-bit float conversion decides: the largest finite
+    value, the round-down / overflow boundary above it, tiny and subnormal magnitudes, zeros."""
+    x = (r.standard_normal(dims) * top / 6).astype(np.float32)
+    edge = np.array([top, top * 1.03, top * 1.04, -top * 1.2, 3 * top, 2.0 ** -10, 2.0 ** -10 * 1.01, 2.0 ** -9,
+                     1.5 * 2.0 ** -9, 2.0 ** -7 * 1.0625, -2.0 ** -17, 2.0 ** -16, 1e-30, 0.0, -0.0, 0.4375, 0.46875,
+                     17.0, 18.0, 19.0, 0.099, -0.0991], np.float32)
+    x.reshape(-1)[:edge.size] = edge
+    return x
+
+
+def quantize_f32_to_e4m3():
+    """f32 -> f8_e4m3 with a common dst scale (the fp8 GEMM's weight / activation quantization)."""
+    r = _r(216)
+    dims = (24, 64)
+    q = {"dst_scale": W.Quant(np.array([0.5], np.float32), W.F32, 0)}
+    return W.Reorder("quantize_f32_to_e4m3", W.QTensor(_f8_edge_values(r, dims, 224.0), W.F32, dims), W.F8_E4M3, quant=q)
+
+
+def quantize_f32_to_e5m2():
+    r = _r(217)
+    dims = (16, 48)
+    x = _f8_edge_values(r, dims, 57344.0)
+    x.reshape(-1)[40:44] = [np.inf, -np.inf, 61184.0, 61500.0]
+    return W.Reorder("quantize_f32_to_e5m2", W.QTensor(x, W.F32, dims), W.F8_E5M2)
+
+
+def quantize_bf16_to_e4m3_per_column():
+    r = _r(218)
+    K, N = 40, 32
+    x = W.QTensor(W.f32_to_bf16(r.standard_normal((K, N)).astype(np.float32)), W.BF16, (K, N))
+    q = {"dst_scale": W.Quant(r.uniform(0.005, 0.02, (1, N)).astype(np.float32), W.F32, 2)}
+    return W.Reorder("quantize_bf16_to_e4m3_per_column", x, W.F8_E4M3, quant=q)
+
+
+def transpose_f32_to_e5m2():
+    r = _r(219)
+    return W.Reorder("transpose_f32_to_e5m2", _f32(r, (18, 30), 100.0), W.F8_E5M2, dst_strides=(1, 18))
+
+
 def transpose_f32_to_bf16():
     """f32 row-major -> bf16 column-major."""
     r = _r(203)
@@ -134,4 +174,5 @@ CASES = {f.__name__: f for f in (
     quantize_weights_per_column, quantize_activations_u8, transpose_f32_to_bf16, dequantize_s8_per_column,
     compress_f32_to_s4, compress_f32_to_u4, decompress_s4_grouped, decompress_u4_plain,
     quantize_experts_per_column, accumulate_with_sum, saturate_s32_to_s8, shift_u8_to_s8, widen_e4m3_to_f32,
-    narrow_bf16_to_f16_transposed, quantize_activations_per_row)}
+    narrow_bf16_to_f16_transposed, quantize_activations_per_row, quantize_f32_to_e4m3, quantize_f32_to_e5m2,
+    quantize_bf16_to_e4m3_per_column, transpose_f32_to_e5m2)}
