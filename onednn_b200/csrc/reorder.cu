@@ -45,12 +45,6 @@ struct ReorderArgs {
     float beta;
 };
 
-__device__ __forceinline__ int64_t rq_off(const RQuant &q, const int64_t *idx, int ndims) {
-    int64_t off = 0;
-    for (int d = 0; d < ndims; ++d) off += (idx[d] / q.grp[d]) * q.str[d];
-    return off;
-}
-
 __device__ __forceinline__ bool dt_is_int(int dt) { return dt == DT_S32 || dt == DT_S8 || dt == DT_U8; }
 
 __device__ __forceinline__ unsigned quantize_nibble(float v, bool sgn) {
@@ -58,25 +52,31 @@ __device__ __forceinline__ unsigned quantize_nibble(float v, bool sgn) {
     return (unsigned)__float2int_rn(v) & 0xFu;
 }
 
+// IDX: the type the linear index is decomposed in (32-bit division where the tensor allows it)
+template <typename IDX>
 __global__ void __launch_bounds__(256) reorder_kernel(const __grid_constant__ ReorderArgs a) {
     const bool dst4 = a.dst_dt == DT_S4 || a.dst_dt == DT_U4;
     const bool src4 = a.src_dt == DT_S4 || a.src_dt == DT_U4;
     const int dst_zp = a.dst_zp ? __ldg(a.dst_zp) : 0;
     for (int64_t l = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; l < a.work;
             l += (int64_t)gridDim.x * blockDim.x) {
-        int64_t idx[RMAX], rem = l, i_off = 0, o_off = 0;
+        IDX rem = (IDX)l;
+        int64_t i_off = 0, o_off = 0, q_ss = 0, q_ds = 0, q_sz = 0; // tensor and parameter offsets
 #pragma unroll
         for (int k = 0; k < RMAX; ++k) {
             if (k >= a.ndims) break;
             const int d = a.order[k];
-            int64_t extent = a.dims[d];
+            IDX extent = (IDX)a.dims[d];
             if (dst4 && k == 0) extent >>= 1; // a thread owns elements (2j, 2j+1) of the innermost dim
-            int64_t i = rem % extent;
+            IDX i = rem % extent;
             rem /= extent;
             if (dst4 && k == 0) i *= 2;
-            idx[d] = i;
-            i_off += i * a.sstr[d];
-            o_off += i * a.dstr[d];
+            i_off += (int64_t)i * a.sstr[d];
+            o_off += (int64_t)i * a.dstr[d];
+            // groups exist on the last two dims only; elsewhere the divisor is 1
+            q_ss += (int64_t)(a.src_scale.grp[d] == 1 ? i : i / (IDX)a.src_scale.grp[d]) * a.src_scale.str[d];
+            q_ds += (int64_t)i * a.dst_scale.str[d];
+            q_sz += (int64_t)(a.src_zp.grp[d] == 1 ? i : i / (IDX)a.src_zp.grp[d]) * a.src_zp.str[d];
         }
         if (dst4) {
             const int64_t s1 = a.sstr[a.order[0]];
@@ -86,10 +86,10 @@ __global__ void __launch_bounds__(256) reorder_kernel(const __grid_constant__ Re
             continue;
         }
         float src_scale = 1.f, dst_scale = 1.f;
-        if (a.src_scale.ptr) src_scale = load_float(a.src_scale.dt, a.src_scale.ptr, rq_off(a.src_scale, idx, a.ndims));
-        if (a.dst_scale.ptr) dst_scale = __ldg((const float *)a.dst_scale.ptr + rq_off(a.dst_scale, idx, a.ndims));
+        if (a.src_scale.ptr) src_scale = load_float(a.src_scale.dt, a.src_scale.ptr, q_ss);
+        if (a.dst_scale.ptr) dst_scale = __ldg((const float *)a.dst_scale.ptr + q_ds);
         int zp = 0;
-        if (a.src_zp.ptr) zp = (int)load_float(a.src_zp.dt, a.src_zp.ptr, rq_off(a.src_zp, idx, a.ndims));
+        if (a.src_zp.ptr) zp = (int)load_float(a.src_zp.dt, a.src_zp.ptr, q_sz);
         // integer sources subtract in integer arithmetic, the others (and 4-bit ones, which the
         // reference widens to the floating-point dst type first) in float
         float diff;
@@ -560,7 +560,8 @@ dnnl_status_t qmm::execute_reorder(const dnnl_primitive_desc &pd, dnnl_stream_t 
         if (typed) typed<<<dim3((unsigned)gx, (unsigned)gy), 256, 0, stream->stream>>>(a);
         else reorder_dense4_kernel<<<dim3((unsigned)gx, (unsigned)gy), 256, 0, stream->stream>>>(a);
     } else {
-        reorder_kernel<<<(unsigned)blocks, 256, 0, stream->stream>>>(a);
+        if (nelems < ((int64_t)1 << 31)) reorder_kernel<unsigned><<<(unsigned)blocks, 256, 0, stream->stream>>>(a);
+        else reorder_kernel<int64_t><<<(unsigned)blocks, 256, 0, stream->stream>>>(a);
     }
     count_launch();
     const bool ok = cudaGetLastError() == cudaSuccess;

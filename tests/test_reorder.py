@@ -78,6 +78,30 @@ def test_cuda_reorder_feeds_the_matmul(gpu):
     assert np.allclose(got, want, rtol=1e-5, atol=0)
 
 
+@pytest.mark.gpu
+def test_cuda_reorder_feeds_the_fp8_matmul(gpu):
+    """f32 activations and weights quantized to e4m3 by reorders (common dst scales), then the fp8
+    matmul with the same scales; the oracle runs on the oracle's own quantized tensors."""
+    from onednn_b200.runner import run_problem, run_reorder
+    eng, strm = gpu
+    r = np.random.Generator(np.random.PCG64(78))
+    M, K, N = 64, 256, 128
+    p = W.fp8_prefill(M, K, N)
+    quantized = {}
+    for name, dims, scale in (("src", (M, K), 0.02), ("wei", (K, N), 0.01)):
+        x = W.QTensor(r.standard_normal(dims).astype(np.float32), W.F32, dims)
+        ro = W.Reorder(name, x, W.F8_E4M3, quant={"dst_scale": W.Quant(np.array([scale], np.float32), W.F32, 0)})
+        q, impl = run_reorder(ro, eng, strm)
+        assert impl == "cuda:ref:reorder"
+        assert np.array_equal(q, O.run_port_reorder(ro)), name
+        quantized[name] = W.QTensor(q.reshape(dims).copy(), W.F8_E4M3, dims)
+    p.src, p.wei = quantized["src"], quantized["wei"]
+    got, impl = run_problem(p, eng, strm)
+    assert impl == "cuda:tcgen05:fp8", impl
+    from util import assert_parity, summation_slack
+    assert_parity(got, O.run_port(p), p.dst_dt, "fp8 matmul on reorder-quantized tensors", summation_slack(p))
+
+
 def test_reorder_descriptor_checks():
     """Checks that need no device: creation on a device-less engine is not possible, so only the
     argument validation that precedes any engine use is exercised through the C ABI."""
