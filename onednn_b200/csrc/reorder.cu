@@ -298,6 +298,55 @@ __global__ void __launch_bounds__(256) reorder_cols4_kernel(const __grid_constan
     }
 }
 
+// Layout-changing reorder of a matrix (or a batch of them): the src is contiguous along dim dr,
+// the dst along dim dc.  A CTA converts a 32 x 32 tile, reading along dr and, after a trip
+// through shared memory, writing along dc, so both sides move whole sectors.  No sum.
+__global__ void __launch_bounds__(256)
+reorder_transpose_kernel(const __grid_constant__ ReorderArgs a, int dr, int dc, int db) {
+    __shared__ float tile[32][33];
+    const int tx = threadIdx.x % 32, ty = threadIdx.x / 32;
+    const int64_t r0 = (int64_t)blockIdx.x * 32, c0 = (int64_t)blockIdx.y * 32, b = blockIdx.z;
+    const int dst_zp = a.dst_zp ? __ldg(a.dst_zp) : 0;
+    int64_t sb = 0, ob = 0, q_ss = 0, q_ds = 0, q_sz = 0; // the batch index's share of every offset
+    if (db >= 0) {
+        sb = b * a.sstr[db];
+        ob = b * a.dstr[db];
+        q_ss = b * a.src_scale.str[db];
+        q_ds = b * a.dst_scale.str[db];
+        q_sz = b * a.src_zp.str[db];
+    }
+    const int64_t r = r0 + tx;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const int64_t c = c0 + ty + 8 * j;
+        if (r >= a.dims[dr] || c >= a.dims[dc]) continue;
+        const int64_t i_off = sb + r * a.sstr[dr] + c * a.sstr[dc];
+        float src_scale = 1.f, dst_scale = 1.f;
+        int zp = 0;
+        if (a.src_scale.ptr)
+            src_scale = load_float(a.src_scale.dt, a.src_scale.ptr,
+                    q_ss + (r / a.src_scale.grp[dr]) * a.src_scale.str[dr] + (c / a.src_scale.grp[dc]) * a.src_scale.str[dc]);
+        if (a.dst_scale.ptr) dst_scale = __ldg((const float *)a.dst_scale.ptr + q_ds + r * a.dst_scale.str[dr] + c * a.dst_scale.str[dc]);
+        if (a.src_zp.ptr)
+            zp = (int)load_float(a.src_zp.dt, a.src_zp.ptr,
+                    q_sz + (r / a.src_zp.grp[dr]) * a.src_zp.str[dr] + (c / a.src_zp.grp[dc]) * a.src_zp.str[dc]);
+        const float diff = dt_is_int(a.src_dt) ? (float)(load_int(a.src_dt, a.src, i_off) - zp)
+                                                : __fsub_rn(load_float(a.src_dt, a.src, i_off), (float)zp);
+        float d = __fmul_rn(src_scale, diff);
+        if (a.dst_scale.ptr) d = __fdiv_rn(d, dst_scale); // x / 1 = x
+        if (a.dst_zp) d = __fadd_rn(d, (float)dst_zp);
+        tile[ty + 8 * j][tx] = d;
+    }
+    __syncthreads();
+    const int64_t c = c0 + tx;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const int64_t rr = r0 + ty + 8 * j;
+        if (rr >= a.dims[dr] || c >= a.dims[dc]) continue;
+        store_float(a.dst_dt, tile[tx][ty + 8 * j], a.dst, ob + rr * a.dstr[dr] + c * a.dstr[dc]);
+    }
+}
+
 typedef void (*reorder_kernel_fn)(const ReorderArgs);
 
 template <int SDT>
@@ -560,8 +609,23 @@ dnnl_status_t qmm::execute_reorder(const dnnl_primitive_desc &pd, dnnl_stream_t 
         if (typed) typed<<<dim3((unsigned)gx, (unsigned)gy), 256, 0, stream->stream>>>(a);
         else reorder_dense4_kernel<<<dim3((unsigned)gx, (unsigned)gy), 256, 0, stream->stream>>>(a);
     } else {
-        if (nelems < ((int64_t)1 << 31)) reorder_kernel<unsigned><<<(unsigned)blocks, 256, 0, stream->stream>>>(a);
-        else reorder_kernel<int64_t><<<(unsigned)blocks, 256, 0, stream->stream>>>(a);
+        // a matrix (or a batch of matrices) whose contiguous dim changes: the tiled kernel
+        int dr = -1, dc = -1;
+        if (!src4 && !dst4 && a.beta == 0.f && (a.ndims == 2 || a.ndims == 3)) {
+            for (int d = a.ndims - 2; d < a.ndims; ++d) {
+                if (a.sstr[d] == 1 && a.dims[d] > 1) dr = d;
+                if (a.dstr[d] == 1 && a.dims[d] > 1) dc = d;
+            }
+        }
+        const int64_t gy = dc >= 0 ? (a.dims[dc] + 31) / 32 : 0, gz = a.ndims == 3 ? a.dims[0] : 1;
+        if (dr >= 0 && dc >= 0 && dr != dc && gy <= 65535 && gz <= 65535) {
+            const dim3 grid((unsigned)((a.dims[dr] + 31) / 32), (unsigned)gy, (unsigned)gz);
+            reorder_transpose_kernel<<<grid, 256, 0, stream->stream>>>(a, dr, dc, a.ndims == 3 ? 0 : -1);
+        } else if (nelems < ((int64_t)1 << 31)) {
+            reorder_kernel<unsigned><<<(unsigned)blocks, 256, 0, stream->stream>>>(a);
+        } else {
+            reorder_kernel<int64_t><<<(unsigned)blocks, 256, 0, stream->stream>>>(a);
+        }
     }
     count_launch();
     const bool ok = cudaGetLastError() == cudaSuccess;

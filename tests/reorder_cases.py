@@ -82,6 +82,26 @@ def transpose_f32_to_e5m2():
     return W.Reorder("transpose_f32_to_e5m2", _f32(r, (18, 30), 100.0), W.F8_E5M2, dst_strides=(1, 18))
 
 
+def dequantize_experts_transposed():
+    """s8 [G,K,N] row-major -> f32 with K and N swapped in memory, one src scale per column and
+    a common src zero-point."""
+    r = _r(220)
+    G, K, N = 3, 40, 34
+    q = {"src_scale": W.Quant(r.uniform(0.01, 0.1, (1, 1, N)).astype(np.float32), W.F32, 4),
+         "src_zp": W.Quant(np.array([-2], np.int32), W.S32, 0)}
+    src = W.QTensor(r.integers(-128, 128, (G, K, N)).astype(np.int8), W.S8, (G, K, N))
+    return W.Reorder("dequantize_experts_transposed", src, W.F32, dst_strides=(K * N, 1, K), quant=q)
+
+
+def quantize_transposed_per_row():
+    """f32 [K,N] column-major -> s8 row-major with one dst scale per row of the matrix."""
+    r = _r(221)
+    K, N = 70, 33
+    x = W.QTensor((r.standard_normal((K, N)) * 0.1).astype(np.float32), W.F32, (K, N), strides=(1, K))
+    q = {"dst_scale": W.Quant(r.uniform(0.001, 0.003, (K, 1)).astype(np.float32), W.F32, 1)}
+    return W.Reorder("quantize_transposed_per_row", x, W.S8, quant=q)
+
+
 def transpose_f32_to_bf16():
     """f32 row-major -> bf16 column-major."""
     r = _r(203)
@@ -175,4 +195,5 @@ CASES = {f.__name__: f for f in (
     compress_f32_to_s4, compress_f32_to_u4, decompress_s4_grouped, decompress_u4_plain,
     quantize_experts_per_column, accumulate_with_sum, saturate_s32_to_s8, shift_u8_to_s8, widen_e4m3_to_f32,
     narrow_bf16_to_f16_transposed, quantize_activations_per_row, quantize_f32_to_e4m3, quantize_f32_to_e5m2,
-    quantize_bf16_to_e4m3_per_column, transpose_f32_to_e5m2)}
+    quantize_bf16_to_e4m3_per_column, transpose_f32_to_e5m2, dequantize_experts_transposed,
+    quantize_transposed_per_row)}
