@@ -196,20 +196,22 @@ def run_gpu(args):
     eng = api.engine(api.engine.kind.gpu, local_rank)
     tstream = torch.cuda.current_stream()
     strm = api.stream(eng, tstream.cuda_stream)
-    ptrs, keep = device_buffers(p, torch, dev)
-    prep = Prepared(p, eng, args.kernel).bind_device(ptrs)
-    # decode streams ~L2-sized weights: rotate among copies so no step finds them in L2
-    rotate = []
-    if name == "int4_decode":
-        for _ in range(3):
-            w2 = keep["wei"].clone()
-            keep["wei%d" % len(rotate)] = w2
-            pr2 = dict(ptrs)
-            pr2["wei"] = w2.data_ptr()
-            rotate.append(Prepared(p, eng, args.kernel).bind_device(pr2))
-    preps = rotate or [prep]
-
-    dst_t = keep["dst"]
+    # A step must not find its inputs in the 126 MB L2 left there by the step before: when one
+    # rank's working set is not clearly larger than L2 (decode, and every workload once it is
+    # sharded), consecutive steps use different copies of all buffers, enough of them that a
+    # cycle through the copies moves 2.5 x L2.
+    L2_BYTES = 126e6
+    ws = float(p.algorithmic_bytes())
+    nsets = 1 if ws > 1.5 * L2_BYTES else int(min(8, max(2, np.ceil(2.5 * L2_BYTES / max(ws, 1.0)))))
+    sets = []
+    for _ in range(nsets):
+        ptrs_s, keep_s = device_buffers(p, torch, dev)
+        sets.append((Prepared(p, eng, args.kernel).bind_device(ptrs_s), keep_s))
+    prep, keep = sets[0]
+    preps = [s[0] for s in sets]
+    l2_note = ("working set %.0f MB > 126 MB L2" % (ws / 1e6)) if nsets == 1 else \
+        ("%d copies of all buffers rotated, %.0f MB per cycle %s 126 MB L2" %
+         (nsets, nsets * ws / 1e6, ">" if nsets * ws > L2_BYTES else "< (L2-resident workload)"))
     elem = {W.BF16: torch.bfloat16, W.F16: torch.float16, W.F32: torch.float32, W.S32: torch.int32,
             W.S8: torch.int8, W.U8: torch.uint8}[p.dst_dt]
     rows_per_rank = None
@@ -220,10 +222,10 @@ def run_gpu(args):
             e0, e1 = sharding.expert_range(full.groups, r, world)
             rows_per_rank.append(int((ends[e1 - 1] if e1 > e0 else (ends[e0 - 1] if e0 else 0)) - (ends[e0 - 1] if e0 else 0)))
 
-    def gather():
+    def gather(i=0):
         if world == 1:
             return None
-        local = dst_t.view(elem).view(p.M, p.N)
+        local = sets[i % nsets][1]["dst"].view(elem).view(p.M, p.N)
         # the gathered result stays in the collective's blocked layout ([rank][M][N/g] column
         # slices, [rank][rows][N] expert blocks): no interleaving copy inside the step
         if rows_per_rank is not None:
@@ -231,8 +233,8 @@ def run_gpu(args):
         return sharding.gather_columns_blocked(local, full.N, world)
 
     def step(i):
-        preps[i % len(preps)].execute(strm)
-        return gather()
+        preps[i % nsets].execute(strm)
+        return gather(i)
 
     def barrier():
         if world > 1:
@@ -252,9 +254,9 @@ def run_gpu(args):
     e0.record()
     for i in range(args.steps):
         k_ev[i][0].record()
-        preps[i % len(preps)].execute(strm)
+        preps[i % nsets].execute(strm)
         k_ev[i][1].record()
-        gather()
+        gather(i)
     e1.record()
     barrier()
     launches = api.launch_count() - launches0
@@ -266,7 +268,7 @@ def run_gpu(args):
         i = 0
         while time.time() < t_end:
             for _ in range(50):
-                preps[i % len(preps)].execute(strm)
+                preps[i % nsets].execute(strm)
                 i += 1
             torch.cuda.synchronize()
     barrier()
@@ -278,14 +280,15 @@ def run_gpu(args):
     # ---- end-to-end: src from pinned host memory, dst back to the host, every step
     src_host = torch.from_numpy(p.src.data.view(np.uint8).reshape(-1).copy()).pin_memory()
     g0 = gather()
-    out_bytes = int(g0.numel() * g0.element_size()) if g0 is not None else dst_t.numel()
+    out_bytes = int(g0.numel() * g0.element_size()) if g0 is not None else keep["dst"].numel()
     dst_host = torch.empty(out_bytes, dtype=torch.uint8).pin_memory()
     e2e_steps = max(3, min(args.steps, 10))
 
     def e2e_step(i):
-        keep["src"].copy_(src_host, non_blocking=True)
+        k = sets[i % nsets][1]
+        k["src"].copy_(src_host, non_blocking=True)
         g = step(i)
-        res = dst_t if g is None else g.reshape(-1).view(torch.uint8)
+        res = k["dst"] if g is None else g.reshape(-1).view(torch.uint8)
         dst_host[:res.numel()].copy_(res, non_blocking=True)
 
     e2e_step(0)
@@ -326,8 +329,7 @@ def run_gpu(args):
                        "kernel": prep.impl, "parallelism": ("%s x%d + NCCL all-gather into [rank][M][N/g] blocks"
                                        % ("expert-shard" if full.offsets is not None else "n-shard", world))
                        if world > 1 else "single",
-                       "l2": "weight copies rotated (3 x %.0f MB)" % (p.wei.data.nbytes / 1e6) if rotate
-                             else "working set %.0f MB > 126 MB L2" % (p.algorithmic_bytes() / 1e6),
+                       "l2": l2_note,
                        "e2e": "src H2D from pinned memory and dst D2H every step; weights resident"},
             "roofline": {"bound": bound, "achieved": achieved, "peak": peak, "unit": runit,
                          "frac": achieved / peak, "traffic": dram_traffic(wkey, world),
@@ -478,17 +480,34 @@ def run_reorder_bench(args):
     eng = api.engine(api.engine.kind.gpu, local_rank)
     strm = api.stream(eng, torch.cuda.current_stream().cuda_stream)
     g = torch.Generator(device=dev).manual_seed(20266 + rank)
-    src = torch.randn((K, Nl), generator=g, device=dev, dtype=torch.float32) * 0.05
-    sc = (src.abs().amax(dim=0, keepdim=True) / 127.0).contiguous()
-    dst = torch.zeros((K, Nl), device=dev, dtype=torch.int8)
     src_md, dst_md = api.memory.desc((K, Nl), W.F32, api.tag.ab), api.memory.desc((K, Nl), W.S8, api.tag.ab)
     attr = api.primitive_attr()
     attr.set_scales(api.ARG_DST, 2, (), W.F32)
     pd = api.reorder.primitive_desc(eng, src_md, eng, dst_md, attr)
-    prim = api.reorder(pd)
     key = api.ARG_ATTR_SCALES | api.ARG_DST
-    ex_args = {api.ARG_FROM: api.memory(src_md, eng, src.data_ptr()), api.ARG_TO: api.memory(dst_md, eng, dst.data_ptr()),
-               key: api.memory(pd.query_md(api.QUERY_EXEC_ARG_MD, key), eng, sc.data_ptr())}
+    # as in the matmul arm: copies of the buffers in rotation when one rank's tensors do not exceed L2 clearly
+    ws = float(K * Nl * 5)
+    nsets = 1 if ws > 1.5 * 126e6 else int(min(8, max(2, np.ceil(2.5 * 126e6 / ws))))
+    bufs = []
+    for _ in range(nsets):
+        s_ = torch.randn((K, Nl), generator=g, device=dev, dtype=torch.float32) * 0.05
+        c_ = (s_.abs().amax(dim=0, keepdim=True) / 127.0).contiguous()
+        d_ = torch.zeros((K, Nl), device=dev, dtype=torch.int8)
+        bufs.append((s_, d_, c_, {api.ARG_FROM: api.memory(src_md, eng, s_.data_ptr()),
+                                  api.ARG_TO: api.memory(dst_md, eng, d_.data_ptr()),
+                                  key: api.memory(pd.query_md(api.QUERY_EXEC_ARG_MD, key), eng, c_.data_ptr())}))
+    src, dst = bufs[0][0], bufs[0][1]
+
+    class _Rotating:
+        """Executes the reorder on the next set of buffers at every call."""
+        def __init__(self):
+            self.prim, self.i = api.reorder(pd), 0
+
+        def execute(self, strm, _unused=None):
+            self.prim.execute(strm, bufs[self.i % nsets][3])
+            self.i += 1
+
+    prim, ex_args = _Rotating(), None
 
     def barrier():
         if world > 1:
@@ -528,7 +547,7 @@ def run_reorder_bench(args):
     f0.record()
     for _ in range(e2e_steps):
         src.copy_(src_host, non_blocking=True)
-        prim.execute(strm, ex_args)
+        prim.prim.execute(strm, bufs[0][3])  # the set whose src was just copied in
         dst_host.copy_(dst, non_blocking=True)
     f1.record()
     barrier()
@@ -546,7 +565,8 @@ def run_reorder_bench(args):
                 "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
                 "config": {"workload": wkey, "kernel": pd.impl_info_str(),
                            "parallelism": "column blocks, one tensor per rank, no collective" if world > 1 else "single",
-                           "l2": "working set %.0f MB > 126 MB L2" % (launch_gb * 1e3),
+                           "l2": ("working set %.0f MB > 126 MB L2" % (launch_gb * 1e3)) if nsets == 1 else
+                                 ("%d copies of all buffers rotated, %.0f MB per cycle > 126 MB L2" % (nsets, nsets * ws / 1e6)),
                            "e2e": "f32 src H2D from pinned memory and s8 dst D2H every step"},
                 "roofline": {"bound": "hbm", "achieved": launch_gb / (ms * 1e-3), "peak": pk["hbm_gbs"], "unit": "GB/s",
                              "frac": launch_gb / (ms * 1e-3) / pk["hbm_gbs"], "traffic": dram_traffic(wkey, world),
