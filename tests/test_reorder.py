@@ -102,12 +102,48 @@ def test_cuda_reorder_feeds_the_fp8_matmul(gpu):
     assert_parity(got, O.run_port(p), p.dst_dt, "fp8 matmul on reorder-quantized tensors", summation_slack(p))
 
 
-def test_reorder_descriptor_checks():
-    """Checks that need no device: creation on a device-less engine is not possible, so only the
-    argument validation that precedes any engine use is exercised through the C ABI."""
+def test_reorder_descriptor_checks(host_engine):
+    """Creation-time validation on a device-less engine: the error codes of
+    src/common/reorder.cpp:67-150 and the combinations the implementation list covers."""
     import ctypes as C
     from onednn_b200 import api
-    L = api.lib()
+    md, tag, eng = api.memory.desc, api.tag, host_engine
+
+    def status(src_md, dst_md, attr=None):
+        try:
+            api.reorder.primitive_desc(eng, src_md, eng, dst_md, attr)
+        except api.error as e:
+            return e.status
+        return api.success
+
+    def attr_with(fn):
+        a = api.primitive_attr()
+        fn(a)
+        return a
+
+    f32, s8 = md((8, 16), W.F32, tag.ab), md((8, 16), W.S8, tag.ab)
     h = C.c_void_p()
-    # null descriptors / engines: invalid_arguments, as dnnl_reorder_primitive_desc_create returns
-    assert L.dnnl_reorder_primitive_desc_create(C.byref(h), None, None, None, None, None) == api.invalid_arguments
+    assert api.lib().dnnl_reorder_primitive_desc_create(C.byref(h), None, None, None, None, None) == api.invalid_arguments
+    pd = api.reorder.primitive_desc(eng, f32, eng, s8, attr_with(lambda a: a.set_scales(api.ARG_DST, 2, (), W.F32)))
+    assert pd.impl_info_str() == "cuda:ref:reorder" and not pd.next_impl()
+    assert pd.query_md(api.QUERY_EXEC_ARG_MD, api.ARG_ATTR_SCALES | api.ARG_DST).get_dims() == (1, 16)
+    assert pd.src_desc() == f32 and pd.dst_desc() == s8
+    # dims must agree; format_tag::any is not a layout to reorder into
+    assert status(f32, md((8, 12), W.S8, tag.ab)) == api.invalid_arguments
+    assert status(f32, md((8, 16), W.S8, tag.any)) == api.invalid_arguments
+    # zero-points only on integer tensors; a scale for s4 sources needs a mask; dst scales take no groups
+    assert status(f32, s8, attr_with(lambda a: a.set_zero_points(api.ARG_SRC, 0, (), W.S32))) == api.invalid_arguments
+    assert status(s8, f32, attr_with(lambda a: a.set_zero_points(api.ARG_SRC, 0, (), W.S32))) == api.success
+    s4 = md((8, 16), W.S4, tag.ab)
+    assert status(s4, f32, attr_with(lambda a: a.set_scales(api.ARG_SRC, 0, (), W.F32))) == api.invalid_arguments
+    assert status(s4, f32, attr_with(lambda a: a.set_scales(api.ARG_SRC, 3, (4, 1), W.BF16))) == api.success
+    assert status(s4, f32, attr_with(lambda a: a.set_scales(api.ARG_SRC, 3, (3, 1), W.BF16))) == api.invalid_arguments
+    assert status(f32, s8, attr_with(lambda a: a.set_scales(api.ARG_DST, 3, (4, 1), W.F32))) == api.invalid_arguments
+    # outside the implementation list: 4-bit targets with arithmetic or from other types, 4-bit to integers
+    assert status(f32, s4) == api.success
+    assert status(f32, s4, attr_with(lambda a: a.set_scales(api.ARG_DST, 0, (), W.F32))) == api.unimplemented
+    assert status(md((8, 16), W.BF16, tag.ab), s4) == api.unimplemented
+    assert status(s4, s8) == api.unimplemented
+    # a 4-bit tensor whose rows do not end on a byte has no plain descriptor in the first place
+    with pytest.raises(api.error):
+        md((8, 15), W.S4, tag.ab)
