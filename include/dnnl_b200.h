@@ -83,6 +83,7 @@ typedef enum { dnnl_any_engine, dnnl_cpu, dnnl_gpu } dnnl_engine_kind_t;
 typedef enum {
     dnnl_stream_in_order = 0x1U,
     dnnl_stream_out_of_order = 0x2U,
+    dnnl_stream_profiling = 0x4U, /* events around every primitive, read by dnnl_query_profiling_data */
     dnnl_stream_default_flags = dnnl_stream_in_order,
     dnnl_stream_flags_max = 0x7fff,
 } dnnl_stream_flags_t;
@@ -313,6 +314,9 @@ dnnl_status_t DNNL_API dnnl_memory_desc_create_host_scalar(dnnl_memory_desc_t *m
 dnnl_status_t DNNL_API dnnl_memory_desc_clone(dnnl_memory_desc_t *memory_desc,
         const_dnnl_memory_desc_t existing_memory_desc);
 dnnl_status_t DNNL_API dnnl_memory_desc_destroy(dnnl_memory_desc_t memory_desc);
+/* dnnl.h:1219: a window of a plain strided tensor (same strides, offset0 moved) */
+dnnl_status_t DNNL_API dnnl_memory_desc_create_submemory(dnnl_memory_desc_t *memory_desc,
+        const_dnnl_memory_desc_t parent_memory_desc, const dnnl_dims_t dims, const dnnl_dims_t offsets);
 dnnl_status_t DNNL_API dnnl_memory_desc_reshape(dnnl_memory_desc_t *out_memory_desc,
         const_dnnl_memory_desc_t in_memory_desc, int ndims, const dnnl_dims_t dims);
 dnnl_status_t DNNL_API dnnl_memory_desc_permute_axes(dnnl_memory_desc_t *out_memory_desc,
@@ -414,6 +418,14 @@ dnnl_status_t DNNL_API dnnl_post_ops_append_binary(dnnl_post_ops_t post_ops, dnn
 dnnl_status_t DNNL_API dnnl_post_ops_get_params_binary(const_dnnl_post_ops_t post_ops, int index,
         dnnl_alg_kind_t *alg_kind, const_dnnl_memory_desc_t *src1_desc);
 dnnl_status_t DNNL_API dnnl_post_ops_append_prelu(dnnl_post_ops_t post_ops, int mask);
+/* dnnl.h:924-959: the third operand belongs to binary_select, which matmul does not apply
+ * (unimplemented); for every other algorithm src2_desc must be NULL or empty */
+dnnl_status_t DNNL_API dnnl_post_ops_append_binary_v2(dnnl_post_ops_t post_ops, dnnl_alg_kind_t alg_kind,
+        const_dnnl_memory_desc_t src1_desc, const_dnnl_memory_desc_t src2_desc);
+dnnl_status_t DNNL_API dnnl_post_ops_get_params_binary_v2(const_dnnl_post_ops_t post_ops, int index,
+        dnnl_alg_kind_t *alg_kind, const_dnnl_memory_desc_t *src1_desc, const_dnnl_memory_desc_t *src2_desc);
+/* dnnl.h:1003 */
+dnnl_status_t DNNL_API dnnl_post_ops_get_params_prelu(const_dnnl_post_ops_t post_ops, int index, int *mask);
 
 /* ---- primitive descriptor / primitive (dnnl.h:51-243, 3774) ------------- */
 dnnl_status_t DNNL_API dnnl_matmul_primitive_desc_create(dnnl_primitive_desc_t *primitive_desc,
@@ -451,6 +463,44 @@ dnnl_status_t DNNL_API dnnl_primitive_get_primitive_desc(const_dnnl_primitive_t 
 dnnl_status_t DNNL_API dnnl_primitive_get_cache_blob(const_dnnl_primitive_t primitive, size_t *size,
         uint8_t *cache_blob);
 dnnl_status_t DNNL_API dnnl_primitive_destroy(dnnl_primitive_t primitive);
+
+/* ---- stream profiling (dnnl.h:4063-4085; streams created with
+ * dnnl_stream_profiling).  One entry per primitive executed since the last
+ * reset; data_kind 1 (dnnl_profiling_data_kind_time) gives nanoseconds of
+ * device time between CUDA events recorded around the primitive's kernels.
+ * Wait on the stream before querying. */
+dnnl_status_t DNNL_API dnnl_reset_profiling(dnnl_stream_t stream);
+dnnl_status_t DNNL_API dnnl_query_profiling_data(dnnl_stream_t stream, int data_kind, int *num_entries,
+        uint64_t *data);
+
+/* ---- value names (dnnl_debug.h:35-54).  The enumerations this header does
+ * not declare are taken as int. */
+#ifndef ONEAPI_DNNL_DNNL_DEBUG_H
+const char DNNL_API *dnnl_status2str(dnnl_status_t v);
+const char DNNL_API *dnnl_dt2str(dnnl_data_type_t v);
+const char DNNL_API *dnnl_fpmath_mode2str(dnnl_fpmath_mode_t v);
+const char DNNL_API *dnnl_accumulation_mode2str(dnnl_accumulation_mode_t v);
+const char DNNL_API *dnnl_engine_kind2str(dnnl_engine_kind_t v);
+const char DNNL_API *dnnl_sparse_encoding2str(dnnl_sparse_encoding_t v);
+const char DNNL_API *dnnl_fmt_tag2str(dnnl_format_tag_t v);
+const char DNNL_API *dnnl_fmt_kind2str(dnnl_format_kind_t v);
+const char DNNL_API *dnnl_prop_kind2str(int v);
+const char DNNL_API *dnnl_prim_kind2str(dnnl_primitive_kind_t v);
+const char DNNL_API *dnnl_alg_kind2str(dnnl_alg_kind_t v);
+const char DNNL_API *dnnl_rnn_flags2str(int v);
+const char DNNL_API *dnnl_rnn_direction2str(int v);
+const char DNNL_API *dnnl_scratchpad_mode2str(dnnl_scratchpad_mode_t v);
+const char DNNL_API *dnnl_rounding_mode2str(dnnl_rounding_mode_t v);
+const char DNNL_API *dnnl_quantization_mode2str(dnnl_quantization_mode_t v);
+const char DNNL_API *dnnl_cpu_isa2str(int v);
+const char DNNL_API *dnnl_cpu_isa_hints2str(int v);
+const char DNNL_API *dnnl_runtime2str(unsigned v);
+#endif
+
+/* Every other function dnnl.h declares (the other primitives' descriptor
+ * constructors, RNN / dropout attributes, sparse encodings other than
+ * grouped, the BLAS-like gemm calls) is exported as a stub that returns
+ * dnnl_unimplemented, so that unchanged programs link. */
 
 #endif /* ONEAPI_DNNL_DNNL_H */
 
@@ -494,7 +544,8 @@ const char *dnnl_cuda_interop_last_error(void);
  *    resident on every GPU that loads the library); larger N is rejected with
  *    dnnl_invalid_arguments.  K and N multiples of 16, src and weights
  *    16-byte aligned, else dnnl_unimplemented.
- *  - The first call on each device looks up the array's device address; make
+ *  - The first call on each device (with that device current) looks up the
+ *    array's device address and opts the kernel in to its shared memory; make
  *    that first call outside any stream capture.
  *  - All calls share the one array: two calls that overlap on the GPU (other
  *    streams, other threads) race.  Serialize them on one stream.
@@ -502,6 +553,16 @@ const char *dnnl_cuda_interop_last_error(void);
  * src zero-point, bit for bit. */
 dnnl_status_t dnnl_cuda_interop_matmul_u8s8s32_zp_static(void *cuda_stream, int64_t M, int64_t N, int64_t K,
         const uint8_t *src, const int8_t *weights, int32_t src_zero_point, int32_t *dst);
+
+/* Companion of the call above (no counterpart in the reference either): the
+ * kernels never trap; a wait inside them that runs out of time records
+ * status 5 (runtime_error) in a word of the same static array and leaves dst
+ * incomplete.  The word is sticky across calls.  This function waits for the
+ * work already enqueued on `cuda_stream`, copies the word of the current
+ * device to *status (0 = every call since the last query ran to completion)
+ * and clears it.  It allocates nothing; it synchronises the stream, so do not
+ * call it while the stream is being captured. */
+dnnl_status_t dnnl_cuda_interop_matmul_u8s8s32_zp_static_status(void *cuda_stream, int *status);
 
 #ifdef __cplusplus
 }

@@ -411,6 +411,15 @@ dnnl_status_t woq_accepts(const dnnl_primitive_desc &pd) {
     return dnnl_success;
 }
 
+// int4 decompression through tensor memory: what the skinny GEMM accepts, with
+// the src rows reachable by TMA (16-byte row pitch unless there is one row)
+dnnl_status_t woq_tc_accepts(const dnnl_primitive_desc &pd) {
+    if (woq_accepts(pd) != dnnl_success) return dnnl_unimplemented;
+    UNIMPL_IF(pd.M() > 1 && pd.src.strides[0] % 8 != 0);
+    UNIMPL_IF(pd.wei.strides[0] % 32 != 0);
+    return dnnl_success;
+}
+
 // weight zero-points the s8-decompression tensor-core kernel handles: one per
 // (expert, column) for grouped problems, one per tensor or per column otherwise
 bool woq_tc_wei_zp_ok(const dnnl_primitive_desc &pd) {
@@ -474,6 +483,10 @@ dnnl_status_t impl_accepts(const dnnl_primitive_desc &pd, int impl, std::string 
             }
             name = "cuda:tcgen05:grouped";
             return grouped_tc_accepts(pd);
+        case IMPL_WOQ_TC:
+            if (pd.grouped) return dnnl_unimplemented;
+            name = "cuda:tcgen05:woq4";
+            return woq_tc_accepts(pd);
         case IMPL_WOQ_GEMV:
             if (pd.grouped) return dnnl_unimplemented;
             name = "cuda:woq:skinny";
@@ -501,6 +514,9 @@ dnnl_status_t select_impl(dnnl_primitive_desc &pd, int first) {
             if (i == IMPL_TCGEN05_GEMM && (pd.attr.zp(DNNL_ARG_SRC).set || pd.attr.zp(DNNL_ARG_WEIGHTS).set))
                 pd.scratch_bytes = gemm_tc_scratch_bytes(pd.M(), pd.N());
             // the skinny GEMM keeps split-K partial sums and arrival counters there
+            if (i == IMPL_WOQ_TC)
+                pd.scratch_bytes = woq_tc_scratch_bytes(
+                        pd.M(), pd.N(), pd.K(), pd.engine->sm_count > 0 ? pd.engine->sm_count : 148);
             if (i == IMPL_WOQ_GEMV)
                 pd.scratch_bytes = woq_skinny_scratch_bytes(
                         pd.N(), pd.K(), pd.engine->sm_count > 0 ? pd.engine->sm_count : 148);
@@ -706,6 +722,7 @@ dnnl_status_t dnnl_primitive_create(dnnl_primitive_t *primitive, const_dnnl_prim
         }
     }
     *primitive = p;
+    if (verbose_level() >= 2) verbose_line("create:cache_miss", p->pd, 0.0); // there is no primitive cache
     return dnnl_success;
 }
 
@@ -800,18 +817,22 @@ extern "C" dnnl_status_t dnnl_primitive_execute(const_dnnl_primitive_t primitive
     for (const auto &e : attr.post_ops.entries) expect_in += e.kind == dnnl_binary;
     if (n_in != expect_in) return dnnl_invalid_arguments;
 
+    // a descriptor made by dnnl_memory_desc_create_submemory starts offset0 elements into the buffer
+    auto at_offset0 = [](void *h, const dnnl_memory_desc &md) -> void * {
+        return h && md.offset0 ? (char *)h + md.offset0 * (dnnl_dim_t)dt_bits(md.data_type) / 8 : h;
+    };
     MatmulArgs a {};
     a.M = pd.M(); a.N = pd.N(); a.K = pd.K();
-    a.src = src->handles[0]; a.src_dt = pd.src.data_type;
+    a.src = at_offset0(src->handles[0], pd.src); a.src_dt = pd.src.data_type;
     a.src_sm = pd.src.strides[0]; a.src_sk = pd.src.strides[1];
-    a.wei = wei->handles[0]; a.wei_dt = pd.wei.data_type;
-    a.dst = dst->handles[0]; a.dst_dt = pd.dst.data_type;
+    a.wei = at_offset0(wei->handles[0], pd.wei); a.wei_dt = pd.wei.data_type;
+    a.dst = at_offset0(dst->handles[0], pd.dst); a.dst_dt = pd.dst.data_type;
     a.dst_sm = pd.dst.strides[0]; a.dst_sn = pd.dst.strides[1];
     const int wl = pd.grouped ? 1 : 0; // leading (expert) dim of the weights
     a.wei_sk = pd.wei.strides[wl + 0]; a.wei_sn = pd.wei.strides[wl + 1];
     a.wei_sg = pd.grouped ? pd.wei.strides[0] : 0;
     if (bias) {
-        a.bias = bias->handles[0]; a.bias_dt = pd.bias.data_type;
+        a.bias = at_offset0(bias->handles[0], pd.bias); a.bias_dt = pd.bias.data_type;
         if (pd.grouped) { a.bias_sg = pd.bias.strides[0]; a.bias_sn = 1; }
         else {
             a.bias_sm = pd.bias.dims[0] > 1 ? pd.bias.strides[0] : 0;
@@ -887,6 +908,7 @@ extern "C" dnnl_status_t dnnl_primitive_execute(const_dnnl_primitive_t primitive
         cudaEventCreate(&ev0); cudaEventCreate(&ev1);
         cudaEventRecord(ev0, stream->stream);
     }
+    profiling_begin(stream);
     void *scratch = primitive->scratch;
     if (pd.scratch_bytes && pd.attr.scratchpad_mode == dnnl_scratchpad_mode_user) {
         dnnl_memory_t sp = am.find(DNNL_ARG_SCRATCHPAD);
@@ -896,6 +918,15 @@ extern "C" dnnl_status_t dnnl_primitive_execute(const_dnnl_primitive_t primitive
     int rc;
     switch (pd.impl) {
         case IMPL_REF: rc = launch_ref(a, stream->stream); break;
+        case IMPL_WOQ_TC:
+            if (!woq_tc_pointers_ok(a)) {
+                rc = launch_ref(a, stream->stream); // misaligned user pointers: generic kernel
+            } else {
+                if (pd.attr.scratchpad_mode == dnnl_scratchpad_mode_user) // counters of a user buffer
+                    cudaMemsetAsync(scratch, 0, ((pd.N() + 255) / 256) * sizeof(int), stream->stream);
+                rc = launch_woq_tc(a, scratch, pd.engine->sm_count, stream->stream);
+            }
+            break;
         case IMPL_WOQ_GEMV:
             if ((uintptr_t)a.wei % 16 || (uintptr_t)a.src % 4 || (uintptr_t)a.wei_scale.ptr % 16
                     || (a.wei_zp.ptr && (uintptr_t)a.wei_zp.ptr % 16)) {
@@ -918,17 +949,14 @@ extern "C" dnnl_status_t dnnl_primitive_execute(const_dnnl_primitive_t primitive
             break;
         default: rc = dnnl_unimplemented;
     }
+    profiling_end(stream);
     if (verbose) {
         cudaEventRecord(ev1, stream->stream);
         cudaEventSynchronize(ev1);
         float ms = 0;
         cudaEventElapsedTime(&ms, ev0, ev1);
         cudaEventDestroy(ev0); cudaEventDestroy(ev1);
-        // same field order as oneDNN's verbose exec line (src/common/verbose.hpp:181)
-        printf("onednn_verbose,v1,primitive,exec,gpu,matmul,%s,undef,src:%d wei:%d dst:%d,,,%lldx%lld:%lldx%lld,%g\n",
-                pd.impl_name.c_str(), (int)pd.src.data_type, (int)pd.wei.data_type, (int)pd.dst.data_type,
-                (long long)a.M, (long long)a.K, (long long)a.K, (long long)a.N, ms);
-        fflush(stdout);
+        verbose_line("exec", pd, ms); // device time of the primitive's kernels
     }
     if (rc == 5) set_last_error(std::string("kernel launch: ") + cudaGetErrorString(cudaGetLastError()));
     return (dnnl_status_t)rc;

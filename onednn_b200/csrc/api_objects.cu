@@ -204,6 +204,7 @@ dnnl_status_t dnnl_stream_destroy(dnnl_stream_t stream) {
         cudaStreamSynchronize(stream->stream);
         cudaStreamDestroy(stream->stream);
     }
+    profiling_clear(stream);
     dnnl_engine_destroy(stream->engine);
     delete stream;
     return dnnl_success;

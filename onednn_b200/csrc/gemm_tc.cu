@@ -27,6 +27,7 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
+#include <mutex>
 #include <string>
 
 #include "device_math.cuh"
@@ -50,7 +51,9 @@ struct TcParams {
     int num_m_tiles, num_n_tiles, num_k_blocks;
     uint32_t idesc;
     int w_kmajor; // weights are `ba` (K contiguous)
-    int mainloop_only; // ONEDNN_CUDA_TC_MAINLOOP_ONLY=1: skip the epilogue (profiling aid)
+#ifdef QMM_PROFILE
+    int mainloop_only; // 1 no epilogue, 2 TMEM reads only, 3 everything but the stores (wrong results)
+#endif
     const int32_t *colsum; // sum_k w[k][n]       (src zero-point compensation)
     const int32_t *rowsum; // sum_k s[m][k]       (weights zero-point compensation)
 };
@@ -129,7 +132,9 @@ __device__ __forceinline__ void store_typed(void *p, float v) {
         *(float *)p = v;
     } else if constexpr (DST == DT_BF16) {
         if (fabsf(v) < 1.17549435e-38f) v = copysignf(0.f, v);
-        *(__nv_bfloat16 *)p = __float2bfloat16_rn(v);
+        unsigned short b = __bfloat16_as_ushort(__float2bfloat16_rn(v));
+        if (v != v) b = (unsigned short)((__float_as_uint(v) >> 16) | 0x40u); // NaN: payload kept, quiet bit set
+        *(unsigned short *)p = b;
     } else if constexpr (DST == DT_F16) {
         *(__half *)p = __float2half_rn(v);
     } else if constexpr (DST == DT_S32) {
@@ -200,13 +205,15 @@ __device__ __forceinline__ void epilogue_rows(const MatmulArgs &a, const TcParam
 #pragma unroll
         for (int j = 0; j < R; ++j) d[j] = __fadd_rn(d[j], z);
     }
-    if (tp.mainloop_only == 3) { // profiling aid: everything but the stores
+#ifdef QMM_PROFILE
+    if (tp.mainloop_only == 3) { // everything but the stores
         float acc = 0.f;
 #pragma unroll
         for (int j = 0; j < R; ++j) acc += d[j];
         if (acc == 123.456f) store_typed<DST>(dptr, acc);
         return;
     }
+#endif
 #pragma unroll
     for (int j = 0; j < R; ++j)
         if (j < rows) store_typed<DST>(dptr + j * dstep, d[j]);
@@ -333,12 +340,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
             const ColTerms ct = load_col_terms<INT>(a, tp, n); // in flight while waiting for the MMAs
             if (!ptx::mbar_wait(&tmem_full[as], aph)) { *abort_flag = 1; atomicExch(a.status, 5); break; }
             ptx::tc_fence_after_sync();
-            if (tp.mainloop_only == 1) { // profiling aid: results are not stored
+#ifdef QMM_PROFILE
+            if (tp.mainloop_only == 1) { // results are not stored
                 ptx::tc_fence_before_sync();
                 __syncwarp();
                 if (lane == 0) ptx::mbar_arrive(&tmem_empty[as]);
                 continue;
             }
+#endif
             if constexpr (CHAIN) {
                 // With a post-op chain the code of 32 unrolled rows exceeds the instruction cache, so the
                 // rows go through a rolled loop of 8-row pieces (8 independent dependency chains each).
@@ -353,7 +362,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
                         if (lane == 0) ptx::mbar_arrive(&tmem_empty[as]);
                     }
                     const int64_t m0 = m_tile + c * 8;
-                    if (tp.mainloop_only == 2) continue; // profiling aid: TMEM reads only
+#ifdef QMM_PROFILE
+                    if (tp.mainloop_only == 2) continue; // TMEM reads only
+#endif
                     if (m0 < a.M) epilogue_rows_any<INT, CHAIN, 8>(a, tp, tt, ct, r, m0, n);
                 }
             } else {
@@ -368,7 +379,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
                         if (lane == 0) ptx::mbar_arrive(&tmem_empty[as]);
                     }
                     const int64_t m0 = m_tile + c * 32;
-                    if (tp.mainloop_only == 2) continue; // profiling aid: TMEM reads only
+#ifdef QMM_PROFILE
+                    if (tp.mainloop_only == 2) continue; // TMEM reads only
+#endif
                     if (m0 < a.M) epilogue_rows_any<INT, CHAIN, 32>(a, tp, tt, ct, r, m0, n);
                 }
             }
@@ -386,14 +399,63 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
 }
 
 // ---- zero-point compensation terms (int8 path) ----------------------------
-// colsum[n] = sum_k w[k][n]; one thread per column, coalesced over n for
-// N-contiguous weights.
-__global__ void colsum_kernel(const __grid_constant__ MatmulArgs a, int32_t *colsum) {
-    const int64_t n = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (n >= a.N) return;
-    int s = 0;
-    for (int64_t k = 0; k < a.K; ++k) s += load_int(a.wei_dt, a.wei, k * a.wei_sk + n * a.wei_sn);
-    colsum[n] = s;
+// colsum[n] += sum over a chunk of k of w[k][n] (colsum zeroed beforehand).
+// A block covers 128 columns x `kchunk` rows with 8 warps: a lane owns four
+// neighbouring columns, the warps take every 8th row, the block adds its
+// warps' sums in shared memory and issues one atomic add per column (integer
+// addition: the result does not depend on the order).  VEC: weights are
+// N-contiguous bytes with a 4-byte aligned pitch, so a lane's four columns are
+// one 32-bit load and dp4a adds each byte into its own sum.
+template <bool VEC>
+__global__ void __launch_bounds__(256) colsum_kernel(const __grid_constant__ MatmulArgs a, int32_t *colsum, int kchunk) {
+    __shared__ int part[8][128];
+    const int lane = threadIdx.x & 31, kl = threadIdx.x >> 5;
+    const int64_t n0 = (int64_t)blockIdx.x * 128 + lane * 4;
+    const int64_t k0 = (int64_t)blockIdx.y * kchunk, k1 = min(a.K, k0 + kchunk);
+    int s0 = 0, s1 = 0, s2 = 0, s3 = 0;
+    if (VEC) {
+        if (n0 < a.N) {
+            const char *col = (const char *)a.wei + n0;
+            if (a.wei_dt == DT_S8) {
+#pragma unroll 4
+                for (int64_t k = k0 + kl; k < k1; k += 8) {
+                    const int v = *(const int *)(col + k * a.wei_sk);
+                    s0 = __dp4a(v, 0x00000001, s0);
+                    s1 = __dp4a(v, 0x00000100, s1);
+                    s2 = __dp4a(v, 0x00010000, s2);
+                    s3 = __dp4a(v, 0x01000000, s3);
+                }
+            } else {
+#pragma unroll 4
+                for (int64_t k = k0 + kl; k < k1; k += 8) {
+                    const unsigned v = *(const unsigned *)(col + k * a.wei_sk);
+                    s0 += v & 0xffu;
+                    s1 += (v >> 8) & 0xffu;
+                    s2 += (v >> 16) & 0xffu;
+                    s3 += v >> 24;
+                }
+            }
+        }
+    } else {
+        for (int64_t k = k0 + kl; k < k1; k += 8) {
+            if (n0 + 0 < a.N) s0 += load_int(a.wei_dt, a.wei, k * a.wei_sk + (n0 + 0) * a.wei_sn);
+            if (n0 + 1 < a.N) s1 += load_int(a.wei_dt, a.wei, k * a.wei_sk + (n0 + 1) * a.wei_sn);
+            if (n0 + 2 < a.N) s2 += load_int(a.wei_dt, a.wei, k * a.wei_sk + (n0 + 2) * a.wei_sn);
+            if (n0 + 3 < a.N) s3 += load_int(a.wei_dt, a.wei, k * a.wei_sk + (n0 + 3) * a.wei_sn);
+        }
+    }
+    part[kl][lane * 4 + 0] = s0;
+    part[kl][lane * 4 + 1] = s1;
+    part[kl][lane * 4 + 2] = s2;
+    part[kl][lane * 4 + 3] = s3;
+    __syncthreads();
+    if (threadIdx.x < 128) {
+        const int64_t n = (int64_t)blockIdx.x * 128 + threadIdx.x;
+        int s = 0;
+#pragma unroll
+        for (int w = 0; w < 8; ++w) s += part[w][threadIdx.x];
+        if (n < a.N) atomicAdd(colsum + n, s);
+    }
 }
 // rowsum[m] = sum_k s[m][k]; one warp per row
 __global__ void rowsum_kernel(const __grid_constant__ MatmulArgs a, int32_t *rowsum) {
@@ -441,11 +503,8 @@ int launch_cfg(const CUtensorMap &mw, const CUtensorMap &ms, const MatmulArgs &a
         cudaStream_t st) {
     using L = SmemLayout<BT_M, STAGES>;
     auto kern = gemm_tc_kernel<KIND, BT_M, STAGES, CHAIN>;
-    static bool configured = false;
-    if (!configured) {
-        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL) != cudaSuccess) return 5;
-        configured = true;
-    }
+    static std::atomic<unsigned long long> configured; // one per instantiation of this template
+    if (!opt_in_dynamic_smem(kern, L::TOTAL, configured)) return 5;
     const int tiles = tp.num_m_tiles * tp.num_n_tiles;
     const int grid = tiles < sm_count ? tiles : sm_count;
     kern<<<grid, num_threads(CHAIN), L::TOTAL, st>>>(mw, ms, a, tp);
@@ -472,15 +531,26 @@ int launch_gemm_tc(const MatmulArgs &a, void *scratch, int sm_count, cudaStream_
     tp.num_n_tiles = (int)((a.N + BT_N - 1) / BT_N);
     tp.num_k_blocks = (int)((a.K + BKB - 1) / BKB);
     tp.w_kmajor = w_kmajor;
-    // profiling aid: 1 = no epilogue, 2 = TMEM reads only, 3 = everything but the stores
+#ifdef QMM_PROFILE // a build with -DQMM_PROFILE reads the switch; the shipped library has no such code
     static const int mainloop_only = getenv("ONEDNN_CUDA_TC_MAINLOOP_ONLY") ? atoi(getenv("ONEDNN_CUDA_TC_MAINLOOP_ONLY")) : 0;
     tp.mainloop_only = mainloop_only;
+#endif
 
     int32_t *colsum = (int32_t *)scratch;
     int32_t *rowsum = colsum ? colsum + ((a.N + 63) / 64) * 64 : nullptr;
     if (int_path && a.src_zp.ptr) {
         if (!scratch) return 5;
-        colsum_kernel<<<(unsigned)((a.N + 127) / 128), 128, 0, st>>>(a, colsum);
+        // enough blocks to fill the GPU, at least 64 rows each
+        const unsigned nb = (unsigned)((a.N + 127) / 128);
+        int64_t chunks = (4 * (int64_t)(sm_count > 0 ? sm_count : 148) + nb - 1) / nb;
+        chunks = chunks < 1 ? 1 : (chunks > (a.K + 63) / 64 ? (a.K + 63) / 64 : chunks);
+        const int kchunk = (int)(((a.K + chunks - 1) / chunks + 7) / 8 * 8);
+        const dim3 grid(nb, (unsigned)((a.K + kchunk - 1) / kchunk));
+        if (cudaMemsetAsync(colsum, 0, (size_t)a.N * sizeof(int32_t), st) != cudaSuccess) return 5;
+        const bool vec = a.wei_sn == 1 && a.wei_sk % 4 == 0 && (uintptr_t)a.wei % 4 == 0 && a.N % 4 == 0
+                && (a.wei_dt == DT_S8 || a.wei_dt == DT_U8);
+        if (vec) colsum_kernel<true><<<grid, 256, 0, st>>>(a, colsum, kchunk);
+        else colsum_kernel<false><<<grid, 256, 0, st>>>(a, colsum, kchunk);
         count_launch();
         tp.colsum = colsum;
     }
@@ -535,16 +605,52 @@ constexpr int64_t STATIC_MAX_N = 131072;
 constexpr int STATIC_HEADER_WORDS = 64;
 static __device__ __align__(256) int32_t g_static_scratch[STATIC_HEADER_WORDS + STATIC_MAX_N];
 
-__global__ void static_scratch_header_kernel(int32_t *hdr, int32_t zero_point) {
-    hdr[0] = zero_point; // read by the GEMM epilogue as the src zero-point
-    hdr[1] = 0; // status word: must start at zero for every call
+// hdr[0]: the src zero-point of the call in flight, read by the GEMM epilogue.
+// hdr[1]: the kernels' status word.  It starts at zero when the library is
+// loaded and is sticky: a call never clears it, so a bounded wait that expired
+// in any earlier call stays visible until ..._static_status reads and resets it.
+__global__ void static_scratch_header_kernel(int32_t *hdr, int32_t zero_point) { hdr[0] = zero_point; }
+__global__ void static_scratch_status_reset_kernel(int32_t *hdr) { hdr[1] = 0; }
+
+// Device address of the static scratch on the current device (looked up once
+// per device; the table is filled under a mutex so that two host threads may
+// make their first calls together).
+constexpr int STATIC_MAX_DEVICES = 64;
+struct StaticScratchSlot {
+    int32_t *ptr = nullptr;
+    int sm_count = 0;
+};
+bool static_scratch_of_current_device(StaticScratchSlot *out) {
+    static StaticScratchSlot slots[STATIC_MAX_DEVICES];
+    static std::mutex mu;
+    int dev = 0;
+    if (!cuda_ok(cudaGetDevice(&dev), "cudaGetDevice")) return false;
+    if (dev < 0 || dev >= STATIC_MAX_DEVICES) {
+        set_last_error("static scratch: device ordinal beyond 63");
+        return false;
+    }
+    std::lock_guard<std::mutex> lock(mu);
+    if (!slots[dev].ptr) { // set-up, once per device; not to be done under stream capture
+        void *p = nullptr;
+        // the array's NAME is a host-side stand-in here; kernels need its device address
+        if (!cuda_ok(cudaGetSymbolAddress(&p, g_static_scratch), "cudaGetSymbolAddress")) return false;
+        int sms = 0;
+        if (!cuda_ok(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev), "cudaDeviceGetAttribute"))
+            return false;
+        slots[dev].sm_count = sms;
+        slots[dev].ptr = (int32_t *)p;
+    }
+    *out = slots[dev];
+    return true;
 }
 
 } // namespace qmm
 
 // Host side of the static scratch: the array's NAME is only a host-side
 // stand-in here; kernels need its device address, looked up once per device
-// (with that device current) by cudaGetSymbolAddress.
+// (with that device current) by cudaGetSymbolAddress.  The call allocates
+// nothing: it enqueues a memset of the column sums, three small kernels and
+// the GEMM on the caller's stream.
 extern "C" dnnl_status_t dnnl_cuda_interop_matmul_u8s8s32_zp_static(void *cuda_stream, int64_t M, int64_t N,
         int64_t K, const uint8_t *src, const int8_t *weights, int32_t src_zero_point, int32_t *dst) {
     using namespace qmm;
@@ -561,22 +667,9 @@ extern "C" dnnl_status_t dnnl_cuda_interop_matmul_u8s8s32_zp_static(void *cuda_s
                        "src / weights pointers 16-byte aligned");
         return (dnnl_status_t)3; // unimplemented
     }
-    int dev = 0;
-    if (!cuda_ok(cudaGetDevice(&dev), "cudaGetDevice")) return (dnnl_status_t)5;
-    constexpr int MAX_DEVICES = 64;
-    static int32_t *scratch_of[MAX_DEVICES] = {};
-    static int sm_count_of[MAX_DEVICES] = {};
-    if (dev < 0 || dev >= MAX_DEVICES) return (dnnl_status_t)3;
-    if (!scratch_of[dev]) { // set-up, once per device; not to be done under stream capture
-        void *p = nullptr;
-        if (!cuda_ok(cudaGetSymbolAddress(&p, g_static_scratch), "cudaGetSymbolAddress")) return (dnnl_status_t)5;
-        int sms = 0;
-        if (!cuda_ok(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev), "cudaDeviceGetAttribute"))
-            return (dnnl_status_t)5;
-        sm_count_of[dev] = sms;
-        scratch_of[dev] = (int32_t *)p;
-    }
-    int32_t *hdr = scratch_of[dev];
+    StaticScratchSlot slot;
+    if (!static_scratch_of_current_device(&slot)) return (dnnl_status_t)5;
+    int32_t *hdr = slot.ptr;
     cudaStream_t st = (cudaStream_t)cuda_stream;
     static_scratch_header_kernel<<<1, 1, 0, st>>>(hdr, src_zero_point);
     count_launch();
@@ -593,7 +686,32 @@ extern "C" dnnl_status_t dnnl_cuda_interop_matmul_u8s8s32_zp_static(void *cuda_s
     a.non_default_attr = 1;
     a.sum_dt = DT_S32;
     a.status = hdr + 1;
-    const int rc = launch_gemm_tc(a, hdr + STATIC_HEADER_WORDS, sm_count_of[dev], st);
+    const int rc = launch_gemm_tc(a, hdr + STATIC_HEADER_WORDS, slot.sm_count, st);
     if (rc == 5) set_last_error(std::string("kernel launch: ") + cudaGetErrorString(cudaGetLastError()));
     return (dnnl_status_t)rc;
+}
+
+// Reads the sticky status word of the static entry point on the current
+// device: waits for the work already enqueued on `cuda_stream`, copies the word
+// to *status (0 = every call since the last query completed; 5 = a bounded
+// wait inside a kernel expired and its dst is incomplete) and resets it.
+// Allocates nothing; synchronises the stream, so it is not for use while the
+// stream is being captured.
+extern "C" dnnl_status_t dnnl_cuda_interop_matmul_u8s8s32_zp_static_status(void *cuda_stream, int *status) {
+    using namespace qmm;
+    if (!status) return (dnnl_status_t)2;
+    StaticScratchSlot slot;
+    if (!static_scratch_of_current_device(&slot)) return (dnnl_status_t)5;
+    cudaStream_t st = (cudaStream_t)cuda_stream;
+    int32_t word = 0;
+    if (!cuda_ok(cudaMemcpyAsync(&word, slot.ptr + 1, sizeof(word), cudaMemcpyDeviceToHost, st), "cudaMemcpyAsync"))
+        return (dnnl_status_t)5;
+    if (!cuda_ok(cudaStreamSynchronize(st), "cudaStreamSynchronize")) return (dnnl_status_t)5;
+    *status = word;
+    if (word != 0) {
+        static_scratch_status_reset_kernel<<<1, 1, 0, st>>>(slot.ptr);
+        count_launch();
+        if (!cuda_ok(cudaGetLastError(), "status reset")) return (dnnl_status_t)5;
+    }
+    return (dnnl_status_t)0;
 }

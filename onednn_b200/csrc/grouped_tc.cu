@@ -450,12 +450,8 @@ int launch_grouped_tc(const MatmulArgs &a, void *scratch, int sm_count, cudaStre
     // epilogue with zero-points / bias / post-ops: its own instantiation
     const bool chain = a.bias != nullptr || a.n_po > 0 || a.wei_zp.ptr != nullptr;
     auto kern = chain ? grouped_tc_kernel<true> : grouped_tc_kernel<false>;
-    static bool configured[2] = {false, false};
-    if (!configured[chain]) {
-        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, G_SMEM_BYTES) != cudaSuccess)
-            return 5;
-        configured[chain] = true;
-    }
+    static std::atomic<unsigned long long> configured[2];
+    if (!opt_in_dynamic_smem(kern, G_SMEM_BYTES, configured[chain])) return 5;
     kern<<<sm_count > 0 ? sm_count : 148, G_THREADS, G_SMEM_BYTES, st>>>(tw, ts, a, plan, rowsum, num_n_tiles, num_k_blocks);
     count_launch();
     return cudaGetLastError() == cudaSuccess ? 0 : 5;

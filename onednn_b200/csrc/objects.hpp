@@ -8,7 +8,9 @@
 
 #include <atomic>
 #include <map>
+#include <mutex>
 #include <string>
+#include <utility>
 #include <vector>
 
 #include "dnnl_b200.h"
@@ -26,6 +28,10 @@ struct dnnl_stream {
     cudaStream_t stream = nullptr;
     bool owned = true;
     unsigned flags = 0;
+    // dnnl_stream_profiling: one (start, stop) event pair per executed primitive
+    std::vector<std::pair<cudaEvent_t, cudaEvent_t>> prof;
+    std::mutex prof_mu;
+    bool prof_open = false;
 };
 
 struct dnnl_memory_desc {
@@ -124,7 +130,8 @@ struct dnnl_primitive_attr {
 // One entry of the implementation list walked by primitive_desc_next_impl.
 enum impl_id_t : int {
     IMPL_TCGEN05_GEMM = 0, // tensor-core int8 / fp8 GEMM
-    IMPL_WOQ_GEMV, // weight-decompression skinny GEMM (M <= 32)
+    IMPL_WOQ_TC, // int4 weight decompression through tensor memory (M <= 32)
+    IMPL_WOQ_GEMV, // weight-decompression skinny GEMM (M <= 32), mma.sync
     IMPL_GROUPED_TC, // grouped (MoE) tensor-core GEMM
     IMPL_REF, // generic kernels, every attribute
     IMPL_COUNT
@@ -159,6 +166,14 @@ bool cuda_ok(cudaError_t e, const char *what);
 int verbose_level();
 size_t dt_bits(dnnl_data_type_t dt);
 size_t md_bytes(const dnnl_memory_desc &md, int index);
+const char *dt_name(int dt);
+// api_misc.cu: the fields of a verbose line that describe the primitive, and the line itself
+std::string pd_info_string(const dnnl_primitive_desc &pd);
+void verbose_line(const char *operation, const dnnl_primitive_desc &pd, double ms);
+// api_misc.cu: event pair around one primitive on a profiling stream
+void profiling_begin(dnnl_stream_t s);
+void profiling_end(dnnl_stream_t s);
+void profiling_clear(dnnl_stream_t s);
 // reorder.cu: enqueues the reorder described by pd on the stream
 dnnl_status_t execute_reorder(const dnnl_primitive_desc &pd, dnnl_stream_t stream, int nargs,
         const dnnl_exec_arg_t *args);

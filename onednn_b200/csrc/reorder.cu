@@ -589,6 +589,7 @@ dnnl_status_t qmm::execute_reorder(const dnnl_primitive_desc &pd, dnnl_stream_t 
         cudaEventCreate(&ev0); cudaEventCreate(&ev1);
         cudaEventRecord(ev0, stream->stream);
     }
+    profiling_begin(stream);
     if (dense4) {
         // x: the columns in chunks of four; y: as many row walkers as fill the SMs eight CTAs deep
         const int64_t cols = a.dims[a.order[0]], rows = nelems / cols;
@@ -629,15 +630,14 @@ dnnl_status_t qmm::execute_reorder(const dnnl_primitive_desc &pd, dnnl_stream_t 
     }
     count_launch();
     const bool ok = cudaGetLastError() == cudaSuccess;
+    profiling_end(stream);
     if (verbose) {
         cudaEventRecord(ev1, stream->stream);
         cudaEventSynchronize(ev1);
         float ms = 0;
         cudaEventElapsedTime(&ms, ev0, ev1);
         cudaEventDestroy(ev0); cudaEventDestroy(ev1);
-        printf("onednn_verbose,v1,primitive,exec,gpu,reorder,%s,undef,src:%d dst:%d,,,%lld,%g\n", pd.impl_name.c_str(),
-                a.src_dt, a.dst_dt, (long long)nelems, ms);
-        fflush(stdout);
+        verbose_line("exec", pd, ms);
     }
     if (!ok) {
         set_last_error("kernel launch: reorder");

@@ -530,11 +530,8 @@ int launch_woq_skinny(const MatmulArgs &a, void *scratch, int sm_count, cudaStre
     const int variant = f16 ? 2 : (zpmma ? 1 : 0);
     auto kern = f16 ? woq_skinny_kernel<true, false>
                     : (zpmma ? woq_skinny_kernel<false, true> : woq_skinny_kernel<false, false>);
-    static bool configured[3] = {false, false, false};
-    if (!configured[variant]) {
-        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess) return 5;
-        configured[variant] = true;
-    }
+    static std::atomic<unsigned long long> configured[3];
+    if (!opt_in_dynamic_smem(kern, SMEM_BYTES, configured[variant])) return 5;
     for (int64_t m0 = 0; m0 < a.M; m0 += MB) { // more than 8 rows: one pass over the weights per 8 rows
         p.m_base = m0;
         p.M = (int)((a.M - m0) < MB ? (a.M - m0) : MB);

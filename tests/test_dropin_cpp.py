@@ -33,7 +33,7 @@ def test_unchanged_dnnl_hpp_program_builds_and_dispatches(tmp_path):
     out = dict(line.split(" ", 1) for line in r.stdout.strip().splitlines())
     assert out["int8_zp"] == "cuda:tcgen05:int8"
     assert out["fp8"] == "cuda:tcgen05:fp8"
-    assert out["int4"] == "cuda:woq:skinny"
+    assert out["int4"] == "cuda:tcgen05:woq4"
     assert out["int4_last"] == "cuda:ref:any"
     assert out["int8_postops"] == "cuda:tcgen05:int8"
     assert out["grouped"] == "cuda:tcgen05:grouped"

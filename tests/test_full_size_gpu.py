@@ -61,7 +61,7 @@ def test_cfg3_int4_decode_full_size(gpu, M):
     eng, strm = gpu
     p = W.int4_decode(M)  # K = 8192, N = 28672, groups of 128
     got, impl = run_problem(p, eng, strm)
-    assert impl == "cuda:woq:skinny"
+    assert impl == "cuda:tcgen05:woq4"
     rows = np.unique(np.array([0, M // 2, M - 1]))
     _check_rows(p, got, rows, _dense_slack(p, rows), "int4 decode M=%d" % M)
     got2, _ = run_problem(p, eng, strm)

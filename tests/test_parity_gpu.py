@@ -131,16 +131,27 @@ WOQ_CASES = {
 }
 
 
+WOQ_CASES.update({
+    "m16": lambda: W.int4_decode(16, 1024, 512),
+    "m32_wide": lambda: W.int4_decode(32, 2048, 1536),
+    "m9_many_tiles": lambda: W.int4_decode(9, 4096, 2080),
+    "k_tail_stage": lambda: W.int4_decode(5, 1104, 512, group=48),
+    "u4_no_zp_f32": lambda: W.int4_decode(3, 768, 256, wei_dt=W.U4, with_zp=False, dst_dt=W.F32),
+})
+
+
+@pytest.mark.parametrize("kernel", ["cuda:tcgen05:woq4", "cuda:woq:skinny"])
 @pytest.mark.parametrize("name", sorted(WOQ_CASES))
-def test_woq_skinny_matches_oracle(gpu, name):
+def test_woq_decode_matches_oracle(gpu, name, kernel):
+    """Both int4 decompression kernels (tensor-memory operand; mma.sync) on every case."""
     eng, strm = gpu
     p = WOQ_CASES[name]()
     want = O.run_port(p)
-    got, impl = run_problem(p, eng, strm, impl="woq")
-    assert impl == "cuda:woq:skinny"
+    got, impl = run_problem(p, eng, strm, impl=kernel)
+    assert impl == kernel
     assert_parity(got, want, p.dst_dt, name, slack_for(p, impl))
     # the arrival counters are left at zero: a second execution gives the same bits
-    got2, _ = run_problem(p, eng, strm, impl="woq")
+    got2, _ = run_problem(p, eng, strm, impl=kernel)
     assert np.array_equal(got, got2)
 
 
