@@ -93,6 +93,9 @@ def _check(status, what):
         raise error(status, what)
 
 
+RUNTIME_DIM_VAL = -(1 << 63)  # DNNL_RUNTIME_DIM_VAL
+
+
 def _dims(seq):
     d = _dims_t()
     for i, v in enumerate(seq):

@@ -595,6 +595,33 @@ dnnl_status_t dnnl_matmul_primitive_desc_create(dnnl_primitive_desc_t *primitive
     if (attr) pd->attr = *attr;
     pd->grouped = src_desc->is_grouped();
 
+    // Run-time shapes (DNNL_RUNTIME_DIM_VAL, src/common/matmul.cpp:630-744): supported for the row
+    // count M of a 2D problem, the one the reference's tutorials leave open (a dynamic batch); every
+    // other dim, the weights and the strides must be known.  The descriptor is checked with M = 1
+    // and settled again, with the M of the memory objects, at every execution.
+    if (pd->src.has_runtime_dims() || pd->wei.has_runtime_dims() || pd->dst.has_runtime_dims()
+            || pd->bias.has_runtime_dims()) {
+        const bool ok = !pd->grouped && pd->src.ndims == 2 && pd->dst.ndims == 2 && pd->wei.ndims == 2
+                && pd->src.dims[0] == DNNL_RUNTIME_DIM_VAL && pd->dst.dims[0] == DNNL_RUNTIME_DIM_VAL
+                && pd->src.dims[1] != DNNL_RUNTIME_DIM_VAL && pd->dst.dims[1] != DNNL_RUNTIME_DIM_VAL
+                && !pd->wei.has_runtime_dims() && !pd->bias.has_runtime_dims()
+                && (pd->bias.ndims == 0 || pd->bias.dims[0] == 1);
+        bool strides_known = true;
+        for (auto *md : {&pd->src, &pd->dst})
+            if (md->format_kind == dnnl_blocked)
+                strides_known = strides_known && md->strides[0] != DNNL_RUNTIME_DIM_VAL && md->strides[1] != DNNL_RUNTIME_DIM_VAL;
+        bool binary_known = true;
+        for (auto &e : pd->attr.post_ops.entries)
+            if (e.kind == dnnl_binary && (e.src1.has_runtime_dims() || (e.src1.ndims == 2 && e.src1.dims[0] != 1)))
+                binary_known = false; // an operand with M rows needs the M
+        if (!ok || !strides_known || !binary_known) {
+            delete pd;
+            return dnnl_unimplemented;
+        }
+        pd->runtime_m = true;
+        pd->src.dims[0] = pd->dst.dims[0] = 1;
+    }
+
     dnnl_status_t st = pd->grouped ? grouped_desc_check(pd->src, pd->wei, bias, pd->dst)
                                    : dense_desc_check(pd->src, pd->wei, bias, pd->dst);
     if (st == dnnl_success) {
@@ -615,6 +642,7 @@ dnnl_status_t dnnl_matmul_primitive_desc_create(dnnl_primitive_desc_t *primitive
         return st;
     }
     fill_quant_mds(*pd);
+    if (pd->runtime_m) pd->src.dims[0] = pd->dst.dims[0] = DNNL_RUNTIME_DIM_VAL; // what queries report
     *primitive_desc = pd;
     return dnnl_success;
 }
@@ -623,6 +651,7 @@ dnnl_status_t dnnl_primitive_desc_next_impl(dnnl_primitive_desc_t pd) {
     if (!pd) return dnnl_invalid_arguments;
     if (pd->kind != dnnl_matmul) return dnnl_last_impl_reached; // one reorder implementation
     dnnl_primitive_desc tmp = *pd;
+    if (tmp.runtime_m) tmp.src.dims[0] = tmp.dst.dims[0] = 1;
     dnnl_status_t st = select_impl(tmp, pd->impl + 1);
     if (st != dnnl_success) return dnnl_last_impl_reached;
     pd->impl = tmp.impl;
@@ -710,7 +739,11 @@ dnnl_status_t dnnl_primitive_create(dnnl_primitive_t *primitive, const_dnnl_prim
     if (!primitive || !pd) return dnnl_invalid_arguments;
     auto *p = new dnnl_primitive;
     p->pd = *pd;
-    if (pd->scratch_bytes && pd->attr.scratchpad_mode == dnnl_scratchpad_mode_library) {
+    if (pd->runtime_m && pd->attr.scratchpad_mode == dnnl_scratchpad_mode_user) { // its size is not known yet
+        delete p;
+        return dnnl_unimplemented;
+    }
+    if (pd->scratch_bytes && !pd->runtime_m && pd->attr.scratchpad_mode == dnnl_scratchpad_mode_library) {
         if (pd->engine->device < 0) { /* device-less engine: nothing to allocate */ }
         else {
             cudaSetDevice(pd->engine->device);
@@ -719,6 +752,7 @@ dnnl_status_t dnnl_primitive_create(dnnl_primitive_t *primitive, const_dnnl_prim
                 return dnnl_out_of_memory;
             }
             cudaMemset(p->scratch, 0, pd->scratch_bytes); // arrival counters start at zero
+            p->scratch_cap = pd->scratch_bytes;
         }
     }
     *primitive = p;
@@ -793,12 +827,49 @@ dnnl_status_t bind_quant(QParam &q, const quant_entry_t &e, dnnl_memory_t mem, i
 extern "C" dnnl_status_t dnnl_primitive_execute(const_dnnl_primitive_t primitive, dnnl_stream_t stream, int nargs,
         const dnnl_exec_arg_t *args) {
     if (!primitive || !stream || nargs < 0 || (nargs > 0 && !args)) return dnnl_invalid_arguments;
-    const dnnl_primitive_desc &pd = primitive->pd;
-    if (stream->engine != pd.engine && stream->engine->device != pd.engine->device) return dnnl_invalid_arguments;
+    if (stream->engine != primitive->pd.engine && stream->engine->device != primitive->pd.engine->device)
+        return dnnl_invalid_arguments;
     for (int i = 0; i < nargs; ++i)
         if (!args[i].memory) return dnnl_invalid_arguments;
-    if (pd.kind == dnnl_reorder) return execute_reorder(pd, stream, nargs, args);
+    if (primitive->pd.kind == dnnl_reorder) return execute_reorder(primitive->pd, stream, nargs, args);
     arg_map_t am {args, nargs};
+    // A primitive created with M left open takes M from the src / dst memory objects, checks the
+    // rest of their descriptors against its own and chooses the implementation (and the scratch
+    // it needs) for this M.
+    dnnl_primitive_desc settled;
+    if (primitive->pd.runtime_m) {
+        dnnl_memory_t s = am.find(DNNL_ARG_SRC), d = am.find(DNNL_ARG_DST);
+        if (!s || !d) return dnnl_invalid_arguments;
+        settled = primitive->pd;
+        const dnnl_memory_desc &sm = s->md, &dm = d->md;
+        if (sm.ndims != 2 || dm.ndims != 2 || sm.has_runtime_dims() || dm.has_runtime_dims() || sm.dims[0] != dm.dims[0]
+                || sm.dims[1] != settled.src.dims[1] || dm.dims[1] != settled.dst.dims[1]
+                || sm.data_type != settled.src.data_type || dm.data_type != settled.dst.data_type
+                || sm.format_kind != dnnl_blocked || dm.format_kind != dnnl_blocked)
+            return dnnl_invalid_arguments;
+        settled.src = sm;
+        settled.dst = dm;
+        settled.runtime_m = false;
+        dnnl_status_t rst = dense_desc_check(settled.src, settled.wei, settled.bias.ndims ? &settled.bias : nullptr, settled.dst);
+        if (rst == dnnl_success) rst = dense_attr_check(settled);
+        if (rst == dnnl_success) rst = select_impl(settled, 0);
+        if (rst != dnnl_success) return rst;
+        if (settled.scratch_bytes > primitive->scratch_cap && settled.engine->device >= 0) {
+            cudaSetDevice(settled.engine->device);
+            // earlier executions may still use the old buffer: they are in order on this stream
+            if (primitive->scratch) {
+                cudaStreamSynchronize(stream->stream);
+                cudaFree(primitive->scratch);
+                primitive->scratch = nullptr;
+                primitive->scratch_cap = 0;
+            }
+            if (!cuda_ok(cudaMalloc(&primitive->scratch, settled.scratch_bytes), "cudaMalloc(scratchpad)"))
+                return dnnl_out_of_memory;
+            cudaMemsetAsync(primitive->scratch, 0, settled.scratch_bytes, stream->stream);
+            primitive->scratch_cap = settled.scratch_bytes;
+        }
+    }
+    const dnnl_primitive_desc &pd = primitive->pd.runtime_m ? settled : primitive->pd;
     const auto &attr = pd.attr;
 
     dnnl_memory_t src = am.find(DNNL_ARG_SRC), wei = am.find(DNNL_ARG_WEIGHTS), dst = am.find(DNNL_ARG_DST);

@@ -48,7 +48,9 @@ size_t dt_bits(dnnl_data_type_t dt) {
 // bytes of a dense-or-strided blocked descriptor (sub-byte types round up)
 size_t md_bytes(const dnnl_memory_desc &md, int index) {
     if (md.format_kind == dnnl_format_kind_host_scalar) return index == 0 ? dt_bits(md.data_type) / 8 : 0;
-    if (md.ndims == 0 || md.has_zero_dim()) return 0;
+    if (md.ndims == 0) return 0;
+    if (md.has_runtime_dims()) return (size_t)DNNL_RUNTIME_DIM_VAL; // DNNL_RUNTIME_SIZE_VAL
+    if (md.has_zero_dim()) return 0;
     if (md.is_grouped()) {
         if (index == 0) return ((size_t)md.nelems() * dt_bits(md.data_type) + 7) / 8;
         if (index == 1) return (size_t)md.group_count * dt_bits(md.offsets_dt) / 8;
@@ -262,9 +264,27 @@ dnnl_status_t dnnl_memory_desc_create_with_strides(dnnl_memory_desc_t *memory_de
     md->ndims = ndims;
     md->data_type = data_type;
     md->format_kind = dnnl_blocked;
+    bool runtime = false;
     for (int i = 0; i < ndims; ++i) {
-        if (dims[i] == DNNL_RUNTIME_DIM_VAL) { delete md; return dnnl_unimplemented; } // runtime dims
+        runtime = runtime || dims[i] == DNNL_RUNTIME_DIM_VAL;
         md->dims[i] = dims[i];
+    }
+    if (runtime) {
+        // dims left open until execution (src/common/memory_desc.cpp:245-300): the given strides
+        // are taken as they are; dense strides are known up to the first open dim from the right
+        dnnl_dim_t acc = 1;
+        for (int i = ndims - 1; i >= 0; --i) {
+            if (strides) {
+                if (strides[i] < 0 && strides[i] != DNNL_RUNTIME_DIM_VAL) { delete md; return dnnl_invalid_arguments; }
+                md->strides[i] = strides[i];
+            } else {
+                md->strides[i] = acc;
+                if (acc != DNNL_RUNTIME_DIM_VAL)
+                    acc = md->dims[i] == DNNL_RUNTIME_DIM_VAL ? DNNL_RUNTIME_DIM_VAL : acc * (md->dims[i] == 0 ? 1 : md->dims[i]);
+            }
+        }
+        *memory_desc = md;
+        return dnnl_success;
     }
     if (strides) {
         for (int i = 0; i < ndims; ++i) {

@@ -48,6 +48,13 @@ struct dnnl_memory_desc {
     dnnl_data_type_t offsets_dt = dnnl_data_type_undef;
 
     bool is_grouped() const { return format_kind == dnnl_format_kind_sparse && encoding == dnnl_grouped; }
+    // a dim (or a stride that depends on one) left open until execution: DNNL_RUNTIME_DIM_VAL
+    bool has_runtime_dims() const {
+        for (int i = 0; i < ndims; ++i)
+            if (dims[i] == DNNL_RUNTIME_DIM_VAL || (format_kind == dnnl_blocked && strides[i] == DNNL_RUNTIME_DIM_VAL))
+                return true;
+        return false;
+    }
     bool is_zero() const { return ndims == 0; }
     dnnl_dim_t nelems() const {
         if (ndims == 0) return 0;
@@ -143,6 +150,9 @@ struct dnnl_primitive_desc {
     dnnl_memory_desc src, wei, bias, dst, scratchpad;
     dnnl_primitive_attr attr;
     bool grouped = false;
+    // M is DNNL_RUNTIME_DIM_VAL in src / dst: shapes, implementation and scratch are settled per
+    // execution from the memory objects' descriptors (impl / impl_name describe M = 1)
+    bool runtime_m = false;
     int impl = IMPL_REF;
     std::string impl_name;
     std::map<int, dnnl_memory_desc> quant_mds; // exec-arg id -> parameter md
@@ -157,7 +167,8 @@ struct dnnl_primitive {
     // scratch owned by the primitive (scratchpad_mode_library); like oneDNN's
     // library scratchpad it makes concurrent execute calls of ONE primitive
     // object unsafe
-    void *scratch = nullptr;
+    mutable void *scratch = nullptr;
+    mutable size_t scratch_cap = 0; // bytes behind `scratch` (grows for runtime-M primitives)
 };
 
 namespace qmm {

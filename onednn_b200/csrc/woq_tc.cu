@@ -89,7 +89,15 @@ struct WtParams {
     uint32_t idesc;
     float *partial; // [ntiles][max_slots][M * NB]
     int *counters; // [ntiles]
+#ifdef QMM_PROFILE
+    int ablate; // 1 no MMAs, 2 converters idle, 4 epilogue idle, 8 no S block, 16 unpack without stores (wrong results)
+#endif
 };
+#ifdef QMM_PROFILE
+#define WT_ABLATE(bit) (p.ablate & (bit))
+#else
+#define WT_ABLATE(bit) false
+#endif
 
 __device__ __forceinline__ uint32_t nib2(uint32_t x, uint32_t magic) { // (x & 0x000F000F) ^ magic
     uint32_t r;
@@ -254,9 +262,11 @@ woq_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
                         const uint64_t bd = ptx::smem_desc_sw128(ss + (q >> 2) * (C::MP * 128) + (q & 3) * 32, 0, 1024);
                         const uint32_t acc = tmem_base + buf * C::ACC_COLS;
                         const uint32_t asl = tmem_base + C::A_COL0 + slot * C::A_SLOT_COLS;
+                        if (!WT_ABLATE(1)) {
 #pragma unroll
-                        for (int j = 0; j < NBLK; ++j) mma_ts_f16(acc + j * C::MP, asl + 8 * j, bd, p.idesc, !fresh);
-                        mma_ts_f16(acc + NBLK * C::MP, tmem_base + C::ONES_COL, bd, p.idesc, !fresh);
+                            for (int j = 0; j < NBLK; ++j) mma_ts_f16(acc + j * C::MP, asl + 8 * j, bd, p.idesc, !fresh);
+                            if (!WT_ABLATE(8)) mma_ts_f16(acc + NBLK * C::MP, tmem_base + C::ONES_COL, bd, p.idesc, !fresh);
+                        }
                         fresh = false;
                         ptx::tc_commit(&a_empty[slot]);
                         if (kpos + 1 == gend) { // group piece complete
@@ -301,6 +311,12 @@ woq_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
                 for (int qs = 0; qs < nst; ++qs, ++ks) {
                     if ((qs & 1) != r) continue;
                     const int slot = ks % A_SLOTS;
+                    if (WT_ABLATE(2)) {
+                        if (!__all_sync(0xffffffffu, ptx::mbar_wait(&a_empty[slot], ((ks / A_SLOTS) & 1) ^ 1))) { ok = false; break; }
+                        __syncwarp();
+                        if (lane == 0) ptx::mbar_arrive(&a_full[slot]);
+                        continue;
+                    }
                     uint32_t R[4][BL / 4];
                     const uint8_t *b0 = sw + qs * 2048;
                     if constexpr (NBLK == 4) {
@@ -325,6 +341,11 @@ woq_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
                         const uint32_t sel = ((4 + (t & 3)) << 12) | ((4 + (t & 3)) << 8) | ((t & 3) << 4) | (t & 3);
                         const uint32_t x01 = prmt(R[0][t >> 2], R[1][t >> 2], sel);
                         const uint32_t x23 = prmt(R[2][t >> 2], R[3][t >> 2], sel);
+                        if (WT_ABLATE(16)) {
+                            if ((nib2(x01, magic) ^ nib2(x01 >> 4, magic) ^ nib2(x23, magic) ^ nib2(x23 >> 4, magic)) == 0x12345u)
+                                tmem_st_16x128b_x2(asl, x01, x23, x01, x23);
+                            continue;
+                        }
                         tmem_st_16x128b_x2(asl + ((uint32_t)(16 * (t & 1)) << 16) + 8 * (t >> 1), nib2(x01, magic),
                                 nib2(x01 >> 4, magic), nib2(x23, magic), nib2(x23 >> 4, magic));
                     }
@@ -386,6 +407,14 @@ woq_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
                 const uint32_t buf = gc & 1;
                 if (!__all_sync(0xffffffffu, ptx::mbar_wait(&acc_full[buf], (gc >> 1) & 1))) { ok = false; break; } // leaves the group loop only
                 ptx::tc_fence_after_sync();
+                if (WT_ABLATE(4)) {
+                    ptx::tc_fence_before_sync();
+                    __syncwarp();
+                    if (lane == 0) ptx::mbar_arrive(&acc_empty[buf]);
+                    ++gc;
+                    kpos = gend;
+                    continue;
+                }
                 const uint32_t acc = tmem_base + ((uint32_t)(32 * q) << 16) + buf * C::ACC_COLS;
                 uint32_t S[MR];
                 tmem_ld_cols<MR>(acc + NBLK * C::MP, S);
@@ -587,6 +616,9 @@ int launch_woq_tc(const MatmulArgs &a, void *scratch, int sm_count, cudaStream_t
     p.idesc = ptx::make_idesc(ptx::CFMT_F32, fmt, fmt, false, false, 128, mp);
     p.counters = (int *)scratch;
     p.partial = (float *)((char *)scratch + ((size_t)pl.ntiles * sizeof(int) + 255) / 256 * 256);
+#ifdef QMM_PROFILE // a build with -DQMM_PROFILE reads the switch; the shipped library has no such code
+    p.ablate = getenv("ONEDNN_CUDA_WOQ_ABLATE") ? atoi(getenv("ONEDNN_CUDA_WOQ_ABLATE")) : 0;
+#endif
 #define QMM_WT(MR, NBLK) (f16 ? wt_launch<MR, NBLK, true>(tw, ts, a, p, pl.grid, st) : wt_launch<MR, NBLK, false>(tw, ts, a, p, pl.grid, st))
     if (pl.mr == 8) return QMM_WT(8, 4);
     if (pl.mr == 16) return QMM_WT(16, 4);

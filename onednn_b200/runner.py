@@ -17,7 +17,9 @@ def _md(t: W.QTensor):
 
 
 class Prepared:
-    def __init__(self, p: W.Problem, eng, impl=None, user_scratchpad=False):
+    def __init__(self, p: W.Problem, eng, impl=None, user_scratchpad=False, runtime_m=False):
+        """runtime_m: the primitive is created with M = DNNL_RUNTIME_DIM_VAL in src and dst (their
+        strides given), and learns M from the memory objects at execution."""
         self.p, self.eng = p, eng
         self.user_scratchpad = user_scratchpad
         grouped = p.offsets is not None
@@ -63,7 +65,14 @@ class Prepared:
         if user_scratchpad:
             attr.set_scratchpad_mode(api.SCRATCHPAD_MODE_USER)
         self.attr = attr
-        self.pd = api.matmul.primitive_desc(eng, self.src_md, self.wei_md, self.dst_md, self.bias_md, attr)
+        pd_src, pd_dst = self.src_md, self.dst_md
+        if runtime_m:
+            pd_src = api.memory.desc((api.RUNTIME_DIM_VAL, p.K), p.src.dt, tuple(p.src.strides))
+            pd_dst = api.memory.desc((api.RUNTIME_DIM_VAL, p.N), p.dst_dt, (p.N, 1))
+        self.pd = api.matmul.primitive_desc(eng, pd_src, self.wei_md, pd_dst, self.bias_md, attr)
+        # descriptors of the quantization parameters come from a descriptor that knows M
+        self.md_pd = api.matmul.primitive_desc(eng, self.src_md, self.wei_md, self.dst_md, self.bias_md, attr) \
+            if runtime_m else self.pd
         if impl is not None:
             while impl not in self.pd.impl_info_str():
                 if not self.pd.next_impl():
@@ -94,7 +103,7 @@ class Prepared:
         if p.bias is not None:
             self.args[api.ARG_BIAS] = put(self.bias_md, [p.bias.data])
         for key, q in self.quant_args.items():
-            md = self.pd.query_md(api.QUERY_EXEC_ARG_MD, key)
+            md = self.md_pd.query_md(api.QUERY_EXEC_ARG_MD, key)
             self.args[key] = put(md, [q.data])
         for key, t in self.binary_args.items():
             self.args[key] = put(_md(t), [t.data])
@@ -195,9 +204,9 @@ def run_reorder(r: W.Reorder, eng, strm):
     return out, pd.impl_info_str()
 
 
-def run_problem(p: W.Problem, eng, strm, impl=None, user_scratchpad=False):
+def run_problem(p: W.Problem, eng, strm, impl=None, user_scratchpad=False, runtime_m=False):
     """Uploads, executes, waits, downloads.  Returns (dst, implementation)."""
-    r = Prepared(p, eng, impl, user_scratchpad).upload()
+    r = Prepared(p, eng, impl, user_scratchpad, runtime_m).upload()
     r.execute(strm)
     strm.wait()
     return r.download(), r.impl

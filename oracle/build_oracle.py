@@ -13,7 +13,11 @@ import subprocess
 import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-REF_DEFAULT = os.environ.get("ONEDNN_REFERENCE_DIR", "/root/reference")
+try:
+    from .refdir import reference_dir
+except ImportError:  # run as a script
+    from refdir import reference_dir
+REF_DEFAULT = reference_dir() or ""
 
 
 def _gxx():

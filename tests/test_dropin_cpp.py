@@ -5,13 +5,18 @@ executes).  Needs the reference's headers; skipped where they are absent."""
 import os
 import shutil
 import subprocess
+import sys
 
 import pytest
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(HERE)
-REF_INC = os.path.join(os.environ.get("ONEDNN_REFERENCE_DIR", "/root/reference"), "include")
-GEN_INC = os.path.join(ROOT, "oracle", "_ref", "include")
+sys.path.insert(0, ROOT)
+from oracle.refdir import reference_dir  # noqa: E402
+
+REF_INC = os.path.join(reference_dir() or "/nonexistent", "include")
+# dnnl_config.h, dnnl_version.h, dnnl_version_hash.h as this library's build writes them
+GEN_INC = os.path.join(ROOT, "onednn_b200", "lib", "include")
 
 
 @pytest.mark.skipif(not os.path.exists(os.path.join(REF_INC, "oneapi", "dnnl", "dnnl.hpp")),
@@ -19,7 +24,7 @@ GEN_INC = os.path.join(ROOT, "oracle", "_ref", "include")
 def test_unchanged_dnnl_hpp_program_builds_and_dispatches(tmp_path):
     from onednn_b200 import api
     if not os.path.exists(os.path.join(GEN_INC, "oneapi", "dnnl", "dnnl_config.h")):
-        pytest.skip("generated dnnl_config.h not built (oracle/build_oracle.py)")
+        pytest.skip("generated dnnl_config.h not built (python -m onednn_b200.build)")
     gxx = "/usr/bin/g++" if os.path.exists("/usr/bin/g++") else shutil.which("g++")
     libdir = os.path.dirname(api.lib_path())
     exe = str(tmp_path / "probe")
@@ -53,3 +58,22 @@ def test_dnnl_hpp_program_executes_on_the_gpu():
     assert r.returncode == 0, (r.stdout, r.stderr)
     assert "s32 cuda:tcgen05:int8 ok" in r.stdout and "f32 cuda:tcgen05:int8 ok" in r.stdout, r.stdout
     assert "reorder cuda:ref:reorder ok" in r.stdout, r.stdout
+
+
+# The reference's own example programs (compiled unchanged by build_dropin.build_reference_examples),
+# run with `gpu` as their engine argument.  matmul_with_weight_only_quantization returns before doing
+# anything on a non-CPU engine (its own main), so it proves linking only; inference_int8_matmul uses
+# DNNL_RUNTIME_DIM_VAL for M.
+@pytest.mark.gpu
+@pytest.mark.parametrize("name", ["ref_example_matmul_grouped", "ref_example_matmul_f8_quantization",
+                                  "ref_example_inference_int8_matmul", "ref_example_matmul_woq"])
+def test_reference_example_passes_on_the_gpu(name):
+    sys.path.insert(0, os.path.join(HERE, "dropin"))
+    import build_dropin
+    exe = build_dropin.build_reference_examples().get(name)
+    if exe is None:
+        pytest.skip("example not built (no oneDNN checkout at build time)")
+    r = subprocess.run([exe, "gpu"], capture_output=True, text=True, timeout=180)
+    assert r.returncode == 0, (r.stdout[-2000:], r.stderr[-2000:])
+    if name != "ref_example_matmul_woq":
+        assert "Example passed on GPU." in r.stdout, r.stdout[-2000:]

@@ -232,3 +232,84 @@ def test_user_scratchpad_descriptor(host_engine):
     assert size(W.moe_grouped(40, 128, 64, 4), True) >= 16 * 5  # one int4 record per expert and a header
     assert size(W.int8_zp(64, 128, 64), True) >= 4 * (64 + 64)  # column and row sums
     assert size(W.fp8_prefill(64, 128, 64), True) == 0
+
+
+def test_runtime_m_descriptor(host_engine):
+    """DNNL_RUNTIME_DIM_VAL for M (src/common/matmul.cpp:630-744; the reference's int8 inference
+    tutorial): accepted for the rows of a 2D problem, reported back by the queries, refused elsewhere."""
+    RT = api.RUNTIME_DIM_VAL
+    open_md = md((RT, 64), W.U8, (64, 1))
+    assert open_md.get_dims() == (RT, 64) and open_md.get_strides() == (64, 1)
+    assert open_md.get_size() == (1 << 64) + RT  # DNNL_RUNTIME_SIZE_VAL
+    a = api.primitive_attr()
+    a.set_scales_mask(WEI, 2)
+    a.set_zero_points_mask(SRC, 0)
+    pd = api.matmul.primitive_desc(host_engine, open_md, md((64, 48), W.S8, tag.any), md((RT, 48), W.S32, (48, 1)), None, a)
+    assert pd.impl_info_str().startswith("cuda:")
+    assert pd.src_desc().get_dims() == (RT, 64) and pd.weights_desc().get_strides() == (48, 1)
+    # K or N left open, or a row-dependent stride: not built
+    assert status_of(lambda: api.matmul.primitive_desc(host_engine, md((8, RT), W.U8, (64, 1)), md((RT, 48), W.S8, (48, 1)),
+                                                        md((8, 48), W.S32, (48, 1)))) == api.unimplemented
+    assert status_of(lambda: api.matmul.primitive_desc(host_engine, md((RT, 64), W.U8, tag.ba), md((64, 48), W.S8, tag.ab),
+                                                        md((RT, 48), W.S32, tag.ab))) == api.unimplemented
+
+
+def test_value_names_and_late_post_op_calls():
+    """dnnl_debug.h names, dnnl_post_ops_append_binary_v2 / get_params_prelu, sub-memory descriptors."""
+    import ctypes as C
+    L = api.lib()
+    for fn, v, want in (("dnnl_status2str", 3, b"unimplemented"), ("dnnl_dt2str", W.F8_E4M3, b"f8_e4m3"),
+                        ("dnnl_dt2str", W.S4, b"s4"), ("dnnl_fmt_tag2str", 3, b"ab"), ("dnnl_engine_kind2str", 2, b"gpu"),
+                        ("dnnl_alg_kind2str", W.ELTWISE["gelu_tanh"], b"eltwise_gelu_tanh"),
+                        ("dnnl_alg_kind2str", W.BINARY["mul"], b"binary_mul"), ("dnnl_prim_kind2str", 14, b"matmul"),
+                        ("dnnl_fpmath_mode2str", 1, b"bf16"), ("dnnl_runtime2str", 2048, b"CUDA")):
+        f = getattr(L, fn)
+        f.restype = C.c_char_p
+        assert f(v) == want, (fn, v, f(v))
+    po = api.post_ops()
+    src1 = md((1, 8), W.F32, tag.ab)
+    assert L.dnnl_post_ops_append_binary_v2(po._h, W.BINARY["add"], src1._h, None) == api.success
+    assert L.dnnl_post_ops_append_binary_v2(po._h, 0x1fffc, src1._h, src1._h) == api.unimplemented  # select
+    po.append_prelu(5)
+    mask = C.c_int(0)
+    assert L.dnnl_post_ops_get_params_prelu(po._h, 1, C.byref(mask)) == api.success and mask.value == 5
+    assert L.dnnl_post_ops_get_params_prelu(po._h, 0, C.byref(mask)) == api.invalid_arguments
+    # a window of a plain tensor keeps the strides and moves offset0
+    parent = md((8, 16), W.S8, tag.ab)
+    sub = C.c_void_p()
+    dims = (C.c_int64 * 12)(4, 8)
+    offs = (C.c_int64 * 12)(2, 8)
+    assert L.dnnl_memory_desc_create_submemory(C.byref(sub), parent._h, dims, offs) == api.success
+    off0 = C.c_int64(0)
+    assert L.dnnl_memory_desc_query(sub, 259, C.byref(off0)) == api.success and off0.value == 2 * 16 + 8
+    L.dnnl_memory_desc_destroy(sub)
+    offs[1] = 12  # 12 + 8 > 16
+    assert L.dnnl_memory_desc_create_submemory(C.byref(sub), parent._h, dims, offs) == api.invalid_arguments
+    # 4-bit elements: the window starts on a byte
+    p4 = md((8, 16), W.S4, tag.ab)
+    offs[1] = 3
+    assert L.dnnl_memory_desc_create_submemory(C.byref(sub), p4._h, dims, offs) == api.invalid_arguments
+
+
+def test_verbose_line_format(host_engine, capfd):
+    """ONEDNN_VERBOSE=2 prints a create line in the reference's field order (src/common/verbose.cpp:1060-1090):
+    operation, engine, primitive, implementation, prop_kind, memory descriptors, attributes, aux, problem."""
+    L = api.lib()
+    L.dnnl_set_verbose(2)
+    try:
+        a = api.primitive_attr()
+        a.set_fpmath_mode(api.fpmath_mode.bf16, True)
+        a.set_scales(WEI, 3, (128, 1), W.BF16)
+        a.set_zero_points(WEI, 3, (128, 1), W.U4)
+        pd = api.matmul.primitive_desc(host_engine, md((8, 256), W.BF16, tag.ab), md((256, 64), W.S4, tag.ab),
+                                       md((8, 64), W.BF16, tag.ab), None, a)
+        api.matmul(pd)
+    finally:
+        L.dnnl_set_verbose(0)
+    out = capfd.readouterr().out
+    line = [l for l in out.splitlines() if l.startswith("onednn_verbose,v1,primitive,create:cache_miss")][-1]
+    f = line.split(",")
+    assert f[4:8] == ["gpu", "matmul", "cuda:tcgen05:woq4", "undef"]
+    assert f[8] == "src:bf16::blocked:ab::f0 wei:s4::blocked:ab::f0 dst:bf16::blocked:ab::f0"
+    assert f[9] == "attr-fpmath:bf16:true attr-scales:wei:3:bf16:128x1 attr-zero-points:wei:3:u4:128x1"
+    assert f[11] == "8x256:256x64"

@@ -302,3 +302,29 @@ def test_grouped_bad_offsets_reports_invalid_arguments(gpu):
         strm.wait()
     assert ei.value.status == api.invalid_arguments
     strm.wait()  # the status word is cleared: the stream stays usable
+
+
+RUNTIME_M_CASES = {
+    "int8_zp_f32": lambda M: W.int8_zp(M, 1024, 1024, per_n_scales=True),
+    "fp8": lambda M: W.fp8_prefill(M, 512, 384),
+    "int4_decode": lambda M: W.int4_decode(M, 1024, 512),
+}
+
+
+@pytest.mark.parametrize("name", sorted(RUNTIME_M_CASES))
+def test_runtime_m_matches_oracle(gpu, name):
+    """M = DNNL_RUNTIME_DIM_VAL at creation (src/common/matmul.cpp:630-744): the same primitive object
+    serves several M, each execution choosing the implementation for the M of its memory objects."""
+    from onednn_b200.runner import Prepared
+    eng, strm = gpu
+    for M in (1, 24, 100):
+        p = RUNTIME_M_CASES[name](M)
+        if p.M > 32 and name == "int4_decode":
+            continue
+        r = Prepared(p, eng, runtime_m=True).upload()
+        r.execute(strm)
+        strm.wait()
+        got = r.download()
+        fixed, impl = run_problem(p, eng, strm)
+        assert np.array_equal(got, fixed), "%s M=%d: runtime-M result differs from the fixed-M primitive (%s)" % (name, M, impl)
+        assert_parity(got, O.run_port(p), p.dst_dt, "%s M=%d" % (name, M), slack_for(p, impl))
