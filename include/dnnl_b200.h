@@ -564,6 +564,26 @@ dnnl_status_t dnnl_cuda_interop_matmul_u8s8s32_zp_static(void *cuda_stream, int6
  * call it while the stream is being captured. */
 dnnl_status_t dnnl_cuda_interop_matmul_u8s8s32_zp_static_status(void *cuda_stream, int *status);
 
+/* ---- assembling a sharded result over NVLink (no counterpart in the reference, which is a
+ * single-device library).  One process per GPU computes an N-slice (or the rows of its experts) of
+ * dst; instead of a collective library, each rank stores its block into EVERY rank's full dst buffer
+ * with plain peer stores and raises a flag there; the wait call blocks the stream (bounded) until
+ * the blocks of all ranks have landed.
+ *   peer_dst[p], peer_flags[p]: device addresses, valid on the calling GPU, of rank p's dst buffer
+ *   and of its flag array (`world` 32-bit words, zero at start); peer-mapped memory such as CUDA IPC
+ *   or symmetric-memory allocations, exchanged once at set-up.
+ *   seg: nseg (<= 64) triples (first src row, first dst row, rows) of the local block.
+ *   epoch: a number that grows with every exchange on these flags.  done: a zeroed 32-bit word of
+ *   local device memory.  Byte sizes, pitches and offsets are multiples of 16.
+ * A consumer must not overwrite a dst buffer that peers may still be filling for a later epoch:
+ * alternate two buffers, or exchange an acknowledgement. */
+dnnl_status_t dnnl_cuda_interop_peer_scatter(dnnl_stream_t stream, int world, int rank, const void *local,
+        int64_t row_bytes, int64_t src_pitch, void *const *peer_dst, int64_t dst_pitch, int64_t dst_col_bytes,
+        int nseg, const int64_t *seg, unsigned *const *peer_flags, unsigned epoch, unsigned *done);
+/* Waits on the stream until flags[0..world) have all reached `epoch`; a wait that runs out (2 s)
+ * records runtime_error for the next dnnl_stream_wait. */
+dnnl_status_t dnnl_cuda_interop_peer_wait(dnnl_stream_t stream, int world, const unsigned *flags, unsigned epoch);
+
 #ifdef __cplusplus
 }
 #endif

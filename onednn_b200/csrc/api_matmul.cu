@@ -1029,6 +1029,9 @@ extern "C" dnnl_status_t dnnl_primitive_execute(const_dnnl_primitive_t primitive
         cudaEventDestroy(ev0); cudaEventDestroy(ev1);
         verbose_line("exec", pd, ms); // device time of the primitive's kernels
     }
-    if (rc == 5) set_last_error(std::string("kernel launch: ") + cudaGetErrorString(cudaGetLastError()));
+    if (rc == 5) { // a launcher that saw the CUDA error itself has recorded it already
+        const cudaError_t e = cudaGetLastError();
+        if (e != cudaSuccess) set_last_error(std::string("kernel launch: ") + cudaGetErrorString(e));
+    }
     return (dnnl_status_t)rc;
 }

@@ -500,6 +500,22 @@ QMM_STUB(dnnl_softmax_forward_primitive_desc_create)
 QMM_STUB(dnnl_sum_primitive_desc_create)
 QMM_STUB(dnnl_vanilla_rnn_backward_primitive_desc_create)
 QMM_STUB(dnnl_vanilla_rnn_forward_primitive_desc_create)
+/* dnnl_ocl.h: the generated dnnl_config.h names the OpenCL runtime class so that programs fill GPU
+   memory through map / unmap; there is no OpenCL behind it */
+QMM_STUB(dnnl_ocl_interop_engine_create)
+QMM_STUB(dnnl_ocl_interop_engine_create_from_cache_blob)
+QMM_STUB(dnnl_ocl_interop_engine_get_cache_blob)
+QMM_STUB(dnnl_ocl_interop_engine_get_cache_blob_id)
+QMM_STUB(dnnl_ocl_interop_engine_get_context)
+QMM_STUB(dnnl_ocl_interop_get_device)
+QMM_STUB(dnnl_ocl_interop_memory_create)
+QMM_STUB(dnnl_ocl_interop_memory_create_v2)
+QMM_STUB(dnnl_ocl_interop_memory_get_mem_object)
+QMM_STUB(dnnl_ocl_interop_memory_get_memory_kind)
+QMM_STUB(dnnl_ocl_interop_memory_set_mem_object)
+QMM_STUB(dnnl_ocl_interop_primitive_execute)
+QMM_STUB(dnnl_ocl_interop_stream_create)
+QMM_STUB(dnnl_ocl_interop_stream_get_command_queue)
 #undef QMM_STUB
 
 /* CPU-only service calls (dnnl.h:3960-4048): there is no CPU engine; they succeed and change nothing,

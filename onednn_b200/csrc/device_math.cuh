@@ -157,6 +157,30 @@ __device__ __forceinline__ float gelu_tanh_f(float s) {
     return (float)(0.5 * (double)s * (1. + (double)v));
 }
 
+// gelu_tanh for results that are requantized to 8-bit integers: the same tanh argument, tanh(t) =
+// 1 - 2 / (exp(2t) + 1) through the hardware's exp2 and reciprocal approximations, and the final
+// 0.5 s (1 + tanh t) = s - s / (exp(2t) + 1) in f32.  Absolute error below 4e-7 max(1, |s|), i.e.
+// a few millionths of an s8 step for values inside the s8 range: the rounded integer differs from
+// the reference's (by one) only where the reference value lies that close to a rounding boundary.
+__device__ __forceinline__ float gelu_tanh_coarse(float s) {
+    const float c0 = 0.79788458347320556640625f, c1 = 0.044715f;
+    const float t = __fmul_rn(__fmul_rn(c0, s), __fadd_rn(1.f, __fmul_rn(__fmul_rn(c1, s), s)));
+    float e, r;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(t * 2.88539008177792681472f)); // exp(2t)
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(e + 1.f));
+    return fmaf(-s, r, s);
+}
+
+// d / scale with a reciprocal computed once (rcp = round(1 / scale)): product, exact remainder,
+// correction -- the correctly rounded quotient whenever no intermediate over- or underflows
+// (Markstein); an infinite or NaN product is returned as it is.
+__device__ __forceinline__ float div_by_scale(float d, float scale, float rcp) {
+    const float q = d * rcp;
+    const float rem = fmaf(-q, scale, d);
+    const float q2 = fmaf(rem, rcp, q);
+    return fabsf(q) < __int_as_float(0x7f800000) ? q2 : q;
+}
+
 __device__ __forceinline__ float eltwise_fwd(int alg, float s, float a, float b) {
     switch (alg) {
         case 0x20: return s > 0 ? s : __fmul_rn(s, a); // relu
@@ -236,7 +260,9 @@ __device__ __forceinline__ bool has_sum(const MatmulArgs &a) {
 // per phase instead of once per element, and the R dependency chains
 // interleave.  Rows at or beyond M (the tail of the last tile) read row M-1 of
 // binary operands and old dst; their results are never stored.
-template <int R>
+// COARSE: the result is requantized to an 8-bit integer, which lets gelu_tanh use its cheap form.
+// FULL: all R rows exist (m0 + R <= M), so no row index has to be clamped.
+template <int R, bool COARSE = false, bool FULL = false>
 __device__ __forceinline__ void apply_post_ops_rows(const MatmulArgs &a, float (&d)[R], int64_t m0, int64_t n) {
     for (int i = 0; i < a.n_po; ++i) {
         const PostOpArg &e = a.po[i];
@@ -251,7 +277,7 @@ __device__ __forceinline__ void apply_post_ops_rows(const MatmulArgs &a, float (
                 QMM_ELT_PHASE(0x21, tanhf(s))
                 QMM_ELT_PHASE(0x26, __fadd_rn(__fmul_rn(al, s), be)) // linear
                 QMM_ELT_PHASE(0x29, logistic_f(s))
-                QMM_ELT_PHASE(0x2b, gelu_tanh_f(s))
+                QMM_ELT_PHASE(0x2b, COARSE ? gelu_tanh_coarse(s) : gelu_tanh_f(s))
                 QMM_ELT_PHASE(0x2c, __fmul_rn(s, logistic_f(__fmul_rn(al, s)))) // swish
                 QMM_ELT_PHASE(0x2e, ((s > al ? s : al) > be ? be : (s > al ? s : al))) // clip
                 QMM_ELT_PHASE(0x31,
@@ -266,18 +292,20 @@ __device__ __forceinline__ void apply_post_ops_rows(const MatmulArgs &a, float (
             float y[R];
             const char *base = (const char *)e.src1;
             const int64_t last = a.M - 1;
+            const int64_t o0 = m0 * e.sm + n * e.sn; // element offset of row m0; row j lies j * sm further
             if (e.src1_dt == DT_F32) {
+                const float *row = (const float *)base + o0;
 #pragma unroll
-                for (int j = 0; j < R; ++j)
-                    y[j] = ((const float *)base)[min(m0 + j, last) * e.sm + n * e.sn];
+                for (int j = 0; j < R; ++j) y[j] = FULL ? row[j * e.sm] : ((const float *)base)[min(m0 + j, last) * e.sm + n * e.sn];
             } else if (e.src1_dt == DT_BF16) {
+                const unsigned short *row = (const unsigned short *)base + o0;
 #pragma unroll
                 for (int j = 0; j < R; ++j)
-                    y[j] = bf16_bits_to_f32(((const unsigned short *)base)[min(m0 + j, last) * e.sm + n * e.sn]);
+                    y[j] = bf16_bits_to_f32(FULL ? row[j * e.sm] : ((const unsigned short *)base)[min(m0 + j, last) * e.sm + n * e.sn]);
             } else {
 #pragma unroll
                 for (int j = 0; j < R; ++j)
-                    y[j] = load_float(e.src1_dt, base, min(m0 + j, last) * e.sm + n * e.sn);
+                    y[j] = load_float(e.src1_dt, base, FULL ? o0 + j * e.sm : min(m0 + j, last) * e.sm + n * e.sn);
             }
             switch (e.alg) {
                 case 0x1fff0:
@@ -296,7 +324,7 @@ __device__ __forceinline__ void apply_post_ops_rows(const MatmulArgs &a, float (
             const int64_t last = a.M - 1;
 #pragma unroll
             for (int j = 0; j < R; ++j) {
-                const float old = load_float(a.sum_dt, a.dst, min(m0 + j, last) * a.dst_sm + n * a.dst_sn);
+                const float old = load_float(a.sum_dt, a.dst, (FULL ? m0 + j : min(m0 + j, last)) * a.dst_sm + n * a.dst_sn);
                 d[j] = __fadd_rn(d[j], __fmul_rn(e.scale, __fsub_rn(old, (float)e.zero_point)));
             }
         }

@@ -102,7 +102,7 @@ __device__ __forceinline__ ColTerms load_col_terms(const MatmulArgs &a, const Tc
 // Per-tensor terms of the epilogue, read once per thread.
 struct TensorTerms {
     bool has_dst_scale, has_dst_zp, dst_zp_per_n, row_scale, row_sum, bias_by_row;
-    float dst_scale, dst_zp, src_scale;
+    float dst_scale, dst_rcp, dst_zp, src_scale;
 };
 
 template <bool INT>
@@ -110,6 +110,7 @@ __device__ __forceinline__ TensorTerms load_tensor_terms(const MatmulArgs &a, co
     TensorTerms t;
     t.has_dst_scale = a.non_default_attr && (a.dst_scale.ptr || a.dst_scale.on_host);
     t.dst_scale = a.dst_scale.ptr ? load_float(a.dst_scale.dt, a.dst_scale.ptr, 0) : a.dst_scale.host_value;
+    t.dst_rcp = __frcp_rn(t.dst_scale);
     // the floating-point reference path has no dst zero-point
     t.has_dst_zp = a.non_default_attr && INT && a.dst_zp.ptr;
     t.dst_zp_per_n = a.dst_zp.mask > 0;
@@ -153,13 +154,14 @@ struct dst_size {
 
 // 32 consecutive dst rows of column n, accumulators in r[0..31].  Absent
 // scales are 1 and an absent bias is 0, which leaves values unchanged.
-template <bool INT, bool CHAIN, int DST, int R>
+// FULL: all R rows exist (m0 + R <= M): no clamped row indices, no predicated stores.
+template <bool INT, bool CHAIN, int DST, int R, bool FULL = false>
 __device__ __forceinline__ void epilogue_rows(const MatmulArgs &a, const TcParams &tp, const TensorTerms &t,
         const ColTerms &c, const uint32_t (&r)[R], int64_t m0, int64_t n) {
     if (n >= a.N) return;
     char *dptr = (char *)a.dst + (m0 * a.dst_sm + n * a.dst_sn) * dst_size<DST>::value;
     const int64_t dstep = a.dst_sm * dst_size<DST>::value;
-    const int rows = (int)min((int64_t)R, a.M - m0);
+    const int rows = FULL ? R : (int)min((int64_t)R, a.M - m0);
     // Phases of straight-line code over the R rows (uniform conditions are
     // tested once per phase, not per row), so the rows' dependency chains
     // interleave; only the stores are predicated on the M tail.
@@ -168,7 +170,7 @@ __device__ __forceinline__ void epilogue_rows(const MatmulArgs &a, const TcParam
         if (t.row_sum) {
 #pragma unroll
             for (int j = 0; j < R; ++j)
-                d[j] = (float)((int)r[j] - c.zs_colsum - c.wei_zp * __ldg(tp.rowsum + min(m0 + j, a.M - 1)));
+                d[j] = (float)((int)r[j] - c.zs_colsum - c.wei_zp * __ldg(tp.rowsum + (FULL ? m0 + j : min(m0 + j, a.M - 1))));
         } else {
 #pragma unroll
             for (int j = 0; j < R; ++j) d[j] = (float)((int)r[j] - c.zs_colsum);
@@ -178,9 +180,15 @@ __device__ __forceinline__ void epilogue_rows(const MatmulArgs &a, const TcParam
         for (int j = 0; j < R; ++j) d[j] = __uint_as_float(r[j]);
     }
     if (t.row_scale) {
+        if (FULL && a.src_scale.dt == DT_F32) {
+            const float *ss = (const float *)a.src_scale.ptr + m0;
 #pragma unroll
-        for (int j = 0; j < R; ++j)
-            d[j] = __fmul_rn(d[j], load_float(a.src_scale.dt, a.src_scale.ptr, min(m0 + j, a.M - 1)));
+            for (int j = 0; j < R; ++j) d[j] = __fmul_rn(d[j], __ldg(ss + j));
+        } else {
+#pragma unroll
+            for (int j = 0; j < R; ++j)
+                d[j] = __fmul_rn(d[j], load_float(a.src_scale.dt, a.src_scale.ptr, FULL ? m0 + j : min(m0 + j, a.M - 1)));
+        }
     } else {
 #pragma unroll
         for (int j = 0; j < R; ++j) d[j] = __fmul_rn(d[j], t.src_scale);
@@ -192,13 +200,13 @@ __device__ __forceinline__ void epilogue_rows(const MatmulArgs &a, const TcParam
 #pragma unroll
             for (int j = 0; j < R; ++j)
                 d[j] = __fadd_rn(d[j],
-                        load_float(a.bias_dt, a.bias, min(m0 + j, a.M - 1) * a.bias_sm + n * a.bias_sn));
+                        load_float(a.bias_dt, a.bias, (FULL ? m0 + j : min(m0 + j, a.M - 1)) * a.bias_sm + n * a.bias_sn));
         }
-        apply_post_ops_rows<R>(a, d, m0, n);
+        apply_post_ops_rows<R, (DST == DT_S8 || DST == DT_U8), FULL>(a, d, m0, n);
     }
-    if (t.has_dst_scale) { // the reference divides
+    if (t.has_dst_scale) { // the reference divides; the same quotient from a reciprocal taken once per thread
 #pragma unroll
-        for (int j = 0; j < R; ++j) d[j] = __fdiv_rn(d[j], t.dst_scale);
+        for (int j = 0; j < R; ++j) d[j] = div_by_scale(d[j], t.dst_scale, t.dst_rcp);
     }
     if (t.has_dst_zp) {
         const float z = t.dst_zp_per_n ? c.dst_zp : t.dst_zp;
@@ -216,12 +224,20 @@ __device__ __forceinline__ void epilogue_rows(const MatmulArgs &a, const TcParam
 #endif
 #pragma unroll
     for (int j = 0; j < R; ++j)
-        if (j < rows) store_typed<DST>(dptr + j * dstep, d[j]);
+        if (FULL || j < rows) store_typed<DST>(dptr + j * dstep, d[j]);
 }
 
-template <bool INT, bool CHAIN, int R>
+// DSTT: the dst data type when the kernel was instantiated for one (post-op chain kernels: a single
+// copy of the chain's code in the instruction stream), -1 to choose at run time.
+template <bool INT, bool CHAIN, int R, int DSTT = -1>
 __device__ __forceinline__ void epilogue_rows_any(const MatmulArgs &a, const TcParams &tp, const TensorTerms &t,
         const ColTerms &c, const uint32_t (&r)[R], int64_t m0, int64_t n) {
+    if constexpr (DSTT >= 0) {
+        // whole pieces (all but the last rows of a ragged M) take the straight path
+        if (m0 + R <= a.M) epilogue_rows<INT, CHAIN, DSTT, R, true>(a, tp, t, c, r, m0, n);
+        else epilogue_rows<INT, CHAIN, DSTT, R, false>(a, tp, t, c, r, m0, n);
+        return;
+    }
     switch (a.dst_dt) {
         case DT_BF16: epilogue_rows<INT, CHAIN, DT_BF16, R>(a, tp, t, c, r, m0, n); break;
         case DT_F32: epilogue_rows<INT, CHAIN, DT_F32, R>(a, tp, t, c, r, m0, n); break;
@@ -232,7 +248,7 @@ __device__ __forceinline__ void epilogue_rows_any(const MatmulArgs &a, const TcP
     }
 }
 
-template <int KIND, int BT_M, int STAGES, bool CHAIN>
+template <int KIND, int BT_M, int STAGES, bool CHAIN, int DSTT = -1>
 __global__ void __launch_bounds__(num_threads(CHAIN), 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmS,
         const __grid_constant__ MatmulArgs a, const __grid_constant__ TcParams tp) {
@@ -310,15 +326,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
                     if (!ptx::mbar_wait(&full_bar[s], ph)) { failed = true; break; }
                     ptx::tc_fence_after_sync();
                     const uint32_t sw = ptx::smem_u32(smem + s * L::STAGE_BYTES), ss = sw + L::W_BYTES;
+                    // weights: MN-major when N-contiguous (one 128-byte row per k), K-major for `ba`; src
+                    // rows: K-major.  One thread issues: descriptors are built once per stage and advanced
+                    // by a constant in their start-address field (16-byte units).
+                    const uint64_t wd0 = tp.w_kmajor ? ptx::smem_desc_sw128(sw, 0, 1024) : ptx::smem_desc_sw128(sw, 128 * BKB, 1024);
+                    const uint64_t wstep = tp.w_kmajor ? (uint64_t)(UMMA_K >> 4) : (uint64_t)((UMMA_K * 128) >> 4);
+                    const uint64_t sd0 = ptx::smem_desc_sw128(ss, 0, 1024);
 #pragma unroll
-                    for (int kk = 0; kk < BKB / UMMA_K; ++kk) {
-                        // weights: MN-major when N-contiguous (one 128-byte row per k),
-                        // K-major for `ba`; src rows: K-major
-                        const uint64_t wd = tp.w_kmajor ? ptx::smem_desc_sw128(sw + kk * UMMA_K, 0, 1024)
-                                                        : ptx::smem_desc_sw128(sw + kk * UMMA_K * 128, 128 * BKB, 1024);
-                        const uint64_t sd = ptx::smem_desc_sw128(ss + kk * UMMA_K, 0, 1024);
-                        ptx::mma_ss<KIND>(tmem_d, wd, sd, tp.idesc, (kb | kk) != 0);
-                    }
+                    for (int kk = 0; kk < BKB / UMMA_K; ++kk)
+                        ptx::mma_ss<KIND>(tmem_d, wd0 + kk * wstep, sd0 + (uint64_t)(kk * (UMMA_K >> 4)), tp.idesc, (kb | kk) != 0);
                     ptx::tc_commit(&empty_bar[s]); // stage reusable once these MMAs have read it
                 }
                 if (failed) { *abort_flag = 1; atomicExch(a.status, 5); break; }
@@ -365,7 +381,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
 #ifdef QMM_PROFILE
                     if (tp.mainloop_only == 2) continue; // TMEM reads only
 #endif
-                    if (m0 < a.M) epilogue_rows_any<INT, CHAIN, 8>(a, tp, tt, ct, r, m0, n);
+                    if (m0 < a.M) epilogue_rows_any<INT, CHAIN, 8, DSTT>(a, tp, tt, ct, r, m0, n);
                 }
             } else {
 #pragma unroll 1
@@ -498,11 +514,11 @@ bool make_map_2d(CUtensorMap *map, const void *base, uint64_t cols, uint64_t row
             == CUDA_SUCCESS;
 }
 
-template <int KIND, int BT_M, int STAGES, bool CHAIN>
+template <int KIND, int BT_M, int STAGES, bool CHAIN, int DSTT = -1>
 int launch_cfg(const CUtensorMap &mw, const CUtensorMap &ms, const MatmulArgs &a, TcParams tp, int sm_count,
         cudaStream_t st) {
     using L = SmemLayout<BT_M, STAGES>;
-    auto kern = gemm_tc_kernel<KIND, BT_M, STAGES, CHAIN>;
+    auto kern = gemm_tc_kernel<KIND, BT_M, STAGES, CHAIN, DSTT>;
     static std::atomic<unsigned long long> configured; // one per instantiation of this template
     if (!opt_in_dynamic_smem(kern, L::TOTAL, configured)) return 5;
     const int tiles = tp.num_m_tiles * tp.num_n_tiles;
@@ -587,13 +603,20 @@ int launch_gemm_tc(const MatmulArgs &a, void *scratch, int sm_count, cudaStream_
     }
     tp.idesc = ptx::make_idesc(cfmt, wfmt, sfmt, !w_kmajor, false, BT_N, BT_M);
     const bool chain = a.n_po > 0 || (a.bias && a.bias_sm != 0); // a bias varying along M rides the generic tail
+    // kernels with a post-op chain are instantiated per dst data type
+#define QMM_TC_CHAIN(KIND, BTM, ST) \
+    (a.dst_dt == DT_S8         ? launch_cfg<KIND, BTM, ST, true, DT_S8>(mw, ms, a, tp, sm_count, st) \
+                    : a.dst_dt == DT_U8   ? launch_cfg<KIND, BTM, ST, true, DT_U8>(mw, ms, a, tp, sm_count, st) \
+                    : a.dst_dt == DT_BF16 ? launch_cfg<KIND, BTM, ST, true, DT_BF16>(mw, ms, a, tp, sm_count, st) \
+                    : a.dst_dt == DT_F16  ? launch_cfg<KIND, BTM, ST, true, DT_F16>(mw, ms, a, tp, sm_count, st) \
+                    : a.dst_dt == DT_F32  ? launch_cfg<KIND, BTM, ST, true, DT_F32>(mw, ms, a, tp, sm_count, st) \
+                                          : launch_cfg<KIND, BTM, ST, true, DT_S32>(mw, ms, a, tp, sm_count, st))
 #define QMM_TC_LAUNCH(KIND) \
-    (tall ? (chain ? launch_cfg<KIND, 256, 4, true>(mw, ms, a, tp, sm_count, st) \
-                   : launch_cfg<KIND, 256, 4, false>(mw, ms, a, tp, sm_count, st)) \
-          : (chain ? launch_cfg<KIND, 128, 6, true>(mw, ms, a, tp, sm_count, st) \
-                   : launch_cfg<KIND, 128, 6, false>(mw, ms, a, tp, sm_count, st)))
+    (tall ? (chain ? QMM_TC_CHAIN(KIND, 256, 4) : launch_cfg<KIND, 256, 4, false>(mw, ms, a, tp, sm_count, st)) \
+          : (chain ? QMM_TC_CHAIN(KIND, 128, 6) : launch_cfg<KIND, 128, 6, false>(mw, ms, a, tp, sm_count, st)))
     return int_path ? QMM_TC_LAUNCH(1) : QMM_TC_LAUNCH(0);
 #undef QMM_TC_LAUNCH
+#undef QMM_TC_CHAIN
 }
 
 // ---- allocation-free variant ----------------------------------------------

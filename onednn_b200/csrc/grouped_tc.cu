@@ -242,14 +242,16 @@ grouped_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
                     ptx::tc_fence_after_sync();
                     const uint32_t sa = ptx::smem_u32(smem + A_OFFSET + sa_i * A_BYTES);
                     const uint32_t sb = ptx::smem_u32(smem + B_OFFSET + sb_i * B_BYTES);
+                    // weights MN-major: 16 k-rows of 128 bytes per MMA, 64-column blocks 8 KB apart; src rows
+                    // K-major: 32 bytes of the row per MMA.  The issuing thread is one instruction stream
+                    // (about five cycles per dependent instruction), so the descriptors are built once per
+                    // stage and advanced by constants in their start-address field (16-byte units).
+                    const uint64_t wd0 = ptx::smem_desc_sw128(sa, GK * 128, 1024);
+                    const uint64_t sd0 = ptx::smem_desc_sw128(sb, 0, 1024);
 #pragma unroll
-                    for (int kk = 0; kk < GK / 16; ++kk) {
-                        // weights MN-major: 16 k-rows of 128 bytes per MMA, 64-column blocks 8 KB apart;
-                        // src rows K-major: 32 bytes of the row per MMA
-                        const uint64_t wd = ptx::smem_desc_sw128(sa + kk * 16 * 128, GK * 128, 1024);
-                        const uint64_t sd = ptx::smem_desc_sw128(sb + kk * 32, 0, 1024);
-                        ptx::mma_ss<2>(tmem_d, wd, sd, idesc, (kb | kk) != 0);
-                    }
+                    for (int kk = 0; kk < GK / 16; ++kk)
+                        ptx::mma_ss<2>(tmem_d, wd0 + (uint64_t)(kk * ((16 * 128) >> 4)), sd0 + (uint64_t)(kk * (32 >> 4)), idesc,
+                                (kb | kk) != 0);
                     // both tiles are reusable once these MMAs have read them
                     ptx::tc_commit(&a_empty[sa_i]);
                     ptx::tc_commit(&b_empty[sb_i]);

@@ -58,10 +58,13 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
 // the wait did not finish within `limit_ns` (default 2 s): the caller then
 // records an error status and leaves its loop.
 __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, uint64_t limit_ns = 2000000000ull) {
-    if (mbar_try_wait(bar, parity)) return true;
+    // the common case first, without touching the timer: a wait that is served within a few
+    // thousand polls (every wait of a healthy pipeline) never reads %globaltimer
+    for (int i = 0; i < 4096; ++i)
+        if (mbar_try_wait(bar, parity)) return true;
     const uint64_t t0 = globaltimer();
     for (;;) {
-        for (int i = 0; i < 64; ++i)
+        for (int i = 0; i < 256; ++i)
             if (mbar_try_wait(bar, parity)) return true;
         if (globaltimer() - t0 > limit_ns) return false;
     }

@@ -19,14 +19,20 @@
 //     column, two k per 32-bit column);
 //   * one thread issues `tcgen05.mma.kind::f16` (A from TMEM, B = the src rows
 //     from shared memory, K-major), D = dst^T in TMEM (lane = dst column,
-//     column = src row), plus one MMA against a constant all-ones A tile whose
-//     result is S[m] = sum_k src[m][k] of the quantization group;
+//     column = src row);
 //   * at the end of every K-group the epilogue warps read the group sums and
 //     fold them into f32 totals in registers:
-//        tot += scale * (acc - (offset + zero_point) * S),
-//     which removes the 128 (+8 for s4) offset of the rebuilt nibbles and the
-//     zero-point after the exact integer-weighted sum; results differ from
-//     the reference's only by f32 summation order.
+//        tot += scale * (acc - (offset + zero_point) * S),   S[m] = sum_k src[m][k] of the group
+//     (they add up S themselves, from the src rows in global memory, while the
+//     group is being multiplied), which removes the 128 (+8 for s4) offset of
+//     the rebuilt nibbles and the zero-point after the exact integer-weighted
+//     sum; results differ from the reference's only by f32 summation order.
+// The hand-offs are per stage, not per k-step: a converter warp fills its part
+// of an operand stage in tensor memory (three of them, so that conversion,
+// multiplication and the release of a stage overlap), arrives once, and frees
+// the shared-memory stage with a plain arrive; the issuing thread's
+// tcgen05.commit frees the operand stage and adds the last arrival to the
+// shared-memory stage (its src tile).
 // Work decomposition is stream-K over (column tile, stage) units, one CTA per
 // SM with equal byte counts; CTAs that share a column tile add their partial
 // sums through a scratchpad in CTA order (deterministic), the last arriver
@@ -36,19 +42,25 @@
 #include <cuda_fp16.h>
 
 #include <cstring>
+#include <string>
 
 #include "device_math.cuh"
 #include "launch.h"
+#include "objects.hpp"
 #include "sm100_ptx.cuh"
 
 namespace qmm {
 
 namespace {
 
-constexpr int CONV_WARPS = 8, EPI_WARPS = 4;
-constexpr int WT_THREADS = 32 * (CONV_WARPS + EPI_WARPS + 2); // + TMA producer + MMA issuer
+// One thread issues a tcgen05.mma about every 63 cycles, whatever its size; two issuing threads in
+// different warps reach twice that, and the MMAs of this kernel are small (N = 16 or 32), so the
+// column blocks of a tile are split between two issuer warps.
+constexpr int CONV_WARPS = 8, EPI_WARPS = 4, MMA_WARPS = 2;
+constexpr int PRODUCER_WARP = CONV_WARPS + EPI_WARPS, MMA_WARP0 = PRODUCER_WARP + 1;
+constexpr int WT_THREADS = 32 * (CONV_WARPS + EPI_WARPS + 1 + MMA_WARPS);
 constexpr int W_STAGE_BYTES = 16384; // raw nibbles per stage
-constexpr int A_SLOTS = 8; // operand slots in tensor memory, one k16 step each
+constexpr int A_STAGES = 3; // operand stages in tensor memory, one shared-memory stage (128 columns) each
 
 // MR: src rows the epilogue reads (8, 16, 32); NBLK: 128-lane MMA blocks per column tile.
 template <int MR, int NBLK>
@@ -61,18 +73,25 @@ struct WtCfg {
     static constexpr int W_BOXES = ROW_BYTES / 128; // TMA boxes [KS rows x 128 B] per stage
     static constexpr int S_BOXES = KS / 64; // src boxes [MP rows x 64 k] per stage
     static constexpr int S_BYTES = S_BOXES * MP * 128;
-    static constexpr int STAGE_BYTES = W_STAGE_BYTES + ((S_BYTES + 1023) / 1024) * 1024;
-    static constexpr int STAGES = NBLK == 4 ? 8 : 6;
+    static constexpr int S_STAGE_BYTES = ((S_BYTES + 1023) / 1024) * 1024;
+    // Two rings: the weight stages are free again as soon as the converters have read them into
+    // registers, the (small) src stages only when the MMAs have run, so the src ring is the deeper one
+    // and the weight ring's round trip is TMA latency plus a shared-memory read.
+    static constexpr int STAGES = NBLK == 4 ? 8 : 6; // weight stages
+    static constexpr int S_STAGES = NBLK == 4 ? 16 : 8; // src stages
+    static constexpr int S_RING_OFFSET = STAGES * W_STAGE_BYTES;
+    static constexpr int OUT_OFFSET = S_RING_OFFSET + S_STAGES * S_STAGE_BYTES;
     static constexpr int OUT_PITCH = NB + 8; // floats per row of the output tile in shared memory
     static constexpr int OUT_BYTES = MR * OUT_PITCH * 4;
-    static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES + OUT_BYTES;
-    static constexpr int SMEM_BYTES = BAR_OFFSET + 512 + 1024;
-    // tensor memory columns
-    static constexpr int ACC_COLS = (NBLK + 1) * MP; // per buffer: NBLK result blocks + the S block
+    static constexpr int SSUM_BYTES = EPI_WARPS * 32 * 4; // per epilogue warp: S[m] of the current group
+    static constexpr int BAR_OFFSET = OUT_OFFSET + OUT_BYTES + SSUM_BYTES;
+    static constexpr int SMEM_BYTES = BAR_OFFSET + 1024 + 1024;
+    // tensor memory columns: two accumulator buffers, then the operand stages
+    static constexpr int ACC_COLS = NBLK * MP; // per buffer: NBLK result blocks
     static constexpr int A_COL0 = 2 * ACC_COLS;
-    static constexpr int A_SLOT_COLS = 8 * NBLK;
-    static constexpr int ONES_COL = A_COL0 + A_SLOTS * A_SLOT_COLS;
-    static_assert(ONES_COL + 8 <= 512, "tensor memory");
+    // an operand stage: [block][k16 step][8 columns of two k each]
+    static constexpr int A_STAGE_COLS = NBLK * SPS * 8;
+    static_assert(A_COL0 + A_STAGES * A_STAGE_COLS <= 512, "tensor memory");
     static_assert(SMEM_BYTES <= 227 * 1024, "shared memory");
 };
 
@@ -86,17 +105,22 @@ struct WtParams {
     int max_slots; // partial-sum slots per column tile
     int sgn4; // weights are s4 (else u4)
     int zp_mode; // 0 none, 1 per (group, column), 2 per tensor
+    int fast_store; // plain epilogue: no post-ops / dst scale, 16-bit or f32 dst rows that take 4-column vectors
     uint32_t idesc;
     float *partial; // [ntiles][max_slots][M * NB]
     int *counters; // [ntiles]
+    const float *step_sums; // [ksteps][MR]: sum of the 16 src values of row m in k16 step k (pre-kernel)
 #ifdef QMM_PROFILE
     int ablate; // 1 no MMAs, 2 converters idle, 4 epilogue idle, 8 no S block, 16 unpack without stores (wrong results)
+    unsigned long long *trace; // [role][256] globaltimer stamps of CTA 0 (role 0 producer, 1 MMA, 2 converter 0, 3 epilogue)
 #endif
 };
 #ifdef QMM_PROFILE
 #define WT_ABLATE(bit) (p.ablate & (bit))
+#define WT_TRACE(role, idx) do { if (p.trace && blockIdx.x == 0 && (idx) < 256) p.trace[(role) * 256 + (idx)] = ptx::globaltimer(); } while (0)
 #else
 #define WT_ABLATE(bit) false
+#define WT_TRACE(role, idx) do { } while (0)
 #endif
 
 __device__ __forceinline__ uint32_t nib2(uint32_t x, uint32_t magic) { // (x & 0x000F000F) ^ magic
@@ -116,7 +140,28 @@ __device__ __forceinline__ void tmem_st_16x128b_x2(uint32_t taddr, uint32_t r0, 
                  "r"(r2), "r"(r3)
                  : "memory");
 }
-__device__ __forceinline__ void tmem_st_32x8(uint32_t taddr, uint32_t v) {
+// The same for S consecutive k16 steps (8 columns each): 16 lanes x 8S columns in one instruction
+template <int S>
+__device__ __forceinline__ void tmem_st_16x128b_steps(uint32_t taddr, const uint32_t (&r)[4 * S]) {
+    if constexpr (S == 4) {
+        asm volatile(
+                "tcgen05.st.sync.aligned.16x128b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};" ::"r"(taddr),
+                "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]),
+                "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+                : "memory");
+    } else {
+        static_assert(S == 8, "4 or 8 k16 steps per stage");
+        asm volatile(
+                "tcgen05.st.sync.aligned.16x128b.x16.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+                "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};" ::"r"(taddr),
+                "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]),
+                "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]),
+                "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]),
+                "r"(r[31])
+                : "memory");
+    }
+}
+__device__ __forceinline__ void tmem_st_32x8_unused(uint32_t taddr, uint32_t v) {
     asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %1, %1, %1, %1, %1, %1, %1};" ::"r"(taddr), "r"(v)
                  : "memory");
 }
@@ -129,6 +174,23 @@ __device__ __forceinline__ void mma_ts_f16(uint32_t tmem_d, uint32_t tmem_a, uin
             "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}" ::"r"(tmem_d),
             "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(en)
             : "memory");
+}
+// Read-only loads that stay where they are written (requested well ahead of their use; a plain
+// load may be moved down to the use and stalls the warp there)
+__device__ __forceinline__ uint32_t ldg_u32_here(const void *ptr) {
+    uint32_t v;
+    asm volatile("ld.global.nc.u32 %0, [%1];" : "=r"(v) : "l"(ptr));
+    return v;
+}
+__device__ __forceinline__ uint32_t ldg_u16_here(const void *ptr) {
+    unsigned short v;
+    asm volatile("ld.global.nc.u16 %0, [%1];" : "=h"(v) : "l"(ptr));
+    return v;
+}
+__device__ __forceinline__ uint32_t ldg_u8_here(const void *ptr) {
+    uint32_t v;
+    asm volatile("ld.global.nc.u8 %0, [%1];" : "=r"(v) : "l"(ptr));
+    return v;
 }
 template <int N>
 __device__ __forceinline__ void tmem_ld_cols(uint32_t taddr, uint32_t (&r)[N]) {
@@ -168,12 +230,15 @@ woq_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
     using C = WtCfg<MR, NBLK>;
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-    float *out_tile = (float *)(smem + C::STAGES * C::STAGE_BYTES);
-    uint64_t *full = (uint64_t *)(smem + C::BAR_OFFSET);
+    float *out_tile = (float *)(smem + C::OUT_OFFSET);
+    float *ssum_all = (float *)(smem + C::OUT_OFFSET + C::OUT_BYTES);
+    uint64_t *full = (uint64_t *)(smem + C::BAR_OFFSET); // weight stages
     uint64_t *empty = full + C::STAGES;
-    uint64_t *a_full = empty + C::STAGES;
-    uint64_t *a_empty = a_full + A_SLOTS;
-    uint64_t *acc_full = a_empty + A_SLOTS;
+    uint64_t *s_full = empty + C::STAGES; // src stages
+    uint64_t *s_empty = s_full + C::S_STAGES;
+    uint64_t *a_full = s_empty + C::S_STAGES;
+    uint64_t *a_empty = a_full + A_STAGES;
+    uint64_t *acc_full = a_empty + A_STAGES;
     uint64_t *acc_empty = acc_full + 2;
     uint32_t *tmem_slot = (uint32_t *)(acc_empty + 2);
     volatile int *abort_flag = (volatile int *)(tmem_slot + 1);
@@ -183,14 +248,18 @@ woq_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
     if (threadIdx.x == 0) {
         for (int s = 0; s < C::STAGES; ++s) {
             ptx::mbar_init(&full[s], 1);
-            ptx::mbar_init(&empty[s], 1);
+            ptx::mbar_init(&empty[s], CONV_WARPS / 2); // the stage's four converter warps
         }
-        for (int s = 0; s < A_SLOTS; ++s) {
-            ptx::mbar_init(&a_full[s], 4); // the four converter warps of one k16 step
-            ptx::mbar_init(&a_empty[s], 1);
+        for (int s = 0; s < C::S_STAGES; ++s) {
+            ptx::mbar_init(&s_full[s], 1);
+            ptx::mbar_init(&s_empty[s], MMA_WARPS);
+        }
+        for (int s = 0; s < A_STAGES; ++s) {
+            ptx::mbar_init(&a_full[s], CONV_WARPS / 2);
+            ptx::mbar_init(&a_empty[s], MMA_WARPS);
         }
         for (int s = 0; s < 2; ++s) {
-            ptx::mbar_init(&acc_full[s], 1);
+            ptx::mbar_init(&acc_full[s], MMA_WARPS);
             ptx::mbar_init(&acc_empty[s], EPI_WARPS);
         }
         *abort_flag = 0;
@@ -198,49 +267,54 @@ woq_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
         ptx::prefetch_tensormap(&tmW);
         ptx::prefetch_tensormap(&tmS);
     }
-    if (warp == CONV_WARPS + EPI_WARPS + 1) ptx::tmem_alloc(tmem_slot, 512);
+    if (warp == MMA_WARP0) ptx::tmem_alloc(tmem_slot, 512);
     ptx::tc_fence_before_sync();
     __syncthreads();
     ptx::tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
-    if (warp < 4) { // the all-ones operand tile (its MMA yields the sum of the src values of a group)
-        tmem_st_32x8(tmem_base + ((uint32_t)(32 * warp) << 16) + C::ONES_COL, F16 ? 0x3C003C00u : 0x3F803F80u);
-        tmem_st_wait();
-    }
-    ptx::tc_fence_before_sync();
-    __syncthreads();
-    ptx::tc_fence_after_sync();
 
     const int64_t total = (int64_t)p.ntiles * p.kstages;
     const int64_t L0 = (int64_t)blockIdx.x * p.per;
     const int64_t L1 = L0 + p.per < total ? L0 + p.per : total;
 
-    if (warp == CONV_WARPS + EPI_WARPS) {
+    if (warp == PRODUCER_WARP) {
         // ------------------------------------------------ TMA producer
         if (lane == 0) {
             uint32_t it = 0;
+            int s = 0, ss_i = 0;
+            uint32_t ph = 1, sph = 1; // parities of the empty barriers' previous phases: fresh barriers pass
             for (int64_t L = L0; L < L1 && !*abort_flag;) {
                 const Segment sg = segment_at(L, L1, p.kstages);
                 const int xbyte = sg.tile * C::ROW_BYTES;
                 for (int st = sg.sb; st < sg.se; ++st, ++it) {
-                    const int s = it % C::STAGES;
-                    if (!ptx::mbar_wait(&empty[s], ((it / C::STAGES) & 1) ^ 1)) { *abort_flag = 1; atomicExch(a.status, 5); break; }
-                    uint8_t *sw = smem + s * C::STAGE_BYTES, *ss = sw + W_STAGE_BYTES;
-                    ptx::mbar_arrive_expect_tx(&full[s], W_STAGE_BYTES + C::S_BYTES);
+                    if (!ptx::mbar_wait(&empty[s], ph)) { *abort_flag = 1; atomicExch(a.status, 5); break; }
+                    uint8_t *sw = smem + s * W_STAGE_BYTES;
+                    ptx::mbar_arrive_expect_tx(&full[s], W_STAGE_BYTES);
 #pragma unroll
                     for (int b = 0; b < C::W_BOXES; ++b)
                         ptx::tma_load_2d(sw + b * (C::KS * 128), &tmW, &full[s], xbyte + b * 128, st * C::KS);
+                    if (!ptx::mbar_wait(&s_empty[ss_i], sph)) { *abort_flag = 1; atomicExch(a.status, 5); break; }
+                    uint8_t *ss = smem + C::S_RING_OFFSET + ss_i * C::S_STAGE_BYTES;
+                    ptx::mbar_arrive_expect_tx(&s_full[ss_i], C::S_BYTES);
 #pragma unroll
                     for (int b = 0; b < C::S_BOXES; ++b)
-                        ptx::tma_load_2d(ss + b * (C::MP * 128), &tmS, &full[s], st * C::KS + b * 64, 0);
+                        ptx::tma_load_2d(ss + b * (C::MP * 128), &tmS, &s_full[ss_i], st * C::KS + b * 64, 0);
+                    WT_TRACE(0, it);
+                    if (++s == C::STAGES) { s = 0; ph ^= 1; }
+                    if (++ss_i == C::S_STAGES) { ss_i = 0; sph ^= 1; }
                 }
                 L += sg.se - sg.sb;
             }
         }
-    } else if (warp == CONV_WARPS + EPI_WARPS + 1) {
-        // ------------------------------------------------ MMA issuer
+    } else if (warp >= MMA_WARP0) {
+        // ------------------------------------------------ MMA issuers: warp i takes the column blocks
+        // [i * NBLK / MMA_WARPS, (i + 1) * NBLK / MMA_WARPS) of every k16 step; both walk the same barriers
+        constexpr int JB = NBLK / MMA_WARPS;
+        const int j0 = (warp - MMA_WARP0) * JB;
         if (lane == 0) {
-            uint32_t it = 0, ks = 0, gc = 0;
+            uint32_t it = 0, gc = 0;
+            int s = 0, as = 0;
+            uint32_t ph = 0, aph = 0; // parities of the full barriers
             bool failed = false;
             for (int64_t L = L0; L < L1 && !failed && !*abort_flag;) {
                 const Segment sg = segment_at(L, L1, p.kstages);
@@ -249,26 +323,52 @@ woq_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
                 int gend = min(kend, (kpos / p.group_steps + 1) * p.group_steps); // end of the current group piece
                 bool fresh = true; // the next MMA starts a group piece
                 for (int st = sg.sb; st < sg.se && !failed; ++st, ++it) {
-                    const int s = it % C::STAGES;
-                    if (!ptx::mbar_wait(&full[s], (it / C::STAGES) & 1)) { failed = true; break; }
-                    const uint32_t ss = ptx::smem_u32(smem + s * C::STAGE_BYTES + W_STAGE_BYTES);
+                    if (!ptx::mbar_wait(&s_full[s], ph) || !ptx::mbar_wait(&a_full[as], aph)) { failed = true; break; }
+                    ptx::tc_fence_after_sync();
+                    const uint32_t ss = ptx::smem_u32(smem + C::S_RING_OFFSET + s * C::S_STAGE_BYTES);
+                    const uint32_t ast = tmem_base + C::A_COL0 + as * C::A_STAGE_COLS;
                     const int nst = min(C::SPS, kend - st * C::SPS);
-                    for (int q = 0; q < nst; ++q, ++ks, ++kpos) {
+                    // The issuing thread is a single instruction stream, about five cycles per dependent
+                    // instruction, so the common stage - whole, inside one group piece - is straight-line
+                    // code: descriptor and tensor-memory addresses are a base plus compile-time offsets.
+                    if (nst == C::SPS && kpos + C::SPS <= gend && !WT_ABLATE(1)) {
+                        const uint32_t buf = gc & 1;
+                        if (fresh) {
+                            if (!ptx::mbar_wait(&acc_empty[buf], ((gc >> 1) & 1) ^ 1)) { failed = true; break; }
+                            ptx::tc_fence_after_sync();
+                        }
+                        const uint32_t accb = tmem_base + buf * C::ACC_COLS + j0 * C::MP;
+                        const uint32_t astb = ast + j0 * (8 * C::SPS);
+                        const uint64_t bd0 = ptx::smem_desc_sw128(ss, 0, 1024);
+#pragma unroll
+                        for (int q = 0; q < C::SPS; ++q) {
+                            // the start-address field counts 16-byte units: later steps add a constant to it
+                            const uint64_t bd = bd0 + (uint64_t)(((q >> 2) * (C::MP * 128) + (q & 3) * 32) >> 4);
+#pragma unroll
+                            for (int j = 0; j < JB; ++j)
+                                mma_ts_f16(accb + j * C::MP, astb + j * (8 * C::SPS) + 8 * q, bd, p.idesc, q > 0 || !fresh);
+                        }
+                        kpos += C::SPS;
+                        fresh = false;
+                        if (kpos == gend) { // group piece complete
+                            ptx::tc_commit(&acc_full[buf]);
+                            ++gc;
+                            fresh = true;
+                            gend = min(kend, gend + p.group_steps);
+                        }
+                    } else {
+                    for (int q = 0; q < nst; ++q, ++kpos) {
                         const uint32_t buf = gc & 1;
                         if (fresh && !ptx::mbar_wait(&acc_empty[buf], ((gc >> 1) & 1) ^ 1)) { failed = true; break; }
-                        const int slot = ks % A_SLOTS;
-                        if (!ptx::mbar_wait(&a_full[slot], (ks / A_SLOTS) & 1)) { failed = true; break; }
-                        ptx::tc_fence_after_sync();
+                        if (fresh) ptx::tc_fence_after_sync();
                         const uint64_t bd = ptx::smem_desc_sw128(ss + (q >> 2) * (C::MP * 128) + (q & 3) * 32, 0, 1024);
                         const uint32_t acc = tmem_base + buf * C::ACC_COLS;
-                        const uint32_t asl = tmem_base + C::A_COL0 + slot * C::A_SLOT_COLS;
                         if (!WT_ABLATE(1)) {
 #pragma unroll
-                            for (int j = 0; j < NBLK; ++j) mma_ts_f16(acc + j * C::MP, asl + 8 * j, bd, p.idesc, !fresh);
-                            if (!WT_ABLATE(8)) mma_ts_f16(acc + NBLK * C::MP, tmem_base + C::ONES_COL, bd, p.idesc, !fresh);
+                            for (int j = 0; j < JB; ++j)
+                                mma_ts_f16(acc + (j0 + j) * C::MP, ast + (j0 + j) * (8 * C::SPS) + 8 * q, bd, p.idesc, !fresh);
                         }
                         fresh = false;
-                        ptx::tc_commit(&a_empty[slot]);
                         if (kpos + 1 == gend) { // group piece complete
                             ptx::tc_commit(&acc_full[buf]);
                             ++gc;
@@ -276,7 +376,13 @@ woq_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
                             gend = min(kend, gend + p.group_steps);
                         }
                     }
-                    ptx::tc_commit(&empty[s]); // the stage's src tile has been read; the converters are through it too
+                    }
+                    if (failed) break;
+                    ptx::tc_commit(&a_empty[as]); // the operand stage may be rewritten once these MMAs have read it
+                    ptx::tc_commit(&s_empty[s]); // ... and the stage's src tile has been read
+                    if (j0 == 0) WT_TRACE(1, it);
+                    if (++s == C::S_STAGES) { s = 0; ph ^= 1; }
+                    if (++as == A_STAGES) { as = 0; aph ^= 1; }
                 }
                 L += sg.se - sg.sb;
             }
@@ -284,10 +390,13 @@ woq_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
         }
     } else if (warp < CONV_WARPS) {
         // ------------------------------------------------ converters
-        // Warp (q = warp % 4, r = warp / 4): TMEM lanes 32q..32q+31 of every block, k16 steps of parity r.
-        // Its slice of a tile's k-row is the 16*NBLK bytes at 16*NBLK*q; lane (g, tig) owns 2*NBLK of them
-        // (4*NBLK columns) and, per step, the k-rows 2tig, 2tig+1, 2tig+8, 2tig+9: exactly the registers
-        // of the 16x128b.x2 store, byte t = 2j + h going to block j, lanes 32q + 16h + g (low nibble) and +8.
+        // Warp (q = warp % 4, r = warp / 4): TMEM lanes 32q..32q+31 of every block, the stages of parity r
+        // (two stages of a lane quarter are in flight at a time).  Its slice of a tile's k-row is the
+        // 16*NBLK bytes at 16*NBLK*q; lane (g, tig) owns 2*NBLK of them (4*NBLK columns) and, per k16
+        // step, the k-rows 2tig, 2tig+1, 2tig+8, 2tig+9: the registers of a 16x128b store, byte t = 2j + h
+        // going to block j, lanes 32q + 16h + g (low nibble) and +8.  A tcgen05.st costs the same few
+        // cycles of the SM's store pipe whatever its size, so one store carries all the k16 steps of a
+        // stage for its 16 lanes (x8 or x16: four 32-bit columns per repetition, two repetitions per step).
         const int q = warp & 3, r = warp >> 2;
         const int g = lane >> 2, tig = lane & 3;
         constexpr int BL = 2 * NBLK; // bytes per lane and k-row
@@ -298,62 +407,75 @@ woq_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
         const uint32_t lds0 = box_off + (2 * tig) * 128 + ((chunk ^ (uint32_t)(2 * tig)) << 4) + within;
         const uint32_t lds1 = box_off + (2 * tig + 1) * 128 + ((chunk ^ (uint32_t)(2 * tig + 1)) << 4) + within;
         const uint32_t magic = F16 ? (p.sgn4 ? 0x00080008u : 0u) : (p.sgn4 ? 0x43084308u : 0x43004300u);
-        uint32_t it = 0, ks = 0;
+        uint32_t it = 0;
+        int s = 0, as = 0;
+        uint32_t ph = 0, aph = 1;
         bool ok = true;
         for (int64_t L = L0; L < L1 && ok && !*abort_flag;) {
             const Segment sg = segment_at(L, L1, p.kstages);
             const int kend = min(sg.se * C::SPS, p.ksteps);
             for (int st = sg.sb; st < sg.se && ok; ++st, ++it) {
-                const int s = it % C::STAGES;
-                if (!__all_sync(0xffffffffu, ptx::mbar_wait(&full[s], (it / C::STAGES) & 1))) { ok = false; break; }
-                const uint8_t *sw = smem + s * C::STAGE_BYTES;
-                const int nst = min(C::SPS, kend - st * C::SPS);
-                for (int qs = 0; qs < nst; ++qs, ++ks) {
-                    if ((qs & 1) != r) continue;
-                    const int slot = ks % A_SLOTS;
-                    if (WT_ABLATE(2)) {
-                        if (!__all_sync(0xffffffffu, ptx::mbar_wait(&a_empty[slot], ((ks / A_SLOTS) & 1) ^ 1))) { ok = false; break; }
-                        __syncwarp();
-                        if (lane == 0) ptx::mbar_arrive(&a_full[slot]);
-                        continue;
-                    }
-                    uint32_t R[4][BL / 4];
-                    const uint8_t *b0 = sw + qs * 2048;
-                    if constexpr (NBLK == 4) {
-                        const uint2 v0 = *reinterpret_cast<const uint2 *>(b0 + lds0);
-                        const uint2 v1 = *reinterpret_cast<const uint2 *>(b0 + lds1);
-                        const uint2 v2 = *reinterpret_cast<const uint2 *>(b0 + lds0 + 1024);
-                        const uint2 v3 = *reinterpret_cast<const uint2 *>(b0 + lds1 + 1024);
-                        R[0][0] = v0.x; R[0][1] = v0.y; R[1][0] = v1.x; R[1][1] = v1.y;
-                        R[2][0] = v2.x; R[2][1] = v2.y; R[3][0] = v3.x; R[3][1] = v3.y;
-                    } else {
-                        R[0][0] = *reinterpret_cast<const uint32_t *>(b0 + lds0);
-                        R[1][0] = *reinterpret_cast<const uint32_t *>(b0 + lds1);
-                        R[2][0] = *reinterpret_cast<const uint32_t *>(b0 + lds0 + 1024);
-                        R[3][0] = *reinterpret_cast<const uint32_t *>(b0 + lds1 + 1024);
-                    }
-                    if (!__all_sync(0xffffffffu, ptx::mbar_wait(&a_empty[slot], ((ks / A_SLOTS) & 1) ^ 1))) { ok = false; break; }
-                    ptx::tc_fence_after_sync();
-                    const uint32_t asl = tmem_base + ((uint32_t)(32 * q) << 16) + C::A_COL0 + slot * C::A_SLOT_COLS;
+                if ((int)(it & 1) == r) {
+                    if (!__all_sync(0xffffffffu, ptx::mbar_wait(&full[s], ph))) { ok = false; break; }
+                    const uint8_t *sw = smem + s * W_STAGE_BYTES;
+                    const int nst = min(C::SPS, kend - st * C::SPS);
+                    if (warp == 0 && lane == 0) WT_TRACE(2, it);
+                    const uint32_t ast = tmem_base + ((uint32_t)(32 * q) << 16) + C::A_COL0 + as * C::A_STAGE_COLS;
+                    if (!WT_ABLATE(2)) {
+                        // the stage's raw bytes of this lane: [step][row 2tig, 2tig+1, 2tig+8, 2tig+9]; steps beyond
+                        // K (the last stage of a ragged K) read the zeros TMA filled in
+                        uint32_t R[C::SPS][4][BL / 4];
 #pragma unroll
-                    for (int t = 0; t < BL; ++t) {
-                        // byte t of the four rows: low nibble = column 2t, high nibble = column 2t + 1
-                        const uint32_t sel = ((4 + (t & 3)) << 12) | ((4 + (t & 3)) << 8) | ((t & 3) << 4) | (t & 3);
-                        const uint32_t x01 = prmt(R[0][t >> 2], R[1][t >> 2], sel);
-                        const uint32_t x23 = prmt(R[2][t >> 2], R[3][t >> 2], sel);
-                        if (WT_ABLATE(16)) {
-                            if ((nib2(x01, magic) ^ nib2(x01 >> 4, magic) ^ nib2(x23, magic) ^ nib2(x23 >> 4, magic)) == 0x12345u)
-                                tmem_st_16x128b_x2(asl, x01, x23, x01, x23);
-                            continue;
+                        for (int qs = 0; qs < C::SPS; ++qs) {
+                            const uint8_t *b0 = sw + qs * 2048;
+                            if constexpr (NBLK == 4) {
+                                const uint2 v0 = *reinterpret_cast<const uint2 *>(b0 + lds0);
+                                const uint2 v1 = *reinterpret_cast<const uint2 *>(b0 + lds1);
+                                const uint2 v2 = *reinterpret_cast<const uint2 *>(b0 + lds0 + 1024);
+                                const uint2 v3 = *reinterpret_cast<const uint2 *>(b0 + lds1 + 1024);
+                                R[qs][0][0] = v0.x; R[qs][0][1] = v0.y; R[qs][1][0] = v1.x; R[qs][1][1] = v1.y;
+                                R[qs][2][0] = v2.x; R[qs][2][1] = v2.y; R[qs][3][0] = v3.x; R[qs][3][1] = v3.y;
+                            } else {
+                                R[qs][0][0] = *reinterpret_cast<const uint32_t *>(b0 + lds0);
+                                R[qs][1][0] = *reinterpret_cast<const uint32_t *>(b0 + lds1);
+                                R[qs][2][0] = *reinterpret_cast<const uint32_t *>(b0 + lds0 + 1024);
+                                R[qs][3][0] = *reinterpret_cast<const uint32_t *>(b0 + lds1 + 1024);
+                            }
                         }
-                        tmem_st_16x128b_x2(asl + ((uint32_t)(16 * (t & 1)) << 16) + 8 * (t >> 1), nib2(x01, magic),
-                                nib2(x01 >> 4, magic), nib2(x23, magic), nib2(x23 >> 4, magic));
+                        // the stage's bytes are in registers: the producer may refill it
+                        __syncwarp();
+                        if (lane == 0) ptx::mbar_arrive(&empty[s]);
+                        if (!__all_sync(0xffffffffu, ptx::mbar_wait(&a_empty[as], aph))) { ok = false; break; }
+                        ptx::tc_fence_after_sync();
+#pragma unroll
+                        for (int t = 0; t < BL; ++t) {
+                            // byte t of every row: low nibble = column 2t, high nibble = column 2t + 1
+                            const uint32_t sel = ((4 + (t & 3)) << 12) | ((4 + (t & 3)) << 8) | ((t & 3) << 4) | (t & 3);
+                            uint32_t o[4 * C::SPS];
+#pragma unroll
+                            for (int qs = 0; qs < C::SPS; ++qs) {
+                                const uint32_t x01 = prmt(R[qs][0][t >> 2], R[qs][1][t >> 2], sel);
+                                const uint32_t x23 = prmt(R[qs][2][t >> 2], R[qs][3][t >> 2], sel);
+                                o[4 * qs + 0] = nib2(x01, magic);
+                                o[4 * qs + 1] = nib2(x01 >> 4, magic);
+                                o[4 * qs + 2] = nib2(x23, magic);
+                                o[4 * qs + 3] = nib2(x23 >> 4, magic);
+                            }
+                            // block j = t / 2 holds its SPS steps in consecutive columns; lanes 16 (t & 1) ...
+                            tmem_st_16x128b_steps<C::SPS>(ast + ((uint32_t)(16 * (t & 1)) << 16) + (t >> 1) * (8 * C::SPS), o);
+                        }
+                        tmem_st_wait();
+                    } else {
+                        __syncwarp();
+                        if (lane == 0) ptx::mbar_arrive(&empty[s]);
+                        if (!__all_sync(0xffffffffu, ptx::mbar_wait(&a_empty[as], aph))) { ok = false; break; }
                     }
-                    tmem_st_wait();
                     ptx::tc_fence_before_sync();
-                    __syncwarp();
-                    if (lane == 0) ptx::mbar_arrive(&a_full[slot]);
+                    __syncwarp(); // every lane's stores to tensor memory are done
+                    if (lane == 0) ptx::mbar_arrive(&a_full[as]);
                 }
+                if (++s == C::STAGES) { s = 0; ph ^= 1; }
+                if (++as == A_STAGES) { as = 0; aph ^= 1; }
             }
             L += sg.se - sg.sb;
         }
@@ -366,6 +488,7 @@ woq_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
         const int eh = lane >> 4, ehi = (lane >> 3) & 1, eg = lane & 7;
         const int col_in_tile = 32 * NBLK * q + 4 * NBLK * eg + 2 * eh + ehi;
         const int tid = threadIdx.x - CONV_WARPS * 32; // 0 .. 127
+        float *ssum = ssum_all + q * 32;
         const float off = (F16 ? 0.f : 128.f) + (p.sgn4 ? 8.f : 0.f);
         const float acc_scale = F16 ? 16777216.f : 1.f; // the f16 nibbles are u * 2^-24
         const float zt = p.zp_mode == 2 ? (float)load_int(a.wei_zp.dt, a.wei_zp.ptr, 0) : 0.f;
@@ -375,20 +498,71 @@ woq_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
 #pragma unroll
             for (int m = 0; m < MR; ++m) tot[j][m] = 0.f;
         uint32_t gc = 0;
+        // Parameters of one group piece, requested one piece ahead of their use so that their global
+        // loads are in flight while the piece before is folded: raw scale / zero-point words of the
+        // lane's NBLK columns, and (lane m) the src sums of row m for the piece's first eight k16 steps.
+        struct Request {
+            int kpos, gend, gi;
+            uint32_t sc_raw[NBLK], zp_raw[NBLK];
+            float s16[8];
+        };
+        auto raw_load = [&](int dt, const void *ptr, int64_t i) -> uint32_t {
+            switch (dt) {
+                case DT_F32: case DT_S32: return ldg_u32_here((const char *)ptr + i * 4);
+                case DT_BF16: case DT_F16: return ldg_u16_here((const char *)ptr + i * 2);
+                case DT_S8: case DT_U8: return ldg_u8_here((const char *)ptr + i);
+                default: return ldg_u8_here((const char *)ptr + (i >> 1)); // two 4-bit values per byte
+            }
+        };
+        auto raw_float = [&](int dt, uint32_t r) -> float {
+            return dt == DT_F32 ? __uint_as_float(r) : dt == DT_BF16 ? __uint_as_float(r << 16)
+                                                                      : __half2float(__ushort_as_half((unsigned short)r));
+        };
+        auto raw_int = [&](int dt, uint32_t r, int64_t i) -> float {
+            switch (dt) {
+                case DT_S32: return (float)(int)r;
+                case DT_S8: return (float)(signed char)r;
+                case DT_U8: return (float)r;
+                case DT_U4: return (float)((i & 1) ? (r >> 4) : (r & 15u));
+                default: { const int v = (i & 1) ? (int)(r >> 4) : (int)(r & 15u); return (float)((v ^ 8) - 8); } // s4
+            }
+        };
+        auto request = [&](Request &rq, int kpos, int kend, int64_t n_base) {
+            rq.kpos = kpos;
+            rq.gi = kpos / p.group_steps;
+            rq.gend = min(kend, (rq.gi + 1) * p.group_steps);
+#pragma unroll
+            for (int j = 0; j < NBLK; ++j) {
+                const int64_t n = n_base + 4 * j;
+                rq.sc_raw[j] = 0u;
+                rq.zp_raw[j] = 0u;
+                if (n < a.N) {
+                    rq.sc_raw[j] = raw_load(a.wei_scale.dt, a.wei_scale.ptr,
+                            ((a.wei_scale.mask & 1) ? (int64_t)rq.gi * a.wei_scale.ld : 0) + n);
+                    if (p.zp_mode == 1) rq.zp_raw[j] = raw_load(a.wei_zp.dt, a.wei_zp.ptr, (int64_t)rq.gi * a.wei_zp.ld + n);
+                }
+            }
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                rq.s16[i] = 0.f;
+                if (lane < p.M && kpos + i < rq.gend) rq.s16[i] = __uint_as_float(ldg_u32_here(p.step_sums + (int64_t)(kpos + i) * MR + lane));
+            }
+        };
         // The four warps meet at named barriers, so none of them may leave the loops early: after an
         // expired wait (or once another role has given up) a warp skips its waits and tensor-memory
         // reads but still walks through every barrier; the status word tells the host that dst is invalid.
         bool ok = true;
+        Request rq;
         for (int64_t L = L0; L < L1;) {
             const Segment sg = segment_at(L, L1, p.kstages);
             const int64_t n_base = (int64_t)sg.tile * C::NB + col_in_tile;
             const int kend = min(sg.se * C::SPS, p.ksteps);
             int kpos = sg.sb * C::SPS;
             if (*abort_flag) ok = false;
+            if (ok && kpos < kend) request(rq, kpos, kend, n_base);
             while (kpos < kend && ok) {
-                const int gi = kpos / p.group_steps;
-                const int gend = min(kend, (gi + 1) * p.group_steps);
-                // parameters of this group for the lane's NBLK columns (in flight while waiting)
+                // turn the words requested one piece ago into this piece's factors ...
+                const int gi = rq.gi, gend = rq.gend;
                 float sc[NBLK], oz[NBLK];
 #pragma unroll
                 for (int j = 0; j < NBLK; ++j) {
@@ -396,14 +570,20 @@ woq_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
                     sc[j] = 0.f;
                     oz[j] = 0.f;
                     if (n < a.N) {
-                        sc[j] = load_float(a.wei_scale.dt, a.wei_scale.ptr,
-                                        ((a.wei_scale.mask & 1) ? (int64_t)gi * a.wei_scale.ld : 0) + n)
-                                * acc_scale;
-                        float z = zt;
-                        if (p.zp_mode == 1) z = (float)load_int(a.wei_zp.dt, a.wei_zp.ptr, (int64_t)gi * a.wei_zp.ld + n);
+                        sc[j] = raw_float(a.wei_scale.dt, rq.sc_raw[j]) * acc_scale;
+                        const float z = p.zp_mode == 1 ? raw_int(a.wei_zp.dt, rq.zp_raw[j], (int64_t)gi * a.wei_zp.ld + n) : zt;
                         oz[j] = (off + z) / acc_scale;
                     }
                 }
+                {   // S[m] of this piece: lane m adds its steps (beyond the eight requested ahead: loaded here)
+                    float sm = ((rq.s16[0] + rq.s16[1]) + (rq.s16[2] + rq.s16[3])) + ((rq.s16[4] + rq.s16[5]) + (rq.s16[6] + rq.s16[7]));
+                    if (lane < p.M)
+                        for (int k = kpos + 8; k < gend; ++k) sm += __ldg(p.step_sums + (int64_t)k * MR + lane);
+                    ssum[lane] = sm;
+                }
+                // ... and request the next piece's
+                if (gend < kend) request(rq, gend, kend, n_base);
+                __syncwarp();
                 const uint32_t buf = gc & 1;
                 if (!__all_sync(0xffffffffu, ptx::mbar_wait(&acc_full[buf], (gc >> 1) & 1))) { ok = false; break; } // leaves the group loop only
                 ptx::tc_fence_after_sync();
@@ -411,32 +591,34 @@ woq_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
                     ptx::tc_fence_before_sync();
                     __syncwarp();
                     if (lane == 0) ptx::mbar_arrive(&acc_empty[buf]);
-                    ++gc;
-                    kpos = gend;
-                    continue;
-                }
-                const uint32_t acc = tmem_base + ((uint32_t)(32 * q) << 16) + buf * C::ACC_COLS;
-                uint32_t S[MR];
-                tmem_ld_cols<MR>(acc + NBLK * C::MP, S);
+                } else {
+                    const uint32_t acc = tmem_base + ((uint32_t)(32 * q) << 16) + buf * C::ACC_COLS;
+                    constexpr int MH = MR > 16 ? 16 : MR; // accumulator columns read at a time
 #pragma unroll
-                for (int j = 0; j < NBLK; ++j) {
-                    uint32_t v[MR];
-                    tmem_ld_cols<MR>(acc + j * C::MP, v);
-                    ptx::tmem_ld_wait();
-                    if (j == NBLK - 1) { // the buffer has been read: hand it back
-                        ptx::tc_fence_before_sync();
-                        __syncwarp();
-                        if (lane == 0) ptx::mbar_arrive(&acc_empty[buf]);
+                    for (int j = 0; j < NBLK; ++j) {
+#pragma unroll
+                        for (int h = 0; h < MR / MH; ++h) {
+                            uint32_t v[MH];
+                            tmem_ld_cols<MH>(acc + j * C::MP + h * MH, v);
+                            ptx::tmem_ld_wait();
+                            if (j == NBLK - 1 && h == MR / MH - 1) { // the buffer has been read: hand it back
+                                ptx::tc_fence_before_sync();
+                                __syncwarp();
+                                if (lane == 0) ptx::mbar_arrive(&acc_empty[buf]);
+                            }
+#pragma unroll
+                            for (int m = 0; m < MH; ++m)
+                                tot[j][h * MH + m] = fmaf(sc[j], fmaf(-oz[j], ssum[h * MH + m], __uint_as_float(v[m])), tot[j][h * MH + m]);
+                        }
                     }
-#pragma unroll
-                    for (int m = 0; m < MR; ++m)
-                        tot[j][m] = fmaf(sc[j], fmaf(-oz[j], __uint_as_float(S[m]), __uint_as_float(v[m])), tot[j][m]);
                 }
+                __syncwarp(); // ssum is rewritten for the next piece
                 ++gc;
                 kpos = gend;
             }
             // ---- end of the segment: totals -> shared-memory tile [m][column] -> reduction across the
             // CTAs that share the column tile -> bias, post-ops, store
+            if (tid == 0) WT_TRACE(3, 2 * (gc & 63));
 #pragma unroll
             for (int j = 0; j < NBLK; ++j)
 #pragma unroll
@@ -447,13 +629,16 @@ woq_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
             epi_barrier();
             const int first = (int)(((int64_t)sg.tile * p.kstages) / p.per);
             const int last = (int)((((int64_t)sg.tile + 1) * p.kstages - 1) / p.per);
+            constexpr int NB4 = C::NB / 4; // float4 groups per row: 128 or 64
+            const int nvec = p.M * NB4;
             const int nelem = p.M * C::NB;
+            const int count = last - first + 1;
             bool finalize = true;
-            float *base = p.partial + ((int64_t)sg.tile * p.max_slots) * nelem;
-            if (last > first) {
-                const int count = last - first + 1, slot = (int)blockIdx.x - first;
-                for (int i = tid; i < nelem; i += EPI_WARPS * 32)
-                    base[(int64_t)slot * nelem + i] = out_tile[(i / C::NB) * C::OUT_PITCH + (i % C::NB)];
+            float4 *base = reinterpret_cast<float4 *>(p.partial + ((int64_t)sg.tile * p.max_slots) * nelem);
+            if (count > 1) {
+                const int slot = (int)blockIdx.x - first;
+                for (int i = tid; i < nvec; i += EPI_WARPS * 32)
+                    base[(int64_t)slot * nvec + i] = *reinterpret_cast<const float4 *>(out_tile + (i / NB4) * C::OUT_PITCH + (i % NB4) * 4);
                 __threadfence();
                 epi_barrier();
                 if (tid == 0) *last_flag = atomicAdd(&p.counters[sg.tile], 1) == count - 1;
@@ -468,25 +653,60 @@ woq_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
                 float ssc = 1.f;
                 if (a.src_scale.ptr) ssc = load_float(a.src_scale.dt, a.src_scale.ptr, 0);
                 else if (a.src_scale.on_host) ssc = a.src_scale.host_value;
-                const int count = last - first + 1;
-                for (int i = tid; i < nelem; i += EPI_WARPS * 32) {
-                    const int m = i / C::NB, c = i % C::NB;
+                for (int i = tid; i < nvec; i += EPI_WARPS * 32) {
+                    const int m = i / NB4, c = (i % NB4) * 4;
                     const int64_t n = (int64_t)sg.tile * C::NB + c;
-                    float v;
-                    if (last > first) {
-                        v = 0.f;
-                        for (int sl = 0; sl < count; ++sl) v += __ldcg(base + (int64_t)sl * nelem + i);
+                    float4 v;
+                    if (count > 1) { // the slots in CTA order: the same sum whichever CTA arrives last
+                        v = __ldcg(base + i);
+                        float4 w1 = make_float4(0.f, 0.f, 0.f, 0.f), w2 = w1, w3 = w1;
+                        if (count > 1) w1 = __ldcg(base + (int64_t)nvec + i);
+                        if (count > 2) w2 = __ldcg(base + 2 * (int64_t)nvec + i);
+                        if (count > 3) w3 = __ldcg(base + 3 * (int64_t)nvec + i);
+                        v.x += w1.x; v.y += w1.y; v.z += w1.z; v.w += w1.w;
+                        if (count > 2) { v.x += w2.x; v.y += w2.y; v.z += w2.z; v.w += w2.w; }
+                        if (count > 3) { v.x += w3.x; v.y += w3.y; v.z += w3.z; v.w += w3.w; }
+                        for (int sl = 4; sl < count; ++sl) {
+                            const float4 w = __ldcg(base + (int64_t)sl * nvec + i);
+                            v.x += w.x; v.y += w.y; v.z += w.z; v.w += w.w;
+                        }
                     } else {
-                        v = out_tile[m * C::OUT_PITCH + c];
+                        v = *reinterpret_cast<const float4 *>(out_tile + m * C::OUT_PITCH + c);
                     }
-                    if (n < a.N) {
-                        float d = v * ssc;
-                        if (a.bias) d = __fadd_rn(d, load_float(a.bias_dt, a.bias, m * a.bias_sm + n * a.bias_sn));
-                        finish_store(a, d, m, n, false);
+                    float d[4] = {v.x * ssc, v.y * ssc, v.z * ssc, v.w * ssc};
+                    if (p.fast_store && n + 3 < a.N) {
+                        if (a.bias) {
+#pragma unroll
+                            for (int e = 0; e < 4; ++e)
+                                d[e] = __fadd_rn(d[e], load_float(a.bias_dt, a.bias, m * a.bias_sm + (n + e) * a.bias_sn));
+                        }
+                        const int64_t o = (int64_t)m * a.dst_sm + n;
+                        if (a.dst_dt == DT_F32) {
+                            *reinterpret_cast<float4 *>((float *)a.dst + o) = make_float4(d[0], d[1], d[2], d[3]);
+                        } else if (a.dst_dt == DT_BF16) {
+                            uint2 pk;
+                            pk.x = (uint32_t)f32_to_bf16_bits(d[0]) | ((uint32_t)f32_to_bf16_bits(d[1]) << 16);
+                            pk.y = (uint32_t)f32_to_bf16_bits(d[2]) | ((uint32_t)f32_to_bf16_bits(d[3]) << 16);
+                            *reinterpret_cast<uint2 *>((unsigned short *)a.dst + o) = pk;
+                        } else {
+                            uint2 pk;
+                            pk.x = (uint32_t)__half_as_ushort(__float2half_rn(d[0])) | ((uint32_t)__half_as_ushort(__float2half_rn(d[1])) << 16);
+                            pk.y = (uint32_t)__half_as_ushort(__float2half_rn(d[2])) | ((uint32_t)__half_as_ushort(__float2half_rn(d[3])) << 16);
+                            *reinterpret_cast<uint2 *>((unsigned short *)a.dst + o) = pk;
+                        }
+                    } else {
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            if (n + e >= a.N) continue;
+                            float de = d[e];
+                            if (a.bias) de = __fadd_rn(de, load_float(a.bias_dt, a.bias, m * a.bias_sm + (n + e) * a.bias_sn));
+                            finish_store(a, de, m, n + e, false);
+                        }
                     }
                 }
             }
             epi_barrier(); // the tile and the flag are reused by the next segment
+            if (tid == 0) WT_TRACE(3, 2 * (gc & 63) + 1);
             L += sg.se - sg.sb;
         }
         if (!ok) { *abort_flag = 1; atomicExch(a.status, 5); }
@@ -495,11 +715,36 @@ woq_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
     // ---------------------------------------------------- teardown
     ptx::tc_fence_before_sync();
     __syncthreads();
-    if (warp == CONV_WARPS + EPI_WARPS + 1) {
+    if (warp == MMA_WARP0) {
         __syncwarp();
         ptx::tc_fence_after_sync();
         ptx::tmem_dealloc(tmem_base, 512);
     }
+}
+
+// sums[k][m] = sum of src[m][16k .. 16k+15] (bf16 / f16), zero for m >= M: the S terms of the
+// zero-point / offset correction at k16-step granularity; one thread per (k, m).
+template <int MR, bool F16>
+__global__ void woq_step_sums_kernel(const __grid_constant__ MatmulArgs a, float *sums, int ksteps) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= ksteps * MR) return;
+    const int k = i / MR, m = i % MR;
+    float s = 0.f;
+    if (m < a.M) {
+        const uint4 *ptr = reinterpret_cast<const uint4 *>((const char *)a.src + ((int64_t)m * a.src_sm + (int64_t)k * 16) * 2);
+        const uint4 v0 = __ldg(ptr), v1 = __ldg(ptr + 1);
+        const uint32_t w[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            if (F16) {
+                const __half2 h = *reinterpret_cast<const __half2 *>(&w[e]);
+                s += __low2float(h) + __high2float(h);
+            } else {
+                s += __uint_as_float(w[e] << 16) + __uint_as_float(w[e] & 0xffff0000u);
+            }
+        }
+    }
+    sums[i] = s;
 }
 
 typedef CUresult (*encode_tiled_fn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
@@ -547,17 +792,28 @@ int wt_launch(const CUtensorMap &tw, const CUtensorMap &ts, const MatmulArgs &a,
     auto kern = woq_tc_kernel<MR, NBLK, F16>;
     static std::atomic<unsigned long long> configured;
     if (!opt_in_dynamic_smem(kern, C::SMEM_BYTES, configured)) return 5;
+    const int nsum = p.ksteps * MR;
+    woq_step_sums_kernel<MR, F16><<<(nsum + 255) / 256, 256, 0, st>>>(a, const_cast<float *>(p.step_sums), p.ksteps);
     kern<<<grid, WT_THREADS, C::SMEM_BYTES, st>>>(tw, ts, a, p);
-    count_launch();
-    return cudaGetLastError() == cudaSuccess ? 0 : 5;
+    count_launch(2);
+    const cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) {
+        set_last_error(std::string("cuda:tcgen05:woq4 launch: ") + cudaGetErrorString(e));
+        return 5;
+    }
+    return 0;
 }
 
 } // namespace
 
+// counters | src step sums [ceil(K/16)][MR] | split-K partial sums
+static size_t wt_sums_offset(const WtPlan &pl) { return ((size_t)pl.ntiles * sizeof(int) + 255) / 256 * 256; }
+static size_t wt_partial_offset(const WtPlan &pl, int64_t K) {
+    return wt_sums_offset(pl) + (((size_t)((K + 15) / 16) * pl.mr * sizeof(float)) + 255) / 256 * 256;
+}
 size_t woq_tc_scratch_bytes(int64_t M, int64_t N, int64_t K, int sm_count) {
     const WtPlan pl = wt_plan(M, N, K, sm_count);
-    return ((size_t)pl.ntiles * sizeof(int) + 255) / 256 * 256
-            + (size_t)pl.ntiles * pl.max_slots * (size_t)M * (128 * pl.nblk) * sizeof(float);
+    return wt_partial_offset(pl, K) + (size_t)pl.ntiles * pl.max_slots * (size_t)M * (128 * pl.nblk) * sizeof(float);
 }
 
 bool woq_tc_pointers_ok(const MatmulArgs &a) {
@@ -611,13 +867,21 @@ int launch_woq_tc(const MatmulArgs &a, void *scratch, int sm_count, cudaStream_t
     p.max_slots = pl.max_slots;
     p.sgn4 = a.wei_dt == DT_S4;
     p.zp_mode = !a.wei_zp.ptr ? 0 : (a.wei_zp.mask ? 1 : 2);
+    {
+        const int es = a.dst_dt == DT_F32 ? 4 : 2;
+        p.fast_store = a.n_po == 0 && !a.dst_scale.ptr && !a.dst_scale.on_host
+                && (a.dst_dt == DT_F32 || a.dst_dt == DT_BF16 || a.dst_dt == DT_F16) && a.dst_sn == 1
+                && (a.dst_sm * es) % (4 * es) == 0 && (uintptr_t)a.dst % (4 * es) == 0;
+    }
     const bool f16 = a.src_dt == DT_F16;
     const uint32_t fmt = f16 ? ptx::FMT_F16 : ptx::FMT_BF16;
     p.idesc = ptx::make_idesc(ptx::CFMT_F32, fmt, fmt, false, false, 128, mp);
     p.counters = (int *)scratch;
-    p.partial = (float *)((char *)scratch + ((size_t)pl.ntiles * sizeof(int) + 255) / 256 * 256);
+    p.step_sums = (const float *)((char *)scratch + wt_sums_offset(pl));
+    p.partial = (float *)((char *)scratch + wt_partial_offset(pl, a.K));
 #ifdef QMM_PROFILE // a build with -DQMM_PROFILE reads the switch; the shipped library has no such code
     p.ablate = getenv("ONEDNN_CUDA_WOQ_ABLATE") ? atoi(getenv("ONEDNN_CUDA_WOQ_ABLATE")) : 0;
+    p.trace = getenv("ONEDNN_CUDA_WOQ_TRACE") ? (unsigned long long *)strtoull(getenv("ONEDNN_CUDA_WOQ_TRACE"), nullptr, 16) : nullptr;
 #endif
 #define QMM_WT(MR, NBLK) (f16 ? wt_launch<MR, NBLK, true>(tw, ts, a, p, pl.grid, st) : wt_launch<MR, NBLK, false>(tw, ts, a, p, pl.grid, st))
     if (pl.mr == 8) return QMM_WT(8, 4);

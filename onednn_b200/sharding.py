@@ -6,9 +6,12 @@ zero-points, bias, binary post-op operands); src and per-row parameters are
 replicated.  Each rank runs an ordinary matmul on its slice and the dst
 slices are assembled with an all-gather (``gather_columns``).
 
-Grouped (MoE) problems shard by experts: rank r holds a contiguous block of
-experts and the src rows routed to them; the dst row blocks are assembled
-with a variable-size all-gather (``gather_rows``).
+Grouped (MoE) problems shard by experts, E / g per rank, chosen so that the
+ranks' work is even (``expert_assignment``: heaviest expert first onto the
+least loaded rank that still has room): a rank holds its experts' weights and
+the src rows routed to them, concatenated in expert order; the dst row blocks
+are assembled with a variable-size all-gather (``gather_rows``) and
+``row_map`` says where each row of the unsharded problem lies in them.
 """
 import numpy as np
 
@@ -65,20 +68,68 @@ def expert_range(E, rank, world):
     return E * rank // world, E * (rank + 1) // world
 
 
+def expert_assignment(rows_per_expert, world):
+    """Experts of every rank (sorted), E // world (+1 for the first E % world ranks) each.
+
+    An expert costs its weight stream (the same for every non-empty expert) or
+    its rows' arithmetic, whichever is larger: with K x N weights of one byte
+    and a tensor rate of about 240 flop per byte of HBM, the two meet near 128
+    rows.  Experts go, heaviest first, to the rank with the smallest cost so far
+    that still has room (ties: lower rank), which is deterministic."""
+    E = len(rows_per_expert)
+    cap = [E // world + (1 if r < E % world else 0) for r in range(world)]
+    cost = [0 if n == 0 else max(128, int(n)) for n in rows_per_expert]
+    order = sorted(range(E), key=lambda e: (-cost[e], e))
+    load, own = [0] * world, [[] for _ in range(world)]
+    for e in order:
+        r = min((r for r in range(world) if len(own[r]) < cap[r]), key=lambda r: (load[r], r))
+        own[r].append(e)
+        load[r] += cost[e]
+    return [sorted(o) for o in own]
+
+
+def _expert_rows(p):
+    ends = p.offsets.astype(np.int64)
+    begins = np.concatenate([[0], ends[:-1]])
+    return begins, ends
+
+
+def row_map(p: W.Problem, world: int):
+    """(rank, row inside that rank's block) of every row of the unsharded grouped problem."""
+    begins, ends = _expert_rows(p)
+    own = expert_assignment((ends - begins).tolist(), world)
+    rank_of = np.zeros(p.M, np.int64)
+    local = np.zeros(p.M, np.int64)
+    for r, experts in enumerate(own):
+        at = 0
+        for e in experts:
+            n = int(ends[e] - begins[e])
+            rank_of[begins[e]:ends[e]] = r
+            local[begins[e]:ends[e]] = at + np.arange(n)
+            at += n
+    return rank_of, local
+
+
 def shard_experts(p: W.Problem, rank: int, world: int) -> W.Problem:
     assert p.offsets is not None
-    e0, e1 = expert_range(p.groups, rank, world)
-    ends = p.offsets.astype(np.int64)
-    r0 = int(ends[e0 - 1]) if e0 > 0 else 0
-    r1 = int(ends[e1 - 1]) if e1 > e0 else r0
-    src = W.QTensor(np.ascontiguousarray(p.src.data.reshape(p.M, p.K)[r0:r1]), p.src.dt, (r1 - r0, p.K))
-    wei = W.QTensor(np.ascontiguousarray(p.wei.data[e0:e1]), p.wei.dt, (e1 - e0, p.K, p.N))
+    begins, ends = _expert_rows(p)
+    experts = expert_assignment((ends - begins).tolist(), world)[rank]
+    src2d = p.src.data.reshape(p.M, p.K)
+    parts = [src2d[begins[e]:ends[e]] for e in experts]
+    m = int(sum(len(x) for x in parts))
+    src = W.QTensor(np.ascontiguousarray(np.concatenate(parts, axis=0)) if parts else src2d[:0].copy(), p.src.dt, (m, p.K))
+    wei = W.QTensor(np.ascontiguousarray(p.wei.data[experts]), p.wei.dt, (len(experts), p.K, p.N))
     quant = {}
     for name, q in p.quant.items():
         assert name.startswith("wei") and (q.mask & 1), "only per-expert weight parameters are sharded"
-        quant[name] = W.Quant(np.ascontiguousarray(q.data[e0:e1]), q.dt, q.mask, q.groups)
-    off = (ends[e0:e1] - r0).astype(np.int32)
-    return W.Problem("%s[e %d:%d]" % (p.name, e0, e1), r1 - r0, p.N, p.K, src, wei, p.dst_dt, None, quant,
+        quant[name] = W.Quant(np.ascontiguousarray(q.data[experts]), q.dt, q.mask, q.groups)
+    bias = p.bias
+    if bias is not None:  # one row per expert
+        bias = W.QTensor(np.ascontiguousarray(bias.data.reshape(p.groups, p.N)[experts]), bias.dt, (len(experts), p.N))
+    for po in p.post_ops:
+        assert po.src1 is None, "binary post-op operands of grouped problems are not sharded"
+    off = np.cumsum([int(ends[e] - begins[e]) for e in experts]).astype(np.int32)
+    return W.Problem("%s[experts of rank %d]" % (p.name, rank), m, p.N, p.K, src, wei, p.dst_dt, bias, quant,
                      list(p.post_ops), p.apply_to_int, p.fpmath, offsets=off)
 
 
@@ -152,3 +203,72 @@ def gather_rows(local, rows_per_rank, dist=None, group=None):
     dist.all_gather_into_tensor(flat, send.contiguous(), group=group)
     out = flat.view(world, mmax, local.shape[1])
     return torch.cat([out[r, :rows_per_rank[r]] for r in range(world)], dim=0)
+
+
+class PeerGather:
+    """Assembles the shards of one dst in every rank's full [M, N] buffer with the library's own
+    peer-store kernels (``dnnl_cuda_interop_peer_scatter`` / ``_peer_wait``) instead of a collective
+    library.  The full buffers and the flag words live in symmetric memory (torch's allocator does the
+    CUDA IPC exchange once, at construction); after that a step is two kernel launches per rank.
+
+    full: the unsharded problem, p: this rank's shard.  ``dst`` is the [M, N] torch view of this
+    rank's full buffer."""
+
+    def __init__(self, full, p, rank, world, torch, dist, dev):
+        import ctypes as C
+        import torch.distributed._symmetric_memory as symm
+        from . import api
+        self.C, self.api, self.world, self.rank = C, api, world, rank
+        es = W.nbytes(full.dst_dt, 1)
+        self.nbytes = full.M * full.N * es
+        self.buf = symm.empty(max(16, self.nbytes), dtype=torch.uint8, device=dev)
+        self.flags = symm.empty(64, dtype=torch.int32, device=dev)
+        self.buf.zero_()
+        self.flags.zero_()
+        self.done = torch.zeros(1, dtype=torch.int32, device=dev)
+        torch.cuda.synchronize()
+        hb = symm.rendezvous(self.buf, dist.group.WORLD)
+        hf = symm.rendezvous(self.flags, dist.group.WORLD)
+        self.peer_dst = (C.c_void_p * world)(*[int(x) for x in hb.buffer_ptrs])
+        self.peer_flags = (C.c_void_p * world)(*[int(x) for x in hf.buffer_ptrs])
+        self._keep = (hb, hf)
+        self.epoch = 0
+        elem = {W.BF16: torch.bfloat16, W.F16: torch.float16, W.F32: torch.float32, W.S32: torch.int32,
+                W.S8: torch.int8, W.U8: torch.uint8}[full.dst_dt]
+        self.dst = self.buf[:self.nbytes].view(elem).view(full.M, full.N)
+        if full.offsets is None:
+            lo, hi = column_range(full.N, rank, world)
+            segs = [(0, 0, full.M)]
+            self.row_bytes, self.src_pitch, self.dst_pitch, self.col_bytes = (hi - lo) * es, (hi - lo) * es, full.N * es, lo * es
+        else:
+            begins, ends = _expert_rows(full)
+            segs, at = [], 0
+            for e in expert_assignment((ends - begins).tolist(), world)[rank]:
+                n = int(ends[e] - begins[e])
+                if n:
+                    segs.append((at, int(begins[e]), n))
+                at += n
+            segs = segs or [(0, 0, 0)]
+            self.row_bytes = self.src_pitch = self.dst_pitch = full.N * es
+            self.col_bytes = 0
+        self.nseg = len(segs)
+        self.segs = (C.c_int64 * (3 * self.nseg))(*[v for t in segs for v in t])
+        L = api.lib()
+        L.dnnl_cuda_interop_peer_scatter.argtypes = [
+            C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_int64, C.c_int64, C.c_void_p, C.c_int64, C.c_int64, C.c_int,
+            C.c_void_p, C.c_void_p, C.c_uint, C.c_void_p]
+        L.dnnl_cuda_interop_peer_wait.argtypes = [C.c_void_p, C.c_int, C.c_void_p, C.c_uint]
+        self.L = L
+
+    def step(self, strm, local_dst_ptr):
+        """Enqueues scatter + wait on the library stream; the assembled result is complete on this
+        rank once the stream has passed the wait."""
+        self.epoch += 1
+        st = self.L.dnnl_cuda_interop_peer_scatter(strm._h, self.world, self.rank, local_dst_ptr, self.row_bytes,
+                                                   self.src_pitch, self.peer_dst, self.dst_pitch, self.col_bytes,
+                                                   self.nseg, self.segs, self.peer_flags, self.epoch, self.done.data_ptr())
+        if st != 0:
+            raise self.api.error(st, "peer scatter")
+        st = self.L.dnnl_cuda_interop_peer_wait(strm._h, self.world, self.flags.data_ptr(), self.epoch)
+        if st != 0:
+            raise self.api.error(st, "peer wait")

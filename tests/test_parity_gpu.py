@@ -328,3 +328,22 @@ def test_runtime_m_matches_oracle(gpu, name):
         fixed, impl = run_problem(p, eng, strm)
         assert np.array_equal(got, fixed), "%s M=%d: runtime-M result differs from the fixed-M primitive (%s)" % (name, M, impl)
         assert_parity(got, O.run_port(p), p.dst_dt, "%s M=%d" % (name, M), slack_for(p, impl))
+
+
+def test_two_engines_in_one_process(gpu):
+    """An engine per device in one process (the ordinary oneDNN usage): the opt-in to large shared
+    memory belongs to the (kernel, device) pair, so every kernel family must launch on the second
+    device too.  Plain kernels only, no peer memory.  Needs two visible GPUs."""
+    from onednn_b200 import api
+    if api.engine.get_count(api.engine.kind.gpu) < 2:
+        pytest.skip("one GPU visible")
+    eng0, strm0 = gpu
+    eng1 = api.engine(api.engine.kind.gpu, 1)
+    strm1 = api.stream(eng1)
+    for make in (lambda: W.int8_zp(64, 256, 256), lambda: W.int4_decode(4, 512, 256), lambda: W.moe_grouped(96, 256, 128, 8),
+                 lambda: W.fp8_prefill(96, 512, 384)):
+        p = make()
+        want = O.run_port(p)
+        for eng, strm in ((eng0, strm0), (eng1, strm1), (eng0, strm0)):
+            got, impl = run_problem(p, eng, strm)
+            assert_parity(got, want, p.dst_dt, "%s via %s" % (p.name, impl), slack_for(p, impl))

@@ -28,8 +28,14 @@ dist.init_process_group("gloo", rank=rank, world_size=world)
 def as_f32(p, out):
     return torch.from_numpy(np.ascontiguousarray(W.to_f32(out, p.dst_dt).reshape(p.M, p.N)))
 
+def biased_moe():
+    p = W.moe_grouped(48, 64, 32, 6, sizes=[20, 1, 0, 9, 15, 3])
+    r = np.random.Generator(np.random.PCG64(3))
+    p.bias = W.QTensor(r.standard_normal((6, p.N)).astype(np.float32), W.F32, (6, p.N))
+    return p
+
 problems = [W.int8_zp(24, 64, 96, per_n_scales=True), W.int8_postops(16, 64, 80), W.fp8_prefill(8, 64, 48),
-            W.int4_decode(3, 128, 64), W.moe_grouped(40, 64, 32, 5, sizes=[7, 0, 13, 20, 0])]
+            W.int4_decode(3, 128, 64), W.moe_grouped(40, 64, 32, 5, sizes=[7, 0, 13, 20, 0]), biased_moe()]
 for p in problems:
     local = S.shard(p, rank, world)
     got_local = as_f32(local, O.run_port(local))
@@ -40,9 +46,11 @@ for p in problems:
         assert torch.equal(torch.cat([blocks[r, :, :widths[r]] for r in range(world)], dim=1), full)
     else:
         rows = [S.shard(p, r, world).M for r in range(world)]
-        full = S.gather_rows(got_local, rows)
+        stacked = S.gather_rows(got_local, rows)  # rank blocks, one after the other
         blocks = S.gather_rows_blocked(got_local, rows)  # [rank][tallest block][N]
-        assert torch.equal(torch.cat([blocks[r, :rows[r]] for r in range(world)], dim=0), full)
+        assert torch.equal(torch.cat([blocks[r, :rows[r]] for r in range(world)], dim=0), stacked)
+        rank_of, local_row = S.row_map(p, world)  # where each row of the unsharded problem lies
+        full = blocks[torch.from_numpy(rank_of), torch.from_numpy(local_row)]
     want = as_f32(p, O.run_port(p))
     assert full.shape == want.shape, (p.name, full.shape, want.shape)
     assert torch.equal(full, want), "%s: sharded result differs on rank %d" % (p.name, rank)
@@ -97,8 +105,23 @@ def test_expert_shards_cover_all_rows(world):
     from onednn_b200 import workloads as W
     from onednn_b200.sharding import shard
     p = W.moe_grouped(64, 32, 16, 8)
+    from onednn_b200.sharding import row_map, expert_assignment
     shards = [shard(p, r, world) for r in range(world)]
     assert sum(s.M for s in shards) == p.M
     assert sum(s.groups for s in shards) == p.groups
-    src = np.concatenate([s.src.data.reshape(s.M, s.K) for s in shards], axis=0)
-    assert np.array_equal(src, p.src.data.reshape(p.M, p.K))
+    assert all(s.groups == p.groups // world for s in shards)
+    rank_of, local = row_map(p, world)
+    src = p.src.data.reshape(p.M, p.K)
+    for m in range(p.M):
+        s = shards[rank_of[m]]
+        assert np.array_equal(s.src.data.reshape(s.M, s.K)[local[m]], src[m])
+    # the benchmark's distribution: the heaviest rank carries at most 1.3 x the mean cost, unless the
+    # largest expert alone (with the cheapest companions its rank must take) already exceeds that
+    big = W.moe_grouped(8192, 16, 16, 64)
+    ends = big.offsets.astype(np.int64)
+    rows = np.diff(np.concatenate([[0], ends])).tolist()
+    own = expert_assignment(rows, world)
+    cost = [sum(0 if rows[e] == 0 else max(128, rows[e]) for e in o) for o in own]
+    assert sorted(sum(own, [])) == list(range(64))
+    floor = max(rows) + (64 // world - 1) * 128
+    assert max(cost) <= max(1.3 * (sum(cost) / world), floor)
