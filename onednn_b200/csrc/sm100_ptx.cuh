@@ -69,6 +69,52 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, uint64
         if (globaltimer() - t0 > limit_ns) return false;
     }
 }
+// Lane-predicated forms for warp-uniform issuing code.  A role that one thread could play is
+// written as code that the whole warp runs, with only the instruction itself predicated on
+// `issue` (true in one lane): the loop counters, addresses and descriptors around it then stay
+// warp-uniform values, which the compiler keeps in uniform registers, instead of per-thread
+// values that must be moved there before every tcgen05 / TMA instruction.
+__device__ __forceinline__ void mbar_arrive_expect_tx_if(bool issue, uint64_t *bar, uint32_t bytes) {
+    asm volatile("{\n\t.reg .pred q;\n\tsetp.ne.b32 q, %2, 0;\n\t@q mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n\t}"
+                 ::"r"(smem_u32(bar)), "r"(bytes), "r"((uint32_t)issue)
+                 : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_if(bool issue, uint64_t *bar) {
+    asm volatile("{\n\t.reg .pred q;\n\tsetp.ne.b32 q, %1, 0;\n\t@q mbarrier.arrive.shared::cta.b64 _, [%0];\n\t}"
+                 ::"r"(smem_u32(bar)), "r"((uint32_t)issue)
+                 : "memory");
+}
+__device__ __forceinline__ void tma_load_2d_if(bool issue, void *dst, const void *map, uint64_t *bar, int x, int y) {
+    asm volatile(
+            "{\n\t.reg .pred q;\n\tsetp.ne.b32 q, %5, 0;\n\t"
+            "@q cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n\t}"
+            ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"((uint32_t)issue)
+            : "memory");
+}
+__device__ __forceinline__ void tc_commit_if(bool issue, uint64_t *bar) {
+    asm volatile("{\n\t.reg .pred q;\n\tsetp.ne.b32 q, %1, 0;\n\t"
+                 "@q tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t}" ::"r"(smem_u32(bar)), "r"((uint32_t)issue)
+                 : "memory");
+}
+
+// The same for a whole warp that may wait long: between polls the warp sleeps a few dozen
+// nanoseconds, so that a dozen waiting warps do not fill the SM's shared-memory instruction queue
+// with polls that the working warps' loads, arrives and tensor-memory stores then queue behind.
+__device__ __forceinline__ bool mbar_wait_relaxed(uint64_t *bar, uint32_t parity, uint64_t limit_ns = 2000000000ull) {
+    if (mbar_try_wait(bar, parity)) return true;
+    for (int i = 0; i < 8192; ++i) {
+        __nanosleep(32);
+        if (mbar_try_wait(bar, parity)) return true;
+    }
+    const uint64_t t0 = globaltimer();
+    for (;;) {
+        for (int i = 0; i < 256; ++i) {
+            __nanosleep(64);
+            if (mbar_try_wait(bar, parity)) return true;
+        }
+        if (globaltimer() - t0 > limit_ns) return false;
+    }
+}
 
 // ---- TMA ------------------------------------------------------------------
 __device__ __forceinline__ void prefetch_tensormap(const CUtensorMap *m) {

@@ -23,10 +23,13 @@
 //   * at the end of every K-group the epilogue warps read the group sums and
 //     fold them into f32 totals in registers:
 //        tot += scale * (acc - (offset + zero_point) * S),   S[m] = sum_k src[m][k] of the group
-//     (they add up S themselves, from the src rows in global memory, while the
-//     group is being multiplied), which removes the 128 (+8 for s4) offset of
-//     the rebuilt nibbles and the zero-point after the exact integer-weighted
-//     sum; results differ from the reference's only by f32 summation order.
+//     which removes the 128 (+8 for s4) offset of the rebuilt nibbles and the
+//     zero-point after the exact integer-weighted sum; results differ from the
+//     reference's only by f32 summation order.  S comes from a small pre-kernel
+//     (sums per k16 step); those sums, the scales and the zero-points of a
+//     stage's groups travel by TMA in the same ring stage as the src tile, so
+//     the epilogue never waits for a global load of its own (under this
+//     kernel's load a load takes microseconds).
 // The hand-offs are per stage, not per k-step: a converter warp fills its part
 // of an operand stage in tensor memory (three of them, so that conversion,
 // multiplication and the release of a stage overlap), arrives once, and frees
@@ -57,8 +60,11 @@ namespace {
 // different warps reach twice that, and the MMAs of this kernel are small (N = 16 or 32), so the
 // column blocks of a tile are split between two issuer warps.
 constexpr int CONV_WARPS = 8, EPI_WARPS = 4, MMA_WARPS = 2;
-constexpr int PRODUCER_WARP = CONV_WARPS + EPI_WARPS, MMA_WARP0 = PRODUCER_WARP + 1;
-constexpr int WT_THREADS = 32 * (CONV_WARPS + EPI_WARPS + 1 + MMA_WARPS);
+// A thread issues a stage of TMA copies in a few hundred cycles (a wait, an expect-tx and about 70
+// cycles per copy), which is the time a stage may take: the weights and the rest (src tile, sums,
+// scales, zero-points) have a producer thread each, in different warps.
+constexpr int PRODUCER_WARP = CONV_WARPS + EPI_WARPS, MMA_WARP0 = PRODUCER_WARP + 1, PARAM_WARP = MMA_WARP0 + MMA_WARPS;
+constexpr int WT_THREADS = 32 * (CONV_WARPS + EPI_WARPS + 2 + MMA_WARPS);
 constexpr int W_STAGE_BYTES = 16384; // raw nibbles per stage
 constexpr int A_STAGES = 3; // operand stages in tensor memory, one shared-memory stage (128 columns) each
 
@@ -73,26 +79,28 @@ struct WtCfg {
     static constexpr int W_BOXES = ROW_BYTES / 128; // TMA boxes [KS rows x 128 B] per stage
     static constexpr int S_BOXES = KS / 64; // src boxes [MP rows x 64 k] per stage
     static constexpr int S_BYTES = S_BOXES * MP * 128;
-    static constexpr int S_STAGE_BYTES = ((S_BYTES + 1023) / 1024) * 1024;
-    // Two rings: the weight stages are free again as soon as the converters have read them into
-    // registers, the (small) src stages only when the MMAs have run, so the src ring is the deeper one
-    // and the weight ring's round trip is TMA latency plus a shared-memory read.
+    // Two rings.  The weight stages are free again as soon as the converters have read them into
+    // registers, so that ring's round trip is TMA latency plus a shared-memory read.  The other ring
+    // carries, per stage, the src tile and the stage's parameters (step sums, scale and zero-point
+    // rows of its groups); its stages are small, are freed by the MMAs and the epilogue, and their size
+    // and number depend on the data types and the group size (WtParams).
     static constexpr int STAGES = NBLK == 4 ? 8 : 6; // weight stages
-    static constexpr int S_STAGES = NBLK == 4 ? 16 : 8; // src stages
-    static constexpr int S_RING_OFFSET = STAGES * W_STAGE_BYTES;
-    static constexpr int OUT_OFFSET = S_RING_OFFSET + S_STAGES * S_STAGE_BYTES;
+    static constexpr int S_STAGES_MAX = 16;
+    static constexpr int SUMS_BYTES = SPS * MR * 4;
+    static constexpr int OUT_OFFSET = STAGES * W_STAGE_BYTES;
     static constexpr int OUT_PITCH = NB + 8; // floats per row of the output tile in shared memory
     static constexpr int OUT_BYTES = MR * OUT_PITCH * 4;
     static constexpr int SSUM_BYTES = EPI_WARPS * 32 * 4; // per epilogue warp: S[m] of the current group
     static constexpr int BAR_OFFSET = OUT_OFFSET + OUT_BYTES + SSUM_BYTES;
-    static constexpr int SMEM_BYTES = BAR_OFFSET + 1024 + 1024;
+    static constexpr int S_RING_OFFSET = ((BAR_OFFSET + 512 + 1023) / 1024) * 1024;
+    static constexpr int SMEM_LIMIT = 227 * 1024 - 1024; // minus the alignment slack of the dynamic array
     // tensor memory columns: two accumulator buffers, then the operand stages
     static constexpr int ACC_COLS = NBLK * MP; // per buffer: NBLK result blocks
     static constexpr int A_COL0 = 2 * ACC_COLS;
     // an operand stage: [block][k16 step][8 columns of two k each]
     static constexpr int A_STAGE_COLS = NBLK * SPS * 8;
     static_assert(A_COL0 + A_STAGES * A_STAGE_COLS <= 512, "tensor memory");
-    static_assert(SMEM_BYTES <= 227 * 1024, "shared memory");
+    static_assert(S_RING_OFFSET + 6 * (S_BYTES + 1024) <= SMEM_LIMIT, "shared memory");
 };
 
 struct WtParams {
@@ -110,6 +118,11 @@ struct WtParams {
     float *partial; // [ntiles][max_slots][M * NB]
     int *counters; // [ntiles]
     const float *step_sums; // [ksteps][MR]: sum of the 16 src values of row m in k16 step k (pre-kernel)
+    // the src / parameter ring: stage = src tile | step sums | scale rows | zero-point rows
+    int s_stages, s_stage_bytes;
+    int off_sums, off_sc, off_zp; // byte offsets inside a stage
+    int sc_box_bytes, zp_box_bytes; // what one TMA copy of the rows brings
+    int sc_row_bytes, zp_row_bytes; // pitch of a row of NB columns in shared memory
 #ifdef QMM_PROFILE
     int ablate; // 1 no MMAs, 2 converters idle, 4 epilogue idle, 8 no S block, 16 unpack without stores (wrong results)
     unsigned long long *trace; // [role][256] globaltimer stamps of CTA 0 (role 0 producer, 1 MMA, 2 converter 0, 3 epilogue)
@@ -117,7 +130,7 @@ struct WtParams {
 };
 #ifdef QMM_PROFILE
 #define WT_ABLATE(bit) (p.ablate & (bit))
-#define WT_TRACE(role, idx) do { if (p.trace && blockIdx.x == 0 && (idx) < 256) p.trace[(role) * 256 + (idx)] = ptx::globaltimer(); } while (0)
+#define WT_TRACE(role, idx) do { if (p.trace && blockIdx.x == 0 && (idx) < 256) p.trace[(role) * 256 + (idx)] = (unsigned long long)clock64(); } while (0)
 #else
 #define WT_ABLATE(bit) false
 #define WT_TRACE(role, idx) do { } while (0)
@@ -133,14 +146,9 @@ __device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
     asm("prmt.b32 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(sel));
     return r;
 }
-// 16 TMEM lanes x 8 columns: thread (g = lane / 4, t = lane % 4) supplies r0 = (lane g, column t),
-// r1 = (lane g + 8, column t), r2 = (lane g, column 4 + t), r3 = (lane g + 8, column 4 + t)
-__device__ __forceinline__ void tmem_st_16x128b_x2(uint32_t taddr, uint32_t r0, uint32_t r1, uint32_t r2, uint32_t r3) {
-    asm volatile("tcgen05.st.sync.aligned.16x128b.x2.b32 [%0], {%1, %2, %3, %4};" ::"r"(taddr), "r"(r0), "r"(r1),
-                 "r"(r2), "r"(r3)
-                 : "memory");
-}
-// The same for S consecutive k16 steps (8 columns each): 16 lanes x 8S columns in one instruction
+// 16 TMEM lanes x 8 columns per k16 step: thread (g = lane / 4, t = lane % 4) supplies r0 = (lane g, column t),
+// r1 = (lane g + 8, column t), r2 = (lane g, column 4 + t), r3 = (lane g + 8, column 4 + t);
+// S consecutive k16 steps (8 columns each): 16 lanes x 8S columns in one instruction
 template <int S>
 __device__ __forceinline__ void tmem_st_16x128b_steps(uint32_t taddr, const uint32_t (&r)[4 * S]) {
     if constexpr (S == 4) {
@@ -161,36 +169,15 @@ __device__ __forceinline__ void tmem_st_16x128b_steps(uint32_t taddr, const uint
                 : "memory");
     }
 }
-__device__ __forceinline__ void tmem_st_32x8_unused(uint32_t taddr, uint32_t v) {
-    asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %1, %1, %1, %1, %1, %1, %1};" ::"r"(taddr), "r"(v)
-                 : "memory");
-}
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
-// D[tmem] (+)= A[tmem] * B[smem]
-__device__ __forceinline__ void mma_ts_f16(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t idesc, bool acc) {
+// D[tmem] (+)= A[tmem] * B[smem], issued by the lane(s) with `issue` set
+__device__ __forceinline__ void mma_ts_f16(bool issue, uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t idesc, bool acc) {
     const uint32_t en = acc ? 1u : 0u;
     asm volatile(
-            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-            "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}" ::"r"(tmem_d),
-            "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(en)
+            "{\n\t.reg .pred p, q;\n\tsetp.ne.b32 p, %4, 0;\n\tsetp.ne.b32 q, %5, 0;\n\t"
+            "@q tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}" ::"r"(tmem_d),
+            "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(en), "r"((uint32_t)issue)
             : "memory");
-}
-// Read-only loads that stay where they are written (requested well ahead of their use; a plain
-// load may be moved down to the use and stalls the warp there)
-__device__ __forceinline__ uint32_t ldg_u32_here(const void *ptr) {
-    uint32_t v;
-    asm volatile("ld.global.nc.u32 %0, [%1];" : "=r"(v) : "l"(ptr));
-    return v;
-}
-__device__ __forceinline__ uint32_t ldg_u16_here(const void *ptr) {
-    unsigned short v;
-    asm volatile("ld.global.nc.u16 %0, [%1];" : "=h"(v) : "l"(ptr));
-    return v;
-}
-__device__ __forceinline__ uint32_t ldg_u8_here(const void *ptr) {
-    uint32_t v;
-    asm volatile("ld.global.nc.u8 %0, [%1];" : "=r"(v) : "l"(ptr));
-    return v;
 }
 template <int N>
 __device__ __forceinline__ void tmem_ld_cols(uint32_t taddr, uint32_t (&r)[N]) {
@@ -207,6 +194,11 @@ __device__ __forceinline__ void tmem_ld_cols(uint32_t taddr, uint32_t (&r)[N]) {
     } else {
         ptx::tmem_ld_32x32(taddr, r);
     }
+}
+// The general store (post-ops, dst scale, any dst type) is rare and large: kept out of line so that
+// the hot loops of the five roles stay close together in the instruction cache.
+__device__ __noinline__ void finish_store_cold(const MatmulArgs &a, float d, int64_t m, int64_t n) {
+    finish_store(a, d, m, n, false);
 }
 __device__ __forceinline__ void epi_barrier() { asm volatile("bar.sync 1, %0;" ::"n"(EPI_WARPS * 32) : "memory"); }
 
@@ -226,7 +218,8 @@ __device__ __forceinline__ Segment segment_at(int64_t L, int64_t L1, int kstages
 template <int MR, int NBLK, bool F16>
 __global__ void __launch_bounds__(WT_THREADS, 1)
 woq_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmS,
-        const __grid_constant__ MatmulArgs a, const __grid_constant__ WtParams p) {
+        const __grid_constant__ CUtensorMap tmSums, const __grid_constant__ CUtensorMap tmSc,
+        const __grid_constant__ CUtensorMap tmZp, const __grid_constant__ MatmulArgs a, const __grid_constant__ WtParams p) {
     using C = WtCfg<MR, NBLK>;
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -235,8 +228,8 @@ woq_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
     uint64_t *full = (uint64_t *)(smem + C::BAR_OFFSET); // weight stages
     uint64_t *empty = full + C::STAGES;
     uint64_t *s_full = empty + C::STAGES; // src stages
-    uint64_t *s_empty = s_full + C::S_STAGES;
-    uint64_t *a_full = s_empty + C::S_STAGES;
+    uint64_t *s_empty = s_full + C::S_STAGES_MAX;
+    uint64_t *a_full = s_empty + C::S_STAGES_MAX;
     uint64_t *a_empty = a_full + A_STAGES;
     uint64_t *acc_full = a_empty + A_STAGES;
     uint64_t *acc_empty = acc_full + 2;
@@ -250,9 +243,9 @@ woq_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
             ptx::mbar_init(&full[s], 1);
             ptx::mbar_init(&empty[s], CONV_WARPS / 2); // the stage's four converter warps
         }
-        for (int s = 0; s < C::S_STAGES; ++s) {
+        for (int s = 0; s < p.s_stages; ++s) {
             ptx::mbar_init(&s_full[s], 1);
-            ptx::mbar_init(&s_empty[s], MMA_WARPS);
+            ptx::mbar_init(&s_empty[s], MMA_WARPS + EPI_WARPS); // the src tile and the parameters have been read
         }
         for (int s = 0; s < A_STAGES; ++s) {
             ptx::mbar_init(&a_full[s], CONV_WARPS / 2);
@@ -266,6 +259,9 @@ woq_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
         ptx::fence_barrier_init();
         ptx::prefetch_tensormap(&tmW);
         ptx::prefetch_tensormap(&tmS);
+        ptx::prefetch_tensormap(&tmSums);
+        ptx::prefetch_tensormap(&tmSc);
+        if (p.zp_mode == 1) ptx::prefetch_tensormap(&tmZp);
     }
     if (warp == MMA_WARP0) ptx::tmem_alloc(tmem_slot, 512);
     ptx::tc_fence_before_sync();
@@ -279,42 +275,81 @@ woq_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
 
     if (warp == PRODUCER_WARP) {
         // ------------------------------------------------ TMA producer
-        if (lane == 0) {
+        // (the whole warp walks the loop, lane 0 issues: see the lane-predicated forms)
+        {
+            const bool issue = lane == 0;
             uint32_t it = 0;
-            int s = 0, ss_i = 0;
-            uint32_t ph = 1, sph = 1; // parities of the empty barriers' previous phases: fresh barriers pass
-            for (int64_t L = L0; L < L1 && !*abort_flag;) {
+            int s = 0;
+            uint32_t ph = 1; // parity of the empty barrier's previous phase: a fresh barrier passes
+            bool ok = true;
+            for (int64_t L = L0; L < L1 && ok && !*abort_flag;) {
                 const Segment sg = segment_at(L, L1, p.kstages);
                 const int xbyte = sg.tile * C::ROW_BYTES;
                 for (int st = sg.sb; st < sg.se; ++st, ++it) {
-                    if (!ptx::mbar_wait(&empty[s], ph)) { *abort_flag = 1; atomicExch(a.status, 5); break; }
+                    if (!__all_sync(0xffffffffu, ptx::mbar_wait(&empty[s], ph))) { ok = false; break; }
                     uint8_t *sw = smem + s * W_STAGE_BYTES;
-                    ptx::mbar_arrive_expect_tx(&full[s], W_STAGE_BYTES);
+                    ptx::mbar_arrive_expect_tx_if(issue, &full[s], W_STAGE_BYTES);
 #pragma unroll
                     for (int b = 0; b < C::W_BOXES; ++b)
-                        ptx::tma_load_2d(sw + b * (C::KS * 128), &tmW, &full[s], xbyte + b * 128, st * C::KS);
-                    if (!ptx::mbar_wait(&s_empty[ss_i], sph)) { *abort_flag = 1; atomicExch(a.status, 5); break; }
-                    uint8_t *ss = smem + C::S_RING_OFFSET + ss_i * C::S_STAGE_BYTES;
-                    ptx::mbar_arrive_expect_tx(&s_full[ss_i], C::S_BYTES);
-#pragma unroll
-                    for (int b = 0; b < C::S_BOXES; ++b)
-                        ptx::tma_load_2d(ss + b * (C::MP * 128), &tmS, &s_full[ss_i], st * C::KS + b * 64, 0);
-                    WT_TRACE(0, it);
+                        ptx::tma_load_2d_if(issue, sw + b * (C::KS * 128), &tmW, &full[s], xbyte + b * 128, st * C::KS);
+                    if (issue) WT_TRACE(0, it);
                     if (++s == C::STAGES) { s = 0; ph ^= 1; }
-                    if (++ss_i == C::S_STAGES) { ss_i = 0; sph ^= 1; }
                 }
                 L += sg.se - sg.sb;
             }
+            if (!ok && issue) { *abort_flag = 1; atomicExch(a.status, 5); }
         }
-    } else if (warp >= MMA_WARP0) {
+    } else if (warp == PARAM_WARP) {
+        // ------------------------------------------------ second producer: src tile, step sums and,
+        // where a group piece can begin in the stage, the scale / zero-point rows of the stage's groups
+        {
+            const bool issue = lane == 0;
+            int s = 0;
+            uint32_t ph = 1;
+            [[maybe_unused]] uint32_t pit = 0;
+            const uint32_t base_tx = C::S_BYTES + C::SUMS_BYTES;
+            const uint32_t par_tx = p.sc_box_bytes + (p.zp_mode == 1 ? p.zp_box_bytes : 0);
+            bool ok = true;
+            for (int64_t L = L0; L < L1 && ok && !*abort_flag;) {
+                const Segment sg = segment_at(L, L1, p.kstages);
+                const int xpair = sg.tile * (C::NB / 2); // parameter maps count pairs of columns
+                int first = sg.sb * C::SPS;
+                int gi0 = first / p.group_steps, r = first - gi0 * p.group_steps; // group of the stage's first step, steps into it
+                for (int st = sg.sb; st < sg.se; ++st) {
+                    if (!__all_sync(0xffffffffu, ptx::mbar_wait(&s_empty[s], ph))) { ok = false; break; }
+                    uint8_t *ss = smem + C::S_RING_OFFSET + s * p.s_stage_bytes;
+                    const bool params = st == sg.sb || r == 0 || p.group_steps - r < C::SPS;
+                    ptx::mbar_arrive_expect_tx_if(issue, &s_full[s], base_tx + (params ? par_tx : 0u));
+#pragma unroll
+                    for (int b = 0; b < C::S_BOXES; ++b)
+                        ptx::tma_load_2d_if(issue, ss + b * (C::MP * 128), &tmS, &s_full[s], st * C::KS + b * 64, 0);
+                    ptx::tma_load_2d_if(issue, ss + p.off_sums, &tmSums, &s_full[s], 0, first);
+                    if (params) {
+                        ptx::tma_load_2d_if(issue, ss + p.off_sc, &tmSc, &s_full[s], xpair, gi0);
+                        if (p.zp_mode == 1) ptx::tma_load_2d_if(issue, ss + p.off_zp, &tmZp, &s_full[s], xpair, gi0);
+                    }
+                    if (issue) WT_TRACE(12, pit);
+                    ++pit;
+                    first += C::SPS;
+                    r += C::SPS;
+                    while (r >= p.group_steps) { r -= p.group_steps; ++gi0; }
+                    if (++s == p.s_stages) { s = 0; ph ^= 1; }
+                }
+                L += sg.se - sg.sb;
+            }
+            if (!ok && issue) { *abort_flag = 1; atomicExch(a.status, 5); }
+        }
+    } else if (warp >= MMA_WARP0 && warp < MMA_WARP0 + MMA_WARPS) {
         // ------------------------------------------------ MMA issuers: warp i takes the column blocks
         // [i * NBLK / MMA_WARPS, (i + 1) * NBLK / MMA_WARPS) of every k16 step; both walk the same barriers
         constexpr int JB = NBLK / MMA_WARPS;
         const int j0 = (warp - MMA_WARP0) * JB;
-        if (lane == 0) {
+        // (the whole warp walks the loop, lane 0 issues)
+        {
+            const bool issue = lane == 0;
             uint32_t it = 0, gc = 0;
             int s = 0, as = 0;
-            uint32_t ph = 0, aph = 0; // parities of the full barriers
+            uint32_t aph = 0; // parity of the operand-stage barriers
             bool failed = false;
             for (int64_t L = L0; L < L1 && !failed && !*abort_flag;) {
                 const Segment sg = segment_at(L, L1, p.kstages);
@@ -323,20 +358,22 @@ woq_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
                 int gend = min(kend, (kpos / p.group_steps + 1) * p.group_steps); // end of the current group piece
                 bool fresh = true; // the next MMA starts a group piece
                 for (int st = sg.sb; st < sg.se && !failed; ++st, ++it) {
-                    if (!ptx::mbar_wait(&s_full[s], ph) || !ptx::mbar_wait(&a_full[as], aph)) { failed = true; break; }
+                    // (the converters have seen the stage's src tile arrive before they arrive here)
+                    if (!__all_sync(0xffffffffu, ptx::mbar_wait(&a_full[as], aph))) { failed = true; break; }
+                    if (j0 == 0 && issue) WT_TRACE(5, it);
                     ptx::tc_fence_after_sync();
-                    const uint32_t ss = ptx::smem_u32(smem + C::S_RING_OFFSET + s * C::S_STAGE_BYTES);
+                    const uint32_t ss = ptx::smem_u32(smem + C::S_RING_OFFSET + s * p.s_stage_bytes);
                     const uint32_t ast = tmem_base + C::A_COL0 + as * C::A_STAGE_COLS;
                     const int nst = min(C::SPS, kend - st * C::SPS);
-                    // The issuing thread is a single instruction stream, about five cycles per dependent
-                    // instruction, so the common stage - whole, inside one group piece - is straight-line
-                    // code: descriptor and tensor-memory addresses are a base plus compile-time offsets.
+                    // The common stage - whole, inside one group piece - is straight-line code:
+                    // descriptor and tensor-memory addresses are a base plus compile-time offsets.
                     if (nst == C::SPS && kpos + C::SPS <= gend && !WT_ABLATE(1)) {
                         const uint32_t buf = gc & 1;
                         if (fresh) {
-                            if (!ptx::mbar_wait(&acc_empty[buf], ((gc >> 1) & 1) ^ 1)) { failed = true; break; }
+                            if (!__all_sync(0xffffffffu, ptx::mbar_wait(&acc_empty[buf], ((gc >> 1) & 1) ^ 1))) { failed = true; break; }
                             ptx::tc_fence_after_sync();
                         }
+                        if (j0 == 0 && issue) WT_TRACE(6, it);
                         const uint32_t accb = tmem_base + buf * C::ACC_COLS + j0 * C::MP;
                         const uint32_t astb = ast + j0 * (8 * C::SPS);
                         const uint64_t bd0 = ptx::smem_desc_sw128(ss, 0, 1024);
@@ -346,47 +383,49 @@ woq_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
                             const uint64_t bd = bd0 + (uint64_t)(((q >> 2) * (C::MP * 128) + (q & 3) * 32) >> 4);
 #pragma unroll
                             for (int j = 0; j < JB; ++j)
-                                mma_ts_f16(accb + j * C::MP, astb + j * (8 * C::SPS) + 8 * q, bd, p.idesc, q > 0 || !fresh);
+                                mma_ts_f16(issue, accb + j * C::MP, astb + j * (8 * C::SPS) + 8 * q, bd, p.idesc, q > 0 || !fresh);
                         }
                         kpos += C::SPS;
                         fresh = false;
                         if (kpos == gend) { // group piece complete
-                            ptx::tc_commit(&acc_full[buf]);
+                            ptx::tc_commit_if(issue, &acc_full[buf]);
                             ++gc;
                             fresh = true;
                             gend = min(kend, gend + p.group_steps);
                         }
                     } else {
-                    for (int q = 0; q < nst; ++q, ++kpos) {
-                        const uint32_t buf = gc & 1;
-                        if (fresh && !ptx::mbar_wait(&acc_empty[buf], ((gc >> 1) & 1) ^ 1)) { failed = true; break; }
-                        if (fresh) ptx::tc_fence_after_sync();
-                        const uint64_t bd = ptx::smem_desc_sw128(ss + (q >> 2) * (C::MP * 128) + (q & 3) * 32, 0, 1024);
-                        const uint32_t acc = tmem_base + buf * C::ACC_COLS;
-                        if (!WT_ABLATE(1)) {
+                        for (int q = 0; q < nst; ++q, ++kpos) {
+                            const uint32_t buf = gc & 1;
+                            if (fresh) {
+                                if (!__all_sync(0xffffffffu, ptx::mbar_wait(&acc_empty[buf], ((gc >> 1) & 1) ^ 1))) { failed = true; break; }
+                                ptx::tc_fence_after_sync();
+                            }
+                            const uint64_t bd = ptx::smem_desc_sw128(ss + (q >> 2) * (C::MP * 128) + (q & 3) * 32, 0, 1024);
+                            const uint32_t acc = tmem_base + buf * C::ACC_COLS;
+                            if (!WT_ABLATE(1)) {
 #pragma unroll
-                            for (int j = 0; j < JB; ++j)
-                                mma_ts_f16(acc + (j0 + j) * C::MP, ast + (j0 + j) * (8 * C::SPS) + 8 * q, bd, p.idesc, !fresh);
+                                for (int j = 0; j < JB; ++j)
+                                    mma_ts_f16(issue, acc + (j0 + j) * C::MP, ast + (j0 + j) * (8 * C::SPS) + 8 * q, bd, p.idesc, !fresh);
+                            }
+                            fresh = false;
+                            if (kpos + 1 == gend) { // group piece complete
+                                ptx::tc_commit_if(issue, &acc_full[buf]);
+                                ++gc;
+                                fresh = true;
+                                gend = min(kend, gend + p.group_steps);
+                            }
                         }
-                        fresh = false;
-                        if (kpos + 1 == gend) { // group piece complete
-                            ptx::tc_commit(&acc_full[buf]);
-                            ++gc;
-                            fresh = true;
-                            gend = min(kend, gend + p.group_steps);
-                        }
-                    }
                     }
                     if (failed) break;
-                    ptx::tc_commit(&a_empty[as]); // the operand stage may be rewritten once these MMAs have read it
-                    ptx::tc_commit(&s_empty[s]); // ... and the stage's src tile has been read
-                    if (j0 == 0) WT_TRACE(1, it);
-                    if (++s == C::S_STAGES) { s = 0; ph ^= 1; }
+                    ptx::tc_commit_if(issue, &a_empty[as]); // the operand stage may be rewritten once these MMAs have read it
+                    ptx::tc_commit_if(issue, &s_empty[s]); // ... and the stage's src tile has been read
+                    if (j0 == 0 && issue) WT_TRACE(1, it);
+                    if (++s == p.s_stages) s = 0;
                     if (++as == A_STAGES) { as = 0; aph ^= 1; }
                 }
                 L += sg.se - sg.sb;
             }
-            if (failed) { *abort_flag = 1; atomicExch(a.status, 5); }
+            if (failed && issue) { *abort_flag = 1; atomicExch(a.status, 5); }
         }
     } else if (warp < CONV_WARPS) {
         // ------------------------------------------------ converters
@@ -408,15 +447,15 @@ woq_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
         const uint32_t lds1 = box_off + (2 * tig + 1) * 128 + ((chunk ^ (uint32_t)(2 * tig + 1)) << 4) + within;
         const uint32_t magic = F16 ? (p.sgn4 ? 0x00080008u : 0u) : (p.sgn4 ? 0x43084308u : 0x43004300u);
         uint32_t it = 0;
-        int s = 0, as = 0;
-        uint32_t ph = 0, aph = 1;
+        int s = 0, as = 0, rs = 0;
+        uint32_t ph = 0, aph = 1, rph = 0;
         bool ok = true;
         for (int64_t L = L0; L < L1 && ok && !*abort_flag;) {
             const Segment sg = segment_at(L, L1, p.kstages);
             const int kend = min(sg.se * C::SPS, p.ksteps);
             for (int st = sg.sb; st < sg.se && ok; ++st, ++it) {
                 if ((int)(it & 1) == r) {
-                    if (!__all_sync(0xffffffffu, ptx::mbar_wait(&full[s], ph))) { ok = false; break; }
+                    if (!__all_sync(0xffffffffu, ptx::mbar_wait_relaxed(&full[s], ph))) { ok = false; break; }
                     const uint8_t *sw = smem + s * W_STAGE_BYTES;
                     const int nst = min(C::SPS, kend - st * C::SPS);
                     if (warp == 0 && lane == 0) WT_TRACE(2, it);
@@ -445,8 +484,9 @@ woq_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
                         // the stage's bytes are in registers: the producer may refill it
                         __syncwarp();
                         if (lane == 0) ptx::mbar_arrive(&empty[s]);
-                        if (!__all_sync(0xffffffffu, ptx::mbar_wait(&a_empty[as], aph))) { ok = false; break; }
+                        if (!__all_sync(0xffffffffu, ptx::mbar_wait_relaxed(&a_empty[as], aph))) { ok = false; break; }
                         ptx::tc_fence_after_sync();
+                        if (warp == 0 && lane == 0) WT_TRACE(7, it);
 #pragma unroll
                         for (int t = 0; t < BL; ++t) {
                             // byte t of every row: low nibble = column 2t, high nibble = column 2t + 1
@@ -468,14 +508,18 @@ woq_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
                     } else {
                         __syncwarp();
                         if (lane == 0) ptx::mbar_arrive(&empty[s]);
-                        if (!__all_sync(0xffffffffu, ptx::mbar_wait(&a_empty[as], aph))) { ok = false; break; }
+                        if (!__all_sync(0xffffffffu, ptx::mbar_wait_relaxed(&a_empty[as], aph))) { ok = false; break; }
                     }
+                    // the MMA warps wait for the operand stage only: the stage's src tile must be there too
+                    if (!__all_sync(0xffffffffu, ptx::mbar_wait_relaxed(&s_full[rs], rph))) { ok = false; break; }
                     ptx::tc_fence_before_sync();
                     __syncwarp(); // every lane's stores to tensor memory are done
                     if (lane == 0) ptx::mbar_arrive(&a_full[as]);
+                    if (warp == 0 && lane == 0) WT_TRACE(8, it);
                 }
                 if (++s == C::STAGES) { s = 0; ph ^= 1; }
                 if (++as == A_STAGES) { as = 0; aph ^= 1; }
+                if (++rs == p.s_stages) { rs = 0; rph ^= 1; }
             }
             L += sg.se - sg.sb;
         }
@@ -498,123 +542,143 @@ woq_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
 #pragma unroll
             for (int m = 0; m < MR; ++m) tot[j][m] = 0.f;
         uint32_t gc = 0;
-        // Parameters of one group piece, requested one piece ahead of their use so that their global
-        // loads are in flight while the piece before is folded: raw scale / zero-point words of the
-        // lane's NBLK columns, and (lane m) the src sums of row m for the piece's first eight k16 steps.
-        struct Request {
-            int kpos, gend, gi;
-            uint32_t sc_raw[NBLK], zp_raw[NBLK];
-            float s16[8];
-        };
-        auto raw_load = [&](int dt, const void *ptr, int64_t i) -> uint32_t {
-            switch (dt) {
-                case DT_F32: case DT_S32: return ldg_u32_here((const char *)ptr + i * 4);
-                case DT_BF16: case DT_F16: return ldg_u16_here((const char *)ptr + i * 2);
-                case DT_S8: case DT_U8: return ldg_u8_here((const char *)ptr + i);
-                default: return ldg_u8_here((const char *)ptr + (i >> 1)); // two 4-bit values per byte
-            }
-        };
-        auto raw_float = [&](int dt, uint32_t r) -> float {
-            return dt == DT_F32 ? __uint_as_float(r) : dt == DT_BF16 ? __uint_as_float(r << 16)
-                                                                      : __half2float(__ushort_as_half((unsigned short)r));
-        };
-        auto raw_int = [&](int dt, uint32_t r, int64_t i) -> float {
-            switch (dt) {
-                case DT_S32: return (float)(int)r;
-                case DT_S8: return (float)(signed char)r;
-                case DT_U8: return (float)r;
-                case DT_U4: return (float)((i & 1) ? (r >> 4) : (r & 15u));
-                default: { const int v = (i & 1) ? (int)(r >> 4) : (int)(r & 15u); return (float)((v ^ 8) - 8); } // s4
-            }
-        };
-        auto request = [&](Request &rq, int kpos, int kend, int64_t n_base) {
-            rq.kpos = kpos;
-            rq.gi = kpos / p.group_steps;
-            rq.gend = min(kend, (rq.gi + 1) * p.group_steps);
+        // The scales, zero-points and src sums of a piece come from the ring stage in which the piece
+        // begins (TMA put them there with the src tile); sums of later stages are added as they arrive.
+        // (one warp-uniform branch on the type, then NBLK loads)
+        auto read_scales = [&](const uint8_t *rows, int row, float (&out)[NBLK]) {
+            const uint8_t *e = rows + row * p.sc_row_bytes;
+            if (a.wei_scale.dt == DT_BF16) {
 #pragma unroll
-            for (int j = 0; j < NBLK; ++j) {
-                const int64_t n = n_base + 4 * j;
-                rq.sc_raw[j] = 0u;
-                rq.zp_raw[j] = 0u;
-                if (n < a.N) {
-                    rq.sc_raw[j] = raw_load(a.wei_scale.dt, a.wei_scale.ptr,
-                            ((a.wei_scale.mask & 1) ? (int64_t)rq.gi * a.wei_scale.ld : 0) + n);
-                    if (p.zp_mode == 1) rq.zp_raw[j] = raw_load(a.wei_zp.dt, a.wei_zp.ptr, (int64_t)rq.gi * a.wei_zp.ld + n);
+                for (int j = 0; j < NBLK; ++j)
+                    out[j] = __uint_as_float((uint32_t) reinterpret_cast<const unsigned short *>(e)[col_in_tile + 4 * j] << 16);
+            } else if (a.wei_scale.dt == DT_F32) {
+#pragma unroll
+                for (int j = 0; j < NBLK; ++j) out[j] = reinterpret_cast<const float *>(e)[col_in_tile + 4 * j];
+            } else {
+#pragma unroll
+                for (int j = 0; j < NBLK; ++j) out[j] = __half2float(reinterpret_cast<const __half *>(e)[col_in_tile + 4 * j]);
+            }
+        };
+        auto read_zps = [&](const uint8_t *rows, int row, float (&out)[NBLK]) {
+            const uint8_t *e = rows + row * p.zp_row_bytes;
+            const int dt = a.wei_zp.dt;
+            if (dt == DT_U4 || dt == DT_S4) { // tiles start at even columns: the nibble is the column's parity
+                const uint32_t sh = (col_in_tile & 1) * 4, flip = dt == DT_S4 ? 8u : 0u;
+#pragma unroll
+                for (int j = 0; j < NBLK; ++j) {
+                    const uint32_t v = (e[(col_in_tile + 4 * j) >> 1] >> sh) & 15u;
+                    out[j] = (float)((int)(v ^ flip) - (int)flip);
                 }
-            }
+            } else if (dt == DT_U8) {
 #pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                rq.s16[i] = 0.f;
-                if (lane < p.M && kpos + i < rq.gend) rq.s16[i] = __uint_as_float(ldg_u32_here(p.step_sums + (int64_t)(kpos + i) * MR + lane));
+                for (int j = 0; j < NBLK; ++j) out[j] = (float)e[col_in_tile + 4 * j];
+            } else if (dt == DT_S8) {
+#pragma unroll
+                for (int j = 0; j < NBLK; ++j) out[j] = (float)reinterpret_cast<const signed char *>(e)[col_in_tile + 4 * j];
+            } else {
+#pragma unroll
+                for (int j = 0; j < NBLK; ++j) out[j] = (float)reinterpret_cast<const int *>(e)[col_in_tile + 4 * j];
             }
         };
+        const float inv_acc_scale = 1.f / acc_scale; // a power of two
         // The four warps meet at named barriers, so none of them may leave the loops early: after an
         // expired wait (or once another role has given up) a warp skips its waits and tensor-memory
         // reads but still walks through every barrier; the status word tells the host that dst is invalid.
         bool ok = true;
-        Request rq;
+        int rs = 0; // ring stage
+        uint32_t rph = 0;
+        [[maybe_unused]] uint32_t eit = 0;
         for (int64_t L = L0; L < L1;) {
             const Segment sg = segment_at(L, L1, p.kstages);
-            const int64_t n_base = (int64_t)sg.tile * C::NB + col_in_tile;
             const int kend = min(sg.se * C::SPS, p.ksteps);
             int kpos = sg.sb * C::SPS;
             if (*abort_flag) ok = false;
-            if (ok && kpos < kend) request(rq, kpos, kend, n_base);
-            while (kpos < kend && ok) {
-                // turn the words requested one piece ago into this piece's factors ...
-                const int gi = rq.gi, gend = rq.gend;
-                float sc[NBLK], oz[NBLK];
+            float sc[NBLK], oz[NBLK], sm = 0.f;
+            int gi = kpos / p.group_steps; // group of kpos
+            int gend = kpos; // end of the open piece
+            bool open = false;
+            for (int st = sg.sb; st < sg.se && ok; ++st) {
+                if (!__all_sync(0xffffffffu, ptx::mbar_wait_relaxed(&s_full[rs], rph))) { ok = false; break; }
+                if (tid == 0) WT_TRACE(9, eit);
+                ++eit;
+                const uint8_t *stage = smem + C::S_RING_OFFSET + rs * p.s_stage_bytes;
+                const float *sums = reinterpret_cast<const float *>(stage + p.off_sums);
+                const int first = st * C::SPS, k1 = min(kend, first + C::SPS);
+                const int gi0 = gi; // kpos == first here: the group of the stage's first step
+                bool released = false;
+                while (kpos < k1 && ok) {
+                    if (!open) { // a piece begins: its factors are in this stage
+                        gend = min(kend, (gi + 1) * p.group_steps);
+                        read_scales(stage + p.off_sc, gi - gi0, sc); // columns beyond N: zeros
+                        if (p.zp_mode == 1) {
+                            read_zps(stage + p.off_zp, gi - gi0, oz);
+                        } else {
 #pragma unroll
-                for (int j = 0; j < NBLK; ++j) {
-                    const int64_t n = n_base + 4 * j;
-                    sc[j] = 0.f;
-                    oz[j] = 0.f;
-                    if (n < a.N) {
-                        sc[j] = raw_float(a.wei_scale.dt, rq.sc_raw[j]) * acc_scale;
-                        const float z = p.zp_mode == 1 ? raw_int(a.wei_zp.dt, rq.zp_raw[j], (int64_t)gi * a.wei_zp.ld + n) : zt;
-                        oz[j] = (off + z) / acc_scale;
+                            for (int j = 0; j < NBLK; ++j) oz[j] = zt;
+                        }
+#pragma unroll
+                        for (int j = 0; j < NBLK; ++j) {
+                            sc[j] *= acc_scale;
+                            oz[j] = (off + oz[j]) * inv_acc_scale;
+                        }
+                        sm = 0.f;
+                        open = true;
                     }
-                }
-                {   // S[m] of this piece: lane m adds its steps (beyond the eight requested ahead: loaded here)
-                    float sm = ((rq.s16[0] + rq.s16[1]) + (rq.s16[2] + rq.s16[3])) + ((rq.s16[4] + rq.s16[5]) + (rq.s16[6] + rq.s16[7]));
-                    if (lane < p.M)
-                        for (int k = kpos + 8; k < gend; ++k) sm += __ldg(p.step_sums + (int64_t)k * MR + lane);
-                    ssum[lane] = sm;
-                }
-                // ... and request the next piece's
-                if (gend < kend) request(rq, gend, kend, n_base);
-                __syncwarp();
-                const uint32_t buf = gc & 1;
-                if (!__all_sync(0xffffffffu, ptx::mbar_wait(&acc_full[buf], (gc >> 1) & 1))) { ok = false; break; } // leaves the group loop only
-                ptx::tc_fence_after_sync();
-                if (WT_ABLATE(4)) {
-                    ptx::tc_fence_before_sync();
+                    const int upto = min(gend, k1);
+                    if (lane < MR) {
+#pragma unroll
+                        for (int i = 0; i < C::SPS; ++i)
+                            if (first + i >= kpos && first + i < upto) sm += sums[i * MR + lane];
+                    }
+                    kpos = upto;
+                    if (kpos < gend) break; // the piece goes on in the next stage
+                    open = false;
+                    if (gend == (gi + 1) * p.group_steps) ++gi; // (else: the segment ends inside the group)
+                    ssum[lane] = sm; // S[m] of the piece
                     __syncwarp();
-                    if (lane == 0) ptx::mbar_arrive(&acc_empty[buf]);
-                } else {
-                    const uint32_t acc = tmem_base + ((uint32_t)(32 * q) << 16) + buf * C::ACC_COLS;
-                    constexpr int MH = MR > 16 ? 16 : MR; // accumulator columns read at a time
+                    if (kpos == k1) { // nothing more to read in this stage: hand it back before folding
+                        if (lane == 0) ptx::mbar_arrive(&s_empty[rs]);
+                        released = true;
+                    }
+                    const uint32_t buf = gc & 1;
+                    if (!__all_sync(0xffffffffu, ptx::mbar_wait_relaxed(&acc_full[buf], (gc >> 1) & 1))) { ok = false; break; }
+                    ptx::tc_fence_after_sync();
+                    if (tid == 0) WT_TRACE(10, eit - 1);
+                    if (WT_ABLATE(4)) {
+                        ptx::tc_fence_before_sync();
+                        __syncwarp();
+                        if (lane == 0) ptx::mbar_arrive(&acc_empty[buf]);
+                    } else {
+                        const uint32_t acc = tmem_base + ((uint32_t)(32 * q) << 16) + buf * C::ACC_COLS;
+                        constexpr int MH = MR > 16 ? 16 : MR; // accumulator columns read at a time
 #pragma unroll
-                    for (int j = 0; j < NBLK; ++j) {
+                        for (int j = 0; j < NBLK; ++j) {
 #pragma unroll
-                        for (int h = 0; h < MR / MH; ++h) {
-                            uint32_t v[MH];
-                            tmem_ld_cols<MH>(acc + j * C::MP + h * MH, v);
-                            ptx::tmem_ld_wait();
-                            if (j == NBLK - 1 && h == MR / MH - 1) { // the buffer has been read: hand it back
-                                ptx::tc_fence_before_sync();
-                                __syncwarp();
-                                if (lane == 0) ptx::mbar_arrive(&acc_empty[buf]);
+                            for (int h = 0; h < MR / MH; ++h) {
+                                uint32_t v[MH];
+                                tmem_ld_cols<MH>(acc + j * C::MP + h * MH, v);
+                                ptx::tmem_ld_wait();
+                                if (j == NBLK - 1 && h == MR / MH - 1) { // the buffer has been read: hand it back
+                                    ptx::tc_fence_before_sync();
+                                    __syncwarp();
+                                    if (lane == 0) ptx::mbar_arrive(&acc_empty[buf]);
+                                }
+#pragma unroll
+                                for (int m = 0; m < MH; ++m)
+                                    tot[j][h * MH + m] = fmaf(sc[j], fmaf(-oz[j], ssum[h * MH + m], __uint_as_float(v[m])), tot[j][h * MH + m]);
                             }
-#pragma unroll
-                            for (int m = 0; m < MH; ++m)
-                                tot[j][h * MH + m] = fmaf(sc[j], fmaf(-oz[j], ssum[h * MH + m], __uint_as_float(v[m])), tot[j][h * MH + m]);
                         }
                     }
+                    __syncwarp(); // ssum is rewritten for the next piece
+                    if (tid == 0) WT_TRACE(11, eit - 1);
+                    ++gc;
                 }
-                __syncwarp(); // ssum is rewritten for the next piece
-                ++gc;
-                kpos = gend;
+                if (!ok) break;
+                if (!released) {
+                    __syncwarp();
+                    if (lane == 0) ptx::mbar_arrive(&s_empty[rs]);
+                }
+                if (++rs == p.s_stages) { rs = 0; rph ^= 1; }
             }
             // ---- end of the segment: totals -> shared-memory tile [m][column] -> reduction across the
             // CTAs that share the column tile -> bias, post-ops, store
@@ -700,7 +764,7 @@ woq_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
                             if (n + e >= a.N) continue;
                             float de = d[e];
                             if (a.bias) de = __fadd_rn(de, load_float(a.bias_dt, a.bias, m * a.bias_sm + (n + e) * a.bias_sn));
-                            finish_store(a, de, m, n + e, false);
+                            finish_store_cold(a, de, m, n + e);
                         }
                     }
                 }
@@ -785,16 +849,91 @@ WtPlan wt_plan(int64_t M, int64_t N, int64_t K, int sm_count) {
     return pl;
 }
 
+struct WtMaps {
+    CUtensorMap w, s, sums, sc, zp;
+};
+
+// Parameter rows as TMA sees them: elements of two columns each (1, 2, 4 or 8 bytes), so that a
+// tile's 256 or 128 pairs fit the 256-element limit of a box; rows beyond the last group and
+// columns beyond N read as zeros.
+bool wt_encode_rows(encode_tiled_fn enc, CUtensorMap *tm, const void *ptr, int bits, int64_t ncols, int64_t nrows,
+        int64_t ld, int nb, int box_rows) {
+    const int pair_bytes = 2 * bits / 8;
+    const CUtensorMapDataType dt = pair_bytes == 1 ? CU_TENSOR_MAP_DATA_TYPE_UINT8
+            : pair_bytes == 2                     ? CU_TENSOR_MAP_DATA_TYPE_UINT16
+            : pair_bytes == 4                     ? CU_TENSOR_MAP_DATA_TYPE_UINT32
+                                                  : CU_TENSOR_MAP_DATA_TYPE_UINT64;
+    int64_t pitch = ld * bits / 8;
+    if (nrows <= 1) pitch = (ncols * bits / 8 + 15) / 16 * 16; // unused, but checked
+    cuuint64_t dims[2] = {(cuuint64_t)(ncols / 2), (cuuint64_t)nrows};
+    cuuint64_t strides[1] = {(cuuint64_t)pitch};
+    cuuint32_t box[2] = {(cuuint32_t)(nb / 2), (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    return enc(tm, dt, 2, const_cast<void *>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE)
+            == CUDA_SUCCESS;
+}
+
+int wt_bits(int dt) {
+    switch (dt) {
+        case DT_F32: case DT_S32: return 32;
+        case DT_BF16: case DT_F16: return 16;
+        case DT_S8: case DT_U8: return 8;
+        default: return 4;
+    }
+}
+
+// Rows of a parameter that one stage can need: the groups its k16 steps touch.
+int wt_rows_per_stage(int group_steps, int sps) {
+    if (group_steps % sps == 0) return 1;
+    if (sps % group_steps == 0) return sps / group_steps;
+    return (sps + group_steps - 2) / group_steps + 1;
+}
+
 template <int MR, int NBLK, bool F16>
-int wt_launch(const CUtensorMap &tw, const CUtensorMap &ts, const MatmulArgs &a, const WtParams &p, int grid,
-        cudaStream_t st) {
+int wt_launch(encode_tiled_fn enc, WtMaps &tm, const MatmulArgs &a, WtParams &p, int grid, cudaStream_t st) {
     using C = WtCfg<MR, NBLK>;
     auto kern = woq_tc_kernel<MR, NBLK, F16>;
+    // the src / parameter ring takes what the fixed parts leave
+    const int rb = wt_rows_per_stage(p.group_steps, C::SPS);
+    const int ngroups = (p.ksteps + p.group_steps - 1) / p.group_steps;
+    const int sc_bits = wt_bits(a.wei_scale.dt), zp_bits = p.zp_mode == 1 ? wt_bits(a.wei_zp.dt) : 0;
+    auto up128 = [](int v) { return (v + 127) / 128 * 128; };
+    p.sc_row_bytes = C::NB * sc_bits / 8;
+    p.zp_row_bytes = C::NB * zp_bits / 8;
+    p.sc_box_bytes = rb * p.sc_row_bytes;
+    p.zp_box_bytes = rb * p.zp_row_bytes;
+    p.off_sums = C::S_BYTES;
+    p.off_sc = p.off_sums + up128(C::SUMS_BYTES);
+    p.off_zp = p.off_sc + up128(p.sc_box_bytes);
+    p.s_stage_bytes = (p.off_zp + up128(p.zp_box_bytes) + 1023) / 1024 * 1024;
+    p.s_stages = (C::SMEM_LIMIT - C::S_RING_OFFSET) / p.s_stage_bytes;
+    if (p.s_stages > C::S_STAGES_MAX) p.s_stages = C::S_STAGES_MAX;
+    if (p.s_stages < 4) {
+        set_last_error("cuda:tcgen05:woq4: the parameter rows of a stage do not fit in shared memory");
+        return 5;
+    }
+    const int smem_bytes = C::S_RING_OFFSET + p.s_stages * p.s_stage_bytes + 1024;
+    {
+        cuuint64_t dims[2] = {(cuuint64_t)MR, (cuuint64_t)p.ksteps};
+        cuuint64_t strides[1] = {(cuuint64_t)(MR * 4)};
+        cuuint32_t box[2] = {(cuuint32_t)MR, (cuuint32_t)C::SPS};
+        cuuint32_t estr[2] = {1, 1};
+        if (enc(&tm.sums, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float *>(p.step_sums), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE)
+                != CUDA_SUCCESS)
+            return 5;
+    }
+    if (!wt_encode_rows(enc, &tm.sc, a.wei_scale.ptr, sc_bits, a.N, (a.wei_scale.mask & 1) ? ngroups : 1, a.wei_scale.ld, C::NB, rb))
+        return 5;
+    tm.zp = tm.sc;
+    if (p.zp_mode == 1 && !wt_encode_rows(enc, &tm.zp, a.wei_zp.ptr, zp_bits, a.N, ngroups, a.wei_zp.ld, C::NB, rb)) return 5;
     static std::atomic<unsigned long long> configured;
-    if (!opt_in_dynamic_smem(kern, C::SMEM_BYTES, configured)) return 5;
+    if (!opt_in_dynamic_smem(kern, 227 * 1024, configured)) return 5;
     const int nsum = p.ksteps * MR;
     woq_step_sums_kernel<MR, F16><<<(nsum + 255) / 256, 256, 0, st>>>(a, const_cast<float *>(p.step_sums), p.ksteps);
-    kern<<<grid, WT_THREADS, C::SMEM_BYTES, st>>>(tw, ts, a, p);
+    kern<<<grid, WT_THREADS, smem_bytes, st>>>(tm.w, tm.s, tm.sums, tm.sc, tm.zp, a, p);
     count_launch(2);
     const cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) {
@@ -817,7 +956,8 @@ size_t woq_tc_scratch_bytes(int64_t M, int64_t N, int64_t K, int sm_count) {
 }
 
 bool woq_tc_pointers_ok(const MatmulArgs &a) {
-    return (uintptr_t)a.wei % 16 == 0 && (uintptr_t)a.src % 16 == 0;
+    return (uintptr_t)a.wei % 16 == 0 && (uintptr_t)a.src % 16 == 0 && (uintptr_t)a.wei_scale.ptr % 16 == 0
+            && (uintptr_t)a.wei_zp.ptr % 16 == 0;
 }
 
 // `scratch`: woq_tc_scratch_bytes(...) bytes whose counters (the first
@@ -829,7 +969,8 @@ int launch_woq_tc(const MatmulArgs &a, void *scratch, int sm_count, cudaStream_t
     if (!enc || !scratch) return 5;
     const WtPlan pl = wt_plan(a.M, a.N, a.K, sm_count);
     const int nb = 128 * pl.nblk, ks = W_STAGE_BYTES / (nb / 2), mp = pl.mr < 16 ? 16 : pl.mr;
-    CUtensorMap tw, ts;
+    WtMaps tm;
+    CUtensorMap &tw = tm.w, &ts = tm.s;
     {
         cuuint64_t dims[2] = {(cuuint64_t)(a.N / 2), (cuuint64_t)a.K};
         cuuint64_t strides[1] = {(cuuint64_t)(a.wei_sk / 2)};
@@ -883,7 +1024,7 @@ int launch_woq_tc(const MatmulArgs &a, void *scratch, int sm_count, cudaStream_t
     p.ablate = getenv("ONEDNN_CUDA_WOQ_ABLATE") ? atoi(getenv("ONEDNN_CUDA_WOQ_ABLATE")) : 0;
     p.trace = getenv("ONEDNN_CUDA_WOQ_TRACE") ? (unsigned long long *)strtoull(getenv("ONEDNN_CUDA_WOQ_TRACE"), nullptr, 16) : nullptr;
 #endif
-#define QMM_WT(MR, NBLK) (f16 ? wt_launch<MR, NBLK, true>(tw, ts, a, p, pl.grid, st) : wt_launch<MR, NBLK, false>(tw, ts, a, p, pl.grid, st))
+#define QMM_WT(MR, NBLK) (f16 ? wt_launch<MR, NBLK, true>(enc, tm, a, p, pl.grid, st) : wt_launch<MR, NBLK, false>(enc, tm, a, p, pl.grid, st))
     if (pl.mr == 8) return QMM_WT(8, 4);
     if (pl.mr == 16) return QMM_WT(16, 4);
     return QMM_WT(32, 2);
