@@ -252,10 +252,11 @@ def measure(args, name, kw, ctx):
     # cycle through the copies moves 2.5 x L2.
     ws = float(p.algorithmic_bytes())
     nsets = 1 if ws > 1.5 * L2_BYTES else int(min(8, max(2, np.ceil(2.5 * L2_BYTES / max(ws, 1.0)))))
-    sets = []
+    sets, set_ptrs = [], []
     for _ in range(nsets):
         ptrs_s, keep_s = device_buffers(p, torch, dev)
         sets.append((Prepared(p, eng, args.kernel).bind_device(ptrs_s), keep_s))
+        set_ptrs.append(ptrs_s)
     prep = sets[0][0]
     preps = [s[0] for s in sets]
     l2_note = ("working set %.0f MB > 126 MB L2" % (ws / 1e6)) if nsets == 1 else \
@@ -278,12 +279,25 @@ def measure(args, name, kw, ctx):
         dist.all_reduce(ok_t, op=dist.ReduceOp.MIN)
         if float(ok_t[0]) == 0:
             peers = None
+    # the tcgen05 GEMM stores into every rank's buffer from its own epilogue (no scatter pass): its
+    # dst memory is this rank's column slice inside the full buffer
+    # (two ranks: with more, the 64-byte runs a warp's dst store covers use NVLink half as well as the
+    # scatter kernel's 512-byte ones, and every element leaves world - 1 times)
+    fused = None
+    if (peers is not None and world == 2 and not grouped and prep.impl in ("cuda:tcgen05:int8", "cuda:tcgen05:fp8")
+            and not p.post_ops and (p.bias is None or p.bias.dims[0] == 1)):
+        fused = []
+        for i in range(nsets):
+            ptrs_f = dict(set_ptrs[i])
+            ptrs_f["dst"] = peers[i].slice_ptr
+            fused.append(Prepared(p, eng, args.kernel, dst_ld=full.N).bind_device(ptrs_f))
 
     def gather(i=0):
         if world == 1:
             return None
         if peers is not None:
-            peers[i % nsets].step(strm, sets[i % nsets][1]["dst"].data_ptr())
+            if fused is None:
+                peers[i % nsets].step(strm, sets[i % nsets][1]["dst"].data_ptr())
             return peers[i % nsets].dst
         local = sets[i % nsets][1]["dst"].view(elem).view(p.M, p.N)
         # the gathered result stays in the collective's blocked layout ([rank][M][N/g] column
@@ -297,9 +311,15 @@ def measure(args, name, kw, ctx):
             dist.barrier()
         torch.cuda.synchronize()
 
+    def execute(i):
+        if fused is not None:
+            peers[i % nsets].fused_step(strm, fused[i % nsets])
+        else:
+            preps[i % nsets].execute(strm)
+
     K = args.steps
     for i in range(max(3, args.warmup)):
-        preps[i % nsets].execute(strm)
+        execute(i)
         gather(i)
     barrier()
 
@@ -317,7 +337,7 @@ def measure(args, name, kw, ctx):
         for j in range(K):
             if k_ev:
                 k_ev[j][0].record()
-            preps[step_no % nsets].execute(strm)
+            execute(step_no)
             if k_ev:
                 k_ev[j][1].record()
             gather(step_no)
@@ -366,7 +386,7 @@ def measure(args, name, kw, ctx):
     # ---- parity of the assembled result, outside the timed region
     parity = None
     if not args.no_parity:
-        preps[0].execute(strm)
+        execute(0)
         g = gather(0)
         torch.cuda.synchronize()
         if rank == 0:
@@ -435,7 +455,9 @@ def measure(args, name, kw, ctx):
         "config": {"workload": wkey, "kernel": prep.impl,
                    "parallelism": ("%s x%d + %s"
                                    % ("expert-shard (balanced by rows)" if grouped else "n-shard", world,
-                                      "peer stores of every rank's block into every rank's [M,N] dst, flag wait (own kernels)"
+                                      ("dst stores of the GEMM epilogue repeated into every rank's [M,N] dst, flag wait (own kernels)"
+                                       if fused is not None else
+                                       "peer stores of every rank's block into every rank's [M,N] dst, flag wait (own kernels)")
                                       if peers is not None else "NCCL all-gather into [rank][M][N/g] blocks"))
                    if world > 1 else "single",
                    "l2": l2_note,

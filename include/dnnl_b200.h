@@ -583,6 +583,14 @@ dnnl_status_t dnnl_cuda_interop_peer_scatter(dnnl_stream_t stream, int world, in
 /* Waits on the stream until flags[0..world) have all reached `epoch`; a wait that runs out (2 s)
  * records runtime_error for the next dnnl_stream_wait. */
 dnnl_status_t dnnl_cuda_interop_peer_wait(dnnl_stream_t stream, int world, const unsigned *flags, unsigned epoch);
+/* The fused form for the tcgen05 GEMM (`cuda:tcgen05:int8` / `fp8`): the next executions of the
+ * primitive store every dst element into all `world` buffers at the offset the primitive's dst
+ * memory has inside dst_bases[rank], and the kernel's last CTA publishes `epoch` in
+ * peer_flags[r][rank] of every rank r: dnnl_cuda_interop_peer_wait is then the whole exchange.
+ * Call again with the next epoch before each execution; world <= 1 or dst_bases == NULL switches it
+ * off.  dnnl_unimplemented for other implementations (use dnnl_cuda_interop_peer_scatter). */
+dnnl_status_t dnnl_cuda_interop_primitive_replicate_dst(dnnl_primitive_t primitive, int world, int rank,
+        void *const *dst_bases, size_t buffer_bytes, unsigned *const *peer_flags, unsigned *done, unsigned epoch);
 
 #ifdef __cplusplus
 }

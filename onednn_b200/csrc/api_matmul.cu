@@ -1015,6 +1015,17 @@ extern "C" dnnl_status_t dnnl_primitive_execute(const_dnnl_primitive_t primitive
         case IMPL_TCGEN05_GEMM:
             // TMA needs 16-byte aligned base pointers; a misaligned user
             // pointer is served by the generic kernel instead
+            if (primitive->peers.count) {
+                // replicated dst: the memory must lie in this rank's buffer, so that the same offset
+                // exists in every peer's; the generic kernel does not replicate
+                const char *d = (const char *)a.dst;
+                if (d < primitive->peers_own_base || d >= primitive->peers_own_base + primitive->peers_bytes
+                        || !gemm_tc_pointers_ok(a)) {
+                    set_last_error("replicated dst: the dst memory is outside the registered buffer or misaligned");
+                    return dnnl_invalid_arguments;
+                }
+                a.peers = primitive->peers;
+            }
             if (!gemm_tc_pointers_ok(a)) rc = launch_ref(a, stream->stream);
             else rc = launch_gemm_tc(a, scratch, pd.engine->sm_count, stream->stream);
             break;

@@ -128,24 +128,34 @@ __device__ __forceinline__ TensorTerms load_tensor_terms(const MatmulArgs &a, co
 // (src/cpu/simple_q10n.hpp:41-81; src/common/bfloat16.cpp:22-47: f32
 // subnormals flush to signed zero before the bf16 rounding).
 template <int DST>
-__device__ __forceinline__ void store_typed(void *p, float v) {
+__device__ __forceinline__ uint32_t typed_bits(float v) {
     if constexpr (DST == DT_F32) {
-        *(float *)p = v;
+        return __float_as_uint(v);
     } else if constexpr (DST == DT_BF16) {
         if (fabsf(v) < 1.17549435e-38f) v = copysignf(0.f, v);
         unsigned short b = __bfloat16_as_ushort(__float2bfloat16_rn(v));
         if (v != v) b = (unsigned short)((__float_as_uint(v) >> 16) | 0x40u); // NaN: payload kept, quiet bit set
-        *(unsigned short *)p = b;
+        return b;
     } else if constexpr (DST == DT_F16) {
-        *(__half *)p = __float2half_rn(v);
+        return __half_as_ushort(__float2half_rn(v));
     } else if constexpr (DST == DT_S32) {
         v = fminf(fmaxf(v, -2147483648.f), 2147483520.f);
-        *(int *)p = __float2int_rn(v);
+        return (uint32_t)__float2int_rn(v);
     } else if constexpr (DST == DT_S8) {
-        *(signed char *)p = (signed char)__float2int_rn(fminf(fmaxf(v, -128.f), 127.f));
+        return (uint32_t)(unsigned char)(signed char)__float2int_rn(fminf(fmaxf(v, -128.f), 127.f));
     } else {
-        *(unsigned char *)p = (unsigned char)__float2int_rn(fminf(fmaxf(v, 0.f), 255.f));
+        return (uint32_t)(unsigned char)__float2int_rn(fminf(fmaxf(v, 0.f), 255.f));
     }
+}
+template <int DST>
+__device__ __forceinline__ void store_bits(void *p, uint32_t b) {
+    if constexpr (DST == DT_F32 || DST == DT_S32) *(uint32_t *)p = b;
+    else if constexpr (DST == DT_BF16 || DST == DT_F16) *(unsigned short *)p = (unsigned short)b;
+    else *(unsigned char *)p = (unsigned char)b;
+}
+template <int DST>
+__device__ __forceinline__ void store_typed(void *p, float v) {
+    store_bits<DST>(p, typed_bits<DST>(v));
 }
 template <int DST>
 struct dst_size {
@@ -222,9 +232,27 @@ __device__ __forceinline__ void epilogue_rows(const MatmulArgs &a, const TcParam
         return;
     }
 #endif
+    // (kernels with a post-op chain have no replicated form: they are short of registers as it is)
+    if (CHAIN || a.peers.count == 0) {
 #pragma unroll
-    for (int j = 0; j < R; ++j)
-        if (FULL || j < rows) store_typed<DST>(dptr + j * dstep, d[j]);
+        for (int j = 0; j < R; ++j)
+            if (FULL || j < rows) store_typed<DST>(dptr + j * dstep, d[j]);
+    } else {
+        // every rank's copy of dst: the value is converted once and stored count + 1 times (plain
+        // stores through peer-mapped addresses; the kernel's last CTA publishes the flags)
+        uint32_t b[R];
+#pragma unroll
+        for (int j = 0; j < R; ++j) b[j] = typed_bits<DST>(d[j]);
+#pragma unroll
+        for (int j = 0; j < R; ++j)
+            if (FULL || j < rows) store_bits<DST>(dptr + j * dstep, b[j]);
+        for (int q = 0; q < a.peers.count; ++q) {
+            char *pp = dptr + a.peers.delta[q];
+#pragma unroll
+            for (int j = 0; j < R; ++j)
+                if (FULL || j < rows) store_bits<DST>(pp + j * dstep, b[j]);
+        }
+    }
 }
 
 // DSTT: the dst data type when the kernel was instantiated for one (post-op chain kernels: a single
@@ -405,12 +433,24 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
     }
 
     // ---------------------------------------------------- teardown
+    if (!CHAIN && a.peers.count) __threadfence_system(); // this thread's peer stores, before the CTA is counted
     ptx::tc_fence_before_sync();
     __syncthreads();
     if (warp == 1) {
         __syncwarp();
         ptx::tc_fence_after_sync();
         ptx::tmem_dealloc(tmem_base, TMEM_COLS);
+    }
+    if (!CHAIN && a.peers.count && threadIdx.x == 0) {
+        // the last CTA to get here tells every rank that this rank's block is complete
+        if (atomicAdd(a.peers.done, 1u) == gridDim.x - 1) {
+            __threadfence_system();
+            for (int r = 0; r < a.peers.world; ++r) {
+                volatile unsigned *f = a.peers.flags[r] + a.peers.rank;
+                *f = a.peers.epoch;
+            }
+            *a.peers.done = 0u;
+        }
     }
 }
 
@@ -603,6 +643,7 @@ int launch_gemm_tc(const MatmulArgs &a, void *scratch, int sm_count, cudaStream_
     }
     tp.idesc = ptx::make_idesc(cfmt, wfmt, sfmt, !w_kmajor, false, BT_N, BT_M);
     const bool chain = a.n_po > 0 || (a.bias && a.bias_sm != 0); // a bias varying along M rides the generic tail
+    if (chain && a.peers.count) return 3; // refused when the replication is registered; not reached
     // kernels with a post-op chain are instantiated per dst data type
 #define QMM_TC_CHAIN(KIND, BTM, ST) \
     (a.dst_dt == DT_S8         ? launch_cfg<KIND, BTM, ST, true, DT_S8>(mw, ms, a, tp, sm_count, st) \

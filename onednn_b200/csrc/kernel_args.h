@@ -41,6 +41,19 @@ struct PostOpArg {
     int64_t sm, sn; // element strides of src1, 0 on a broadcast dim
 };
 
+// Replication of dst stores into the same place of other GPUs' buffers (a sharded matmul whose
+// full result every rank wants): the kernel repeats each dst store at `delta[i]` bytes from the
+// local address, and the last CTA to finish publishes `epoch` in flags[r][rank] of every rank r.
+constexpr int MAX_PEERS = 16;
+struct PeerReplication {
+    int count; // peers stored to besides the local dst (0: off)
+    int world, rank;
+    unsigned epoch;
+    unsigned *done; // local counter of finished CTAs, zero between launches
+    long long delta[MAX_PEERS - 1];
+    unsigned *flags[MAX_PEERS]; // flag array [world] of every rank, as mapped on this GPU
+};
+
 struct MatmulArgs {
     int64_t M, N, K;
     const void *src;
@@ -67,6 +80,7 @@ struct MatmulArgs {
     const int32_t *dst_offsets;
     // device status word: kernels record errors here instead of trapping
     int *status;
+    PeerReplication peers;
 };
 
 } // namespace qmm

@@ -169,6 +169,10 @@ struct dnnl_primitive {
     // object unsafe
     mutable void *scratch = nullptr;
     mutable size_t scratch_cap = 0; // bytes behind `scratch` (grows for runtime-M primitives)
+    // dnnl_cuda_interop_primitive_replicate_dst: where the next executions repeat their dst stores
+    mutable qmm::PeerReplication peers {};
+    mutable const char *peers_own_base = nullptr;
+    mutable size_t peers_bytes = 0;
 };
 
 namespace qmm {

@@ -21,7 +21,6 @@ namespace qmm {
 
 namespace {
 
-constexpr int MAX_PEERS = 16;
 constexpr int MAX_SEGMENTS = 64;
 
 struct ScatterArgs {
@@ -150,5 +149,43 @@ extern "C" dnnl_status_t dnnl_cuda_interop_peer_wait(dnnl_stream_t stream, int w
         set_last_error(std::string("peer wait launch: ") + cudaGetErrorString(e));
         return dnnl_runtime_error;
     }
+    return dnnl_success;
+}
+
+// Fused form of the scatter for the tcgen05 GEMM: the following executions of `primitive` store
+// every dst element into all `world` buffers (the primitive's dst memory must lie inside
+// dst_bases[rank]; the same byte offset is used in the others) and publish `epoch` in
+// peer_flags[r][rank] of every rank r when the kernel's last CTA has finished, so that
+// dnnl_cuda_interop_peer_wait(stream, world, flags, epoch) on each rank is the whole exchange.
+// buffer_bytes: size of each buffer.  `done`: one zeroed 32-bit word of local device memory.
+// world <= 1 or dst_bases == NULL switches the replication off.  Returns dnnl_unimplemented for
+// primitives whose implementation has no fused form (use dnnl_cuda_interop_peer_scatter then).
+extern "C" dnnl_status_t dnnl_cuda_interop_primitive_replicate_dst(dnnl_primitive_t primitive, int world, int rank,
+        void *const *dst_bases, size_t buffer_bytes, unsigned *const *peer_flags, unsigned *done, unsigned epoch) {
+    if (!primitive) return dnnl_invalid_arguments;
+    if (world <= 1 || !dst_bases) {
+        primitive->peers = PeerReplication {};
+        primitive->peers_own_base = nullptr;
+        primitive->peers_bytes = 0;
+        return dnnl_success;
+    }
+    if (world > MAX_PEERS || rank < 0 || rank >= world || !peer_flags || !done || !buffer_bytes) return dnnl_invalid_arguments;
+    if (primitive->pd.kind != dnnl_matmul || primitive->pd.impl != IMPL_TCGEN05_GEMM) return dnnl_unimplemented;
+    // the kernels that carry a post-op chain (or a bias that varies along M) have no replicated form
+    if (!primitive->pd.attr.post_ops.entries.empty() || (primitive->pd.bias.ndims > 0 && primitive->pd.bias.dims[0] != 1))
+        return dnnl_unimplemented;
+    PeerReplication r {};
+    r.world = world;
+    r.rank = rank;
+    r.epoch = epoch;
+    r.done = done;
+    for (int p = 0; p < world; ++p) {
+        if (!dst_bases[p] || !peer_flags[p]) return dnnl_invalid_arguments;
+        r.flags[p] = peer_flags[p];
+        if (p != rank) r.delta[r.count++] = (const char *)dst_bases[p] - (const char *)dst_bases[rank];
+    }
+    primitive->peers = r;
+    primitive->peers_own_base = (const char *)dst_bases[rank];
+    primitive->peers_bytes = buffer_bytes;
     return dnnl_success;
 }

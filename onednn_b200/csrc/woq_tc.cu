@@ -56,15 +56,14 @@ namespace qmm {
 
 namespace {
 
-// One thread issues a tcgen05.mma about every 63 cycles, whatever its size; two issuing threads in
-// different warps reach twice that, and the MMAs of this kernel are small (N = 16 or 32), so the
-// column blocks of a tile are split between two issuer warps.
-constexpr int CONV_WARPS = 8, EPI_WARPS = 4, MMA_WARPS = 2;
+// A warp issues a tcgen05.mma about every 40 to 65 cycles, whatever its size; issuing warps add up,
+// and the MMAs of this kernel are small (N = 16 or 32), so every 128-column block of a tile has an
+// issuer warp of its own where the registers allow it (WtCfg::MMA_WARPS).
+constexpr int CONV_WARPS = 8, EPI_WARPS = 4;
 // A thread issues a stage of TMA copies in a few hundred cycles (a wait, an expect-tx and about 70
 // cycles per copy), which is the time a stage may take: the weights and the rest (src tile, sums,
 // scales, zero-points) have a producer thread each, in different warps.
-constexpr int PRODUCER_WARP = CONV_WARPS + EPI_WARPS, MMA_WARP0 = PRODUCER_WARP + 1, PARAM_WARP = MMA_WARP0 + MMA_WARPS;
-constexpr int WT_THREADS = 32 * (CONV_WARPS + EPI_WARPS + 2 + MMA_WARPS);
+constexpr int PRODUCER_WARP = CONV_WARPS + EPI_WARPS, PARAM_WARP = PRODUCER_WARP + 1, MMA_WARP0 = PARAM_WARP + 1;
 constexpr int W_STAGE_BYTES = 16384; // raw nibbles per stage
 constexpr int A_STAGES = 3; // operand stages in tensor memory, one shared-memory stage (128 columns) each
 
@@ -72,6 +71,11 @@ constexpr int A_STAGES = 3; // operand stages in tensor memory, one shared-memor
 template <int MR, int NBLK>
 struct WtCfg {
     static constexpr int MP = MR < 16 ? 16 : MR; // MMA N extent (a multiple of 16)
+    // Issuing warps: one per 128-column block where the epilogue's registers allow it.  Sixteen warps
+    // may use 128 registers each; one more warp puts five on a scheduler, whose quarter of the
+    // register file then gives 96 - enough for the 8-row epilogue only.
+    static constexpr int MMA_WARPS = MR == 8 ? NBLK : 2;
+    static constexpr int THREADS = 32 * (CONV_WARPS + EPI_WARPS + 2 + MMA_WARPS);
     static constexpr int NB = 128 * NBLK; // dst columns per tile
     static constexpr int ROW_BYTES = NB / 2; // packed bytes per k-row of a tile: 256 or 128
     static constexpr int KS = W_STAGE_BYTES / ROW_BYTES; // k-rows per stage: 64 or 128
@@ -216,7 +220,7 @@ __device__ __forceinline__ Segment segment_at(int64_t L, int64_t L1, int kstages
 }
 
 template <int MR, int NBLK, bool F16>
-__global__ void __launch_bounds__(WT_THREADS, 1)
+__global__ void __launch_bounds__((WtCfg<MR, NBLK>::THREADS), 1)
 woq_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmS,
         const __grid_constant__ CUtensorMap tmSums, const __grid_constant__ CUtensorMap tmSc,
         const __grid_constant__ CUtensorMap tmZp, const __grid_constant__ MatmulArgs a, const __grid_constant__ WtParams p) {
@@ -245,14 +249,14 @@ woq_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
         }
         for (int s = 0; s < p.s_stages; ++s) {
             ptx::mbar_init(&s_full[s], 1);
-            ptx::mbar_init(&s_empty[s], MMA_WARPS + EPI_WARPS); // the src tile and the parameters have been read
+            ptx::mbar_init(&s_empty[s], C::MMA_WARPS + EPI_WARPS); // the src tile and the parameters have been read
         }
         for (int s = 0; s < A_STAGES; ++s) {
             ptx::mbar_init(&a_full[s], CONV_WARPS / 2);
-            ptx::mbar_init(&a_empty[s], MMA_WARPS);
+            ptx::mbar_init(&a_empty[s], C::MMA_WARPS);
         }
         for (int s = 0; s < 2; ++s) {
-            ptx::mbar_init(&acc_full[s], MMA_WARPS);
+            ptx::mbar_init(&acc_full[s], C::MMA_WARPS);
             ptx::mbar_init(&acc_empty[s], EPI_WARPS);
         }
         *abort_flag = 0;
@@ -339,10 +343,10 @@ woq_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
             }
             if (!ok && issue) { *abort_flag = 1; atomicExch(a.status, 5); }
         }
-    } else if (warp >= MMA_WARP0 && warp < MMA_WARP0 + MMA_WARPS) {
+    } else if (warp >= MMA_WARP0) {
         // ------------------------------------------------ MMA issuers: warp i takes the column blocks
-        // [i * NBLK / MMA_WARPS, (i + 1) * NBLK / MMA_WARPS) of every k16 step; both walk the same barriers
-        constexpr int JB = NBLK / MMA_WARPS;
+        // [i * NBLK / MMA_WARPS, (i + 1) * NBLK / MMA_WARPS) of every k16 step; all walk the same barriers
+        constexpr int JB = NBLK / C::MMA_WARPS;
         const int j0 = (warp - MMA_WARP0) * JB;
         // (the whole warp walks the loop, lane 0 issues)
         {
@@ -933,7 +937,7 @@ int wt_launch(encode_tiled_fn enc, WtMaps &tm, const MatmulArgs &a, WtParams &p,
     if (!opt_in_dynamic_smem(kern, 227 * 1024, configured)) return 5;
     const int nsum = p.ksteps * MR;
     woq_step_sums_kernel<MR, F16><<<(nsum + 255) / 256, 256, 0, st>>>(a, const_cast<float *>(p.step_sums), p.ksteps);
-    kern<<<grid, WT_THREADS, smem_bytes, st>>>(tm.w, tm.s, tm.sums, tm.sc, tm.zp, a, p);
+    kern<<<grid, C::THREADS, smem_bytes, st>>>(tm.w, tm.s, tm.sums, tm.sc, tm.zp, a, p);
     count_launch(2);
     const cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) {

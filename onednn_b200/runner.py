@@ -17,9 +17,10 @@ def _md(t: W.QTensor):
 
 
 class Prepared:
-    def __init__(self, p: W.Problem, eng, impl=None, user_scratchpad=False, runtime_m=False):
+    def __init__(self, p: W.Problem, eng, impl=None, user_scratchpad=False, runtime_m=False, dst_ld=None):
         """runtime_m: the primitive is created with M = DNNL_RUNTIME_DIM_VAL in src and dst (their
-        strides given), and learns M from the memory objects at execution."""
+        strides given), and learns M from the memory objects at execution.
+        dst_ld: row pitch of dst in elements when dst is a column slice of a wider matrix."""
         self.p, self.eng = p, eng
         self.user_scratchpad = user_scratchpad
         grouped = p.offsets is not None
@@ -28,7 +29,7 @@ class Prepared:
             self.dst_md = api.memory.desc.grouped((p.M, p.N), p.dst_dt, 0, p.groups)
         else:
             self.src_md = _md(p.src)
-            self.dst_md = api.memory.desc((p.M, p.N), p.dst_dt, api.tag.ab)
+            self.dst_md = api.memory.desc((p.M, p.N), p.dst_dt, api.tag.ab if dst_ld is None else (dst_ld, 1))
         self.wei_md = _md(p.wei)
         self.bias_md = _md(p.bias) if p.bias is not None else None
 

@@ -258,7 +258,30 @@ class PeerGather:
             C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_int64, C.c_int64, C.c_void_p, C.c_int64, C.c_int64, C.c_int,
             C.c_void_p, C.c_void_p, C.c_uint, C.c_void_p]
         L.dnnl_cuda_interop_peer_wait.argtypes = [C.c_void_p, C.c_int, C.c_void_p, C.c_uint]
+        L.dnnl_cuda_interop_primitive_replicate_dst.argtypes = [
+            C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_size_t, C.c_void_p, C.c_void_p, C.c_uint]
         self.L = L
+        self.es = es
+        self.full_N = full.N
+        # where this rank's column slice begins inside its own full buffer (dense problems)
+        self.slice_ptr = int(self.buf.data_ptr()) + (self.col_bytes if full.offsets is None else 0)
+
+    def fused_step(self, strm, prep):
+        """The exchange fused into the matmul kernel: `prep` (a runner.Prepared whose dst memory is
+        this rank's slice INSIDE the full buffer, row pitch N) stores every dst element into all
+        ranks' buffers and publishes the flag itself; only the wait is a launch of its own.  Raises
+        api.error(unimplemented) for implementations without the fused form."""
+        self.epoch += 1
+        st = self.L.dnnl_cuda_interop_primitive_replicate_dst(
+            prep.prim._h, self.world, self.rank, self.peer_dst, self.C.c_size_t(max(16, self.nbytes)), self.peer_flags,
+            self.done.data_ptr(), self.epoch)
+        if st != 0:
+            self.epoch -= 1
+            raise self.api.error(st, "replicate dst")
+        prep.execute(strm)
+        st = self.L.dnnl_cuda_interop_peer_wait(strm._h, self.world, self.flags.data_ptr(), self.epoch)
+        if st != 0:
+            raise self.api.error(st, "peer wait")
 
     def step(self, strm, local_dst_ptr):
         """Enqueues scatter + wait on the library stream; the assembled result is complete on this

@@ -347,3 +347,70 @@ def test_two_engines_in_one_process(gpu):
         for eng, strm in ((eng0, strm0), (eng1, strm1), (eng0, strm0)):
             got, impl = run_problem(p, eng, strm)
             assert_parity(got, want, p.dst_dt, "%s via %s" % (p.name, impl), slack_for(p, impl))
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("make", [lambda: W.int8_zp(256, 1024, 1024), lambda: W.fp8_prefill(300, 512, 640),
+                                  lambda: W.int8_zp(300, 512, 2048, per_n_scales=True)], ids=["int8_zp", "fp8", "int8_zp_f32"])
+def test_replicated_dst_fills_every_buffer(gpu, make):
+    """The fused exchange of the tensor-core GEMM, checked on ONE GPU: the two 'ranks' run one
+    after the other on the same stream (their kernels only store and raise flags, neither waits
+    for the other), each writing its column slice into both full buffers; the flag wait that
+    follows finds both flags set.  Both buffers must then hold the oracle's full result."""
+    import ctypes as C
+    import torch
+    from onednn_b200 import api, sharding
+    from onednn_b200.runner import Prepared
+    eng, strm = gpu
+    full = make()
+    want = O.run_port(full)
+    es = W.nbytes(full.dst_dt, 1)
+    world = 2
+    dev = torch.device("cuda:0")
+    bufs = [torch.zeros(full.M * full.N * es, dtype=torch.uint8, device=dev) for _ in range(world)]
+    flags = [torch.zeros(64, dtype=torch.int32, device=dev) for _ in range(world)]
+    done = torch.zeros(1, dtype=torch.int32, device=dev)
+    bases = (C.c_void_p * world)(*[b.data_ptr() for b in bufs])
+    flagp = (C.c_void_p * world)(*[f.data_ptr() for f in flags])
+    L = api.lib()
+    L.dnnl_cuda_interop_primitive_replicate_dst.argtypes = [
+        C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_size_t, C.c_void_p, C.c_void_p, C.c_uint]
+    L.dnnl_cuda_interop_peer_wait.argtypes = [C.c_void_p, C.c_int, C.c_void_p, C.c_uint]
+    keep = []
+    for epoch in (1, 2):  # twice: the CTA counter must be back at zero
+        for b in bufs:
+            b.zero_()
+        for rank in range(world):
+            p = sharding.shard(full, rank, world)
+            lo, _ = sharding.column_range(full.N, rank, world)
+            prep = Prepared(p, eng, dst_ld=full.N)
+            assert prep.impl in ("cuda:tcgen05:int8", "cuda:tcgen05:fp8")
+            ptrs = {}
+            def put(name, arr):
+                t = torch.from_numpy(np.ascontiguousarray(arr).view(np.uint8).reshape(-1).copy()).to(dev)
+                keep.append(t)
+                ptrs[name] = t.data_ptr()
+            put("src", p.src.data)
+            put("wei", p.wei.data)
+            if p.bias is not None:
+                put("bias", p.bias.data)
+            for name, q in p.quant.items():
+                put(name, q.data)
+            for i, e in enumerate(p.post_ops):
+                if e.kind == W.PO_BINARY:
+                    put("po%d" % i, e.src1.data)
+            ptrs["dst"] = bufs[rank].data_ptr() + lo * es
+            prep.bind_device(ptrs)
+            torch.cuda.synchronize()  # torch's copies and fills run on its own stream
+            st = L.dnnl_cuda_interop_primitive_replicate_dst(prep.prim._h, world, rank, bases, C.c_size_t(bufs[0].numel()), flagp,
+                                                             done.data_ptr(), epoch)
+            assert st == 0
+            prep.execute(strm)
+            keep.append(prep)
+        for rank in range(world):
+            assert L.dnnl_cuda_interop_peer_wait(strm._h, world, flags[rank].data_ptr(), epoch) == 0
+        strm.wait()
+        for b in bufs:
+            got = b.cpu().numpy().view(W.NP_STORAGE[full.dst_dt]).reshape(full.M, full.N)
+            assert_parity(got, want, full.dst_dt, "%s replicated, epoch %d" % (full.name, epoch), slack_for(full, "cuda:tcgen05"))
+        assert int(done.item()) == 0
