@@ -9,26 +9,35 @@
 // zero-points: sum_k s (w - z) = sum_k s w - z sum_k s, with the src row sums
 // from a small pre-kernel.
 //
-// The tensor cores take 16-bit operands from shared memory, so the int8
-// weights are widened on the way: TMA brings a raw [64 k x 128 n] s8 tile,
-// converter warps rewrite it as bf16 (exact: 8 significant bits) in the
-// MN-major 128B-swizzled layout the MMA reads, and `tcgen05.mma kind::f16`
-// multiplies it with the src rows (K-major, straight from TMA).  As in the
-// 8-bit GEMM the kernel computes dst^T: weights are the A operand (128 dst
-// columns = TMEM lanes), src rows the B operand, so an epilogue lane owns one
-// dst column, keeps its scale in a register and stores coalesced rows.
+// tcgen05.mma takes its A operand from TENSOR MEMORY, so the widened weights
+// never pass through shared memory: TMA brings a raw [64 k x 128 n] s8 tile
+// (128B-swizzled rows), converter warps read four k-rows of four columns per
+// lane and k16 step, pair the k-rows with one PRMT, widen them to bf16 (exact:
+// 8 significant bits) and write the stage's operand - 128 TMEM lanes x 32
+// columns, the fragment layout of `tcgen05.st.16x128b` - with two stores per
+// warp; `tcgen05.mma kind::f16` multiplies it with the src rows (K-major,
+// straight from TMA).  Shared memory carries the raw bytes once in, once out,
+// and the src rows; the bf16 copy (2 bytes per weight written and read again)
+// is gone from it.  As in the 8-bit GEMM the kernel computes dst^T: weights
+// are the A operand (128 dst columns = TMEM lanes), src rows the B operand, so
+// an epilogue lane owns one dst column, keeps its scale in a register and
+// stores coalesced rows.  Which column a TMEM lane holds is a permutation
+// inside each group of 32 (lane 16h + 8i + g <-> column 4g + 2h + i), chosen
+// so that a converter lane's four bytes go to the lanes its stores can reach.
 //
-// Tiles are (expert, 128 columns, up to 256 rows of that expert); the MMA's N
-// extent is the tile's row count rounded up to 16, so small experts cost
-// little tensor time.  Tile order: expert, column block, row block fastest,
-// so CTAs running together share weight tiles through L2.  A small planning
-// kernel turns the offsets (cumulative END rows, validated like
-// ref_grouped_gemm.cpp:164-213) into per-expert tile ranges on the device:
-// no host synchronisation.  One persistent CTA per SM: warp 0 streams the raw
-// weight tiles (ring of 8: they come from HBM), the last warp the src rows
-// (ring of 4: they come from L2), warps 2-9 convert into a ring of 2 bf16
-// tiles, warp 1 issues the MMAs, the next four warps run the epilogue; two
-// TMEM accumulator buffers.  Every mbarrier wait is bounded.
+// Tiles are (expert, 128 columns, up to 192 rows of that expert): two
+// accumulator buffers of 192 columns and four operand slots of 32 fill the 512
+// columns of tensor memory.  The MMA's N extent is the tile's row count
+// rounded up to 16, so small experts cost little tensor time.  Tile order:
+// expert, column block, row block fastest, so CTAs running together share
+// weight tiles through L2.  A small planning kernel turns the offsets
+// (cumulative END rows, validated like ref_grouped_gemm.cpp:164-213) into
+// per-expert tile ranges on the device: no host synchronisation.  One
+// persistent CTA per SM: warp 0 streams the raw weight tiles (ring of 8: they
+// come from HBM), the last warp the src rows (ring of 6), warps 2-9 convert
+// (two per lane quarter, alternating stages), warp 1 issues the MMAs, the next
+// four warps run the epilogue.  The issuing loops are warp-uniform code with
+// lane-predicated instructions.  Every mbarrier wait is bounded.
 #include <cuda.h>
 
 #include "device_math.cuh"
@@ -40,21 +49,26 @@ namespace qmm {
 namespace {
 
 constexpr int GT_N = 128; // dst columns per tile = TMEM lanes = UMMA M
-constexpr int GT_M = 256; // most src rows per tile = UMMA N
+constexpr int GT_M = 192; // most src rows per tile = UMMA N
 constexpr int GK = 64; // k per stage: one 128-byte swizzle row of bf16 src
-// Three rings, one per kind of tile, because their needs differ: the raw weights come from HBM
-// (deep ring of small tiles to cover its latency), the src rows from L2, and the bf16 copy is
-// produced and consumed on the SM (two slots: one being written, one being multiplied).
-constexpr int RAW_STAGES = 8, A_STAGES = 2, B_STAGES = 4;
+// Two shared-memory rings and one in tensor memory: the raw weights come from HBM (deep ring of small
+// tiles to cover its latency), the src rows from L2, and the widened operand is produced and consumed
+// on the SM (four slots of 32 columns beside the two accumulators).
+constexpr int RAW_STAGES = 8, A_SLOTS = 4, B_STAGES = 6;
 constexpr int RAW_BYTES = GK * GT_N; // s8 weights as loaded
-constexpr int A_BYTES = GK * GT_N * 2; // the same tile as bf16: two 64-column blocks of [64 k][128 B]
 constexpr int B_BYTES = GT_M * GK * 2; // src rows, K-major
 constexpr int CONV_WARPS = 8, EPI_WARPS = 4;
-constexpr int G_THREADS = 32 * (3 + CONV_WARPS + EPI_WARPS);
+constexpr int MMA_WARPS = 2; // issuers: one takes the even stages, one the odd ones
+constexpr int G_THREADS = 32 * (3 + CONV_WARPS + EPI_WARPS + 1);
+constexpr int MMA_WARP1 = 3 + CONV_WARPS + EPI_WARPS; // the second issuer is the last warp
 constexpr int ACC_STAGES = 2;
-constexpr int A_OFFSET = 0, B_OFFSET = A_STAGES * A_BYTES, RAW_OFFSET = B_OFFSET + B_STAGES * B_BYTES;
+constexpr int A_SLOT_COLS = GK / 2; // two k per 32-bit column
+constexpr int A_COL0 = ACC_STAGES * GT_M;
+static_assert(A_COL0 + A_SLOTS * A_SLOT_COLS <= 512, "tensor memory");
+constexpr int B_OFFSET = 0, RAW_OFFSET = B_OFFSET + B_STAGES * B_BYTES;
 constexpr int G_BAR_OFFSET = RAW_OFFSET + RAW_STAGES * RAW_BYTES;
 constexpr int G_SMEM_BYTES = G_BAR_OFFSET + 512 + 1024;
+static_assert(G_SMEM_BYTES <= 227 * 1024, "shared memory");
 
 // plan[0] = {total tiles, groups, 0, 0}; plan[1 + g] = {first src row, first dst row, rows, first tile}
 struct Tile {
@@ -122,6 +136,28 @@ __device__ __forceinline__ void s8x4_to_bf16x4(uint32_t w, uint32_t &o0, uint32_
     o1 = bf16x2_sub(p1 & 0xff7fff7fu, p1 & 0xff80ff80u);
 }
 
+// 16 TMEM lanes x 32 columns (the four k16 steps of a stage): thread (g = lane / 4, t = lane % 4)
+// supplies, for step s, r[4s] = (lane g, column 8s + t), r[4s + 1] = (lane g + 8, column 8s + t),
+// r[4s + 2] = (lane g, column 8s + 4 + t), r[4s + 3] = (lane g + 8, column 8s + 4 + t)
+__device__ __forceinline__ void tmem_st_16x128b_x8(uint32_t taddr, const uint32_t (&r)[16]) {
+    asm volatile(
+            "tcgen05.st.sync.aligned.16x128b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};" ::"r"(taddr),
+            "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]),
+            "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+            : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait_() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+// D[tmem] (+)= A[tmem] * B[smem], issued by the lane(s) with `issue` set
+__device__ __forceinline__ void mma_ts_bf16(bool issue, uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t idesc, bool acc) {
+    asm volatile(
+            "{\n\t.reg .pred p, q;\n\tsetp.ne.b32 p, %4, 0;\n\tsetp.ne.b32 q, %5, 0;\n\t"
+            "@q tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}" ::"r"(tmem_d),
+            "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"((uint32_t)acc), "r"((uint32_t)issue)
+            : "memory");
+}
+// the dst column (inside its group of 32) that TMEM lane l holds
+__device__ __forceinline__ int lane_column(int l) { return 4 * (l & 7) + 2 * (l >> 4) + ((l >> 3) & 1); }
+
 // Sum over k of every src row (bf16), one warp per row: the factor of a weight zero-point,
 // sum_k s (w - z) = sum_k s w - z sum_k s.
 __global__ void grouped_rowsum_kernel(const __grid_constant__ MatmulArgs a, float *rowsum) {
@@ -139,37 +175,39 @@ __global__ void __launch_bounds__(G_THREADS, 1)
 grouped_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmS,
         const __grid_constant__ MatmulArgs a, const int4 *plan, const float *rowsum, int num_n_tiles,
         int num_k_blocks) {
-    constexpr uint32_t TMEM_COLS = ACC_STAGES * GT_M;
+    constexpr uint32_t TMEM_COLS = 512;
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint64_t *raw_full = (uint64_t *)(smem + G_BAR_OFFSET); // raw weight tile has landed
     uint64_t *raw_empty = raw_full + RAW_STAGES; // the converters have read it
     uint64_t *b_full = raw_empty + RAW_STAGES; // src rows have landed
     uint64_t *b_empty = b_full + B_STAGES; // the MMAs have read them
-    uint64_t *a_full = b_empty + B_STAGES; // the weights are rewritten as bf16
-    uint64_t *a_empty = a_full + A_STAGES; // the MMAs have read them
-    uint64_t *tmem_full = a_empty + A_STAGES;
+    uint64_t *a_full = b_empty + B_STAGES; // the stage's operand is in tensor memory
+    uint64_t *a_empty = a_full + A_SLOTS; // the MMAs have read it
+    uint64_t *tmem_full = a_empty + A_SLOTS;
     uint64_t *tmem_empty = tmem_full + ACC_STAGES;
-    uint32_t *tmem_base_slot = (uint32_t *)(tmem_empty + ACC_STAGES);
+    uint64_t *first_issued = tmem_empty + ACC_STAGES; // the tile's first stage (which overwrites the accumulator) is in the pipe
+    uint32_t *tmem_base_slot = (uint32_t *)(first_issued + ACC_STAGES);
     volatile int *abort_flag = (volatile int *)(tmem_base_slot + 1);
 
     const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
     if (threadIdx.x == 0) {
         for (int s = 0; s < RAW_STAGES; ++s) {
             ptx::mbar_init(&raw_full[s], 1);
-            ptx::mbar_init(&raw_empty[s], CONV_WARPS);
+            ptx::mbar_init(&raw_empty[s], CONV_WARPS / 2); // the stage's four converter warps
         }
         for (int s = 0; s < B_STAGES; ++s) {
             ptx::mbar_init(&b_full[s], 1);
             ptx::mbar_init(&b_empty[s], 1);
         }
-        for (int s = 0; s < A_STAGES; ++s) {
-            ptx::mbar_init(&a_full[s], CONV_WARPS);
+        for (int s = 0; s < A_SLOTS; ++s) {
+            ptx::mbar_init(&a_full[s], CONV_WARPS / 2);
             ptx::mbar_init(&a_empty[s], 1);
         }
         for (int s = 0; s < ACC_STAGES; ++s) {
-            ptx::mbar_init(&tmem_full[s], 1);
+            ptx::mbar_init(&tmem_full[s], MMA_WARPS);
             ptx::mbar_init(&tmem_empty[s], EPI_WARPS);
+            ptx::mbar_init(&first_issued[s], 1);
         }
         *abort_flag = 0;
         ptx::fence_barrier_init();
@@ -186,122 +224,146 @@ grouped_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
 
     if (warp == 0) {
         // ------------------------------------------------ TMA producer of the raw weight tiles
-        if (lane == 0) {
-            uint32_t it = 0;
-            for (int t = blockIdx.x; t < num_tiles && !*abort_flag; t += gridDim.x) {
-                const Tile tl = decode_tile(plan, groups, num_n_tiles, t);
-                for (int kb = 0; kb < num_k_blocks; ++kb, ++it) {
-                    const int s = it % RAW_STAGES;
-                    const uint32_t ph = (it / RAW_STAGES) & 1;
-                    if (!ptx::mbar_wait(&raw_empty[s], ph ^ 1)) { *abort_flag = 1; atomicExch(a.status, 5); break; }
-                    ptx::mbar_arrive_expect_tx(&raw_full[s], RAW_BYTES);
-                    ptx::tma_load_3d(smem + RAW_OFFSET + s * RAW_BYTES, &tmW, &raw_full[s], tl.n0, kb * GK, tl.g);
-                }
+        // (the whole warp walks the loop, lane 0 issues: the addresses stay warp-uniform values)
+        const bool issue = lane == 0;
+        int s = 0;
+        uint32_t ph = 1; // parity of the empty barrier's previous phase: a fresh barrier passes
+        bool ok = true;
+        for (int t = blockIdx.x; t < num_tiles && ok && !*abort_flag; t += gridDim.x) {
+            const Tile tl = decode_tile(plan, groups, num_n_tiles, t);
+            for (int kb = 0; kb < num_k_blocks; ++kb) {
+                if (!__all_sync(0xffffffffu, ptx::mbar_wait(&raw_empty[s], ph))) { ok = false; break; }
+                ptx::mbar_arrive_expect_tx_if(issue, &raw_full[s], RAW_BYTES);
+                ptx::tma_load_3d_if(issue, smem + RAW_OFFSET + s * RAW_BYTES, &tmW, &raw_full[s], tl.n0, kb * GK, tl.g);
+                if (++s == RAW_STAGES) { s = 0; ph ^= 1; }
             }
         }
+        if (!ok && issue) { *abort_flag = 1; atomicExch(a.status, 5); }
     } else if (warp == 2 + CONV_WARPS + EPI_WARPS) {
         // ------------------------------------------------ TMA producer of the src rows
-        if (lane == 0) {
-            uint32_t it = 0;
-            for (int t = blockIdx.x; t < num_tiles && !*abort_flag; t += gridDim.x) {
-                const Tile tl = decode_tile(plan, groups, num_n_tiles, t);
-                const int nbox = (tl.rows + 63) / 64; // src boxes of 64 rows
-                for (int kb = 0; kb < num_k_blocks; ++kb, ++it) {
-                    const int s = it % B_STAGES;
-                    const uint32_t ph = (it / B_STAGES) & 1;
-                    if (!ptx::mbar_wait(&b_empty[s], ph ^ 1)) { *abort_flag = 1; atomicExch(a.status, 5); break; }
-                    uint8_t *bt = smem + B_OFFSET + s * B_BYTES;
-                    ptx::mbar_arrive_expect_tx(&b_full[s], nbox * 64 * GK * 2);
-                    for (int j = 0; j < nbox; ++j)
-                        ptx::tma_load_2d(bt + j * 64 * GK * 2, &tmS, &b_full[s], kb * GK, tl.src_row + 64 * j);
-                }
+        const bool issue = lane == 0;
+        int s = 0;
+        uint32_t ph = 1;
+        bool ok = true;
+        for (int t = blockIdx.x; t < num_tiles && ok && !*abort_flag; t += gridDim.x) {
+            const Tile tl = decode_tile(plan, groups, num_n_tiles, t);
+            const int nbox = (tl.rows + 63) / 64; // src boxes of 64 rows
+            for (int kb = 0; kb < num_k_blocks; ++kb) {
+                if (!__all_sync(0xffffffffu, ptx::mbar_wait(&b_empty[s], ph))) { ok = false; break; }
+                uint8_t *bt = smem + B_OFFSET + s * B_BYTES;
+                ptx::mbar_arrive_expect_tx_if(issue, &b_full[s], nbox * 64 * GK * 2);
+                for (int j = 0; j < nbox; ++j)
+                    ptx::tma_load_2d_if(issue, bt + j * 64 * GK * 2, &tmS, &b_full[s], kb * GK, tl.src_row + 64 * j);
+                if (++s == B_STAGES) { s = 0; ph ^= 1; }
             }
         }
-    } else if (warp == 1) {
-        // ------------------------------------------------ MMA issuer
-        if (lane == 0) {
-            uint32_t it = 0, acc_it = 0;
-            for (int t = blockIdx.x; t < num_tiles && !*abort_flag; t += gridDim.x, ++acc_it) {
-                const Tile tl = decode_tile(plan, groups, num_n_tiles, t);
-                const uint32_t n_mma = (uint32_t)max(16, (tl.rows + 15) & ~15);
-                const uint32_t idesc
-                        = ptx::make_idesc(ptx::CFMT_F32, ptx::FMT_BF16, ptx::FMT_BF16, true, false, GT_N, n_mma);
-                const int as = acc_it % ACC_STAGES;
-                const uint32_t aph = (acc_it / ACC_STAGES) & 1;
-                if (!ptx::mbar_wait(&tmem_empty[as], aph ^ 1)) { *abort_flag = 1; atomicExch(a.status, 5); break; }
-                ptx::tc_fence_after_sync();
-                const uint32_t tmem_d = tmem_base + as * GT_M;
-                bool failed = false;
-                for (int kb = 0; kb < num_k_blocks; ++kb, ++it) {
-                    const int sa_i = it % A_STAGES, sb_i = it % B_STAGES;
-                    if (!ptx::mbar_wait(&a_full[sa_i], (it / A_STAGES) & 1)
-                            || !ptx::mbar_wait(&b_full[sb_i], (it / B_STAGES) & 1)) {
-                        failed = true;
-                        break;
-                    }
+        if (!ok && issue) { *abort_flag = 1; atomicExch(a.status, 5); }
+    } else if (warp == 1 || warp == MMA_WARP1) {
+        // ------------------------------------------------ MMA issuers (warp-uniform, lane 0 issues)
+        // A warp issues an MMA every 40 to 65 cycles and pays two waits and two commits per stage, more
+        // than the MMAs of a stage take: two warps share the work, stage by stage.  The MMAs of one thread
+        // run in order; the only order needed between the two threads is that the tile's first stage,
+        // which overwrites the accumulator, is in the pipe before anything is added to it.
+        const int me = warp == 1 ? 0 : 1;
+        const bool issue = lane == 0;
+        int sa = 0, sb = 0;
+        uint32_t pa = 0, pb = 0; // parities of the full barriers
+        uint32_t acc_it = 0, it = 0;
+        bool ok = true;
+        for (int t = blockIdx.x; t < num_tiles && ok && !*abort_flag; t += gridDim.x, ++acc_it) {
+            const Tile tl = decode_tile(plan, groups, num_n_tiles, t);
+            const uint32_t n_mma = (uint32_t)max(16, (tl.rows + 15) & ~15);
+            const uint32_t idesc = ptx::make_idesc(ptx::CFMT_F32, ptx::FMT_BF16, ptx::FMT_BF16, false, false, GT_N, n_mma);
+            const int as = acc_it % ACC_STAGES;
+            const uint32_t aph = (acc_it / ACC_STAGES) & 1;
+            const bool first_mine = (int)(it & 1) == me; // this warp issues the tile's first stage
+            if (first_mine) {
+                if (!__all_sync(0xffffffffu, ptx::mbar_wait(&tmem_empty[as], aph ^ 1))) { ok = false; break; }
+            } else {
+                if (!__all_sync(0xffffffffu, ptx::mbar_wait(&first_issued[as], aph))) { ok = false; break; }
+            }
+            ptx::tc_fence_after_sync();
+            const uint32_t tmem_d = tmem_base + as * GT_M;
+            for (int kb = 0; kb < num_k_blocks; ++kb, ++it) {
+                if ((int)(it & 1) == me) {
+                    if (!__all_sync(0xffffffffu, ptx::mbar_wait(&a_full[sa], pa) && ptx::mbar_wait(&b_full[sb], pb))) { ok = false; break; }
                     ptx::tc_fence_after_sync();
-                    const uint32_t sa = ptx::smem_u32(smem + A_OFFSET + sa_i * A_BYTES);
-                    const uint32_t sb = ptx::smem_u32(smem + B_OFFSET + sb_i * B_BYTES);
-                    // weights MN-major: 16 k-rows of 128 bytes per MMA, 64-column blocks 8 KB apart; src rows
-                    // K-major: 32 bytes of the row per MMA.  The issuing thread is one instruction stream
-                    // (about five cycles per dependent instruction), so the descriptors are built once per
-                    // stage and advanced by constants in their start-address field (16-byte units).
-                    const uint64_t wd0 = ptx::smem_desc_sw128(sa, GK * 128, 1024);
-                    const uint64_t sd0 = ptx::smem_desc_sw128(sb, 0, 1024);
+                    // src rows K-major: 32 bytes of the row per MMA; the descriptor is built once per stage
+                    // and advanced by a constant in its start-address field (16-byte units)
+                    const uint64_t sd0 = ptx::smem_desc_sw128(ptx::smem_u32(smem + B_OFFSET + sb * B_BYTES), 0, 1024);
+                    const uint32_t ta = tmem_base + A_COL0 + sa * A_SLOT_COLS;
 #pragma unroll
                     for (int kk = 0; kk < GK / 16; ++kk)
-                        ptx::mma_ss<2>(tmem_d, wd0 + (uint64_t)(kk * ((16 * 128) >> 4)), sd0 + (uint64_t)(kk * (32 >> 4)), idesc,
-                                (kb | kk) != 0);
-                    // both tiles are reusable once these MMAs have read them
-                    ptx::tc_commit(&a_empty[sa_i]);
-                    ptx::tc_commit(&b_empty[sb_i]);
+                        mma_ts_bf16(issue, tmem_d, ta + 8 * kk, sd0 + (uint64_t)(kk * (32 >> 4)), idesc, (kb | kk) != 0);
+                    // the operand slot and the src tile are reusable once these MMAs have read them
+                    ptx::tc_commit_if(issue, &a_empty[sa]);
+                    ptx::tc_commit_if(issue, &b_empty[sb]);
+                    if (kb == 0) { // the other issuer may add to the accumulator from here on
+                        ptx::tc_fence_before_sync();
+                        ptx::mbar_arrive_if(issue, &first_issued[as]);
+                    }
                 }
-                if (failed) { *abort_flag = 1; atomicExch(a.status, 5); break; }
-                ptx::tc_commit(&tmem_full[as]); // accumulator complete
+                if (++sa == A_SLOTS) { sa = 0; pa ^= 1; }
+                if (++sb == B_STAGES) { sb = 0; pb ^= 1; }
             }
+            if (!ok) break;
+            ptx::tc_commit_if(issue, &tmem_full[as]); // this thread's share of the accumulator is complete
         }
+        if (!ok && issue) { *abort_flag = 1; atomicExch(a.status, 5); }
     } else if (warp < 2 + CONV_WARPS) {
-        // ------------------------------------------------ converters: s8 tile -> bf16 MMA operand
-        const int ct = threadIdx.x - 64; // 0 .. 32 CONV_WARPS - 1
-        const int c = ct & 7; // 16-byte chunk of the raw row: columns 16c .. 16c+15
-        const int blk = c >> 2, q = 2 * (c & 3); // 64-column block and 16-byte chunk pair of the bf16 row
-        // A 16-byte store is served a quarter-warp (8 lanes, here one k-row) at a time: the lanes of
-        // block 0 store their even chunk first and those of block 1 their odd one, so that the eight
-        // stores of a quarter-warp fall on eight different 16-byte bank groups.
-        const int q_first = q + blk, q_second = q + 1 - blk;
+        // ------------------------------------------------ converters: s8 tile -> bf16 operand in tensor memory
+        // Warp (q = warp % 4, r): TMEM lanes 32q .. 32q+31, the stages of parity r.  Lane (g, t) reads,
+        // per k16 step, the four bytes of columns 32q + 4g .. +3 in the k-rows 2t, 2t+1, 2t+8, 2t+9; byte
+        // 2h + i of those goes to TMEM lane 32q + 16h + 8i + g, so one 16-lane store per h carries the
+        // stage's four steps.
+        const int q = warp & 3, r = (warp - 2) >> 2;
+        const int g = lane >> 2, tq = lane & 3;
+        const uint32_t chunk = (uint32_t)(2 * q + (g >> 2)), within = (uint32_t)(4 * (g & 3));
+        // 128B swizzle of the raw rows: 16-byte chunk index XOR (row & 7)
+        uint32_t off[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const uint32_t row = 2 * tq + (i & 1) + 8 * (i >> 1);
+            off[i] = row * 128 + ((chunk ^ (row & 7)) << 4) + within;
+        }
         uint32_t it = 0;
+        int sr = 0, sa = 0;
+        uint32_t pr = 0, pa = 1;
         bool ok = true;
         for (int t = blockIdx.x; t < num_tiles && ok && !*abort_flag; t += gridDim.x) {
             for (int kb = 0; kb < num_k_blocks; ++kb, ++it) {
-                const int sr = it % RAW_STAGES, sa_i = it % A_STAGES;
-                // the raw tile has landed, and the MMAs have finished with the bf16 slot to overwrite
-                if (!__all_sync(0xffffffffu,
-                            ptx::mbar_wait(&raw_full[sr], (it / RAW_STAGES) & 1)
-                                    && ptx::mbar_wait(&a_empty[sa_i], ((it / A_STAGES) & 1) ^ 1))) {
-                    ok = false;
-                    break;
-                }
-                const uint8_t *raw = smem + RAW_OFFSET + sr * RAW_BYTES;
-                uint8_t *at = smem + A_OFFSET + sa_i * A_BYTES + blk * (GK * 128);
+                if ((int)(it & 1) == r) {
+                    if (!__all_sync(0xffffffffu, ptx::mbar_wait_relaxed(&raw_full[sr], pr))) { ok = false; break; }
+                    const uint8_t *raw = smem + RAW_OFFSET + sr * RAW_BYTES;
+                    uint32_t w[4][4]; // [step][k-row]
 #pragma unroll
-                for (int i = 0; i < 16 / CONV_WARPS; ++i) {
-                    const int r = (ct >> 3) + 4 * CONV_WARPS * i; // k-row
-                    const uint4 w = *reinterpret_cast<const uint4 *>(raw + r * 128 + c * 16);
-                    uint4 lo, hi;
-                    s8x4_to_bf16x4(w.x, lo.x, lo.y);
-                    s8x4_to_bf16x4(w.y, lo.z, lo.w);
-                    s8x4_to_bf16x4(w.z, hi.x, hi.y);
-                    s8x4_to_bf16x4(w.w, hi.z, hi.w);
-                    uint8_t *row = at + r * 128;
-                    *reinterpret_cast<uint4 *>(row + ((q_first ^ (r & 7)) << 4)) = blk ? hi : lo;
-                    *reinterpret_cast<uint4 *>(row + ((q_second ^ (r & 7)) << 4)) = blk ? lo : hi;
+                    for (int st = 0; st < 4; ++st)
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) w[st][i] = *reinterpret_cast<const uint32_t *>(raw + st * 2048 + off[i]);
+                    // the stage's bytes are in registers: the producer may refill it
+                    __syncwarp();
+                    if (lane == 0) ptx::mbar_arrive(&raw_empty[sr]);
+                    if (!__all_sync(0xffffffffu, ptx::mbar_wait_relaxed(&a_empty[sa], pa))) { ok = false; break; }
+                    ptx::tc_fence_after_sync();
+                    const uint32_t slot = tmem_base + ((uint32_t)(32 * q) << 16) + A_COL0 + sa * A_SLOT_COLS;
+#pragma unroll
+                    for (int h = 0; h < 2; ++h) {
+                        const uint32_t sel = h ? 0x7362u : 0x5140u; // [a.b(2h), b.b(2h), a.b(2h+1), b.b(2h+1)]
+                        uint32_t o[16];
+#pragma unroll
+                        for (int st = 0; st < 4; ++st) {
+                            s8x4_to_bf16x4(prmt_(w[st][0], w[st][1], sel), o[4 * st + 0], o[4 * st + 1]);
+                            s8x4_to_bf16x4(prmt_(w[st][2], w[st][3], sel), o[4 * st + 2], o[4 * st + 3]);
+                        }
+                        tmem_st_16x128b_x8(slot + ((uint32_t)(16 * h) << 16), o);
+                    }
+                    tmem_st_wait_();
+                    ptx::tc_fence_before_sync();
+                    __syncwarp(); // every lane's stores to tensor memory are done
+                    if (lane == 0) ptx::mbar_arrive(&a_full[sa]);
                 }
-                ptx::fence_proxy_async(); // the MMA reads these bytes through the async proxy
-                __syncwarp();
-                if (lane == 0) {
-                    ptx::mbar_arrive(&a_full[sa_i]);
-                    ptx::mbar_arrive(&raw_empty[sr]);
-                }
+                if (++sr == RAW_STAGES) { sr = 0; pr ^= 1; }
+                if (++sa == A_SLOTS) { sa = 0; pa ^= 1; }
             }
         }
         if (!ok) { *abort_flag = 1; atomicExch(a.status, 5); }
@@ -313,7 +375,7 @@ grouped_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
             const Tile tl = decode_tile(plan, groups, num_n_tiles, t);
             const int as = acc_it % ACC_STAGES;
             const uint32_t aph = (acc_it / ACC_STAGES) & 1;
-            const int64_t n = tl.n0 + lane_base + lane;
+            const int64_t n = tl.n0 + lane_base + lane_column(lane);
             float scale = 1.f;
             if (a.wei_scale.ptr && n < a.N)
                 scale = load_float(a.wei_scale.dt, a.wei_scale.ptr,
@@ -415,7 +477,7 @@ int launch_grouped_tc(const MatmulArgs &a, void *scratch, int sm_count, cudaStre
     encode_tiled_fn enc = grouped_get_encode();
     if (!enc || !scratch) return 5;
     CUtensorMap tw, ts;
-    { // weights as bytes [G][K][N]: raw tile of 64 k x 128 n; a dense [K][N] matrix is one group
+    { // weights as bytes [G][K][N]: raw tile of 64 k x 128 n, 128B swizzle; a dense [K][N] matrix is one group
         const int64_t groups = a.group_count > 0 ? a.group_count : 1;
         const int64_t group_pitch = a.group_count > 0 ? a.wei_sg : a.K * a.wei_sk;
         cuuint64_t dims[3] = {(cuuint64_t)a.N, (cuuint64_t)a.K, (cuuint64_t)groups};
@@ -423,7 +485,7 @@ int launch_grouped_tc(const MatmulArgs &a, void *scratch, int sm_count, cudaStre
         cuuint32_t box[3] = {GT_N, GK, 1};
         cuuint32_t estr[3] = {1, 1, 1};
         if (enc(&tw, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void *>(a.wei), dims, strides, box, estr,
-                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE)
                 != CUDA_SUCCESS)
             return 5;

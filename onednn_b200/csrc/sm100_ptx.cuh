@@ -91,6 +91,13 @@ __device__ __forceinline__ void tma_load_2d_if(bool issue, void *dst, const void
             ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"((uint32_t)issue)
             : "memory");
 }
+__device__ __forceinline__ void tma_load_3d_if(bool issue, void *dst, const void *map, uint64_t *bar, int x, int y, int z) {
+    asm volatile(
+            "{\n\t.reg .pred q;\n\tsetp.ne.b32 q, %6, 0;\n\t"
+            "@q cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];\n\t}"
+            ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"(z), "r"((uint32_t)issue)
+            : "memory");
+}
 __device__ __forceinline__ void tc_commit_if(bool issue, uint64_t *bar) {
     asm volatile("{\n\t.reg .pred q;\n\tsetp.ne.b32 q, %1, 0;\n\t"
                  "@q tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t}" ::"r"(smem_u32(bar)), "r"((uint32_t)issue)
