@@ -33,6 +33,9 @@
 #include "device_math.cuh"
 #include "launch.h"
 #include "objects.hpp"
+// waits of this kernel are long (a tile's mainloop, a ring that is full): let the hardware hold the
+// polling thread for up to this many nanoseconds per poll (measured: 3 % on the fp8 GEMM)
+#define QMM_TRY_WAIT_HINT_NS 2000
 #include "sm100_ptx.cuh"
 
 namespace qmm {

@@ -43,8 +43,20 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t *bar, uint32_t by
 __device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
+// One poll.  QMM_TRY_WAIT_HINT_NS (a build switch) gives the instruction a suspend-time hint: the
+// thread may then sleep in hardware until the phase completes or the time has passed, instead of
+// coming back at once and executing the polling loop's instructions.
 __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
     uint32_t ok;
+#ifdef QMM_TRY_WAIT_HINT_NS
+    asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(ok)
+            : "r"(smem_u32(bar)), "r"(parity), "r"((uint32_t)QMM_TRY_WAIT_HINT_NS)
+            : "memory");
+#else
     asm volatile(
             "{\n\t.reg .pred p;\n\t"
             "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
@@ -52,6 +64,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
             : "=r"(ok)
             : "r"(smem_u32(bar)), "r"(parity)
             : "memory");
+#endif
     return ok != 0;
 }
 // Waits for the phase with the given parity to complete.  Returns false when
