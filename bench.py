@@ -9,8 +9,10 @@ describe the headline workload, the fp8 prefill GEMM (e4m3 [4096,4096] x e4m3
 [4096,14336] -> bf16, per-tensor scales, bf16 bias), and `workloads` carries
 the same fields for every workload.  For N > 1 (launched under torchrun) dense
 problems are sharded by output columns and the grouped one by experts; every
-rank computes its shard and the shards are assembled with an NCCL all-gather;
-the total problem is fixed, so scaling is "strong".
+rank computes its shard and the full dst is assembled on every rank by the
+library's own peer-store kernels (fused into the GEMM epilogue at two ranks;
+`--gather nccl`, or no peer-mapped memory: an NCCL all-gather); the total
+problem is fixed, so scaling is "strong".
 
 Per workload:
   value     whole-job throughput with inputs resident in HBM: blocks of K steps,
