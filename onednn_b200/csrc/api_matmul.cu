@@ -244,7 +244,7 @@ dnnl_status_t grouped_attr_check(const dnnl_primitive_desc &pd) {
 dnnl_status_t ref_dense_accepts(const dnnl_primitive_desc &pd) {
     const auto s = pd.src.data_type, w = pd.wei.data_type, d = pd.dst.data_type;
     const auto &attr = pd.attr;
-    UNIMPL_IF(pd.src.ndims != 2); // batched matmul is not built yet
+    UNIMPL_IF(pd.src.ndims != 2); // a batched problem comes here as its 2D core (batch_core)
     const bool with_bias = pd.bias.ndims != 0;
     const dnnl_dim_t K = pd.K();
     if (is_int8(s)) { // ref_matmul_int8.hpp:44-92
@@ -573,6 +573,38 @@ void fill_quant_mds(dnnl_primitive_desc &pd) {
 
 const dnnl_memory_desc g_zero_md;
 
+// The 2D core of a batched descriptor: the last two dims of every tensor, quantization masks
+// without the batch bits.  Parameters that vary along a batch dim are not built.
+dnnl_status_t batch_core(const dnnl_primitive_desc &pd, dnnl_primitive_desc &core) {
+    core = pd;
+    core.batched = false;
+    const int nd = pd.dst.ndims, nb = nd - 2;
+    auto last2 = [&](dnnl_memory_desc &md) {
+        if (md.ndims == 0) return;
+        dnnl_memory_desc m = md;
+        m.ndims = 2;
+        for (int i = 0; i < 2; ++i) {
+            m.dims[i] = md.dims[nb + i];
+            m.strides[i] = md.strides[nb + i];
+        }
+        md = m;
+    };
+    last2(core.src); last2(core.wei); last2(core.dst); last2(core.bias);
+    for (auto &e : core.attr.post_ops.entries)
+        if (e.kind == dnnl_binary) {
+            if (e.src1.ndims != nd) return dnnl_unimplemented;
+            last2(e.src1);
+        }
+    const int batch_bits = (1 << nb) - 1;
+    for (auto *m : {&core.attr.scales, &core.attr.zero_points, &core.attr.reductions})
+        for (auto &kv : *m) {
+            if (kv.second.mask & batch_bits) return dnnl_unimplemented;
+            kv.second.mask >>= nb;
+        }
+    return dnnl_success;
+}
+
+
 } // namespace
 
 extern "C" {
@@ -636,7 +668,24 @@ dnnl_status_t dnnl_matmul_primitive_desc_create(dnnl_primitive_desc_t *primitive
             if (e.kind == dnnl_sum && e.sum_dt == dnnl_data_type_undef) e.sum_dt = pd->dst.data_type;
         st = pd->grouped ? grouped_attr_check(*pd) : dense_attr_check(*pd);
     }
-    if (st == dnnl_success) st = select_impl(*pd, 0);
+    // Batched (ndims > 2, src/common/matmul.cpp:630-744 with broadcast of size-1 batch dims): the
+    // implementation is chosen for the 2D core and run once per matrix of the batch.
+    const bool batched = st == dnnl_success && !pd->grouped && pd->dst.ndims > 2;
+    if (batched) {
+        if (pd->runtime_m || pd->src.format_kind != dnnl_blocked || pd->wei.format_kind != dnnl_blocked
+                || pd->dst.format_kind != dnnl_blocked)
+            st = dnnl_unimplemented;
+        dnnl_primitive_desc core;
+        if (st == dnnl_success) st = batch_core(*pd, core);
+        if (st == dnnl_success) st = select_impl(core, 0);
+        if (st == dnnl_success) {
+            pd->batched = true;
+            pd->impl = core.impl;
+            pd->impl_name = core.impl_name;
+            pd->scratch_bytes = core.scratch_bytes;
+            pd->scratchpad = core.scratchpad;
+        }
+    } else if (st == dnnl_success) st = select_impl(*pd, 0);
     if (st != dnnl_success) {
         delete pd;
         return st;
@@ -652,8 +701,11 @@ dnnl_status_t dnnl_primitive_desc_next_impl(dnnl_primitive_desc_t pd) {
     if (pd->kind != dnnl_matmul) return dnnl_last_impl_reached; // one reorder implementation
     dnnl_primitive_desc tmp = *pd;
     if (tmp.runtime_m) tmp.src.dims[0] = tmp.dst.dims[0] = 1;
+    if (pd->batched && batch_core(*pd, tmp) != dnnl_success) return dnnl_last_impl_reached;
     dnnl_status_t st = select_impl(tmp, pd->impl + 1);
     if (st != dnnl_success) return dnnl_last_impl_reached;
+    pd->scratch_bytes = tmp.scratch_bytes;
+    pd->scratchpad = tmp.scratchpad;
     pd->impl = tmp.impl;
     pd->impl_name = tmp.impl_name;
     return dnnl_success;
@@ -824,52 +876,10 @@ dnnl_status_t bind_quant(QParam &q, const quant_entry_t &e, dnnl_memory_t mem, i
 
 } // namespace
 
-extern "C" dnnl_status_t dnnl_primitive_execute(const_dnnl_primitive_t primitive, dnnl_stream_t stream, int nargs,
-        const dnnl_exec_arg_t *args) {
-    if (!primitive || !stream || nargs < 0 || (nargs > 0 && !args)) return dnnl_invalid_arguments;
-    if (stream->engine != primitive->pd.engine && stream->engine->device != primitive->pd.engine->device)
-        return dnnl_invalid_arguments;
-    for (int i = 0; i < nargs; ++i)
-        if (!args[i].memory) return dnnl_invalid_arguments;
-    if (primitive->pd.kind == dnnl_reorder) return execute_reorder(primitive->pd, stream, nargs, args);
-    arg_map_t am {args, nargs};
-    // A primitive created with M left open takes M from the src / dst memory objects, checks the
-    // rest of their descriptors against its own and chooses the implementation (and the scratch
-    // it needs) for this M.
-    dnnl_primitive_desc settled;
-    if (primitive->pd.runtime_m) {
-        dnnl_memory_t s = am.find(DNNL_ARG_SRC), d = am.find(DNNL_ARG_DST);
-        if (!s || !d) return dnnl_invalid_arguments;
-        settled = primitive->pd;
-        const dnnl_memory_desc &sm = s->md, &dm = d->md;
-        if (sm.ndims != 2 || dm.ndims != 2 || sm.has_runtime_dims() || dm.has_runtime_dims() || sm.dims[0] != dm.dims[0]
-                || sm.dims[1] != settled.src.dims[1] || dm.dims[1] != settled.dst.dims[1]
-                || sm.data_type != settled.src.data_type || dm.data_type != settled.dst.data_type
-                || sm.format_kind != dnnl_blocked || dm.format_kind != dnnl_blocked)
-            return dnnl_invalid_arguments;
-        settled.src = sm;
-        settled.dst = dm;
-        settled.runtime_m = false;
-        dnnl_status_t rst = dense_desc_check(settled.src, settled.wei, settled.bias.ndims ? &settled.bias : nullptr, settled.dst);
-        if (rst == dnnl_success) rst = dense_attr_check(settled);
-        if (rst == dnnl_success) rst = select_impl(settled, 0);
-        if (rst != dnnl_success) return rst;
-        if (settled.scratch_bytes > primitive->scratch_cap && settled.engine->device >= 0) {
-            cudaSetDevice(settled.engine->device);
-            // earlier executions may still use the old buffer: they are in order on this stream
-            if (primitive->scratch) {
-                cudaStreamSynchronize(stream->stream);
-                cudaFree(primitive->scratch);
-                primitive->scratch = nullptr;
-                primitive->scratch_cap = 0;
-            }
-            if (!cuda_ok(cudaMalloc(&primitive->scratch, settled.scratch_bytes), "cudaMalloc(scratchpad)"))
-                return dnnl_out_of_memory;
-            cudaMemsetAsync(primitive->scratch, 0, settled.scratch_bytes, stream->stream);
-            primitive->scratch_cap = settled.scratch_bytes;
-        }
-    }
-    const dnnl_primitive_desc &pd = primitive->pd.runtime_m ? settled : primitive->pd;
+// One 2D (or grouped) problem: `pd` holds two-dimensional descriptors; a descriptor's offset0 says
+// where in the buffer its matrix begins (sub-memories, and the matrices of a batch).
+static dnnl_status_t execute_matmul_2d(const_dnnl_primitive_t primitive, const dnnl_primitive_desc &pd,
+        dnnl_stream_t stream, arg_map_t &am, int nargs, const dnnl_exec_arg_t *args) {
     const auto &attr = pd.attr;
 
     dnnl_memory_t src = am.find(DNNL_ARG_SRC), wei = am.find(DNNL_ARG_WEIGHTS), dst = am.find(DNNL_ARG_DST);
@@ -948,7 +958,7 @@ extern "C" dnnl_status_t dnnl_primitive_execute(const_dnnl_primitive_t primitive
             po.kind = PO_BINARY;
             dnnl_memory_t m = am.find(DNNL_ARG_ATTR_MULTIPLE_POST_OP(i) | DNNL_ARG_SRC_1);
             if (!m || !m->handles[0]) return dnnl_invalid_arguments;
-            po.src1 = m->handles[0];
+            po.src1 = at_offset0(m->handles[0], e.src1);
             po.src1_dt = e.src1.data_type;
             po.sm = e.src1.dims[0] > 1 ? e.src1.strides[0] : 0;
             po.sn = e.src1.dims[1] > 1 ? e.src1.strides[1] : 0;
@@ -1045,4 +1055,83 @@ extern "C" dnnl_status_t dnnl_primitive_execute(const_dnnl_primitive_t primitive
         if (e != cudaSuccess) set_last_error(std::string("kernel launch: ") + cudaGetErrorString(e));
     }
     return (dnnl_status_t)rc;
+}
+
+extern "C" dnnl_status_t dnnl_primitive_execute(const_dnnl_primitive_t primitive, dnnl_stream_t stream, int nargs,
+        const dnnl_exec_arg_t *args) {
+    if (!primitive || !stream || nargs < 0 || (nargs > 0 && !args)) return dnnl_invalid_arguments;
+    if (stream->engine != primitive->pd.engine && stream->engine->device != primitive->pd.engine->device)
+        return dnnl_invalid_arguments;
+    for (int i = 0; i < nargs; ++i)
+        if (!args[i].memory) return dnnl_invalid_arguments;
+    if (primitive->pd.kind == dnnl_reorder) return execute_reorder(primitive->pd, stream, nargs, args);
+    arg_map_t am {args, nargs};
+    // A primitive created with M left open takes M from the src / dst memory objects, checks the
+    // rest of their descriptors against its own and chooses the implementation (and the scratch
+    // it needs) for this M.
+    dnnl_primitive_desc settled;
+    if (primitive->pd.runtime_m) {
+        dnnl_memory_t s = am.find(DNNL_ARG_SRC), d = am.find(DNNL_ARG_DST);
+        if (!s || !d) return dnnl_invalid_arguments;
+        settled = primitive->pd;
+        const dnnl_memory_desc &sm = s->md, &dm = d->md;
+        if (sm.ndims != 2 || dm.ndims != 2 || sm.has_runtime_dims() || dm.has_runtime_dims() || sm.dims[0] != dm.dims[0]
+                || sm.dims[1] != settled.src.dims[1] || dm.dims[1] != settled.dst.dims[1]
+                || sm.data_type != settled.src.data_type || dm.data_type != settled.dst.data_type
+                || sm.format_kind != dnnl_blocked || dm.format_kind != dnnl_blocked)
+            return dnnl_invalid_arguments;
+        settled.src = sm;
+        settled.dst = dm;
+        settled.runtime_m = false;
+        dnnl_status_t rst = dense_desc_check(settled.src, settled.wei, settled.bias.ndims ? &settled.bias : nullptr, settled.dst);
+        if (rst == dnnl_success) rst = dense_attr_check(settled);
+        if (rst == dnnl_success) rst = select_impl(settled, 0);
+        if (rst != dnnl_success) return rst;
+        if (settled.scratch_bytes > primitive->scratch_cap && settled.engine->device >= 0) {
+            cudaSetDevice(settled.engine->device);
+            // earlier executions may still use the old buffer: they are in order on this stream
+            if (primitive->scratch) {
+                cudaStreamSynchronize(stream->stream);
+                cudaFree(primitive->scratch);
+                primitive->scratch = nullptr;
+                primitive->scratch_cap = 0;
+            }
+            if (!cuda_ok(cudaMalloc(&primitive->scratch, settled.scratch_bytes), "cudaMalloc(scratchpad)"))
+                return dnnl_out_of_memory;
+            cudaMemsetAsync(primitive->scratch, 0, settled.scratch_bytes, stream->stream);
+            primitive->scratch_cap = settled.scratch_bytes;
+        }
+    }
+    if (primitive->pd.batched) {
+        // a matmul per matrix of the batch, in order on the stream (they share the scratch)
+        const dnnl_primitive_desc &bp = primitive->pd;
+        dnnl_primitive_desc core;
+        dnnl_status_t bst = batch_core(bp, core);
+        if (bst != dnnl_success) return bst;
+        core.impl = bp.impl; core.impl_name = bp.impl_name; core.scratch_bytes = bp.scratch_bytes;
+        const int nd = bp.dst.ndims, nb = nd - 2;
+        dnnl_dim_t count = 1;
+        for (int d = 0; d < nb; ++d) count *= bp.dst.dims[d];
+        if (bp.dst.has_zero_dim()) count = 0;
+        for (dnnl_dim_t b = 0; b < count; ++b) {
+            dnnl_dim_t idx[DNNL_MAX_NDIMS], rem = b;
+            for (int d = nb - 1; d >= 0; --d) { idx[d] = rem % bp.dst.dims[d]; rem /= bp.dst.dims[d]; }
+            auto off = [&](const dnnl_memory_desc &md) {
+                dnnl_dim_t o = md.offset0;
+                for (int d = 0; d < nb; ++d) o += (md.dims[d] == 1 ? 0 : idx[d]) * md.strides[d];
+                return o;
+            };
+            core.src.offset0 = off(bp.src);
+            core.wei.offset0 = off(bp.wei);
+            core.dst.offset0 = off(bp.dst);
+            if (bp.bias.ndims) core.bias.offset0 = off(bp.bias);
+            for (size_t i = 0; i < bp.attr.post_ops.entries.size(); ++i)
+                if (bp.attr.post_ops.entries[i].kind == dnnl_binary)
+                    core.attr.post_ops.entries[i].src1.offset0 = off(bp.attr.post_ops.entries[i].src1);
+            bst = execute_matmul_2d(primitive, core, stream, am, nargs, args);
+            if (bst != dnnl_success) return bst;
+        }
+        return dnnl_success;
+    }
+    return execute_matmul_2d(primitive, primitive->pd.runtime_m ? settled : primitive->pd, stream, am, nargs, args);
 }

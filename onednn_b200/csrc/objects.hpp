@@ -153,6 +153,7 @@ struct dnnl_primitive_desc {
     // M is DNNL_RUNTIME_DIM_VAL in src / dst: shapes, implementation and scratch are settled per
     // execution from the memory objects' descriptors (impl / impl_name describe M = 1)
     bool runtime_m = false;
+    bool batched = false; // ndims > 2: the implementation runs once per matrix of the batch
     int impl = IMPL_REF;
     std::string impl_name;
     std::map<int, dnnl_memory_desc> quant_mds; // exec-arg id -> parameter md
