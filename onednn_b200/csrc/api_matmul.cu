@@ -376,7 +376,10 @@ dnnl_status_t tc_accepts(const dnnl_primitive_desc &pd) {
     if (sz.set) UNIMPL_IF(sz.group_ndims || sz.mask != 0 || sz.dt != dnnl_s32 || sz.on_host);
     if (wz.set) UNIMPL_IF(wz.group_ndims || !(wz.mask == 0 || wz.mask == 2) || wz.on_host);
     UNIMPL_IF(!attr.reductions.empty());
-    // |acc - compensation| must stay within s32 as in the reference's own sum
+    // The kernel adds K products of 8-bit values in s32 and subtracts the zero-point terms afterwards;
+    // the reference adds (s - zs)(w - zw) directly.  Both stay inside s32, and so agree, while
+    // K * 255 * 255 < 2^31; longer sums go to the generic kernel, which adds in the reference's order.
+    UNIMPL_IF(int_path && K > 33025);
     return dnnl_success;
 }
 
