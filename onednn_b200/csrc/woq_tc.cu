@@ -145,6 +145,11 @@ __device__ __forceinline__ uint32_t nib2(uint32_t x, uint32_t magic) { // (x & 0
     asm("lop3.b32 %0, %1, 0x000F000F, %2, 0x6a;" : "=r"(r) : "r"(x), "r"(magic));
     return r;
 }
+__device__ __forceinline__ uint32_t nib2_hi(uint32_t x, uint32_t magic) { // (x & 0x00F000F0) ^ magic
+    uint32_t r;
+    asm("lop3.b32 %0, %1, 0x00F000F0, %2, 0x6a;" : "=r"(r) : "r"(x), "r"(magic));
+    return r;
+}
 __device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
     uint32_t r;
     asm("prmt.b32 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(sel));
@@ -449,7 +454,13 @@ woq_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
         // 128B swizzle: 16-byte chunk index XOR (row & 7); rows 2tig (+8) and 2tig+1 (+8)
         const uint32_t lds0 = box_off + (2 * tig) * 128 + ((chunk ^ (uint32_t)(2 * tig)) << 4) + within;
         const uint32_t lds1 = box_off + (2 * tig + 1) * 128 + ((chunk ^ (uint32_t)(2 * tig + 1)) << 4) + within;
+        // bf16 src: a nibble u becomes the bf16 128 + u (shifted down to the mantissa's low bits first).
+        // f16 src: a low nibble is the subnormal u * 2^-24 where it stands and a high nibble u * 2^-20,
+        // no shift; the epilogue's per-column factor undoes the power of two.  (The operand must have
+        // the src's format: an MMA with an f16 A and a bf16 B is an illegal instruction.)
+        // s4: the sign bit flipped, u = w + 8.
         const uint32_t magic = F16 ? (p.sgn4 ? 0x00080008u : 0u) : (p.sgn4 ? 0x43084308u : 0x43004300u);
+        const uint32_t magic_hi = p.sgn4 ? 0x00800080u : 0u;
         uint32_t it = 0;
         int s = 0, as = 0, rs = 0;
         uint32_t ph = 0, aph = 1, rph = 0;
@@ -501,9 +512,9 @@ woq_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
                                 const uint32_t x01 = prmt(R[qs][0][t >> 2], R[qs][1][t >> 2], sel);
                                 const uint32_t x23 = prmt(R[qs][2][t >> 2], R[qs][3][t >> 2], sel);
                                 o[4 * qs + 0] = nib2(x01, magic);
-                                o[4 * qs + 1] = nib2(x01 >> 4, magic);
+                                o[4 * qs + 1] = F16 ? nib2_hi(x01, magic_hi) : nib2(x01 >> 4, magic);
                                 o[4 * qs + 2] = nib2(x23, magic);
-                                o[4 * qs + 3] = nib2(x23 >> 4, magic);
+                                o[4 * qs + 3] = F16 ? nib2_hi(x23, magic_hi) : nib2(x23 >> 4, magic);
                             }
                             // block j = t / 2 holds its SPS steps in consecutive columns; lanes 16 (t & 1) ...
                             tmem_st_16x128b_steps<C::SPS>(ast + ((uint32_t)(16 * (t & 1)) << 16) + (t >> 1) * (8 * C::SPS), o);
@@ -538,7 +549,8 @@ woq_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
         const int tid = threadIdx.x - CONV_WARPS * 32; // 0 .. 127
         float *ssum = ssum_all + q * 32;
         const float off = (F16 ? 0.f : 128.f) + (p.sgn4 ? 8.f : 0.f);
-        const float acc_scale = F16 ? 16777216.f : 1.f; // the f16 nibbles are u * 2^-24
+        // the f16 operand's nibbles are u * 2^-24 (low nibble) or u * 2^-20 (high nibble: this lane's column is odd)
+        const float acc_scale = F16 ? (ehi ? 1048576.f : 16777216.f) : 1.f;
         const float zt = p.zp_mode == 2 ? (float)load_int(a.wei_zp.dt, a.wei_zp.ptr, 0) : 0.f;
         float tot[NBLK][MR];
 #pragma unroll
