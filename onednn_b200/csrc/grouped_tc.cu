@@ -35,8 +35,8 @@
 // per-expert tile ranges on the device: no host synchronisation.  One
 // persistent CTA per SM: warp 0 streams the raw weight tiles (ring of 8: they
 // come from HBM), the last warp the src rows (ring of 6), warps 2-9 convert
-// (two per lane quarter, alternating stages), warp 1 issues the MMAs, the next
-// four warps run the epilogue.  The issuing loops are warp-uniform code with
+// (two per lane quarter, alternating stages), warp 1 and the last three warps
+// issue the MMAs (stage by stage, in turn), four warps run the epilogue.  The issuing loops are warp-uniform code with
 // lane-predicated instructions.  Every mbarrier wait is bounded.
 #include <cuda.h>
 
@@ -61,29 +61,40 @@ constexpr int RAW_STAGES = 8, A_SLOTS = 4, B_STAGES = 6;
 constexpr int RAW_BYTES = GK * GT_N; // s8 weights as loaded
 constexpr int B_BYTES = GT_M * GK * 2; // src rows, K-major
 constexpr int CONV_WARPS = 8, EPI_WARPS = 4;
-constexpr int MMA_WARPS = 2; // issuers: one takes the even stages, one the odd ones
-constexpr int G_THREADS = 32 * (3 + CONV_WARPS + EPI_WARPS + 1);
-constexpr int MMA_WARP1 = 3 + CONV_WARPS + EPI_WARPS; // the second issuer is the last warp
+constexpr int MMA_WARPS = 4; // issuers: stage s belongs to issuer s % MMA_WARPS
+constexpr int G_THREADS = 32 * (3 + CONV_WARPS + EPI_WARPS + MMA_WARPS - 1);
+constexpr int MMA_WARP1 = 3 + CONV_WARPS + EPI_WARPS; // the issuers after the first are the last warps
 constexpr int ACC_STAGES = 2;
 constexpr int A_SLOT_COLS = GK / 2; // two k per 32-bit column
 constexpr int A_COL0 = ACC_STAGES * GT_M;
 static_assert(A_COL0 + A_SLOTS * A_SLOT_COLS <= 512, "tensor memory");
 constexpr int B_OFFSET = 0, RAW_OFFSET = B_OFFSET + B_STAGES * B_BYTES;
 constexpr int G_BAR_OFFSET = RAW_OFFSET + RAW_STAGES * RAW_BYTES;
-constexpr int G_SMEM_BYTES = G_BAR_OFFSET + 512 + 1024;
+constexpr int PLAN_CACHE_GROUPS = 511; // records kept in shared memory (8 KB); more groups: read from global memory
+constexpr int G_PLAN_OFFSET = G_BAR_OFFSET + 512;
+constexpr int G_SMEM_BYTES = G_PLAN_OFFSET + (PLAN_CACHE_GROUPS + 1) * 16 + 1024;
 static_assert(G_SMEM_BYTES <= 227 * 1024, "shared memory");
+
+#ifdef QMM_PROFILE // builds with -DQMM_PROFILE stamp the SM clock of CTA 0 per role and stage; the shipped library has no such code
+__device__ unsigned long long *g_grouped_trace = nullptr;
+#define GT_TRACE(role, idx) do { if (g_grouped_trace && blockIdx.x == 0 && (idx) < 256) g_grouped_trace[(role) * 256 + (idx)] = (unsigned long long)clock64(); } while (0)
+#else
+#define GT_TRACE(role, idx) do { } while (0)
+#endif
 
 // plan[0] = {total tiles, groups, 0, 0}; plan[1 + g] = {first src row, first dst row, rows, first tile}
 struct Tile {
     int g, n0, m0, rows, src_row, dst_row;
 };
+// (`plan` is the kernel's copy of the records in shared memory when they fit: every role looks a tile
+// up when it begins it, and six dependent loads from global memory there cost microseconds per tile)
 __device__ __forceinline__ Tile decode_tile(const int4 *plan, int groups, int num_n_tiles, int t) {
     int lo = 0, hi = groups; // last group whose first tile is <= t, skipping empty groups behind it
     while (hi - lo > 1) {
         const int mid = (lo + hi) >> 1;
-        if (__ldg(&plan[1 + mid]).w <= t) lo = mid; else hi = mid;
+        if (plan[1 + mid].w <= t) lo = mid; else hi = mid;
     }
-    const int4 e = __ldg(&plan[1 + lo]);
+    const int4 e = plan[1 + lo];
     const int r = t - e.w;
     const int mt = (e.z + GT_M - 1) / GT_M;
     Tile tl;
@@ -176,7 +187,8 @@ __global__ void grouped_rowsum_kernel(const __grid_constant__ MatmulArgs a, floa
 template <bool EPI_CHAIN>
 __global__ void __launch_bounds__(G_THREADS, 1)
 grouped_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmS,
-        const __grid_constant__ MatmulArgs a, const int4 *plan, const float *rowsum, int num_n_tiles,
+        const __grid_constant__ CUtensorMap tmS2, const __grid_constant__ CUtensorMap tmS3,
+        const __grid_constant__ MatmulArgs a, const int4 *plan_global, const float *rowsum, int num_n_tiles,
         int num_k_blocks) {
     constexpr uint32_t TMEM_COLS = 512;
     extern __shared__ uint8_t smem_raw[];
@@ -189,8 +201,9 @@ grouped_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
     uint64_t *a_empty = a_full + A_SLOTS; // the MMAs have read it
     uint64_t *tmem_full = a_empty + A_SLOTS;
     uint64_t *tmem_empty = tmem_full + ACC_STAGES;
-    uint64_t *issued = tmem_empty + ACC_STAGES; // per issuer: the MMAs of its latest stage are in the pipe
-    uint32_t *tmem_base_slot = (uint32_t *)(issued + MMA_WARPS);
+    // stages whose MMAs are in the pipe (written by the two issuers in turn, read by the other)
+    volatile uint32_t *stages_issued = (volatile uint32_t *)(tmem_empty + ACC_STAGES);
+    uint32_t *tmem_base_slot = (uint32_t *)(tmem_empty + ACC_STAGES + 1);
     volatile int *abort_flag = (volatile int *)(tmem_base_slot + 1);
 
     const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
@@ -211,19 +224,28 @@ grouped_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
             ptx::mbar_init(&tmem_full[s], MMA_WARPS);
             ptx::mbar_init(&tmem_empty[s], EPI_WARPS);
         }
-        for (int s = 0; s < MMA_WARPS; ++s) ptx::mbar_init(&issued[s], 1);
+        *stages_issued = 0u;
         *abort_flag = 0;
         ptx::fence_barrier_init();
         ptx::prefetch_tensormap(&tmW);
         ptx::prefetch_tensormap(&tmS);
+        ptx::prefetch_tensormap(&tmS2);
+        ptx::prefetch_tensormap(&tmS3);
     }
     if (warp == 1) ptx::tmem_alloc(tmem_base_slot, TMEM_COLS);
     ptx::tc_fence_before_sync();
     __syncthreads();
     ptx::tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_base_slot;
-    const int4 head = __ldg(&plan[0]);
+    const int4 head = __ldg(&plan_global[0]);
     const int num_tiles = head.x, groups = head.y;
+    const int4 *plan = plan_global;
+    if (groups <= PLAN_CACHE_GROUPS) {
+        int4 *cache = reinterpret_cast<int4 *>(smem + G_PLAN_OFFSET);
+        for (int i = threadIdx.x; i <= groups; i += blockDim.x) cache[i] = __ldg(&plan_global[i]);
+        __syncthreads();
+        plan = cache;
+    }
 
     if (warp == 0) {
         // ------------------------------------------------ TMA producer of the raw weight tiles
@@ -231,6 +253,7 @@ grouped_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
         const bool issue = lane == 0;
         int s = 0;
         uint32_t ph = 1; // parity of the empty barrier's previous phase: a fresh barrier passes
+        [[maybe_unused]] uint32_t pit = 0;
         bool ok = true;
         for (int t = blockIdx.x; t < num_tiles && ok && !*abort_flag; t += gridDim.x) {
             const Tile tl = decode_tile(plan, groups, num_n_tiles, t);
@@ -238,6 +261,8 @@ grouped_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
                 if (!__all_sync(0xffffffffu, ptx::mbar_wait(&raw_empty[s], ph))) { ok = false; break; }
                 ptx::mbar_arrive_expect_tx_if(issue, &raw_full[s], RAW_BYTES);
                 ptx::tma_load_3d_if(issue, smem + RAW_OFFSET + s * RAW_BYTES, &tmW, &raw_full[s], tl.n0, kb * GK, tl.g);
+                if (issue) GT_TRACE(0, pit);
+                ++pit;
                 if (++s == RAW_STAGES) { s = 0; ph ^= 1; }
             }
         }
@@ -247,28 +272,33 @@ grouped_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
         const bool issue = lane == 0;
         int s = 0;
         uint32_t ph = 1;
+        [[maybe_unused]] uint32_t bit = 0;
         bool ok = true;
         for (int t = blockIdx.x; t < num_tiles && ok && !*abort_flag; t += gridDim.x) {
             const Tile tl = decode_tile(plan, groups, num_n_tiles, t);
-            const int nbox = (tl.rows + 63) / 64; // src boxes of 64 rows
+            // one copy per stage (issuing a copy costs this thread about as much as the wait): a box of
+            // 64, 128 or 192 rows, whichever covers the tile's rows
+            const int nbox = (tl.rows + 63) / 64;
+            const CUtensorMap *tm = nbox == 1 ? &tmS : nbox == 2 ? &tmS2 : &tmS3;
             for (int kb = 0; kb < num_k_blocks; ++kb) {
                 if (!__all_sync(0xffffffffu, ptx::mbar_wait(&b_empty[s], ph))) { ok = false; break; }
                 uint8_t *bt = smem + B_OFFSET + s * B_BYTES;
                 ptx::mbar_arrive_expect_tx_if(issue, &b_full[s], nbox * 64 * GK * 2);
-                for (int j = 0; j < nbox; ++j)
-                    ptx::tma_load_2d_if(issue, bt + j * 64 * GK * 2, &tmS, &b_full[s], kb * GK, tl.src_row + 64 * j);
+                ptx::tma_load_2d_if(issue, bt, tm, &b_full[s], kb * GK, tl.src_row);
+                if (issue) GT_TRACE(1, bit);
+                ++bit;
                 if (++s == B_STAGES) { s = 0; ph ^= 1; }
             }
         }
         if (!ok && issue) { *abort_flag = 1; atomicExch(a.status, 5); }
-    } else if (warp == 1 || warp == MMA_WARP1) {
+    } else if (warp == 1 || warp >= MMA_WARP1) {
         // ------------------------------------------------ MMA issuers (warp-uniform, lane 0 issues)
-        // A warp issues an MMA every 40 to 65 cycles and pays two waits and two commits per stage, more
-        // than the MMAs of a stage take: two warps share the work, stage by stage, one waiting for its
-        // tiles and committing while the other issues.  The stages enter the pipe in their own order -
-        // each issuer tells the other when its stage is in (a fence and a plain arrive) - so the sums are
-        // added in the same order every time and a second execution gives the same bits.
-        const int me = warp == 1 ? 0 : 1;
+        // A warp issues an MMA every 40 to 65 cycles (twice that inside this kernel) and pays two waits
+        // and two commits per stage, more than the MMAs of a stage take: four warps share the work,
+        // stage by stage, waiting for their tiles and committing while another one issues.  The stages enter the pipe in their own order -
+        // each issuer tells the other when its stage is in (a fence and a released store) - so the sums
+        // are added in the same order every time and a second execution gives the same bits.
+        const int me = warp == 1 ? 0 : warp - MMA_WARP1 + 1;
         const bool issue = lane == 0;
         int sa = 0, sb = 0;
         uint32_t pa = 0, pb = 0; // parities of the full barriers
@@ -282,14 +312,25 @@ grouped_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
             const uint32_t aph = (acc_it / ACC_STAGES) & 1;
             const uint32_t tmem_d = tmem_base + as * GT_M;
             for (int kb = 0; kb < num_k_blocks; ++kb, ++it) {
-                if ((int)(it & 1) == me) {
+                if ((int)(it % MMA_WARPS) == me) {
                     if (kb == 0) { // the tile's first stage overwrites the accumulator: the epilogue must have read it
                         if (!__all_sync(0xffffffffu, ptx::mbar_wait(&tmem_empty[as], aph ^ 1))) { ok = false; break; }
                     }
-                    if (!__all_sync(0xffffffffu, ptx::mbar_wait(&a_full[sa], pa) && ptx::mbar_wait(&b_full[sb], pb))) { ok = false; break; }
-                    // the stage before this one (the other issuer's) is in the pipe
-                    if (it > 0 && !__all_sync(0xffffffffu, ptx::mbar_wait(&issued[me ^ 1], ((it - 1) >> 1) & 1))) { ok = false; break; }
+                    if (issue) GT_TRACE(2, it);
+                    if (!__all_sync(0xffffffffu, ptx::mbar_wait(&a_full[sa], pa))) { ok = false; break; }
+                    if (issue) GT_TRACE(3, it);
+                    if (!__all_sync(0xffffffffu, ptx::mbar_wait(&b_full[sb], pb))) { ok = false; break; }
+                    if (issue) GT_TRACE(4, it);
+                    // the stage before this one (the other issuer's) is in the pipe: a word in shared memory,
+                    // polled with plain loads (the hand-off is on the critical path of every stage, and a
+                    // woken mbarrier wait costs several hundred cycles more)
+                    {
+                        uint32_t seen = ptx::ld_acquire_shared(stages_issued);
+                        for (int spin = 0; seen < it && spin < (1 << 24); ++spin) seen = ptx::ld_acquire_shared(stages_issued);
+                        if (!__all_sync(0xffffffffu, seen >= it)) { ok = false; break; }
+                    }
                     ptx::tc_fence_after_sync();
+                    if (issue) GT_TRACE(5, it);
                     // src rows K-major: 32 bytes of the row per MMA; the descriptor is built once per stage
                     // and advanced by a constant in its start-address field (16-byte units)
                     const uint64_t sd0 = ptx::smem_desc_sw128(ptx::smem_u32(smem + B_OFFSET + sb * B_BYTES), 0, 1024);
@@ -298,10 +339,11 @@ grouped_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
                     for (int kk = 0; kk < GK / 16; ++kk)
                         mma_ts_bf16(issue, tmem_d, ta + 8 * kk, sd0 + (uint64_t)(kk * (32 >> 4)), idesc, (kb | kk) != 0);
                     ptx::tc_fence_before_sync();
-                    ptx::mbar_arrive_if(issue, &issued[me]);
+                    if (issue) ptx::st_release_shared(stages_issued, it + 1);
                     // the operand slot and the src tile are reusable once these MMAs have read them
                     ptx::tc_commit_if(issue, &a_empty[sa]);
                     ptx::tc_commit_if(issue, &b_empty[sb]);
+                    if (issue) GT_TRACE(6, it);
                 }
                 if (++sa == A_SLOTS) { sa = 0; pa ^= 1; }
                 if (++sb == B_STAGES) { sb = 0; pb ^= 1; }
@@ -334,6 +376,7 @@ grouped_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
             for (int kb = 0; kb < num_k_blocks; ++kb, ++it) {
                 if ((int)(it & 1) == r) {
                     if (!__all_sync(0xffffffffu, ptx::mbar_wait_relaxed(&raw_full[sr], pr))) { ok = false; break; }
+                    if (warp == 2 && lane == 0) GT_TRACE(7, it);
                     const uint8_t *raw = smem + RAW_OFFSET + sr * RAW_BYTES;
                     uint32_t w[4][4]; // [step][k-row]
 #pragma unroll
@@ -345,6 +388,7 @@ grouped_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
                     if (lane == 0) ptx::mbar_arrive(&raw_empty[sr]);
                     if (!__all_sync(0xffffffffu, ptx::mbar_wait_relaxed(&a_empty[sa], pa))) { ok = false; break; }
                     ptx::tc_fence_after_sync();
+                    if (warp == 2 && lane == 0) GT_TRACE(8, it);
                     const uint32_t slot = tmem_base + ((uint32_t)(32 * q) << 16) + A_COL0 + sa * A_SLOT_COLS;
 #pragma unroll
                     for (int h = 0; h < 2; ++h) {
@@ -361,6 +405,7 @@ grouped_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
                     ptx::tc_fence_before_sync();
                     __syncwarp(); // every lane's stores to tensor memory are done
                     if (lane == 0) ptx::mbar_arrive(&a_full[sa]);
+                    if (warp == 2 && lane == 0) GT_TRACE(9, it);
                 }
                 if (++sr == RAW_STAGES) { sr = 0; pr ^= 1; }
                 if (++sa == A_SLOTS) { sa = 0; pa ^= 1; }
@@ -476,7 +521,7 @@ int launch_grouped_tc(const MatmulArgs &a, void *scratch, int sm_count, cudaStre
     if (a.M == 0 || a.N == 0) return 0;
     encode_tiled_fn enc = grouped_get_encode();
     if (!enc || !scratch) return 5;
-    CUtensorMap tw, ts;
+    CUtensorMap tw, ts, ts2, ts3;
     { // weights as bytes [G][K][N]: raw tile of 64 k x 128 n, 128B swizzle; a dense [K][N] matrix is one group
         const int64_t groups = a.group_count > 0 ? a.group_count : 1;
         const int64_t group_pitch = a.group_count > 0 ? a.wei_sg : a.K * a.wei_sk;
@@ -490,12 +535,14 @@ int launch_grouped_tc(const MatmulArgs &a, void *scratch, int sm_count, cudaStre
                 != CUDA_SUCCESS)
             return 5;
     }
-    { // src as 16-bit words [M][K]: boxes of 64 rows x 64 k, 128B swizzle
+    // src as 16-bit words [M][K]: boxes of 64, 128 and 192 rows x 64 k, 128B swizzle
+    CUtensorMap *src_maps[3] = {&ts, &ts2, &ts3};
+    for (int i = 0; i < 3; ++i) {
         cuuint64_t dims[2] = {(cuuint64_t)a.K, (cuuint64_t)a.M};
         cuuint64_t strides[1] = {(cuuint64_t)(a.src_sm * 2)};
-        cuuint32_t box[2] = {GK, 64};
+        cuuint32_t box[2] = {GK, (cuuint32_t)(64 * (i + 1))};
         cuuint32_t estr[2] = {1, 1};
-        if (enc(&ts, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, const_cast<void *>(a.src), dims, strides, box, estr,
+        if (enc(src_maps[i], CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, const_cast<void *>(a.src), dims, strides, box, estr,
                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE)
                 != CUDA_SUCCESS)
@@ -516,7 +563,7 @@ int launch_grouped_tc(const MatmulArgs &a, void *scratch, int sm_count, cudaStre
     auto kern = chain ? grouped_tc_kernel<true> : grouped_tc_kernel<false>;
     static std::atomic<unsigned long long> configured[2];
     if (!opt_in_dynamic_smem(kern, G_SMEM_BYTES, configured[chain])) return 5;
-    kern<<<sm_count > 0 ? sm_count : 148, G_THREADS, G_SMEM_BYTES, st>>>(tw, ts, a, plan, rowsum, num_n_tiles, num_k_blocks);
+    kern<<<sm_count > 0 ? sm_count : 148, G_THREADS, G_SMEM_BYTES, st>>>(tw, ts, ts2, ts3, a, plan, rowsum, num_n_tiles, num_k_blocks);
     count_launch();
     return cudaGetLastError() == cudaSuccess ? 0 : 5;
 }

@@ -82,6 +82,16 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, uint64
         if (globaltimer() - t0 > limit_ns) return false;
     }
 }
+// A 32-bit word in shared memory handed from one warp to another
+__device__ __forceinline__ uint32_t ld_acquire_shared(const volatile uint32_t *p) {
+    uint32_t v;
+    asm volatile("ld.acquire.cta.shared::cta.u32 %0, [%1];" : "=r"(v) : "r"(smem_u32(const_cast<uint32_t *>(p))) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_release_shared(volatile uint32_t *p, uint32_t v) {
+    asm volatile("st.release.cta.shared::cta.u32 [%0], %1;" ::"r"(smem_u32(const_cast<uint32_t *>(p))), "r"(v) : "memory");
+}
+
 // Lane-predicated forms for warp-uniform issuing code.  A role that one thread could play is
 // written as code that the whole warp runs, with only the instruction itself predicated on
 // `issue` (true in one lane): the loop counters, addresses and descriptors around it then stay
