@@ -335,21 +335,27 @@ grouped_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
                     // and advanced by a constant in its start-address field (16-byte units)
                     const uint64_t sd0 = ptx::smem_desc_sw128(ptx::smem_u32(smem + B_OFFSET + sb * B_BYTES), 0, 1024);
                     const uint32_t ta = tmem_base + A_COL0 + sa * A_SLOT_COLS;
+                    if (ptx::elect_one()) { // one elected thread: see elect_one
 #pragma unroll
-                    for (int kk = 0; kk < GK / 16; ++kk)
-                        mma_ts_bf16(issue, tmem_d, ta + 8 * kk, sd0 + (uint64_t)(kk * (32 >> 4)), idesc, (kb | kk) != 0);
-                    ptx::tc_fence_before_sync();
-                    if (issue) ptx::st_release_shared(stages_issued, it + 1);
-                    // the operand slot and the src tile are reusable once these MMAs have read them
-                    ptx::tc_commit_if(issue, &a_empty[sa]);
-                    ptx::tc_commit_if(issue, &b_empty[sb]);
+                        for (int kk = 0; kk < GK / 16; ++kk)
+                            mma_ts_bf16(true, tmem_d, ta + 8 * kk, sd0 + (uint64_t)(kk * (32 >> 4)), idesc, (kb | kk) != 0);
+                        ptx::tc_fence_before_sync();
+                        ptx::st_release_shared(stages_issued, it + 1);
+                        // the operand slot and the src tile are reusable once these MMAs have read them
+                        ptx::tc_commit(&a_empty[sa]);
+                        ptx::tc_commit(&b_empty[sb]);
+                    }
+                    __syncwarp();
                     if (issue) GT_TRACE(6, it);
                 }
                 if (++sa == A_SLOTS) { sa = 0; pa ^= 1; }
                 if (++sb == B_STAGES) { sb = 0; pb ^= 1; }
             }
             if (!ok) break;
-            ptx::tc_commit_if(issue, &tmem_full[as]); // this thread's share of the accumulator is complete
+            // this thread's share of the accumulator is complete (tcgen05.commit covers the MMAs of the
+            // thread that executes it: the elected lane is the same one, the lowest, every time)
+            if (ptx::elect_one()) ptx::tc_commit(&tmem_full[as]);
+            __syncwarp();
         }
         if (!ok && issue) { *abort_flag = 1; atomicExch(a.status, 5); }
     } else if (warp < 2 + CONV_WARPS) {
