@@ -259,8 +259,11 @@ grouped_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
             const Tile tl = decode_tile(plan, groups, num_n_tiles, t);
             for (int kb = 0; kb < num_k_blocks; ++kb) {
                 if (!__all_sync(0xffffffffu, ptx::mbar_wait(&raw_empty[s], ph))) { ok = false; break; }
-                ptx::mbar_arrive_expect_tx_if(issue, &raw_full[s], RAW_BYTES);
-                ptx::tma_load_3d_if(issue, smem + RAW_OFFSET + s * RAW_BYTES, &tmW, &raw_full[s], tl.n0, kb * GK, tl.g);
+                if (ptx::elect_one()) {
+                    ptx::mbar_arrive_expect_tx(&raw_full[s], RAW_BYTES);
+                    ptx::tma_load_3d(smem + RAW_OFFSET + s * RAW_BYTES, &tmW, &raw_full[s], tl.n0, kb * GK, tl.g);
+                }
+                __syncwarp();
                 if (issue) GT_TRACE(0, pit);
                 ++pit;
                 if (++s == RAW_STAGES) { s = 0; ph ^= 1; }
@@ -283,8 +286,11 @@ grouped_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
             for (int kb = 0; kb < num_k_blocks; ++kb) {
                 if (!__all_sync(0xffffffffu, ptx::mbar_wait(&b_empty[s], ph))) { ok = false; break; }
                 uint8_t *bt = smem + B_OFFSET + s * B_BYTES;
-                ptx::mbar_arrive_expect_tx_if(issue, &b_full[s], nbox * 64 * GK * 2);
-                ptx::tma_load_2d_if(issue, bt, tm, &b_full[s], kb * GK, tl.src_row);
+                if (ptx::elect_one()) {
+                    ptx::mbar_arrive_expect_tx(&b_full[s], nbox * 64 * GK * 2);
+                    ptx::tma_load_2d(bt, tm, &b_full[s], kb * GK, tl.src_row);
+                }
+                __syncwarp();
                 if (issue) GT_TRACE(1, bit);
                 ++bit;
                 if (++s == B_STAGES) { s = 0; ph ^= 1; }

@@ -297,10 +297,13 @@ woq_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
                 for (int st = sg.sb; st < sg.se; ++st, ++it) {
                     if (!__all_sync(0xffffffffu, ptx::mbar_wait(&empty[s], ph))) { ok = false; break; }
                     uint8_t *sw = smem + s * W_STAGE_BYTES;
-                    ptx::mbar_arrive_expect_tx_if(issue, &full[s], W_STAGE_BYTES);
+                    if (ptx::elect_one()) {
+                        ptx::mbar_arrive_expect_tx(&full[s], W_STAGE_BYTES);
 #pragma unroll
-                    for (int b = 0; b < C::W_BOXES; ++b)
-                        ptx::tma_load_2d_if(issue, sw + b * (C::KS * 128), &tmW, &full[s], xbyte + b * 128, st * C::KS);
+                        for (int b = 0; b < C::W_BOXES; ++b)
+                            ptx::tma_load_2d(sw + b * (C::KS * 128), &tmW, &full[s], xbyte + b * 128, st * C::KS);
+                    }
+                    __syncwarp();
                     if (issue) WT_TRACE(0, it);
                     if (++s == C::STAGES) { s = 0; ph ^= 1; }
                 }
@@ -328,15 +331,18 @@ woq_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
                     if (!__all_sync(0xffffffffu, ptx::mbar_wait(&s_empty[s], ph))) { ok = false; break; }
                     uint8_t *ss = smem + C::S_RING_OFFSET + s * p.s_stage_bytes;
                     const bool params = st == sg.sb || r == 0 || p.group_steps - r < C::SPS;
-                    ptx::mbar_arrive_expect_tx_if(issue, &s_full[s], base_tx + (params ? par_tx : 0u));
+                    if (ptx::elect_one()) {
+                        ptx::mbar_arrive_expect_tx(&s_full[s], base_tx + (params ? par_tx : 0u));
 #pragma unroll
-                    for (int b = 0; b < C::S_BOXES; ++b)
-                        ptx::tma_load_2d_if(issue, ss + b * (C::MP * 128), &tmS, &s_full[s], st * C::KS + b * 64, 0);
-                    ptx::tma_load_2d_if(issue, ss + p.off_sums, &tmSums, &s_full[s], 0, first);
-                    if (params) {
-                        ptx::tma_load_2d_if(issue, ss + p.off_sc, &tmSc, &s_full[s], xpair, gi0);
-                        if (p.zp_mode == 1) ptx::tma_load_2d_if(issue, ss + p.off_zp, &tmZp, &s_full[s], xpair, gi0);
+                        for (int b = 0; b < C::S_BOXES; ++b)
+                            ptx::tma_load_2d(ss + b * (C::MP * 128), &tmS, &s_full[s], st * C::KS + b * 64, 0);
+                        ptx::tma_load_2d(ss + p.off_sums, &tmSums, &s_full[s], 0, first);
+                        if (params) {
+                            ptx::tma_load_2d(ss + p.off_sc, &tmSc, &s_full[s], xpair, gi0);
+                            if (p.zp_mode == 1) ptx::tma_load_2d(ss + p.off_zp, &tmZp, &s_full[s], xpair, gi0);
+                        }
                     }
+                    __syncwarp();
                     if (issue) WT_TRACE(12, pit);
                     ++pit;
                     first += C::SPS;
@@ -374,6 +380,7 @@ woq_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
                     const uint32_t ss = ptx::smem_u32(smem + C::S_RING_OFFSET + s * p.s_stage_bytes);
                     const uint32_t ast = tmem_base + C::A_COL0 + as * C::A_STAGE_COLS;
                     const int nst = min(C::SPS, kend - st * C::SPS);
+                    bool committed = false; // the straight-line path commits inside its elected branch
                     // The common stage - whole, inside one group piece - is straight-line code:
                     // descriptor and tensor-memory addresses are a base plus compile-time offsets.
                     if (nst == C::SPS && kpos + C::SPS <= gend && !WT_ABLATE(1)) {
@@ -386,22 +393,29 @@ woq_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
                         const uint32_t accb = tmem_base + buf * C::ACC_COLS + j0 * C::MP;
                         const uint32_t astb = ast + j0 * (8 * C::SPS);
                         const uint64_t bd0 = ptx::smem_desc_sw128(ss, 0, 1024);
-#pragma unroll
-                        for (int q = 0; q < C::SPS; ++q) {
-                            // the start-address field counts 16-byte units: later steps add a constant to it
-                            const uint64_t bd = bd0 + (uint64_t)(((q >> 2) * (C::MP * 128) + (q & 3) * 32) >> 4);
-#pragma unroll
-                            for (int j = 0; j < JB; ++j)
-                                mma_ts_f16(issue, accb + j * C::MP, astb + j * (8 * C::SPS) + 8 * q, bd, p.idesc, q > 0 || !fresh);
-                        }
                         kpos += C::SPS;
+                        const bool piece_done = kpos == gend;
+                        if (ptx::elect_one()) { // one elected thread issues (see elect_one)
+#pragma unroll
+                            for (int q = 0; q < C::SPS; ++q) {
+                                // the start-address field counts 16-byte units: later steps add a constant to it
+                                const uint64_t bd = bd0 + (uint64_t)(((q >> 2) * (C::MP * 128) + (q & 3) * 32) >> 4);
+#pragma unroll
+                                for (int j = 0; j < JB; ++j)
+                                    mma_ts_f16(true, accb + j * C::MP, astb + j * (8 * C::SPS) + 8 * q, bd, p.idesc, q > 0 || !fresh);
+                            }
+                            if (piece_done) ptx::tc_commit(&acc_full[buf]); // group piece complete
+                            ptx::tc_commit(&a_empty[as]); // the operand stage may be rewritten once these MMAs have read it
+                            ptx::tc_commit(&s_empty[s]); // ... and the stage's src tile has been read
+                        }
+                        __syncwarp();
                         fresh = false;
-                        if (kpos == gend) { // group piece complete
-                            ptx::tc_commit_if(issue, &acc_full[buf]);
+                        if (piece_done) {
                             ++gc;
                             fresh = true;
                             gend = min(kend, gend + p.group_steps);
                         }
+                        committed = true;
                     } else {
                         for (int q = 0; q < nst; ++q, ++kpos) {
                             const uint32_t buf = gc & 1;
@@ -426,8 +440,10 @@ woq_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
                         }
                     }
                     if (failed) break;
-                    ptx::tc_commit_if(issue, &a_empty[as]); // the operand stage may be rewritten once these MMAs have read it
-                    ptx::tc_commit_if(issue, &s_empty[s]); // ... and the stage's src tile has been read
+                    if (!committed) {
+                        ptx::tc_commit_if(issue, &a_empty[as]); // the operand stage may be rewritten once these MMAs have read it
+                        ptx::tc_commit_if(issue, &s_empty[s]); // ... and the stage's src tile has been read
+                    }
                     if (j0 == 0 && issue) WT_TRACE(1, it);
                     if (++s == p.s_stages) s = 0;
                     if (++as == A_STAGES) { as = 0; aph ^= 1; }
