@@ -385,6 +385,21 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
             const int64_t m_tile = (int64_t)(tile % tp.num_m_tiles) * BT_M + row_base;
             const int64_t n = (int64_t)(tile / tp.num_m_tiles) * BT_N + lane_base + lane;
             const ColTerms ct = load_col_terms<INT>(a, tp, n); // in flight while waiting for the MMAs
+            if constexpr (CHAIN) {
+                // Operands of binary post-ops that have a value per dst element (a residual) are read once,
+                // row by row, in the middle of the chain: a miss there stalls the whole piece.  While the
+                // tile is being multiplied, ask L2 for this warp's part of them (its rows x its 32 columns).
+                for (int i = 0; i < a.n_po; ++i) {
+                    const PostOpArg &e = a.po[i];
+                    if (e.kind != PO_BINARY || e.sm == 0 || e.sn != 1) continue;
+                    const int esz = (e.src1_dt == DT_F32 || e.src1_dt == DT_S32) ? 4 : (e.src1_dt == DT_BF16 || e.src1_dt == DT_F16) ? 2 : 1;
+                    const int64_t nq = (int64_t)(tile / tp.num_m_tiles) * BT_N + lane_base;
+                    if (nq >= a.N) continue;
+                    for (int r = lane; r < ROWS_PER_WARP; r += 32)
+                        if (m_tile + r < a.M)
+                            asm volatile("prefetch.global.L2 [%0];" ::"l"((const char *)e.src1 + ((m_tile + r) * e.sm + nq) * esz));
+                }
+            }
             if (!ptx::mbar_wait(&tmem_full[as], aph)) { *abort_flag = 1; atomicExch(a.status, 5); break; }
             ptx::tc_fence_after_sync();
 #ifdef QMM_PROFILE
@@ -398,21 +413,22 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
             if constexpr (CHAIN) {
                 // With a post-op chain the code of 32 unrolled rows exceeds the instruction cache, so the
                 // rows go through a rolled loop of 8-row pieces (8 independent dependency chains each).
+                constexpr int CR = 8; // rows per piece: 4 leave too few independent chains (152 us on the int8 post-op workload), 16 overflow the instruction cache (175 us), 8: 134 us
 #pragma unroll 1
-                for (int c = 0; c < ROWS_PER_WARP / 8; ++c) {
-                    uint32_t r[8];
-                    ptx::tmem_ld_32x8(tmem_base + ((uint32_t)lane_base << 16) + as * BT_M + row_base + c * 8, r);
+                for (int c = 0; c < ROWS_PER_WARP / CR; ++c) {
+                    uint32_t r[CR];
+                    ptx::tmem_ld_32x8(tmem_base + ((uint32_t)lane_base << 16) + as * BT_M + row_base + c * CR, r);
                     ptx::tmem_ld_wait();
-                    if (c == ROWS_PER_WARP / 8 - 1) { // accumulator fully read: hand the buffer back
+                    if (c == ROWS_PER_WARP / CR - 1) { // accumulator fully read: hand the buffer back
                         ptx::tc_fence_before_sync();
                         __syncwarp();
                         if (lane == 0) ptx::mbar_arrive(&tmem_empty[as]);
                     }
-                    const int64_t m0 = m_tile + c * 8;
+                    const int64_t m0 = m_tile + c * CR;
 #ifdef QMM_PROFILE
                     if (tp.mainloop_only == 2) continue; // TMEM reads only
 #endif
-                    if (m0 < a.M) epilogue_rows_any<INT, CHAIN, 8, DSTT>(a, tp, tt, ct, r, m0, n);
+                    if (m0 < a.M) epilogue_rows_any<INT, CHAIN, CR, DSTT>(a, tp, tt, ct, r, m0, n);
                 }
             } else {
 #pragma unroll 1
