@@ -414,3 +414,67 @@ def test_replicated_dst_fills_every_buffer(gpu, make):
             got = b.cpu().numpy().view(W.NP_STORAGE[full.dst_dt]).reshape(full.M, full.N)
             assert_parity(got, want, full.dst_dt, "%s replicated, epoch %d" % (full.name, epoch), slack_for(full, "cuda:tcgen05"))
         assert int(done.item()) == 0
+
+
+@pytest.mark.gpu
+def test_peer_scatter_and_wait_on_one_gpu(gpu):
+    """The exchange kernels with both 'ranks' on one GPU, one after the other on the same stream
+    (the scatter only stores and raises flags; the wait finds them raised): column blocks of a
+    dense result and row segments of a grouped one must land in both full buffers."""
+    import ctypes as C
+    import torch
+    from onednn_b200 import api
+    eng, strm = gpu
+    dev = torch.device("cuda:0")
+    L = api.lib()
+    L.dnnl_cuda_interop_peer_scatter.argtypes = [
+        C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_int64, C.c_int64, C.c_void_p, C.c_int64, C.c_int64, C.c_int,
+        C.c_void_p, C.c_void_p, C.c_uint, C.c_void_p]
+    L.dnnl_cuda_interop_peer_wait.argtypes = [C.c_void_p, C.c_int, C.c_void_p, C.c_uint]
+    world, M, N, es = 2, 70, 96, 2
+    g = torch.Generator(device="cpu").manual_seed(5)
+    full = torch.randint(0, 2 ** 15, (M, N), dtype=torch.int16, generator=g)
+    bufs = [torch.zeros(M, N, dtype=torch.int16, device=dev) for _ in range(world)]
+    flags = [torch.zeros(64, dtype=torch.int32, device=dev) for _ in range(world)]
+    done = torch.zeros(1, dtype=torch.int32, device=dev)
+    bases = (C.c_void_p * world)(*[b.data_ptr() for b in bufs])
+    flagp = (C.c_void_p * world)(*[f.data_ptr() for f in flags])
+    keep = []
+    # dense: rank r owns columns [48 r, 48 r + 48)
+    for rank in range(world):
+        local = full[:, 48 * rank:48 * rank + 48].contiguous().to(dev)
+        keep.append(local)
+        seg = (C.c_int64 * 3)(0, 0, M)
+        torch.cuda.synchronize()
+        assert L.dnnl_cuda_interop_peer_scatter(strm._h, world, rank, local.data_ptr(), 48 * es, 48 * es, bases, N * es,
+                                                48 * rank * es, 1, seg, flagp, 1, done.data_ptr()) == 0
+    for rank in range(world):
+        assert L.dnnl_cuda_interop_peer_wait(strm._h, world, flags[rank].data_ptr(), 1) == 0
+    strm.wait()
+    for b in bufs:
+        assert torch.equal(b.cpu(), full)
+    # grouped: rank 0 owns rows [0, 10) and [40, 70), rank 1 rows [10, 40), as two / one segments
+    for b in bufs:
+        b.zero_()
+    owned = {0: [(0, 10), (40, 70)], 1: [(10, 40)]}
+    for rank in range(world):
+        local = torch.cat([full[a:b] for a, b in owned[rank]]).contiguous().to(dev)
+        keep.append(local)
+        trip, at = [], 0
+        for a, b in owned[rank]:
+            trip += [at, a, b - a]
+            at += b - a
+        seg = (C.c_int64 * len(trip))(*trip)
+        torch.cuda.synchronize()
+        assert L.dnnl_cuda_interop_peer_scatter(strm._h, world, rank, local.data_ptr(), N * es, N * es, bases, N * es, 0,
+                                                len(owned[rank]), seg, flagp, 2, done.data_ptr()) == 0
+    for rank in range(world):
+        assert L.dnnl_cuda_interop_peer_wait(strm._h, world, flags[rank].data_ptr(), 2) == 0
+    strm.wait()
+    for b in bufs:
+        assert torch.equal(b.cpu(), full)
+    assert int(done.item()) == 0
+    # a flag that nothing raises: the wait gives up after its limit and the stream reports it
+    assert L.dnnl_cuda_interop_peer_wait(strm._h, world, flags[0].data_ptr(), 3) == 0
+    with pytest.raises(api.error):
+        strm.wait()
