@@ -313,3 +313,32 @@ def test_verbose_line_format(host_engine, capfd):
     assert f[8] == "src:bf16::blocked:ab::f0 wei:s4::blocked:ab::f0 dst:bf16::blocked:ab::f0"
     assert f[9] == "attr-fpmath:bf16:true attr-scales:wei:3:bf16:128x1 attr-zero-points:wei:3:u4:128x1"
     assert f[11] == "8x256:256x64"
+
+
+def test_replicated_dst_is_refused_where_no_kernel_has_it(host_engine):
+    """dnnl_cuda_interop_primitive_replicate_dst: only the tensor-core GEMM without a post-op chain
+    repeats its dst stores; other primitives answer unimplemented (the caller then uses the
+    scatter kernel), and world <= 1 switches the replication off."""
+    import ctypes as C
+    from onednn_b200 import api
+    from onednn_b200.runner import Prepared
+    L = api.lib()
+    L.dnnl_cuda_interop_primitive_replicate_dst.argtypes = [
+        C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_size_t, C.c_void_p, C.c_void_p, C.c_uint]
+    bases = (C.c_void_p * 2)(0x1000, 0x2000)
+    flags = (C.c_void_p * 2)(0x3000, 0x4000)
+    done = C.c_void_p(0x5000)
+
+    def call(p, world=2):
+        prep = Prepared(p, host_engine)
+        return prep.impl, L.dnnl_cuda_interop_primitive_replicate_dst(prep.prim._h, world, 0, bases, 4096, flags, done, 1)
+
+    impl, st = call(W.int8_zp(64, 256, 256))
+    assert impl == "cuda:tcgen05:int8" and st == 0
+    assert call(W.int8_zp(64, 256, 256), world=1)[1] == 0
+    impl, st = call(W.int8_postops(64, 256, 256))
+    assert impl == "cuda:tcgen05:int8" and st == api.unimplemented  # a post-op chain
+    impl, st = call(W.int4_decode(4, 512, 256))
+    assert st == api.unimplemented
+    impl, st = call(W.moe_grouped(96, 256, 128, 8))
+    assert st == api.unimplemented
