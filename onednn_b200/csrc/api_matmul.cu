@@ -420,6 +420,11 @@ dnnl_status_t woq_tc_accepts(const dnnl_primitive_desc &pd) {
     if (woq_accepts(pd) != dnnl_success) return dnnl_unimplemented;
     UNIMPL_IF(pd.M() > 1 && pd.src.strides[0] % 8 != 0);
     UNIMPL_IF(pd.wei.strides[0] % 32 != 0);
+    // the scale / zero-point rows of a stage's groups must fit in the kernel's shared-memory ring
+    const auto &ws = pd.attr.scale(DNNL_ARG_WEIGHTS);
+    const auto &wz = pd.attr.zp(DNNL_ARG_WEIGHTS);
+    const dnnl_dim_t group = ws.mask == 3 ? ws.groups[0] : pd.K();
+    UNIMPL_IF(!woq_tc_fits(pd.M(), pd.K(), group, (int)ws.dt, (wz.set && wz.mask == 3) ? (int)wz.dt : -1));
     return dnnl_success;
 }
 

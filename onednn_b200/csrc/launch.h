@@ -54,6 +54,7 @@ size_t woq_skinny_scratch_bytes(int64_t N, int64_t K, int sm_count);
 int launch_woq_tc(const MatmulArgs &a, void *scratch, int sm_count, cudaStream_t st);
 size_t woq_tc_scratch_bytes(int64_t M, int64_t N, int64_t K, int sm_count);
 bool woq_tc_pointers_ok(const MatmulArgs &a);
+bool woq_tc_fits(int64_t M, int64_t K, int64_t group, int scale_dt, int zp_dt);
 
 // tcgen05 grouped (MoE) GEMM, bf16 src x s8 weights (grouped_tc.cu).
 // `scratch`: grouped_tc_scratch_bytes(group_count, M) bytes, no initialisation

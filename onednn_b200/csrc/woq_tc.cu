@@ -922,14 +922,13 @@ int wt_rows_per_stage(int group_steps, int sps) {
     return (sps + group_steps - 2) / group_steps + 1;
 }
 
-template <int MR, int NBLK, bool F16>
-int wt_launch(encode_tiled_fn enc, WtMaps &tm, const MatmulArgs &a, WtParams &p, int grid, cudaStream_t st) {
+// The src / parameter ring takes the shared memory the fixed parts leave: sizes and offsets of a stage
+// and the number of stages.  False when fewer than four stages fit (small groups with wide parameter
+// types): such problems are left to the next implementation when the descriptor is created.
+template <int MR, int NBLK>
+bool wt_ring_layout(int group_steps, int sc_bits, int zp_bits, WtParams &p) {
     using C = WtCfg<MR, NBLK>;
-    auto kern = woq_tc_kernel<MR, NBLK, F16>;
-    // the src / parameter ring takes what the fixed parts leave
-    const int rb = wt_rows_per_stage(p.group_steps, C::SPS);
-    const int ngroups = (p.ksteps + p.group_steps - 1) / p.group_steps;
-    const int sc_bits = wt_bits(a.wei_scale.dt), zp_bits = p.zp_mode == 1 ? wt_bits(a.wei_zp.dt) : 0;
+    const int rb = wt_rows_per_stage(group_steps, C::SPS);
     auto up128 = [](int v) { return (v + 127) / 128 * 128; };
     p.sc_row_bytes = C::NB * sc_bits / 8;
     p.zp_row_bytes = C::NB * zp_bits / 8;
@@ -941,7 +940,17 @@ int wt_launch(encode_tiled_fn enc, WtMaps &tm, const MatmulArgs &a, WtParams &p,
     p.s_stage_bytes = (p.off_zp + up128(p.zp_box_bytes) + 1023) / 1024 * 1024;
     p.s_stages = (C::SMEM_LIMIT - C::S_RING_OFFSET) / p.s_stage_bytes;
     if (p.s_stages > C::S_STAGES_MAX) p.s_stages = C::S_STAGES_MAX;
-    if (p.s_stages < 4) {
+    return p.s_stages >= 4 && rb <= 256;
+}
+
+template <int MR, int NBLK, bool F16>
+int wt_launch(encode_tiled_fn enc, WtMaps &tm, const MatmulArgs &a, WtParams &p, int grid, cudaStream_t st) {
+    using C = WtCfg<MR, NBLK>;
+    auto kern = woq_tc_kernel<MR, NBLK, F16>;
+    const int ngroups = (p.ksteps + p.group_steps - 1) / p.group_steps;
+    const int sc_bits = wt_bits(a.wei_scale.dt), zp_bits = p.zp_mode == 1 ? wt_bits(a.wei_zp.dt) : 0;
+    const int rb = wt_rows_per_stage(p.group_steps, C::SPS);
+    if (!wt_ring_layout<MR, NBLK>(p.group_steps, sc_bits, zp_bits, p)) {
         set_last_error("cuda:tcgen05:woq4: the parameter rows of a stage do not fit in shared memory");
         return 5;
     }
@@ -985,6 +994,20 @@ static size_t wt_partial_offset(const WtPlan &pl, int64_t K) {
 size_t woq_tc_scratch_bytes(int64_t M, int64_t N, int64_t K, int sm_count) {
     const WtPlan pl = wt_plan(M, N, K, sm_count);
     return wt_partial_offset(pl, K) + (size_t)pl.ntiles * pl.max_slots * (size_t)M * (128 * pl.nblk) * sizeof(float);
+}
+
+// Whether the kernel's shared-memory plan holds the problem: `group` = K-group of the weight
+// parameters (K when there is none), scale / zero-point data types as DT_* (zp_dt < 0: no per-group
+// zero-points).
+bool woq_tc_fits(int64_t M, int64_t K, int64_t group, int scale_dt, int zp_dt) {
+    WtParams p {};
+    const int ksteps = (int)((K + 15) / 16);
+    int gs = (int)(group / 16);
+    if (gs < 1 || gs > ksteps) gs = ksteps;
+    const int sc_bits = wt_bits(scale_dt), zp_bits = zp_dt < 0 ? 0 : wt_bits(zp_dt);
+    if (M <= 8) return wt_ring_layout<8, 4>(gs, sc_bits, zp_bits, p);
+    if (M <= 16) return wt_ring_layout<16, 4>(gs, sc_bits, zp_bits, p);
+    return wt_ring_layout<32, 2>(gs, sc_bits, zp_bits, p);
 }
 
 bool woq_tc_pointers_ok(const MatmulArgs &a) {

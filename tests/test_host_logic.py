@@ -342,3 +342,18 @@ def test_replicated_dst_is_refused_where_no_kernel_has_it(host_engine):
     assert st == api.unimplemented
     impl, st = call(W.moe_grouped(96, 256, 128, 8))
     assert st == api.unimplemented
+
+
+def test_decode_problems_with_wide_parameter_rows_go_to_the_next_implementation(host_engine):
+    """cuda:tcgen05:woq4 keeps a stage's scale / zero-point rows in shared memory: groups of 16 with
+    f32 scales and s32 zero-points of a 32-row problem do not fit and are served by the next implementation in the list."""
+    import numpy as np
+    from onednn_b200.runner import Prepared
+    p = W.int4_decode(4, 1024, 512, group=128)
+    assert Prepared(p, host_engine).impl == "cuda:tcgen05:woq4"
+    p = W.int4_decode(32, 1024, 512, group=16)
+    r = np.random.Generator(np.random.PCG64(3))
+    G = 1024 // 16
+    p.quant["wei_scale"] = W.Quant(r.uniform(0.005, 0.02, (G, 512)).astype(np.float32), W.F32, 3, (16, 1))
+    p.quant["wei_zp"] = W.Quant(r.integers(0, 16, (G, 512)).astype(np.int32), W.S32, 3, (16, 1))
+    assert Prepared(p, host_engine).impl == "cuda:woq:skinny"
