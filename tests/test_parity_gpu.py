@@ -106,6 +106,16 @@ def _per_n_scale(p):
     return p
 
 
+def _wide_params(p):
+    """f32 scales and s32 zero-points per (K-group, column): several parameter rows per stage."""
+    r = np.random.Generator(np.random.PCG64(9))
+    g = p.quant["wei_scale"].groups
+    G = p.K // g[0]
+    p.quant["wei_scale"] = W.Quant(r.uniform(0.005, 0.02, (G, p.N)).astype(np.float32), W.F32, 3, g)
+    p.quant["wei_zp"] = W.Quant(r.integers(0, 16, (G, p.N)).astype(np.int32), W.S32, 3, g)
+    return p
+
+
 def _with_bias_relu(p):
     r = np.random.Generator(np.random.PCG64(9))
     p.bias = W.QTensor(W.f32_to_bf16(r.standard_normal((1, p.N), dtype=np.float32)), W.BF16, (1, p.N))
@@ -128,6 +138,9 @@ WOQ_CASES = {
     "f16_src": lambda: W.int4_decode(4, 1024, 256, src_dt=W.F16, dst_dt=W.F16),
     "bias_relu": lambda: _with_bias_relu(W.int4_decode(7, 1024, 512)),
     "f32_dst": lambda: W.int4_decode(2, 512, 256, dst_dt=W.F32),
+    "group16_f32_scales_s32_zp": lambda: _wide_params(W.int4_decode(4, 1024, 512, group=16)),
+    "group64_m32": lambda: W.int4_decode(32, 1024, 512, group=64),
+    "group256_m12": lambda: W.int4_decode(12, 2048, 256, group=256),
 }
 
 
