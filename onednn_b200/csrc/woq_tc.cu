@@ -321,6 +321,8 @@ woq_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
             [[maybe_unused]] uint32_t pit = 0;
             const uint32_t base_tx = C::S_BYTES + C::SUMS_BYTES;
             const uint32_t par_tx = p.sc_box_bytes + (p.zp_mode == 1 ? p.zp_box_bytes : 0);
+            // the step sums come from the pre-kernel, of which this kernel is the programmatic dependent
+            asm volatile("griddepcontrol.wait;" ::: "memory");
             bool ok = true;
             for (int64_t L = L0; L < L1 && ok && !*abort_flag;) {
                 const Segment sg = segment_at(L, L1, p.kstages);
@@ -822,6 +824,9 @@ woq_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
 // zero-point / offset correction at k16-step granularity; one thread per (k, m).
 template <int MR, bool F16>
 __global__ void woq_step_sums_kernel(const __grid_constant__ MatmulArgs a, float *sums, int ksteps) {
+    // the main kernel is launched as this one's programmatic dependent: it may start now and set
+    // itself up; the one warp of it that reads these sums waits for this grid first
+    asm volatile("griddepcontrol.launch_dependents;");
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= ksteps * MR) return;
     const int k = i / MR, m = i % MR;
@@ -974,7 +979,24 @@ int wt_launch(encode_tiled_fn enc, WtMaps &tm, const MatmulArgs &a, WtParams &p,
     if (!opt_in_dynamic_smem(kern, 227 * 1024, configured)) return 5;
     const int nsum = p.ksteps * MR;
     woq_step_sums_kernel<MR, F16><<<(nsum + 255) / 256, 256, 0, st>>>(a, const_cast<float *>(p.step_sums), p.ksteps);
-    kern<<<grid, C::THREADS, smem_bytes, st>>>(tm.w, tm.s, tm.sums, tm.sc, tm.zp, a, p);
+    {
+        // programmatic dependent launch: the kernel's set-up (barriers, tensor memory, descriptor
+        // prefetch) and its weight stream overlap the pre-kernel
+        cudaLaunchConfig_t cfg {};
+        cfg.gridDim = dim3((unsigned)grid);
+        cfg.blockDim = dim3((unsigned)C::THREADS);
+        cfg.dynamicSmemBytes = (size_t)smem_bytes;
+        cfg.stream = st;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        if (cudaLaunchKernelEx(&cfg, kern, tm.w, tm.s, tm.sums, tm.sc, tm.zp, a, p) != cudaSuccess) {
+            (void)cudaGetLastError(); // the attribute was refused: an ordinary launch (the waits in the kernels are no-ops then)
+            kern<<<grid, C::THREADS, smem_bytes, st>>>(tm.w, tm.s, tm.sums, tm.sc, tm.zp, a, p);
+        }
+    }
     count_launch(2);
     const cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) {
