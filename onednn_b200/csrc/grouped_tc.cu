@@ -36,8 +36,8 @@
 // persistent CTA per SM: warp 0 streams the raw weight tiles (ring of 8: they
 // come from HBM), the last warp the src rows (ring of 6), warps 2-9 convert
 // (two per lane quarter, alternating stages), warp 1 and the last three warps
-// issue the MMAs (stage by stage, in turn), four warps run the epilogue.  The issuing loops are warp-uniform code with
-// lane-predicated instructions.  Every mbarrier wait is bounded.
+// issue the MMAs (stage by stage, in turn), four warps run the epilogue.  The issuing loops are warp-uniform code whose
+// tcgen05 / TMA instructions sit in a branch taken by one elected thread.  Every mbarrier wait is bounded.
 #include <cuda.h>
 
 #include "device_math.cuh"
@@ -161,12 +161,12 @@ __device__ __forceinline__ void tmem_st_16x128b_x8(uint32_t taddr, const uint32_
             : "memory");
 }
 __device__ __forceinline__ void tmem_st_wait_() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
-// D[tmem] (+)= A[tmem] * B[smem], issued by the lane(s) with `issue` set
-__device__ __forceinline__ void mma_ts_bf16(bool issue, uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t idesc, bool acc) {
+// D[tmem] (+)= A[tmem] * B[smem]; executed by one (elected) thread
+__device__ __forceinline__ void mma_ts_bf16(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t idesc, bool acc) {
     asm volatile(
-            "{\n\t.reg .pred p, q;\n\tsetp.ne.b32 p, %4, 0;\n\tsetp.ne.b32 q, %5, 0;\n\t"
-            "@q tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}" ::"r"(tmem_d),
-            "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"((uint32_t)acc), "r"((uint32_t)issue)
+            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}" ::"r"(tmem_d),
+            "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"((uint32_t)acc)
             : "memory");
 }
 // the dst column (inside its group of 32) that TMEM lane l holds
@@ -249,7 +249,7 @@ grouped_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
 
     if (warp == 0) {
         // ------------------------------------------------ TMA producer of the raw weight tiles
-        // (the whole warp walks the loop, lane 0 issues: the addresses stay warp-uniform values)
+        // (the whole warp walks the loop, one elected thread issues: the addresses stay warp-uniform values)
         const bool issue = lane == 0;
         int s = 0;
         uint32_t ph = 1; // parity of the empty barrier's previous phase: a fresh barrier passes
@@ -298,7 +298,7 @@ grouped_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
         }
         if (!ok && issue) { *abort_flag = 1; atomicExch(a.status, 5); }
     } else if (warp == 1 || warp >= MMA_WARP1) {
-        // ------------------------------------------------ MMA issuers (warp-uniform, lane 0 issues)
+        // ------------------------------------------------ MMA issuers (warp-uniform loops, an elected thread issues)
         // A warp issues an MMA every 40 to 65 cycles (twice that inside this kernel) and pays two waits
         // and two commits per stage, more than the MMAs of a stage take: four warps share the work,
         // stage by stage, waiting for their tiles and committing while another one issues.  The stages enter the pipe in their own order -
@@ -344,7 +344,7 @@ grouped_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
                     if (ptx::elect_one()) { // one elected thread: see elect_one
 #pragma unroll
                         for (int kk = 0; kk < GK / 16; ++kk)
-                            mma_ts_bf16(true, tmem_d, ta + 8 * kk, sd0 + (uint64_t)(kk * (32 >> 4)), idesc, (kb | kk) != 0);
+                            mma_ts_bf16(tmem_d, ta + 8 * kk, sd0 + (uint64_t)(kk * (32 >> 4)), idesc, (kb | kk) != 0);
                         ptx::tc_fence_before_sync();
                         ptx::st_release_shared(stages_issued, it + 1);
                         // the operand slot and the src tile are reusable once these MMAs have read them

@@ -95,35 +95,11 @@ __device__ __forceinline__ void st_release_shared(volatile uint32_t *p, uint32_t
     asm volatile("st.release.cta.shared::cta.u32 [%0], %1;" ::"r"(smem_u32(const_cast<uint32_t *>(p))), "r"(v) : "memory");
 }
 
-// Lane-predicated forms for warp-uniform issuing code.  A role that one thread could play is
-// written as code that the whole warp runs, with only the instruction itself predicated on
-// `issue` (true in one lane): the loop counters, addresses and descriptors around it then stay
-// warp-uniform values, which the compiler keeps in uniform registers, instead of per-thread
-// values that must be moved there before every tcgen05 / TMA instruction.
-__device__ __forceinline__ void mbar_arrive_expect_tx_if(bool issue, uint64_t *bar, uint32_t bytes) {
-    asm volatile("{\n\t.reg .pred q;\n\tsetp.ne.b32 q, %2, 0;\n\t@q mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n\t}"
-                 ::"r"(smem_u32(bar)), "r"(bytes), "r"((uint32_t)issue)
-                 : "memory");
-}
-__device__ __forceinline__ void mbar_arrive_if(bool issue, uint64_t *bar) {
-    asm volatile("{\n\t.reg .pred q;\n\tsetp.ne.b32 q, %1, 0;\n\t@q mbarrier.arrive.shared::cta.b64 _, [%0];\n\t}"
-                 ::"r"(smem_u32(bar)), "r"((uint32_t)issue)
-                 : "memory");
-}
-__device__ __forceinline__ void tma_load_2d_if(bool issue, void *dst, const void *map, uint64_t *bar, int x, int y) {
-    asm volatile(
-            "{\n\t.reg .pred q;\n\tsetp.ne.b32 q, %5, 0;\n\t"
-            "@q cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n\t}"
-            ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"((uint32_t)issue)
-            : "memory");
-}
-__device__ __forceinline__ void tma_load_3d_if(bool issue, void *dst, const void *map, uint64_t *bar, int x, int y, int z) {
-    asm volatile(
-            "{\n\t.reg .pred q;\n\tsetp.ne.b32 q, %6, 0;\n\t"
-            "@q cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];\n\t}"
-            ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"(z), "r"((uint32_t)issue)
-            : "memory");
-}
+// A commit under a lane predicate, for the rarely taken paths of warp-uniform issuing code (whole
+// warps walk the loops, so that loop counters, addresses and descriptors stay warp-uniform values).
+// The hot paths put a stage's tcgen05 / TMA instructions in a branch taken by the thread elect_one()
+// picks instead: an instruction guarded by a predicate computed from the lane index costs nearly twice
+// as much to issue.
 __device__ __forceinline__ void tc_commit_if(bool issue, uint64_t *bar) {
     asm volatile("{\n\t.reg .pred q;\n\tsetp.ne.b32 q, %1, 0;\n\t"
                  "@q tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t}" ::"r"(smem_u32(bar)), "r"((uint32_t)issue)

@@ -284,7 +284,7 @@ woq_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
 
     if (warp == PRODUCER_WARP) {
         // ------------------------------------------------ TMA producer
-        // (the whole warp walks the loop, lane 0 issues: see the lane-predicated forms)
+        // (the whole warp walks the loop, one elected thread issues: see elect_one)
         {
             const bool issue = lane == 0;
             uint32_t it = 0;
@@ -361,7 +361,7 @@ woq_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ C
         // [i * NBLK / MMA_WARPS, (i + 1) * NBLK / MMA_WARPS) of every k16 step; all walk the same barriers
         constexpr int JB = NBLK / C::MMA_WARPS;
         const int j0 = (warp - MMA_WARP0) * JB;
-        // (the whole warp walks the loop, lane 0 issues)
+        // (the whole warp walks the loop, one elected thread issues)
         {
             const bool issue = lane == 0;
             uint32_t it = 0, gc = 0;
