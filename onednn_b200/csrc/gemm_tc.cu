@@ -57,6 +57,7 @@ struct TcParams {
 #ifdef QMM_PROFILE
     int mainloop_only; // 1 no epilogue, 2 TMEM reads only, 3 everything but the stores (wrong results)
 #endif
+    int after_prekernel; // launched as the programmatic dependent of the column / row sum kernel before it
     const int32_t *colsum; // sum_k w[k][n]       (src zero-point compensation)
     const int32_t *rowsum; // sum_k s[m][k]       (weights zero-point compensation)
 };
@@ -378,6 +379,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
         constexpr int ROWS_PER_WARP = BT_M / (epi_warps(CHAIN) / 4);
         const int row_base = ((warp - 2) / 4) * ROWS_PER_WARP; // its share of the tile's rows
         const TensorTerms tt = load_tensor_terms<INT>(a, tp);
+        // the zero-point sums come from the kernel launched before this one, which runs beside this
+        // kernel's set-up and first mainloop: only the epilogue warps wait for it
+        if (tp.after_prekernel) asm volatile("griddepcontrol.wait;" ::: "memory");
         uint32_t acc_it = 0;
         for (int tile = blockIdx.x; tile < num_tiles && !*abort_flag; tile += gridDim.x, ++acc_it) {
             const int as = acc_it % ACC_STAGES;
@@ -483,6 +487,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
 // one 32-bit load and dp4a adds each byte into its own sum.
 template <bool VEC>
 __global__ void __launch_bounds__(256) colsum_kernel(const __grid_constant__ MatmulArgs a, int32_t *colsum, int kchunk) {
+    asm volatile("griddepcontrol.launch_dependents;"); // the GEMM may start; its epilogue warps wait for this grid
     __shared__ int part[8][128];
     const int lane = threadIdx.x & 31, kl = threadIdx.x >> 5;
     const int64_t n0 = (int64_t)blockIdx.x * 128 + lane * 4;
@@ -534,6 +539,7 @@ __global__ void __launch_bounds__(256) colsum_kernel(const __grid_constant__ Mat
 }
 // rowsum[m] = sum_k s[m][k]; one warp per row
 __global__ void rowsum_kernel(const __grid_constant__ MatmulArgs a, int32_t *rowsum) {
+    asm volatile("griddepcontrol.launch_dependents;");
     const int64_t m = (int64_t)blockIdx.x * (blockDim.x / 32) + threadIdx.x / 32;
     if (m >= a.M) return;
     int s = 0;
@@ -582,7 +588,22 @@ int launch_cfg(const CUtensorMap &mw, const CUtensorMap &ms, const MatmulArgs &a
     if (!opt_in_dynamic_smem(kern, L::TOTAL, configured)) return 5;
     const int tiles = tp.num_m_tiles * tp.num_n_tiles;
     const int grid = tiles < sm_count ? tiles : sm_count;
-    kern<<<grid, num_threads(CHAIN), L::TOTAL, st>>>(mw, ms, a, tp);
+    bool launched = false;
+    if (tp.after_prekernel) { // programmatic dependent of the sum kernel launched just before
+        cudaLaunchConfig_t cfg {};
+        cfg.gridDim = dim3((unsigned)grid);
+        cfg.blockDim = dim3((unsigned)num_threads(CHAIN));
+        cfg.dynamicSmemBytes = (size_t)L::TOTAL;
+        cfg.stream = st;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        launched = cudaLaunchKernelEx(&cfg, kern, mw, ms, a, tp) == cudaSuccess;
+        if (!launched) (void)cudaGetLastError(); // the attribute was refused: an ordinary launch below
+    }
+    if (!launched) kern<<<grid, num_threads(CHAIN), L::TOTAL, st>>>(mw, ms, a, tp);
     count_launch();
     return cudaGetLastError() == cudaSuccess ? 0 : 5;
 }
@@ -635,6 +656,7 @@ int launch_gemm_tc(const MatmulArgs &a, void *scratch, int sm_count, cudaStream_
         count_launch();
         tp.rowsum = rowsum;
     }
+    tp.after_prekernel = tp.colsum != nullptr || tp.rowsum != nullptr;
 
     // 256 dst rows per tile unless that leaves SMs without work
     const int64_t tiles256 = (int64_t)tp.num_n_tiles * ((a.M + 255) / 256);
