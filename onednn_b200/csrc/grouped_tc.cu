@@ -108,6 +108,7 @@ __device__ __forceinline__ Tile decode_tile(const int4 *plan, int groups, int nu
 }
 
 __global__ void grouped_plan_kernel(const __grid_constant__ MatmulArgs a, int4 *plan, int num_n_tiles) {
+    asm volatile("griddepcontrol.launch_dependents;"); // the main kernel may set itself up meanwhile; it waits before it reads the plan
     if (threadIdx.x != 0 || blockIdx.x != 0) return;
     if (a.group_count == 0) { // a dense problem: one group that owns every row
         plan[1] = make_int4(0, 0, (int)a.M, 0);
@@ -175,6 +176,7 @@ __device__ __forceinline__ int lane_column(int l) { return 4 * (l & 7) + 2 * (l 
 // Sum over k of every src row (bf16), one warp per row: the factor of a weight zero-point,
 // sum_k s (w - z) = sum_k s w - z sum_k s.
 __global__ void grouped_rowsum_kernel(const __grid_constant__ MatmulArgs a, float *rowsum) {
+    asm volatile("griddepcontrol.launch_dependents;");
     const int64_t m = (int64_t)blockIdx.x * (blockDim.x / 32) + threadIdx.x / 32;
     if (m >= a.M) return;
     const unsigned short *row = (const unsigned short *)a.src + m * a.src_sm;
@@ -237,6 +239,9 @@ grouped_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
     __syncthreads();
     ptx::tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_base_slot;
+    // launched as the programmatic dependent of the planning (or row-sum) kernel: everything above ran
+    // beside it; the plan and the row sums are read from here on
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     const int4 head = __ldg(&plan_global[0]);
     const int num_tiles = head.x, groups = head.y;
     const int4 *plan = plan_global;
@@ -575,7 +580,24 @@ int launch_grouped_tc(const MatmulArgs &a, void *scratch, int sm_count, cudaStre
     auto kern = chain ? grouped_tc_kernel<true> : grouped_tc_kernel<false>;
     static std::atomic<unsigned long long> configured[2];
     if (!opt_in_dynamic_smem(kern, G_SMEM_BYTES, configured[chain])) return 5;
-    kern<<<sm_count > 0 ? sm_count : 148, G_THREADS, G_SMEM_BYTES, st>>>(tw, ts, ts2, ts3, a, plan, rowsum, num_n_tiles, num_k_blocks);
+    {
+        cudaLaunchConfig_t cfg {};
+        cfg.gridDim = dim3((unsigned)(sm_count > 0 ? sm_count : 148));
+        cfg.blockDim = dim3((unsigned)G_THREADS);
+        cfg.dynamicSmemBytes = (size_t)G_SMEM_BYTES;
+        cfg.stream = st;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        const int4 *plan_c = plan;
+        const float *rowsum_c = rowsum;
+        if (cudaLaunchKernelEx(&cfg, kern, tw, ts, ts2, ts3, a, plan_c, rowsum_c, num_n_tiles, num_k_blocks) != cudaSuccess) {
+            (void)cudaGetLastError(); // the attribute was refused: an ordinary launch
+            kern<<<sm_count > 0 ? sm_count : 148, G_THREADS, G_SMEM_BYTES, st>>>(tw, ts, ts2, ts3, a, plan, rowsum, num_n_tiles, num_k_blocks);
+        }
+    }
     count_launch();
     return cudaGetLastError() == cudaSuccess ? 0 : 5;
 }
