@@ -176,7 +176,11 @@ dnnl_status_t dense_attr_check(const dnnl_primitive_desc &pd) {
         if (e.kind == dnnl_sum) {
             // the sum data type must have the size of the dst type
             if (e.sum_dt != dnnl_data_type_undef) UNIMPL_IF(dt_bits(e.sum_dt) != dt_bits(dst_dt));
+            // a sum zero-point belongs to integer problems and an integer sum type
+            // (src/common/primitive_attr.cpp:366-380)
             UNIMPL_IF(e.zero_point != 0 && !src_int8);
+            const auto sum_dt = e.sum_dt != dnnl_data_type_undef ? e.sum_dt : dst_dt;
+            UNIMPL_IF(e.zero_point != 0 && !one_of(sum_dt, {dnnl_s8, dnnl_u8, dnnl_s32}));
         }
         if (e.kind == dnnl_binary) {
             INVALID_IF(e.src1.ndims != pd.dst.ndims);

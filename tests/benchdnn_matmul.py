@@ -1,0 +1,471 @@
+"""Runs matmul problems written in the syntax of oneDNN's benchdnn driver
+(tests/benchdnn/doc/driver_matmul.md, knobs_attr.md in oneDNN) through this
+library and checks each against the CPU oracle.
+
+Input files hold option lines and problem descriptors:
+
+    --reset
+    --dt=u8:s8:s8,s8:s8:f32          # a comma list multiplies the problems
+    --stag=ab --wtag=ab,ba --dtag=ab
+    --bia-dt=undef,f32 --bia_mask=2
+    --attr-scales=src:common:0.25+wei:per_oc+dst:common:4
+    --attr-post-ops=sum+relu+add:f32:per_oc
+    --batch=shapes_file              # a file beside this one
+    10x30:30x20                      # MxK:KxN
+
+Every descriptor line is run once per element of the cartesian product of the
+option lists in force, as benchdnn does (tests/benchdnn/utils/parser.hpp).
+What this library's matmul path covers is run and compared; a problem outside
+it is reported as SKIPPED with the reason (benchdnn's own word for a
+descriptor the library answers `unimplemented` to), never silently dropped.
+
+Handled: --reset, --batch, --dt, --stag/--wtag/--dtag (ab, ba, any), --bia-dt,
+--bia_mask, --runtime_dims_masks (run-time M), --attr-scales,
+--attr-zero-points, --attr-post-ops (sum, eltwise, binary), --attr-fpmath,
+--attr-scratchpad.  Options that select implementations or engines
+(--skip-impl, --impl, --engine, --match ...) are accepted and ignored.  Batched
+(3D+) descriptors, --strides, --grouped, prelu / depthwise post-ops, run-time K
+or N and the remaining attributes are skipped with their name as the reason.
+
+Policy names follow attr_t::policy2mask (tests/benchdnn/dnn_types.cpp:218-268):
+for the matmul's src / weights / dst, `per_oc` and `per_dim_1` are the last
+dim, `per_ocic` the last two; binary post-op operands use the default masks.
+
+    python tests/benchdnn_matmul.py [--all-impls] FILE [FILE ...]      # needs a B200
+"""
+import itertools
+import os
+import re
+import sys
+import zlib
+
+import numpy as np
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+from onednn_b200 import workloads as W  # noqa: E402
+
+DT = {"f16": W.F16, "bf16": W.BF16, "f32": W.F32, "s32": W.S32, "s8": W.S8, "u8": W.U8,
+      "f8_e5m2": W.F8_E5M2, "f8_e4m3": W.F8_E4M3, "s4": W.S4, "u4": W.U4}
+
+DEFAULTS = {"dt": "f32", "stag": "ab", "wtag": "ab", "dtag": "ab", "bia-dt": "undef", "bia_mask": "2",
+            "runtime_dims_masks": "0", "attr-scales": "", "attr-zero-points": "", "attr-post-ops": "",
+            "attr-fpmath": "", "attr-scratchpad": "library", "strides": "", "grouped": "",
+            "attr-precomputed-reductions": "", "attr-dropout": "", "attr-acc-mode": "", "encoding": "",
+            "attr-rounding-mode": "", "attr-deterministic": ""}
+# options about which implementation or engine runs, or how benchdnn reports
+IGNORED = {"skip-impl", "impl", "engine", "match", "allow-enum-tags-only", "check-ref-impl", "cpu-isa-hints",
+           "mode", "max-ms-per-prb", "fix-times-per-prb", "perf-template", "verbose", "v", "mem-check",
+           "cold-cache", "stream-kind", "global-impl", "global-skip-impl", "start", "repeats-per-prb",
+           "summary", "bia_dt"}
+# named here so that a file using them is reported, not mis-run
+UNSUPPORTED = ("strides", "grouped", "attr-precomputed-reductions", "attr-dropout", "attr-acc-mode", "encoding",
+               "attr-rounding-mode", "attr-deterministic")
+
+ELTWISE_ALIAS = {"srelu": "soft_relu"}
+
+
+class Skip(Exception):
+    """The problem is outside what the driver or the library covers."""
+
+
+# ------------------------------------------------------------------- reading
+def _logical_lines(path):
+    with open(path) as f:
+        pending = ""
+        for raw in f:
+            line = raw.split("#", 1)[0].rstrip()
+            if line.endswith("\\"):
+                pending += line[:-1].strip()
+                continue
+            line = (pending + line.strip()) if pending else line.strip()
+            pending = ""
+            if line:
+                yield line
+        if pending:
+            yield pending
+
+
+def expand(path, state=None):
+    """Yields (settings, descriptor) for every problem of an input file, in
+    file order.  `settings` maps option names to ONE value each."""
+    if state is None:
+        state = {"lists": {k: [v] for k, v in DEFAULTS.items()}, "unknown": set()}
+    lists = state["lists"]
+    here = os.path.dirname(os.path.abspath(path))
+    for line in _logical_lines(path):
+        for tok in line.split():
+            if not tok.startswith("--"):
+                keys = list(lists)
+                for combo in itertools.product(*(lists[k] for k in keys)):
+                    s = dict(zip(keys, combo))
+                    s["_unknown"] = sorted(state["unknown"])
+                    yield s, tok
+                continue
+            name, _, val = tok[2:].partition("=")
+            if name == "reset":
+                lists.update({k: [v] for k, v in DEFAULTS.items()})
+                state["unknown"].clear()
+            elif name == "batch":
+                yield from expand(os.path.join(here, val), state)
+            elif name == "matmul" or name in IGNORED:
+                continue
+            elif name not in DEFAULTS:
+                state["unknown"].add(name)
+            else:
+                lists[name] = val.split(",") if val != "" else [DEFAULTS[name] if name in ("dt",) else ""]
+
+
+def command_line(settings, desc):
+    """The benchdnn command line of one expanded problem (for the report)."""
+    parts = ["--matmul"]
+    for k, v in settings.items():
+        if not k.startswith("_") and v != DEFAULTS[k]:
+            parts.append("--%s=%s" % (k, v))
+    return " ".join(parts + [desc])
+
+
+# ------------------------------------------------------------------ building
+def _policy_mask(policy, nd, matmul_arg):
+    if policy in ("common", "host_scalar"):
+        return 0
+    if policy.lstrip("-").isdigit():
+        return int(policy)
+    if matmul_arg and policy in ("per_oc", "per_dim_1"):
+        return 1 << (nd - 1)
+    if matmul_arg and policy == "per_ocic":
+        return 3 << (nd - 2)
+    table = {"per_dim_0": 1, "per_dim_1": 2, "per_oc": 2, "per_dim_01": 3, "per_tensor": (1 << nd) - 1}
+    if policy not in table:
+        raise Skip("policy " + policy)
+    return table[policy]
+
+
+def _is_number(s):
+    try:
+        float(s)
+        return True
+    except ValueError:
+        return False
+
+
+def _quant_entries(text):
+    """'src:common:0.25+wei:per_ocic:bf16:2x1' -> [(arg, policy, value, dt, groups)]."""
+    out = []
+    for entry in filter(None, text.split("+")):
+        f = entry.split(":")
+        arg, policy = f[0], (f[1] if len(f) > 1 else "common")
+        if arg not in ("src", "wei", "dst"):
+            raise Skip("argument " + arg)
+        value, dt, groups = None, None, (1, 1)
+        for t in f[2:]:
+            if t.endswith("*"):
+                t = t[:-1]
+            if _is_number(t):
+                value = float(t)
+            elif t in DT:
+                dt = DT[t]
+            elif re.fullmatch(r"\d+x\d+", t):
+                groups = tuple(int(x) for x in t.split("x"))
+            elif t:
+                raise Skip("quantization field " + t)
+        out.append((arg, policy, value, dt, groups))
+    return out
+
+
+def _param_shape(mask, groups, dims):
+    shape = [d if (mask >> i) & 1 else 1 for i, d in enumerate(dims)]
+    for i, g in zip((-2, -1), groups):
+        if g > 1:
+            if not (mask >> (len(dims) + i)) & 1 or dims[i] % g:
+                raise Skip("groups %dx%d do not divide the tensor" % tuple(groups))
+            shape[i] = dims[i] // g
+    return tuple(shape)
+
+
+def _fill(r, dt, shape, role):
+    """Small values exact in every data type involved, so that products and
+    short sums are exact and implementations differ only by summation order."""
+    if dt == W.U8:
+        v = r.integers(0, 40 if role == "src" else 8, shape)
+    elif dt in (W.S8, W.S32):
+        v = r.integers(-20, 21, shape) if role in ("src", "wei") else r.integers(-8, 9, shape)
+    elif dt == W.S4:
+        v = r.integers(-8, 8, shape)
+    elif dt == W.U4:
+        v = r.integers(0, 16, shape)
+    elif dt in (W.F8_E4M3, W.F8_E5M2):
+        v = r.integers(-4, 5, shape).astype(np.float32)
+    else:
+        v = r.integers(-8, 9, shape).astype(np.float32) * (0.25 if role in ("src", "wei") else 1.0)
+    return W.to_storage(v, dt)
+
+
+def _tensor(r, dt, dims, tag, role):
+    if tag in ("ab", "any", "abx"):
+        return W.QTensor(_fill(r, dt, dims, role), dt, dims)
+    if tag == "ba":
+        if dt in (W.S4, W.U4):
+            if dims[0] % 2:
+                raise Skip("4-bit tensor with an odd leading dim stored transposed")
+            t = _fill(r, dt, (dims[1], dims[0]), role)
+        else:
+            t = _fill(r, dt, (dims[1], dims[0]), role)
+        return W.QTensor(t, dt, dims, (1, dims[0]))
+    raise Skip("tag " + tag)
+
+
+def build(settings, desc, seed=None):
+    """(Problem, run options) of one expanded benchdnn problem, or raises Skip."""
+    if settings.get("_unknown"):
+        raise Skip("option --" + settings["_unknown"][0])
+    for k in UNSUPPORTED:
+        if settings[k] not in ("", DEFAULTS[k]):
+            raise Skip("--" + k)
+    m = re.fullmatch(r'([0-9x:]+)(?:_?n"?([^"]*)"?)?', desc)
+    if m is None:
+        raise Skip("descriptor " + desc)
+    shape, name = m.group(1), m.group(2)
+    parts = shape.split(":")
+    if len(parts) not in (2, 3):
+        raise Skip("descriptor " + desc)
+    try:
+        sdims = [int(x) for x in parts[0].split("x")]
+        wdims = [int(x) for x in parts[1].split("x")]
+    except ValueError:
+        raise Skip("descriptor " + desc)
+    if len(sdims) != 2 or len(wdims) != 2:
+        raise Skip("batched descriptor")
+    (M, K), (K2, N) = sdims, wdims
+    if K != K2:
+        raise Skip("descriptor " + desc)
+    if 0 in (M, K, N):
+        raise Skip("zero dim")
+    r = np.random.Generator(np.random.PCG64(zlib.crc32((command_line(settings, desc)).encode())
+                                            if seed is None else seed))
+
+    dts = settings["dt"].split(":")
+    if len(dts) == 1:
+        dts = dts * 3
+    if len(dts) != 3 or any(d not in DT for d in dts):
+        raise Skip("data types " + settings["dt"])
+    sdt, wdt, ddt = (DT[d] for d in dts)
+    if ddt not in (W.F32, W.S32, W.BF16, W.F16, W.S8, W.U8):
+        raise Skip("dst type " + dts[2])
+    if settings["dtag"] not in ("ab", "any", "abx"):
+        raise Skip("dst tag " + settings["dtag"])
+    if wdt in (W.S4, W.U4) and N % 2 and settings["wtag"] != "ba":
+        raise Skip("4-bit weights with odd N")
+    src = _tensor(r, sdt, (M, K), settings["stag"], "src")
+    wei = _tensor(r, wdt, (K, N), settings["wtag"], "wei")
+
+    bias = None
+    if settings["bia-dt"] != "undef":
+        if settings["bia-dt"] not in DT:
+            raise Skip("bias type " + settings["bia-dt"])
+        bm = int(settings["bia_mask"])
+        if bm < 1 or bm > 3:
+            raise Skip("bias mask %d" % bm)
+        bdims = (M if bm & 1 else 1, N if bm & 2 else 1)
+        bias = W.QTensor(_fill(r, DT[settings["bia-dt"]], bdims, "bias"), DT[settings["bia-dt"]], bdims)
+
+    opts = {"runtime_m": False, "user_scratchpad": settings["attr-scratchpad"] == "user"}
+    rt = settings["runtime_dims_masks"] or "0"
+    rs, _, rw = rt.partition(":")
+    rs, rw = int(rs or 0), int(rw or 0)
+    if rs == 1 and rw == 0:
+        opts["runtime_m"] = True
+    elif rs or rw:
+        raise Skip("run-time K or N")
+
+    dims_of = {"src": (M, K), "wei": (K, N), "dst": (M, N)}
+    quant = {}
+    for arg, policy, value, dt, groups in _quant_entries(settings["attr-scales"]):
+        mask = _policy_mask(policy, 2, True)
+        dt = W.F32 if dt is None else dt
+        shp = _param_shape(mask, groups, dims_of[arg])
+        if mask == 0:
+            vals = np.full(shp, 1.0 if value is None else value, np.float32)
+        else:
+            vals = np.exp2(r.integers(-3, 2, shp)).astype(np.float32)
+        quant[arg + "_scale"] = W.Quant(W.to_storage(vals, dt), dt, mask, groups)
+    for arg, policy, value, dt, groups in _quant_entries(settings["attr-zero-points"]):
+        mask = _policy_mask(policy, 2, True)
+        dt = W.S32 if dt is None else dt
+        shp = _param_shape(mask, groups, dims_of[arg])
+        if mask == 0:
+            vals = np.full(shp, 0 if value is None else int(value), np.int64)
+        else:
+            lo, hi = (0, 6) if dt in (W.U8, W.U4) else (-3, 4)
+            vals = r.integers(lo, hi, shp)
+        quant[arg + "_zp"] = W.Quant(W.to_storage(vals, dt), dt, mask, groups)
+
+    post_ops, dst_init = [], None
+    for entry in filter(None, settings["attr-post-ops"].split("+")):
+        f = entry.split(":")
+        kind = ELTWISE_ALIAS.get(f[0], f[0])
+        if kind == "sum":
+            scale = float(f[1]) if len(f) > 1 and f[1] else 1.0
+            zp = int(f[2]) if len(f) > 2 and f[2] else 0
+            if len(f) > 3 and f[3] and DT.get(f[3]) != ddt:
+                raise Skip("sum with a data type other than dst's")
+            post_ops.append(W.PostOp(W.PO_SUM, scale=scale, zero_point=zp))
+            dst_init = _fill(r, ddt, (M, N), "dst")
+        elif kind in W.ELTWISE:
+            alpha = float(f[1]) if len(f) > 1 and f[1] else 0.0
+            beta = float(f[2]) if len(f) > 2 and f[2] else 0.0
+            if len(f) > 3 and f[3] and float(f[3]) != 1.0:
+                raise Skip("eltwise with a scale")
+            post_ops.append(W.PostOp(W.PO_ELTWISE, W.ELTWISE[kind], alpha, beta, 1.0))
+        elif kind in W.BINARY:
+            if len(f) < 2 or f[1] not in DT:
+                raise Skip("binary post-op " + entry)
+            if len(f) > 3 and f[3] not in ("", "ab", "any", "abx"):
+                raise Skip("binary post-op tag " + f[3])
+            mask = _policy_mask(f[2] if len(f) > 2 and f[2] else "common", 2, False)
+            bdims = (M if mask & 1 else 1, N if mask & 2 else 1)
+            vals = _fill(r, DT[f[1]], bdims, "binary")
+            if kind == "div":  # no zero divisors
+                z = W.to_f32(vals, DT[f[1]]) == 0
+                vals = W.to_storage(np.where(z, 2.0, W.to_f32(vals, DT[f[1]])), DT[f[1]])
+            post_ops.append(W.PostOp(W.PO_BINARY, W.BINARY[kind], src1=W.QTensor(vals, DT[f[1]], bdims)))
+        else:
+            raise Skip("post-op " + f[0])
+
+    fpmath, apply_to_int = 0, False
+    if settings["attr-fpmath"]:
+        mode, _, flag = settings["attr-fpmath"].partition(":")
+        modes = {"strict": 0, "bf16": 1, "f16": 2, "any": 3, "tf32": 4}
+        if mode not in modes:
+            raise Skip("fpmath " + mode)
+        fpmath, apply_to_int = modes[mode], flag == "true"
+
+    p = W.Problem(name or desc, M, N, K, src, wei, ddt, bias, quant, post_ops, apply_to_int, fpmath)
+    p.dst_init = dst_init
+    return p, opts
+
+
+# ------------------------------------------------------------------ checking
+# eltwise algorithms of the form x * (1 + f(x)) / 2: for negative x the sum 1 + f(x) cancels
+CANCELLING = {W.ELTWISE["gelu_erf"]: 1.0, W.ELTWISE["gelu_tanh"]: 1.0}
+
+
+def cancellation_slack(p):
+    """Absolute allowance for a chain holding gelu_erf / gelu_tanh, or None.
+
+    0.5 x (1 + f(x)) is evaluated in f32 by the reference and by the device
+    alike, but erff / tanhf of two math libraries differ by a few units in the
+    last place of f(x) ~ -1, and the sum 1 + f(x) turns that into an error of
+    those few units of 2^-24 times |x| / 2 however small the result is
+    (benchdnn's own eltwise check judges these algorithms by absolute error for
+    the same reason, tests/benchdnn/eltwise/eltwise.cpp).  The allowance is four
+    units: 4 * 2^-24 * |x|, carried through the factors the rest of the chain
+    multiplies by.  x comes from the oracle run on the chain cut before f."""
+    from oracle import oracle as O
+    idx = next((i for i, po in enumerate(p.post_ops) if po.kind == W.PO_ELTWISE and po.alg in CANCELLING), None)
+    if idx is None:
+        return None
+    quant = {k: v for k, v in p.quant.items() if k not in ("dst_scale", "dst_zp")}
+    q = W.Problem(p.name + "/pre", p.M, p.N, p.K, p.src, p.wei, W.F32, p.bias, quant, p.post_ops[:idx],
+                  p.apply_to_int, p.fpmath)
+    if p.dst_init is not None:
+        init = p.dst_init if p.dst_dt in (W.S4, W.U4) else p.dst_init.reshape(p.M, p.N)
+        q.dst_init = np.ascontiguousarray(W.to_f32(init, p.dst_dt), dtype=np.float32)
+    x = np.abs(O.run_port(q).astype(np.float64))
+    amp = np.ones((p.M, p.N))
+    for po in p.post_ops[idx + 1:]:
+        if po.kind == W.PO_BINARY and po.alg in (W.BINARY["mul"], W.BINARY["div"]):
+            v = np.abs(W.to_f32(po.src1.data, po.src1.dt).astype(np.float64)).reshape(po.src1.dims)
+            amp = amp * v if po.alg == W.BINARY["mul"] else amp / v
+        elif po.kind == W.PO_ELTWISE and po.alg == W.ELTWISE["linear"]:
+            amp = amp * abs(po.alpha)
+    ds = p.quant.get("dst_scale")
+    if ds is not None:
+        amp = amp / np.abs(W.to_f32(ds.data, ds.dt).astype(np.float64)).reshape(-1)[0]
+    return 4.0 * 2.0 ** -24 * x * amp
+
+
+# ------------------------------------------------------------------- running
+def run_one(settings, desc, eng, strm, all_impls=False):
+    """('PASSED' | 'SKIPPED' | 'FAILED', detail).  With all_impls, every
+    implementation that accepts the problem is run, not only the first."""
+    from onednn_b200 import api
+    from onednn_b200.runner import Prepared
+    from oracle import oracle as O
+    from oracle.parity import compare, summation_slack
+    try:
+        p, opts = build(settings, desc)
+    except Skip as e:
+        return "SKIPPED", str(e)
+    try:
+        first = Prepared(p, eng, None, opts["user_scratchpad"], opts["runtime_m"])
+    except api.error as e:
+        if e.status == api.unimplemented:
+            return "SKIPPED", "unimplemented"
+        return "FAILED", "create: %s" % e
+    want = O.run_port(p)
+    libm_slack = cancellation_slack(p)
+    impls = [first.impl]
+    if all_impls:
+        while first.pd.next_impl():
+            impls.append(first.pd.impl_info_str())
+    for impl in impls:
+        run = Prepared(p, eng, impl, opts["user_scratchpad"], opts["runtime_m"]).upload()
+        run.execute(strm)
+        strm.wait()
+        slack = libm_slack
+        if not impl.startswith("cuda:ref") and p.src.dt not in (W.S8, W.U8):
+            slack = summation_slack(p) + (0.0 if libm_slack is None else libm_slack)
+        ok, why = compare(run.download(), want, p.dst_dt, slack)
+        if not ok:
+            return "FAILED", "%s: %s" % (impl, why)
+    return "PASSED", ",".join(impls)
+
+
+def run_file(path, eng, strm, all_impls=False, out=None, limit=None):
+    """Runs every problem of an input file.  Returns a dict: the counts by
+    status, the skip reasons, the implementations that passed (with counts)
+    and the failures.  `out` receives one benchdnn-style line a problem."""
+    rep = {"PASSED": 0, "SKIPPED": 0, "FAILED": 0, "reasons": {}, "impls": {}, "failures": []}
+    for i, (settings, desc) in enumerate(expand(path)):
+        if limit is not None and i >= limit:
+            break
+        status, detail = run_one(settings, desc, eng, strm, all_impls)
+        rep[status] += 1
+        line = command_line(settings, desc)
+        if status == "SKIPPED":
+            rep["reasons"][detail] = rep["reasons"].get(detail, 0) + 1
+        elif status == "PASSED":
+            for impl in detail.split(","):
+                rep["impls"][impl] = rep["impls"].get(impl, 0) + 1
+        else:
+            rep["failures"].append((line, detail))
+        if out is not None:
+            out.write("%d:%s (%s) __REPRO: %s\n" % (i, status, detail, line))
+    return rep
+
+
+def main(argv):
+    from onednn_b200 import api
+    all_impls = "--all-impls" in argv
+    files = [a for a in argv if not a.startswith("--")]
+    if not files:
+        print(__doc__)
+        return 2
+    eng = api.engine(api.engine.kind.gpu, 0)
+    strm = api.stream(eng)
+    total = {"PASSED": 0, "SKIPPED": 0, "FAILED": 0}
+    for path in files:
+        rep = run_file(path, eng, strm, all_impls, sys.stdout)
+        for k in total:
+            total[k] += rep[k]
+        for why, n in sorted(rep["reasons"].items(), key=lambda kv: -kv[1]):
+            print("  skipped %5d: %s" % (n, why))
+        for impl, n in sorted(rep["impls"].items(), key=lambda kv: -kv[1]):
+            print("  passed  %5d: %s" % (n, impl))
+    print("tests:%d passed:%d skipped:%d failed:%d" % (sum(total.values()), total["PASSED"], total["SKIPPED"],
+                                                        total["FAILED"]))
+    return 1 if total["FAILED"] else 0
+
+
+if __name__ == "__main__":
+    sys.exit(main(sys.argv[1:]))

@@ -1,0 +1,136 @@
+"""Matmul problems written in benchdnn's input syntax (tests/benchdnn_matmul.py).
+
+On the CPU: the expansion rules; the C restatement against the live reference
+on this repository's input file and, where the reference checkout is present,
+on the reference's own matmul input files (every 2D problem the driver can
+express), together with the accept / reject decision of this library's
+primitive-descriptor creation.  On the GPU: every problem of this repository's
+input file through every implementation that accepts it."""
+import os
+
+import numpy as np
+import pytest
+
+import benchdnn_matmul as B
+from onednn_b200 import workloads as W
+from oracle import oracle as O
+from oracle.refdir import reference_dir
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+OWN = os.path.join(HERE, "benchdnn_inputs", "matmul_quantized")
+
+
+def test_expansion_multiplies_comma_lists_and_follows_batch_files(tmp_path):
+    (tmp_path / "shapes").write_text("# two shapes\n4x8:8x16\n2x3:3x5_n\"named\"\n")
+    (tmp_path / "main").write_text(
+        "--reset\n--dt=u8:s8:s32,s8:s8:f32 --wtag=ab,ba\n"
+        "--attr-zero-points=src:common:1+wei:common:-1, \\\n"
+        "                   src:per_dim_1\n"
+        "--batch=shapes\n"
+        "--reset --skip-impl=ref\n"
+        "--attr-post-ops=sum+relu\n"
+        "6x4:4x2\n")
+    got = list(B.expand(str(tmp_path / "main")))
+    assert len(got) == 2 * 2 * 2 * 2 + 1
+    first, desc = got[0]
+    assert desc == "4x8:8x16" and first["dt"] == "u8:s8:s32" and first["wtag"] == "ab"
+    assert first["attr-zero-points"] == "src:common:1+wei:common:-1"
+    assert {s["attr-zero-points"] for s, _ in got[:-1]} == {"src:common:1+wei:common:-1", "src:per_dim_1"}
+    last, desc = got[-1]
+    assert desc == "6x4:4x2" and last["dt"] == "f32" and last["attr-zero-points"] == ""
+    assert last["attr-post-ops"] == "sum+relu"
+    assert B.command_line(last, desc) == "--matmul --attr-post-ops=sum+relu 6x4:4x2"
+    assert got[8][1] == '2x3:3x5_n"named"'  # the product is walked per descriptor
+    p, _ = B.build(got[8][0], got[8][1])
+    assert (p.M, p.K, p.N, p.name) == (2, 3, 5, "named")
+
+
+def test_policy_names_give_the_masks_benchdnn_gives_a_matmul():
+    s = dict(B.DEFAULTS, _unknown=[])
+    s.update({"dt": "bf16:s4:bf16", "attr-fpmath": "bf16:true",
+              "attr-scales": "wei:per_ocic:f16:32x1", "attr-zero-points": "wei:per_oc:u8",
+              "attr-post-ops": "add:f32:per_oc+mul:s8:per_dim_0+sub:f32:per_tensor+max:f32"})
+    p, _ = B.build(s, "4x64:64x32")
+    assert p.quant["wei_scale"].mask == 3 and p.quant["wei_scale"].groups == (32, 1)
+    assert p.quant["wei_scale"].data.shape == (2, 32) and p.quant["wei_scale"].dt == W.F16
+    assert p.quant["wei_zp"].mask == 2 and p.quant["wei_zp"].data.shape == (1, 32)
+    assert [po.src1.dims for po in p.post_ops] == [(1, 32), (4, 1), (4, 32), (1, 1)]
+    assert p.apply_to_int and p.fpmath == 1
+    s.update({"dt": "u8:s8:s8", "attr-fpmath": "", "attr-scales": "src:per_dim_0+dst:common:4",
+              "attr-zero-points": "src:per_dim_1+dst:per_dim_1", "attr-post-ops": "", "runtime_dims_masks": "1:0"})
+    p, opts = B.build(s, "4x64:64x32")
+    assert p.quant["src_scale"].mask == 1 and p.quant["src_zp"].mask == 2 and p.quant["dst_zp"].mask == 2
+    assert float(p.quant["dst_scale"].data[0, 0]) == 4.0 and opts["runtime_m"]
+    for bad in ({"runtime_dims_masks": "3:1"}, {"strides": "8x1::"}, {"attr-post-ops": "prelu:per_oc"},
+                {"dt": "f64"}, {"dtag": "ba"}):
+        with pytest.raises(B.Skip):
+            B.build(dict(s, **bad), "4x64:64x32")
+    with pytest.raises(B.Skip):
+        B.build(s, "3x4x64:3x64x32")
+
+
+def _pin(path, host_engine, max_macs, known_stricter=()):
+    """Every buildable problem of the file: restatement == live reference bit
+    for bit, and this library creates a primitive descriptor exactly where
+    the reference does (apart from `known_stricter` scale strings)."""
+    from onednn_b200 import api
+    from onednn_b200.runner import Prepared
+    ran = rejected = 0
+    for settings, desc in B.expand(path):
+        try:
+            p, opts = B.build(settings, desc)
+        except B.Skip:
+            continue
+        if p.M * p.N * p.K > max_macs:
+            continue
+        line = B.command_line(settings, desc)
+        try:
+            want, impl, _ = O.run_ref(p, pin_ref=True)
+        except RuntimeError:
+            want = None
+        try:
+            Prepared(p, host_engine, None, opts["user_scratchpad"], opts["runtime_m"])
+            mine = True
+        except api.error as e:
+            assert e.status == api.unimplemented, line
+            mine = False
+        if settings["attr-scales"] in known_stricter:
+            assert not mine, line
+            continue
+        assert mine == (want is not None), "accepted by %s only: %s" % ("this library" if mine else "the reference", line)
+        if want is None:
+            rejected += 1
+            continue
+        got = O.run_port(p)
+        assert np.array_equal(got.view(np.uint8), want.view(np.uint8)), line
+        ran += 1
+    return ran, rejected
+
+
+def test_own_input_file_restatement_matches_the_live_reference(host_engine):
+    if not O.ref_available():
+        pytest.skip("reference library not built")
+    ran, rejected = _pin(OWN, host_engine, 300000, known_stricter=("dst:per_oc",))
+    assert ran > 2000 and rejected > 0  # a sum zero-point with a float dst is refused by both
+
+
+@pytest.mark.parametrize("name,max_macs,least", [("test_matmul_all", 2000000, 9000), ("test_matmul_ci", 300000, 100)])
+def test_reference_input_files_restatement_matches_the_live_reference(host_engine, name, max_macs, least):
+    ref = reference_dir()
+    if ref is None or not O.ref_available():
+        pytest.skip("reference checkout or library not present")
+    path = os.path.join(ref, "tests", "benchdnn", "inputs", "matmul", name)
+    ran, _ = _pin(path, host_engine, max_macs)
+    assert ran >= least
+
+
+@pytest.mark.gpu
+def test_own_input_file_through_every_implementation(gpu):
+    eng, strm = gpu
+    rep = B.run_file(OWN, eng, strm, all_impls=True)
+    assert not rep["failures"], rep["failures"][:5]
+    assert set(rep["reasons"]) <= {"unimplemented"}, rep["reasons"]
+    assert rep["PASSED"] > 3000 and rep["SKIPPED"] < rep["PASSED"] // 4, rep
+    for impl in ("cuda:tcgen05:int8", "cuda:tcgen05:fp8", "cuda:tcgen05:woq4", "cuda:woq:skinny", "cuda:tcgen05:woq8",
+                 "cuda:ref_int8:any", "cuda:ref:any"):
+        assert rep["impls"].get(impl, 0) >= 20, (impl, rep["impls"])
