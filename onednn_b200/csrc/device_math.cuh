@@ -163,10 +163,11 @@ __device__ __forceinline__ float gelu_tanh_f(float s) {
 // a few millionths of an s8 step for values inside the s8 range: the rounded integer differs from
 // the reference's (by one) only where the reference value lies that close to a rounding boundary.
 __device__ __forceinline__ float gelu_tanh_coarse(float s) {
-    const float c0 = 0.79788458347320556640625f, c1 = 0.044715f;
-    const float t = __fmul_rn(__fmul_rn(c0, s), __fadd_rn(1.f, __fmul_rn(__fmul_rn(c1, s), s)));
+    // 2 t log2(e) = s (k1 + k3 s^2): k1 = 2 log2(e) sqrt(2 / pi), k3 = 0.044715 k1
+    const float k1 = 2.30220826355710f, k3 = 0.10294324250496f;
+    const float t2 = s * fmaf(k3, s * s, k1);
     float e, r;
-    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(t * 2.88539008177792681472f)); // exp(2t)
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(t2)); // exp(2t)
     asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(e + 1.f));
     return fmaf(-s, r, s);
 }

@@ -46,8 +46,15 @@ constexpr int BT_N = 128; // dst columns per tile = TMEM lanes = UMMA M
 constexpr int BKB = 128; // bytes (= 8-bit elements) of K per stage: one swizzle row
 constexpr int UMMA_K = 32; // K per tcgen05.mma for 8-bit operands
 // Epilogue warps: 8 keep up with the MMAs when the epilogue is scale + bias + store; a post-op chain
-// is latency-bound per element, and 16 warps (at 96 registers) hide a third more of it.
-constexpr int epi_warps(bool chain) { return chain ? 16 : 8; }
+// is latency-bound per element: 16 warps (at 96 registers) hide a third more of it than 8, and 24
+// (at 72 registers) another 6 % (int8 post-op workload: 12 warps 150 us, 16: 133, 20: 132, 24: 124-127).
+#ifndef QMM_CHAIN_EPI_WARPS
+#define QMM_CHAIN_EPI_WARPS 24
+#endif
+#ifndef QMM_CHAIN_CR
+#define QMM_CHAIN_CR 8
+#endif
+constexpr int epi_warps(bool chain) { return chain ? QMM_CHAIN_EPI_WARPS : 8; }
 constexpr int num_threads(bool chain) { return 64 + 32 * epi_warps(chain); }
 
 struct TcParams {
@@ -55,7 +62,7 @@ struct TcParams {
     uint32_t idesc;
     int w_kmajor; // weights are `ba` (K contiguous)
 #ifdef QMM_PROFILE
-    int mainloop_only; // 1 no epilogue, 2 TMEM reads only, 3 everything but the stores (wrong results)
+    int mainloop_only; // 1 no epilogue, 2 TMEM reads only, 3 everything but the stores, 4 binary operands read from one address (wrong results)
 #endif
     int after_prekernel; // launched as the programmatic dependent of the column / row sum kernel before it
     const int32_t *colsum; // sum_k w[k][n]       (src zero-point compensation)
@@ -376,8 +383,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
     } else {
         // ------------------------------------------------ epilogue warps
         const int lane_base = (warp % 4) * 32; // TMEM lanes (dst columns) of this warp
-        constexpr int ROWS_PER_WARP = BT_M / (epi_warps(CHAIN) / 4);
-        const int row_base = ((warp - 2) / 4) * ROWS_PER_WARP; // its share of the tile's rows
+        constexpr int GROUPS = epi_warps(CHAIN) / 4; // warps that share a quarter of the lanes
+        constexpr int ROWS_PER_WARP = BT_M / (CHAIN ? 1 : GROUPS);
+        const int group = (warp - 2) / 4;
+        // without a chain each warp takes a contiguous share of the tile's rows; with one, the warps
+        // of a lane quarter take the tile's 8-row pieces in turn (any number of warps divides them)
+        const int row_base = CHAIN ? 0 : group * ROWS_PER_WARP;
         const TensorTerms tt = load_tensor_terms<INT>(a, tp);
         // the zero-point sums come from the kernel launched before this one, which runs beside this
         // kernel's set-up and first mainloop: only the epilogue warps wait for it
@@ -399,9 +410,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
                     const int esz = (e.src1_dt == DT_F32 || e.src1_dt == DT_S32) ? 4 : (e.src1_dt == DT_BF16 || e.src1_dt == DT_F16) ? 2 : 1;
                     const int64_t nq = (int64_t)(tile / tp.num_m_tiles) * BT_N + lane_base;
                     if (nq >= a.N) continue;
-                    for (int r = lane; r < ROWS_PER_WARP; r += 32)
-                        if (m_tile + r < a.M)
-                            asm volatile("prefetch.global.L2 [%0];" ::"l"((const char *)e.src1 + ((m_tile + r) * e.sm + nq) * esz));
+                    constexpr int CRP = QMM_CHAIN_CR, PIECES_P = BT_M / CRP;
+                    for (int idx = lane; idx < (PIECES_P + GROUPS - 1) / GROUPS * CRP; idx += 32) {
+                        const int piece = group + GROUPS * (idx / CRP);
+                        const int64_t m = m_tile + piece * CRP + idx % CRP;
+                        if (piece < PIECES_P && m < a.M)
+                            asm volatile("prefetch.global.L2 [%0];" ::"l"((const char *)e.src1 + (m * e.sm + nq) * esz));
+                    }
                 }
             }
             if (!ptx::mbar_wait(&tmem_full[as], aph)) { *abort_flag = 1; atomicExch(a.status, 5); break; }
@@ -417,18 +432,19 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
             if constexpr (CHAIN) {
                 // With a post-op chain the code of 32 unrolled rows exceeds the instruction cache, so the
                 // rows go through a rolled loop of 8-row pieces (8 independent dependency chains each).
-                constexpr int CR = 8; // rows per piece: 4 leave too few independent chains (152 us on the int8 post-op workload), 16 overflow the instruction cache (175 us), 8: 134 us
+                constexpr int CR = QMM_CHAIN_CR; // rows per piece: 4 leave too few independent chains (152 us on the int8 post-op workload), 16 overflow the instruction cache (175 us), 8: 134 us
+                constexpr int PIECES = BT_M / CR;
 #pragma unroll 1
-                for (int c = 0; c < ROWS_PER_WARP / CR; ++c) {
+                for (int c = group; c < PIECES; c += GROUPS) {
                     uint32_t r[CR];
-                    ptx::tmem_ld_32x8(tmem_base + ((uint32_t)lane_base << 16) + as * BT_M + row_base + c * CR, r);
+                    ptx::tmem_ld_32xn(tmem_base + ((uint32_t)lane_base << 16) + as * BT_M + c * CR, r);
+                    const int64_t m0 = m_tile + c * CR;
                     ptx::tmem_ld_wait();
-                    if (c == ROWS_PER_WARP / CR - 1) { // accumulator fully read: hand the buffer back
+                    if (c + GROUPS >= PIECES) { // accumulator fully read: hand the buffer back
                         ptx::tc_fence_before_sync();
                         __syncwarp();
                         if (lane == 0) ptx::mbar_arrive(&tmem_empty[as]);
                     }
-                    const int64_t m0 = m_tile + c * CR;
 #ifdef QMM_PROFILE
                     if (tp.mainloop_only == 2) continue; // TMEM reads only
 #endif
@@ -618,7 +634,14 @@ bool gemm_tc_pointers_ok(const MatmulArgs &a) {
 
 // `scratch`: gemm_tc_scratch_bytes(M, N) bytes of device memory, needed only
 // when zero-points are present.
-int launch_gemm_tc(const MatmulArgs &a, void *scratch, int sm_count, cudaStream_t st) {
+int launch_gemm_tc(const MatmulArgs &a_in, void *scratch, int sm_count, cudaStream_t st) {
+#ifdef QMM_PROFILE
+    MatmulArgs a = a_in;
+    if (getenv("ONEDNN_CUDA_TC_MAINLOOP_ONLY") && atoi(getenv("ONEDNN_CUDA_TC_MAINLOOP_ONLY")) == 4)
+        for (int i = 0; i < a.n_po; ++i) a.po[i].sm = a.po[i].sn = 0;
+#else
+    const MatmulArgs &a = a_in;
+#endif
     if (a.M == 0 || a.N == 0) return 0;
     if (a.K == 0) return 3;
     const bool int_path = a.src_dt == DT_S8 || a.src_dt == DT_U8;
