@@ -23,9 +23,12 @@ Handled: --reset, --batch, --dt, --stag/--wtag/--dtag (ab, ba, any), --bia-dt,
 --bia_mask, --runtime_dims_masks (run-time M), --attr-scales,
 --attr-zero-points, --attr-post-ops (sum, eltwise, binary), --attr-fpmath,
 --attr-scratchpad.  Options that select implementations or engines
-(--skip-impl, --impl, --engine, --match ...) are accepted and ignored.  Batched
-(3D+) descriptors, --strides, --grouped, prelu / depthwise post-ops, run-time K
-or N and the remaining attributes are skipped with their name as the reason.
+(--skip-impl, --impl, --engine, --match ...) are accepted and ignored.
+Descriptors with batch dims (3D and more, size-1 dims broadcast, tags that
+permute the dims such as acb or bac) run as one batched primitive and are checked
+matrix by matrix against the oracle's 2D result.  --strides, --grouped, prelu /
+depthwise post-ops, run-time K or N and the remaining attributes are skipped with
+their name as the reason.
 
 Policy names follow attr_t::policy2mask (tests/benchdnn/dnn_types.cpp:218-268):
 for the matmul's src / weights / dst, `per_oc` and `per_dim_1` are the last
@@ -134,7 +137,10 @@ def _policy_mask(policy, nd, matmul_arg):
         return 1 << (nd - 1)
     if matmul_arg and policy == "per_ocic":
         return 3 << (nd - 2)
-    table = {"per_dim_0": 1, "per_dim_1": 2, "per_oc": 2, "per_dim_01": 3, "per_tensor": (1 << nd) - 1}
+    table = {"per_dim_0": 1, "per_dim_1": 2, "per_oc": 2, "per_dim_01": 3, "per_dim_2": 4, "per_dim_3": 8,
+             "per_tensor": (1 << nd) - 1}
+    if policy in table and table[policy] >= (1 << nd):
+        raise Skip("policy %s for %d dims" % (policy, nd))
     if policy not in table:
         raise Skip("policy " + policy)
     return table[policy]
@@ -344,6 +350,248 @@ def build(settings, desc, seed=None):
     return p, opts
 
 
+# ------------------------------------------------------------------- batched
+class Batched:
+    """A descriptor with batch dims: the tensors as the library gets them (storage
+    arrays with dims and strides) and, for the oracle, one 2D Problem per matrix
+    of the dst batch (size-1 batch dims of src / weights / bias / binary operands
+    broadcast, src/common/matmul.cpp:630-744)."""
+
+    def __init__(self):
+        self.mats = []  # (batch index tuple, W.Problem)
+        self.tensors = {}  # name -> (storage, dt, dims, strides)
+        self.quant = {}  # name -> (W.Quant with the nd mask)
+        self.post_ops = []  # W.PostOp; binary src1 dims are nd
+        self.fpmath, self.apply_to_int = 0, False
+        self.user_scratchpad = False
+
+
+def _tag_order(tag, nd):
+    """Physical order of the dims, outermost first: 'acb' -> (0, 2, 1)."""
+    if tag in ("any", "abx"):
+        return tuple(range(nd))
+    if len(tag) != nd or sorted(tag) != [chr(ord("a") + i) for i in range(nd)]:
+        raise Skip("tag %s for %d dims" % (tag, nd))
+    return tuple(ord(c) - ord("a") for c in tag)
+
+
+def _layout(logical, order):
+    """(storage, strides in elements) of a logical array stored in `order`."""
+    phys = np.ascontiguousarray(logical.transpose(order))
+    strides = [0] * logical.ndim
+    acc = 1
+    for d in reversed(order):
+        strides[d] = acc
+        acc *= logical.shape[d]
+    return phys.reshape(-1), tuple(strides)
+
+
+def build_batched(settings, desc):
+    """Batched of one expanded problem whose descriptor has batch dims, or raises Skip."""
+    if settings.get("_unknown"):
+        raise Skip("option --" + settings["_unknown"][0])
+    for k in UNSUPPORTED:
+        if settings[k] not in ("", DEFAULTS[k]):
+            raise Skip("--" + k)
+    m = re.fullmatch(r'([0-9x:]+)(?:_?n"?([^"]*)"?)?', desc)
+    parts = m.group(1).split(":") if m else []
+    if len(parts) not in (2, 3):
+        raise Skip("descriptor " + desc)
+    sdims = tuple(int(x) for x in parts[0].split("x"))
+    wdims = tuple(int(x) for x in parts[1].split("x"))
+    nd = len(sdims)
+    if nd < 3 or len(wdims) != nd or nd > 6 or sdims[-1] != wdims[-2]:
+        raise Skip("descriptor " + desc)
+    nb = nd - 2
+    for a, b in zip(sdims[:nb], wdims[:nb]):
+        if a != b and 1 not in (a, b):
+            raise Skip("descriptor " + desc)
+    bdims = tuple(max(a, b) for a, b in zip(sdims[:nb], wdims[:nb]))
+    M, K, N = sdims[-2], sdims[-1], wdims[-1]
+    ddims = bdims + (M, N)
+    if 0 in ddims or K == 0:
+        raise Skip("zero dim")
+    if (settings["runtime_dims_masks"] or "0") not in ("0", "0:0"):
+        raise Skip("run-time dims of a batched problem")
+    r = np.random.Generator(np.random.PCG64(zlib.crc32(command_line(settings, desc).encode())))
+    dts = settings["dt"].split(":")
+    dts = dts * 3 if len(dts) == 1 else dts
+    if len(dts) != 3 or any(d not in DT for d in dts):
+        raise Skip("data types " + settings["dt"])
+    sdt, wdt, ddt = (DT[d] for d in dts)
+    if W.S4 in (sdt, wdt, ddt) or W.U4 in (sdt, wdt, ddt):
+        raise Skip("4-bit types in a batched problem")
+    if ddt not in (W.F32, W.S32, W.BF16, W.F16, W.S8, W.U8):
+        raise Skip("dst type " + dts[2])
+    bp = Batched()
+    bp.ddt, bp.ddims = ddt, ddims
+    bp.user_scratchpad = settings["attr-scratchpad"] == "user"
+    src_l = _fill(r, sdt, sdims, "src")
+    wei_l = _fill(r, wdt, wdims, "wei")
+    bp.tensors["src"] = (*_layout(src_l, _tag_order(settings["stag"], nd)), sdt, sdims)
+    bp.tensors["wei"] = (*_layout(wei_l, _tag_order(settings["wtag"], nd)), wdt, wdims)
+    bp.dst_order = _tag_order(settings["dtag"], nd)
+    bias_l = None
+    if settings["bia-dt"] != "undef":
+        if settings["bia-dt"] not in DT:
+            raise Skip("bias type " + settings["bia-dt"])
+        bm = int(settings["bia_mask"])
+        if bm < 1 or bm >= (1 << nd):
+            raise Skip("bias mask %d" % bm)
+        bia_dims = tuple(d if (bm >> i) & 1 else 1 for i, d in enumerate(ddims))
+        bias_l = _fill(r, DT[settings["bia-dt"]], bia_dims, "bias")
+        bp.tensors["bias"] = (*_layout(bias_l, tuple(range(nd))), DT[settings["bia-dt"]], bia_dims)
+
+    dims_of = {"src": (M, K), "wei": (K, N), "dst": (M, N)}
+    quant2d = {}
+    for text, suffix, default_dt in ((settings["attr-scales"], "_scale", W.F32), (settings["attr-zero-points"], "_zp", W.S32)):
+        for arg, policy, value, dt, groups in _quant_entries(text):
+            mask = _policy_mask(policy, nd, True)
+            if mask & ((1 << nb) - 1):
+                raise Skip("a quantization parameter that varies along the batch")
+            dt = default_dt if dt is None else dt
+            shp = _param_shape(mask >> nb, groups, dims_of[arg])
+            if suffix == "_scale":
+                vals = np.full(shp, 1.0 if value is None else value, np.float32) if mask == 0 \
+                    else np.exp2(r.integers(-3, 2, shp)).astype(np.float32)
+            elif mask == 0:
+                vals = np.full(shp, 0 if value is None else int(value), np.int64)
+            else:
+                vals = r.integers(*((0, 6) if dt in (W.U8, W.U4) else (-3, 4)), shp)
+            data = W.to_storage(vals, dt)
+            quant2d[arg + suffix] = W.Quant(data, dt, mask >> nb, groups)
+            bp.quant[arg + suffix] = W.Quant(data, dt, mask, groups)
+
+    dst_init_l = None
+    binaries = {}
+    for i, entry in enumerate(filter(None, settings["attr-post-ops"].split("+"))):
+        f = entry.split(":")
+        kind = ELTWISE_ALIAS.get(f[0], f[0])
+        if kind == "sum":
+            if len(f) > 3 and f[3] and DT.get(f[3]) != ddt:
+                raise Skip("sum with a data type other than dst's")
+            bp.post_ops.append(W.PostOp(W.PO_SUM, scale=float(f[1]) if len(f) > 1 and f[1] else 1.0,
+                                        zero_point=int(f[2]) if len(f) > 2 and f[2] else 0))
+            dst_init_l = _fill(r, ddt, ddims, "dst")
+        elif kind in W.ELTWISE:
+            if len(f) > 3 and f[3] and float(f[3]) != 1.0:
+                raise Skip("eltwise with a scale")
+            bp.post_ops.append(W.PostOp(W.PO_ELTWISE, W.ELTWISE[kind], float(f[1]) if len(f) > 1 and f[1] else 0.0,
+                                        float(f[2]) if len(f) > 2 and f[2] else 0.0, 1.0))
+        elif kind in W.BINARY:
+            if len(f) < 2 or f[1] not in DT or (len(f) > 3 and f[3] not in ("", "any", "abx")):
+                raise Skip("binary post-op " + entry)
+            mask = _policy_mask(f[2] if len(f) > 2 and f[2] else "common", nd, False)
+            odims = tuple(d if (mask >> j) & 1 else 1 for j, d in enumerate(ddims))
+            vals = _fill(r, DT[f[1]], odims, "binary")
+            if kind == "div":
+                v = W.to_f32(vals, DT[f[1]])
+                vals = W.to_storage(np.where(v == 0, 2.0, v), DT[f[1]])
+            binaries[i] = vals
+            bp.post_ops.append(W.PostOp(W.PO_BINARY, W.BINARY[kind], src1=W.QTensor(vals.reshape(-1), DT[f[1]], odims)))
+        else:
+            raise Skip("post-op " + f[0])
+    if settings["attr-fpmath"]:
+        mode, _, flag = settings["attr-fpmath"].partition(":")
+        modes = {"strict": 0, "bf16": 1, "f16": 2, "any": 3, "tf32": 4}
+        if mode not in modes:
+            raise Skip("fpmath " + mode)
+        bp.fpmath, bp.apply_to_int = modes[mode], flag == "true"
+    bp.dst_init = None if dst_init_l is None else _layout(dst_init_l, bp.dst_order)[0]
+
+    def pick(arr, idx):  # the matrix of `arr` that batch index idx sees (size-1 dims broadcast)
+        return arr[tuple(i if arr.shape[d] > 1 else 0 for d, i in enumerate(idx))]
+
+    for idx in np.ndindex(*bdims):
+        s2, w2 = np.ascontiguousarray(pick(src_l, idx)), np.ascontiguousarray(pick(wei_l, idx))
+        bias2 = None
+        if bias_l is not None:
+            b2 = np.ascontiguousarray(pick(bias_l, idx))
+            bias2 = W.QTensor(b2, DT[settings["bia-dt"]], b2.shape)
+        pos = []
+        for i, po in enumerate(bp.post_ops):
+            if po.kind == W.PO_BINARY:
+                o2 = np.ascontiguousarray(pick(binaries[i], idx))
+                pos.append(W.PostOp(po.kind, po.alg, src1=W.QTensor(o2, po.src1.dt, o2.shape)))
+            else:
+                pos.append(po)
+        p = W.Problem("%s%s" % (desc, list(idx)), M, N, K, W.QTensor(s2, sdt, (M, K)), W.QTensor(w2, wdt, (K, N)), ddt,
+                      bias2, quant2d, pos, bp.apply_to_int, bp.fpmath)
+        if dst_init_l is not None:
+            p.dst_init = np.ascontiguousarray(dst_init_l[idx])
+        bp.mats.append((idx, p))
+    return bp
+
+
+def run_batched(bp, eng, strm, impl=None):
+    """Creates the batched primitive (optionally walking to the named implementation),
+    executes it once and returns (dst as a logical array, implementation, primitive desc)."""
+    from onednn_b200 import api
+    md = {k: api.memory.desc(dims, dt, strides) for k, (_, strides, dt, dims) in bp.tensors.items()}
+    nd = len(bp.ddims)
+    dst_strides = _layout(np.empty(bp.ddims, np.uint8), bp.dst_order)[1]
+    dst_md = api.memory.desc(bp.ddims, bp.ddt, dst_strides)
+    attr = api.primitive_attr()
+    if bp.apply_to_int or bp.fpmath:
+        attr.set_fpmath_mode(bp.fpmath, bp.apply_to_int)
+    arg_of = {"src": api.ARG_SRC, "wei": api.ARG_WEIGHTS, "dst": api.ARG_DST}
+    qkeys = {}
+    for name, q in bp.quant.items():
+        groups = tuple(q.groups) if tuple(q.groups) != (1, 1) else ()
+        if name.endswith("scale"):
+            attr.set_scales(arg_of[name[:3]], q.mask, groups, q.dt)
+            qkeys[name] = api.ARG_ATTR_SCALES | arg_of[name[:3]]
+        else:
+            attr.set_zero_points(arg_of[name[:3]], q.mask, groups, q.dt)
+            qkeys[name] = api.ARG_ATTR_ZERO_POINTS | arg_of[name[:3]]
+    po = api.post_ops()
+    bin_md = {}
+    for i, e in enumerate(bp.post_ops):
+        if e.kind == W.PO_SUM:
+            po.append_sum(e.scale, e.zero_point, 0)
+        elif e.kind == W.PO_ELTWISE:
+            po.append_eltwise(e.alg, e.alpha, e.beta)
+        else:
+            bin_md[i] = api.memory.desc(e.src1.dims, e.src1.dt, tuple(e.src1.strides))
+            po.append_binary(e.alg, bin_md[i])
+    if bp.post_ops:
+        attr.set_post_ops(po)
+    if bp.user_scratchpad:
+        attr.set_scratchpad_mode(api.SCRATCHPAD_MODE_USER)
+    pd = api.matmul.primitive_desc(eng, md["src"], md["wei"], dst_md, md.get("bias"), attr)
+    if impl is not None:
+        while impl not in pd.impl_info_str():
+            if not pd.next_impl():
+                raise api.error(api.unimplemented, "no implementation named *%s*" % impl)
+    if eng is None or strm is None:
+        return None, pd.impl_info_str(), pd
+    prim = api.matmul(pd)
+
+    def mem(d, array):
+        m = api.memory(d, eng)
+        m.write(np.ascontiguousarray(array).view(np.uint8).reshape(-1), 0)
+        return m
+
+    args = {api.ARG_SRC: mem(md["src"], bp.tensors["src"][0]), api.ARG_WEIGHTS: mem(md["wei"], bp.tensors["wei"][0]),
+            api.ARG_DST: mem(dst_md, bp.dst_init if bp.dst_init is not None else np.zeros(dst_md.get_size(0), np.uint8))}
+    if "bias" in md:
+        args[api.ARG_BIAS] = mem(md["bias"], bp.tensors["bias"][0])
+    for name, key in qkeys.items():
+        args[key] = mem(pd.query_md(api.QUERY_EXEC_ARG_MD, key), bp.quant[name].data)
+    for i, d in bin_md.items():
+        args[api.ARG_ATTR_MULTIPLE_POST_OP(i) | api.ARG_SRC_1] = mem(d, bp.post_ops[i].src1.data)
+    if bp.user_scratchpad:
+        smd = pd.query_md(api.QUERY_EXEC_ARG_MD, api.ARG_SCRATCHPAD)
+        if smd.get_size(0):
+            args[api.ARG_SCRATCHPAD] = mem(smd, np.full(smd.get_size(0), 0xA5, np.uint8))
+    prim.execute(strm, args)
+    strm.wait()
+    raw = args[api.ARG_DST].read(np.uint8, 0).view(W.NP_STORAGE[bp.ddt])
+    phys_shape = tuple(bp.ddims[d] for d in bp.dst_order)
+    inverse = np.argsort(bp.dst_order)
+    return raw[:int(np.prod(phys_shape))].reshape(phys_shape).transpose(inverse), pd.impl_info_str(), pd
+
+
 # ------------------------------------------------------------------ checking
 # eltwise algorithms of the form x * (1 + f(x)) / 2: for negative x the sum 1 + f(x) cancels
 CANCELLING = {W.ELTWISE["gelu_erf"]: 1.0, W.ELTWISE["gelu_tanh"]: 1.0}
@@ -395,6 +643,8 @@ def run_one(settings, desc, eng, strm, all_impls=False):
     try:
         p, opts = build(settings, desc)
     except Skip as e:
+        if str(e) == "batched descriptor":
+            return _run_one_batched(settings, desc, eng, strm, all_impls)
         return "SKIPPED", str(e)
     try:
         first = Prepared(p, eng, None, opts["user_scratchpad"], opts["runtime_m"])
@@ -418,6 +668,37 @@ def run_one(settings, desc, eng, strm, all_impls=False):
         ok, why = compare(run.download(), want, p.dst_dt, slack)
         if not ok:
             return "FAILED", "%s: %s" % (impl, why)
+    return "PASSED", ",".join(impls)
+
+
+def _run_one_batched(settings, desc, eng, strm, all_impls):
+    from onednn_b200 import api
+    from oracle import oracle as O
+    from oracle.parity import compare, summation_slack
+    try:
+        bp = build_batched(settings, desc)
+    except Skip as e:
+        return "SKIPPED", str(e)
+    try:
+        _, first, pd = run_batched(bp, eng, None)
+    except api.error as e:
+        if e.status == api.unimplemented:
+            return "SKIPPED", "unimplemented"
+        return "FAILED", "create: %s" % e
+    impls = [first]
+    if all_impls:
+        while pd.next_impl():
+            impls.append(pd.impl_info_str())
+    wants = [(idx, p, O.run_port(p), cancellation_slack(p)) for idx, p in bp.mats]
+    for impl in impls:
+        got, _, _ = run_batched(bp, eng, strm, impl)
+        for idx, p, want, libm_slack in wants:
+            slack = libm_slack
+            if not impl.startswith("cuda:ref") and p.src.dt not in (W.S8, W.U8):
+                slack = summation_slack(p) + (0.0 if libm_slack is None else libm_slack)
+            ok, why = compare(np.ascontiguousarray(got[idx]), want, p.dst_dt, slack)
+            if not ok:
+                return "FAILED", "%s, matrix %s: %s" % (impl, list(idx), why)
     return "PASSED", ",".join(impls)
 
 
