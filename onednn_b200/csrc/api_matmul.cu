@@ -308,7 +308,6 @@ dnnl_status_t ref_dense_accepts(const dnnl_primitive_desc &pd) {
     if (wz.set && wz.group_ndims) UNIMPL_IF(K % wz.group(0) != 0 || pd.N() % wz.group(1) != 0);
     const auto &sz = attr.zp(DNNL_ARG_SRC);
     if (sz.set && sz.group_ndims) UNIMPL_IF(sz.group(0) != 1 || K % sz.group(1) != 0);
-    for (const auto &e : attr.post_ops.entries) UNIMPL_IF(e.kind == dnnl_prelu); // not built
     // strided plain layouts only
     UNIMPL_IF(pd.src.format_kind != dnnl_blocked || pd.wei.format_kind != dnnl_blocked
             || pd.dst.format_kind != dnnl_blocked);
@@ -603,7 +602,7 @@ dnnl_status_t batch_core(const dnnl_primitive_desc &pd, dnnl_primitive_desc &cor
     };
     last2(core.src); last2(core.wei); last2(core.dst); last2(core.bias);
     for (auto &e : core.attr.post_ops.entries)
-        if (e.kind == dnnl_binary) {
+        if (e.kind == dnnl_binary || e.kind == dnnl_prelu) {
             if (e.src1.ndims != nd) return dnnl_unimplemented;
             last2(e.src1);
         }
@@ -656,7 +655,8 @@ dnnl_status_t dnnl_matmul_primitive_desc_create(dnnl_primitive_desc_t *primitive
                 strides_known = strides_known && md->strides[0] != DNNL_RUNTIME_DIM_VAL && md->strides[1] != DNNL_RUNTIME_DIM_VAL;
         bool binary_known = true;
         for (auto &e : pd->attr.post_ops.entries)
-            if (e.kind == dnnl_binary && (e.src1.has_runtime_dims() || (e.src1.ndims == 2 && e.src1.dims[0] != 1)))
+            if ((e.kind == dnnl_binary && (e.src1.has_runtime_dims() || (e.src1.ndims == 2 && e.src1.dims[0] != 1)))
+                    || (e.kind == dnnl_prelu && (e.prelu_mask & 1)))
                 binary_known = false; // an operand with M rows needs the M
         if (!ok || !strides_known || !binary_known) {
             delete pd;
@@ -678,6 +678,32 @@ dnnl_status_t dnnl_matmul_primitive_desc_create(dnnl_primitive_desc_t *primitive
             if (e.kind == dnnl_binary) set_default_format(e.src1);
         for (auto &e : pd->attr.post_ops.entries)
             if (e.kind == dnnl_sum && e.sum_dt == dnnl_data_type_undef) e.sum_dt = pd->dst.data_type;
+        // prelu: f32 weights over the dst dims its mask names, dense, with dim 1 innermost beyond two
+        // dims (ab, acb, acdb, acdeb: src/cpu/primitive_attr_postops.cpp:219-242); kept in src1 so that
+        // the kernels see it as a binary operand
+        for (auto &e : pd->attr.post_ops.entries)
+            if (e.kind == dnnl_prelu && !pd->grouped) {
+                const int nd = pd->dst.ndims;
+                dnnl_memory_desc w;
+                w.ndims = nd;
+                w.data_type = dnnl_f32;
+                w.format_kind = dnnl_blocked;
+                for (int d = 0; d < nd; ++d) w.dims[d] = ((e.prelu_mask >> d) & 1) ? pd->dst.dims[d] : 1;
+                int order[DNNL_MAX_NDIMS]; // outermost first
+                int k = 0;
+                if (nd <= 2) for (int d = 0; d < nd; ++d) order[k++] = d;
+                else {
+                    order[k++] = 0;
+                    for (int d = 2; d < nd; ++d) order[k++] = d;
+                    order[k++] = 1;
+                }
+                dnnl_dim_t acc = 1;
+                for (int i = nd - 1; i >= 0; --i) {
+                    w.strides[order[i]] = acc;
+                    acc *= w.dims[order[i]] == 0 ? 1 : w.dims[order[i]];
+                }
+                e.src1 = w;
+            }
         st = pd->grouped ? grouped_attr_check(*pd) : dense_attr_check(*pd);
     }
     // Batched (ndims > 2, src/common/matmul.cpp:630-744 with broadcast of size-1 batch dims): the
@@ -966,9 +992,11 @@ static dnnl_status_t execute_matmul_2d(const_dnnl_primitive_t primitive, const d
         po.alg = e.alg; po.alpha = e.alpha; po.beta = e.beta; po.scale = e.scale; po.zero_point = e.zero_point;
         if (e.kind == dnnl_sum) { po.kind = PO_SUM; a.sum_dt = e.sum_dt; }
         else if (e.kind == dnnl_eltwise) po.kind = PO_ELTWISE;
-        else if (e.kind == dnnl_binary) {
+        else if (e.kind == dnnl_binary || e.kind == dnnl_prelu) {
             po.kind = PO_BINARY;
-            dnnl_memory_t m = am.find(DNNL_ARG_ATTR_MULTIPLE_POST_OP(i) | DNNL_ARG_SRC_1);
+            const bool prelu = e.kind == dnnl_prelu; // a binary operation on the weights tensor
+            if (prelu) po.alg = ALG_PRELU;
+            dnnl_memory_t m = am.find(DNNL_ARG_ATTR_MULTIPLE_POST_OP(i) | (prelu ? DNNL_ARG_WEIGHTS : DNNL_ARG_SRC_1));
             if (!m || !m->handles[0]) return dnnl_invalid_arguments;
             po.src1 = at_offset0(m->handles[0], e.src1);
             po.src1_dt = e.src1.data_type;
@@ -1138,7 +1166,7 @@ extern "C" dnnl_status_t dnnl_primitive_execute(const_dnnl_primitive_t primitive
             core.dst.offset0 = off(bp.dst);
             if (bp.bias.ndims) core.bias.offset0 = off(bp.bias);
             for (size_t i = 0; i < bp.attr.post_ops.entries.size(); ++i)
-                if (bp.attr.post_ops.entries[i].kind == dnnl_binary)
+                if (bp.attr.post_ops.entries[i].kind == dnnl_binary || bp.attr.post_ops.entries[i].kind == dnnl_prelu)
                     core.attr.post_ops.entries[i].src1.offset0 = off(bp.attr.post_ops.entries[i].src1);
             bst = execute_matmul_2d(primitive, core, stream, am, nargs, args);
             if (bst != dnnl_success) return bst;

@@ -225,6 +225,7 @@ __device__ __forceinline__ float binary_op(int alg, float x, float y) {
         case 0x1fff9: return x < y;
         case 0x1fffa: return x == y;
         case 0x1fffb: return x != y;
+        case ALG_PRELU: return x >= 0 ? x : __fmul_rn(y, x);
         default: return x;
     }
 }

@@ -13,6 +13,9 @@ enum : int {
 };
 
 enum : int { PO_SUM = 1, PO_ELTWISE = 2, PO_BINARY = 3, PO_PRELU = 4 };
+// a prelu post-op reaches the kernels as a binary operation on its weights tensor: x >= 0 ? x : w * x
+// (no dnnl_alg_kind_t has this value)
+constexpr int ALG_PRELU = 0x1ffe0;
 
 constexpr int MAX_POST_OPS = 32;
 

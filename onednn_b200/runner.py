@@ -58,6 +58,9 @@ class Prepared:
                 po.append_sum(e.scale, e.zero_point, 0)
             elif e.kind == W.PO_ELTWISE:
                 po.append_eltwise(e.alg, e.alpha, e.beta)
+            elif e.kind == W.PO_PRELU:
+                po.append_prelu(sum(1 << d for d, n in enumerate(e.src1.dims) if n > 1))
+                self.binary_args[api.ARG_ATTR_MULTIPLE_POST_OP(i) | api.ARG_WEIGHTS] = e.src1
             else:
                 po.append_binary(e.alg, _md(e.src1))
                 self.binary_args[api.ARG_ATTR_MULTIPLE_POST_OP(i) | api.ARG_SRC_1] = e.src1
@@ -150,6 +153,8 @@ class Prepared:
         for i, e in enumerate(p.post_ops):
             if e.kind == W.PO_BINARY:
                 self.args[api.ARG_ATTR_MULTIPLE_POST_OP(i) | api.ARG_SRC_1] = api.memory(_md(e.src1), eng, ptrs["po%d" % i])
+            elif e.kind == W.PO_PRELU:
+                self.args[api.ARG_ATTR_MULTIPLE_POST_OP(i) | api.ARG_WEIGHTS] = api.memory(_md(e.src1), eng, ptrs["po%d" % i])
         return self
 
     def execute(self, strm):

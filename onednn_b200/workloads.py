@@ -32,7 +32,7 @@ ELTWISE = {"relu": 0x20, "tanh": 0x21, "elu": 0x22, "square": 0x23, "abs": 0x24,
 BINARY = {"add": 0x1fff0, "mul": 0x1fff1, "max": 0x1fff2, "min": 0x1fff3,
           "div": 0x1fff4, "sub": 0x1fff5}
 
-PO_SUM, PO_ELTWISE, PO_BINARY = 1, 2, 3
+PO_SUM, PO_ELTWISE, PO_BINARY, PO_PRELU = 1, 2, 3, 4  # PO_PRELU: src1 = f32 weights over the masked dst dims
 
 
 def nbytes(dt: int, nelems: int) -> int:

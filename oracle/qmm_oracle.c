@@ -278,6 +278,13 @@ static float run_post_ops(const qmm_problem_t *p, float res, float dst_old,
             float y = qmm_load_float(
                     e->src1_dt, e->src1, m * e->src1_sm + n * e->src1_sn);
             res = binary_op(e->alg, res, y);
+        } else if (e->kind == QMM_PO_PRELU) {
+            /* primitive_attr_postops.cpp:363-389: non-negative values pass;
+             * the others are multiplied by the f32 weight of their position
+             * (src1 holds the weights over the masked dst dims) */
+            if (!(res >= 0))
+                res = ((const float *)e->src1)[m * e->src1_sm + n * e->src1_sn]
+                        * res;
         }
     }
     return res;

@@ -26,7 +26,7 @@ enum {
     QMM_U8 = 6, QMM_F8_E5M2 = 9, QMM_F8_E4M3 = 10, QMM_S4 = 11, QMM_U4 = 12
 };
 
-enum { QMM_PO_SUM = 1, QMM_PO_ELTWISE = 2, QMM_PO_BINARY = 3 };
+enum { QMM_PO_SUM = 1, QMM_PO_ELTWISE = 2, QMM_PO_BINARY = 3, QMM_PO_PRELU = 4 };
 
 /* eltwise / binary algorithm codes = dnnl_alg_kind_t values
  * (include/oneapi/dnnl/dnnl_types.h) */

@@ -118,6 +118,12 @@ built_t build(const qmm_problem_t &p, const engine &eng, int pin_ref) {
             po.append_sum(e.scale, e.zero_point, to_dt(p.sum_dt));
         } else if (e.kind == QMM_PO_ELTWISE) {
             po.append_eltwise(static_cast<algorithm>(e.alg), e.alpha, e.beta);
+        } else if (e.kind == QMM_PO_PRELU) {
+            memory::desc md({e.src1_sm ? p.M : 1, e.src1_sn ? p.N : 1},
+                    memory::data_type::f32, memory::format_tag::ab);
+            po.append_prelu((e.src1_sm ? 1 : 0) | (e.src1_sn ? 2 : 0));
+            args.emplace(DNNL_ARG_ATTR_MULTIPLE_POST_OP(i) | DNNL_ARG_WEIGHTS,
+                    make_mem(md, eng, e.src1));
         } else {
             memory::desc md({e.src1_sm ? p.M : 1, e.src1_sn ? p.N : 1},
                     to_dt(e.src1_dt), memory::format_tag::ab);

@@ -1,5 +1,5 @@
 """Small problems that walk the attribute combinations the reference's own
-matmul test inputs use (tests/benchdnn/inputs/matmul/test_matmul_int8:25-56,
+matmul test inputs use (tests/benchdnn/inputs/matmul/test_matmul_int8:10-56,
 harness_matmul_grouped_2dby3d), restated as seeded problems.  Shared by a CPU
 test (C restatement against the live reference, where it is built) and a GPU
 test (every implementation that accepts the problem against the C
@@ -134,7 +134,22 @@ def grouped_woq_zero_points_relu():
                      apply_to_int=True, fpmath=2, offsets=np.cumsum(sizes).astype(np.int32))
 
 
+def prelu_per_column_after_sum():
+    """s8:s8:f32 with scales, a sum and a prelu whose f32 weights vary per column (mask 1 << 1)."""
+    r = _r(111)
+    M, K, N = 14, 64, 48
+    q = {"src_scale": W.Quant(np.array([0.25], np.float32), W.F32, 0),
+         "wei_scale": W.Quant(np.array([0.5], np.float32), W.F32, 0),
+         "dst_scale": W.Quant(np.array([4.0], np.float32), W.F32, 0)}
+    po = [W.PostOp(W.PO_SUM, scale=1.0, zero_point=0),
+          W.PostOp(W.PO_PRELU, src1=W.QTensor(r.uniform(-1.0, 1.0, (1, N)).astype(np.float32), W.F32, (1, N)))]
+    p = W.Problem("prelu_per_oc", M, N, K, W.QTensor(_s8(r, (M, K)), W.S8, (M, K)),
+                  W.QTensor(_s8(r, (K, N)), W.S8, (K, N)), W.F32, quant=q, post_ops=po)
+    p.dst_init = r.standard_normal((M, N)).astype(np.float32)
+    return p
+
+
 CASES = {f.__name__: f for f in (
     zero_points_all_common, zero_points_src_per_k, scales_and_post_op_chain, binary_add_full, decompress_f32_common,
     decompress_bf16_per_oc, decompress_bf16_per_element, transposed_tags, grouped_f32_plain,
-    grouped_woq_zero_points_relu)}
+    grouped_woq_zero_points_relu, prelu_per_column_after_sum)}

@@ -21,12 +21,12 @@ descriptor the library answers `unimplemented` to), never silently dropped.
 
 Handled: --reset, --batch, --dt, --stag/--wtag/--dtag (ab, ba, any), --bia-dt,
 --bia_mask, --runtime_dims_masks (run-time M), --attr-scales,
---attr-zero-points, --attr-post-ops (sum, eltwise, binary), --attr-fpmath,
+--attr-zero-points, --attr-post-ops (sum, eltwise, binary, prelu), --attr-fpmath,
 --attr-scratchpad.  Options that select implementations or engines
 (--skip-impl, --impl, --engine, --match ...) are accepted and ignored.
 Descriptors with batch dims (3D and more, size-1 dims broadcast, tags that
 permute the dims such as acb or bac) run as one batched primitive and are checked
-matrix by matrix against the oracle's 2D result.  --strides, --grouped, prelu /
+matrix by matrix against the oracle's 2D result.  --strides, --grouped,
 depthwise post-ops, run-time K or N and the remaining attributes are skipped with
 their name as the reason.
 
@@ -334,6 +334,10 @@ def build(settings, desc, seed=None):
                 z = W.to_f32(vals, DT[f[1]]) == 0
                 vals = W.to_storage(np.where(z, 2.0, W.to_f32(vals, DT[f[1]])), DT[f[1]])
             post_ops.append(W.PostOp(W.PO_BINARY, W.BINARY[kind], src1=W.QTensor(vals, DT[f[1]], bdims)))
+        elif kind == "prelu":  # f32 weights over the dst dims the policy names
+            mask = _policy_mask(f[1] if len(f) > 1 and f[1] else "common", 2, False)
+            wdims = (M if mask & 1 else 1, N if mask & 2 else 1)
+            post_ops.append(W.PostOp(W.PO_PRELU, src1=W.QTensor(_fill(r, W.F32, wdims, "src"), W.F32, wdims)))
         else:
             raise Skip("post-op " + f[0])
 
@@ -489,6 +493,14 @@ def build_batched(settings, desc):
                 vals = W.to_storage(np.where(v == 0, 2.0, v), DT[f[1]])
             binaries[i] = vals
             bp.post_ops.append(W.PostOp(W.PO_BINARY, W.BINARY[kind], src1=W.QTensor(vals.reshape(-1), DT[f[1]], odims)))
+        elif kind == "prelu":
+            # weights are dense with dim 1 innermost (acb, acdb ...: src/cpu/primitive_attr_postops.cpp:219-242)
+            mask = _policy_mask(f[1] if len(f) > 1 and f[1] else "common", nd, False)
+            odims = tuple(d if (mask >> j) & 1 else 1 for j, d in enumerate(ddims))
+            vals = _fill(r, W.F32, odims, "src")
+            binaries[i] = vals
+            storage, strides = _layout(vals, (0,) + tuple(range(2, nd)) + (1,))
+            bp.post_ops.append(W.PostOp(W.PO_PRELU, zero_point=mask, src1=W.QTensor(storage, W.F32, odims, strides)))
         else:
             raise Skip("post-op " + f[0])
     if settings["attr-fpmath"]:
@@ -510,7 +522,7 @@ def build_batched(settings, desc):
             bias2 = W.QTensor(b2, DT[settings["bia-dt"]], b2.shape)
         pos = []
         for i, po in enumerate(bp.post_ops):
-            if po.kind == W.PO_BINARY:
+            if po.kind in (W.PO_BINARY, W.PO_PRELU):
                 o2 = np.ascontiguousarray(pick(binaries[i], idx))
                 pos.append(W.PostOp(po.kind, po.alg, src1=W.QTensor(o2, po.src1.dt, o2.shape)))
             else:
@@ -551,6 +563,9 @@ def run_batched(bp, eng, strm, impl=None):
             po.append_sum(e.scale, e.zero_point, 0)
         elif e.kind == W.PO_ELTWISE:
             po.append_eltwise(e.alg, e.alpha, e.beta)
+        elif e.kind == W.PO_PRELU:
+            bin_md[i] = api.memory.desc(e.src1.dims, e.src1.dt, tuple(e.src1.strides))
+            po.append_prelu(e.zero_point)  # the mask
         else:
             bin_md[i] = api.memory.desc(e.src1.dims, e.src1.dt, tuple(e.src1.strides))
             po.append_binary(e.alg, bin_md[i])
@@ -579,7 +594,8 @@ def run_batched(bp, eng, strm, impl=None):
     for name, key in qkeys.items():
         args[key] = mem(pd.query_md(api.QUERY_EXEC_ARG_MD, key), bp.quant[name].data)
     for i, d in bin_md.items():
-        args[api.ARG_ATTR_MULTIPLE_POST_OP(i) | api.ARG_SRC_1] = mem(d, bp.post_ops[i].src1.data)
+        which = api.ARG_WEIGHTS if bp.post_ops[i].kind == W.PO_PRELU else api.ARG_SRC_1
+        args[api.ARG_ATTR_MULTIPLE_POST_OP(i) | which] = mem(d, bp.post_ops[i].src1.data)
     if bp.user_scratchpad:
         smd = pd.query_md(api.QUERY_EXEC_ARG_MD, api.ARG_SCRATCHPAD)
         if smd.get_size(0):
@@ -626,6 +642,8 @@ def cancellation_slack(p):
             amp = amp * v if po.alg == W.BINARY["mul"] else amp / v
         elif po.kind == W.PO_ELTWISE and po.alg == W.ELTWISE["linear"]:
             amp = amp * abs(po.alpha)
+        elif po.kind == W.PO_PRELU:
+            amp = amp * np.maximum(1.0, np.abs(po.src1.data.astype(np.float64)).reshape(po.src1.dims))
     ds = p.quant.get("dst_scale")
     if ds is not None:
         amp = amp / np.abs(W.to_f32(ds.data, ds.dt).astype(np.float64)).reshape(-1)[0]
