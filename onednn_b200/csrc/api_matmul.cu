@@ -258,8 +258,8 @@ dnnl_status_t ref_dense_accepts(const dnnl_primitive_desc &pd) {
     } else { // ref_matmul.hpp:44-123
         UNIMPL_IF(!one_of(s, {dnnl_f32, dnnl_bf16, dnnl_f16, dnnl_f8_e5m2, dnnl_f8_e4m3}));
         UNIMPL_IF(!one_of(w, {dnnl_f32, dnnl_bf16, dnnl_f16, dnnl_f8_e5m2, dnnl_f8_e4m3, dnnl_u8, dnnl_s8, dnnl_u4, dnnl_s4}));
-        // fp8 / sub-byte float destinations are not built
-        UNIMPL_IF(!one_of(d, {dnnl_f32, dnnl_bf16, dnnl_f16, dnnl_u8, dnnl_s8}));
+        // sub-byte float destinations are not built; 8-bit float ones go to the generic kernel
+        UNIMPL_IF(!one_of(d, {dnnl_f32, dnnl_bf16, dnnl_f16, dnnl_f8_e5m2, dnnl_f8_e4m3, dnnl_u8, dnnl_s8}));
         UNIMPL_IF(!(s == w || one_of(w, {dnnl_bf16, dnnl_f16, dnnl_f8_e5m2, dnnl_f8_e4m3, dnnl_u8, dnnl_s8, dnnl_u4, dnnl_s4})));
         // integer weights convert to the src type only with apply_to_int and
         // an fpmath mode that covers that type (primitive_attr_t::mayiconvert,
@@ -279,7 +279,7 @@ dnnl_status_t ref_dense_accepts(const dnnl_primitive_desc &pd) {
         UNIMPL_IF(s == dnnl_f16 && !one_of(d, {dnnl_f32, dnnl_f16, dnnl_u8, dnnl_s8}));
         if (with_bias) {
             const auto b = pd.bias.data_type;
-            UNIMPL_IF(!one_of(b, {dnnl_f32, dnnl_bf16, dnnl_f16}));
+            UNIMPL_IF(!one_of(b, {dnnl_f32, dnnl_bf16, dnnl_f16, dnnl_f8_e5m2, dnnl_f8_e4m3}));
             UNIMPL_IF(w == dnnl_f32 && b != dnnl_f32);
             UNIMPL_IF(w == dnnl_f16 && !one_of(b, {dnnl_f32, dnnl_f16}));
             UNIMPL_IF(w == dnnl_bf16 && !one_of(b, {dnnl_f32, dnnl_bf16}));
@@ -364,6 +364,7 @@ dnnl_status_t tc_accepts(const dnnl_primitive_desc &pd) {
     const auto &attr = pd.attr;
     const bool int_path = is_int8(s);
     UNIMPL_IF(!((int_path && is_int8(w)) || (is_fp8(s) && is_fp8(w))));
+    UNIMPL_IF(is_fp8(pd.dst.data_type) || (pd.bias.ndims && is_fp8(pd.bias.data_type))); // no 8-bit float stores / bias here
     const dnnl_dim_t M = pd.M(), N = pd.N(), K = pd.K();
     UNIMPL_IF(M == 0 || N == 0 || K == 0);
     UNIMPL_IF(M >= (1LL << 31) || N >= (1LL << 31) || K >= (1LL << 31));
@@ -394,6 +395,7 @@ dnnl_status_t woq_accepts(const dnnl_primitive_desc &pd) {
     const auto s = pd.src.data_type, w = pd.wei.data_type;
     const auto &attr = pd.attr;
     UNIMPL_IF(!(s == dnnl_bf16 || s == dnnl_f16) || !(w == dnnl_s4 || w == dnnl_u4));
+    UNIMPL_IF(is_fp8(pd.dst.data_type) || (pd.bias.ndims && is_fp8(pd.bias.data_type)));
     const dnnl_dim_t M = pd.M(), N = pd.N(), K = pd.K();
     UNIMPL_IF(M < 1 || M > 32 || N % 32 != 0 || K % 16 != 0 || K < 16);
     UNIMPL_IF(N >= (1LL << 31) || K >= (1LL << 31));

@@ -116,6 +116,8 @@ def to_f32(data: np.ndarray, dt: int) -> np.ndarray:
         return data.view(np.float16).astype(np.float32)
     if dt == F8_E4M3:
         return e4m3_to_f32(data)
+    if dt == F8_E5M2:  # the upper byte of a half
+        return (data.astype(np.uint16) << 8).view(np.float16).astype(np.float32)
     if dt in (S4, U4):
         return unpack_int4(data, dt == S4).astype(np.float32)
     return data.astype(np.float32)

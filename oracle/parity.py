@@ -4,7 +4,7 @@ the product.
 
 * s32 and every integer/byte/index result: bit-exact.
 * f32: |got - want| <= 1e-5 * |want|.
-* bf16 / f16: at most 1 ulp of the output type from the reference value.
+* bf16 / f16 / f8_e4m3 / f8_e5m2: at most 1 ulp of the output type from the reference value.
 * s8 / u8 (a requantized f32): at most 1 apart.
 
 Kernels that add the K products in another order than the scalar reference
@@ -34,6 +34,19 @@ def _ordered(bits: np.ndarray) -> np.ndarray:
     """Maps sign-magnitude 16-bit float patterns to monotone integers."""
     b = bits.astype(np.int32)
     return np.where(b & 0x8000, -(b & 0x7FFF), b)
+
+
+def _ordered8(bits: np.ndarray) -> np.ndarray:
+    """Maps sign-magnitude 8-bit float patterns to monotone integers."""
+    b = bits.astype(np.int32)
+    return np.where(b & 0x80, -(b & 0x7F), b)
+
+
+def _ulp8(want_bits: np.ndarray, dt: int) -> np.ndarray:
+    """One unit in the last place of each 8-bit float value, as float64."""
+    mant, bias = (3, 7) if dt == W.F8_E4M3 else (2, 15)
+    e = np.maximum((want_bits.astype(np.int32) >> mant) & ((1 << (7 - mant)) - 1), 1)
+    return np.ldexp(1.0, e - bias - mant)
 
 
 def _ulp16(want_bits: np.ndarray, dt: int) -> np.ndarray:
@@ -119,6 +132,15 @@ def compare(got: np.ndarray, want: np.ndarray, dt: int, slack=None):
         bad = ~(err <= _ulp16(want, dt) + slack)
         return not bad.any(), "beyond 1 ulp + summation slack: %d of %d (>1 ulp at %d, !=0 at %d, max abs err %.3g)" % (
             int(bad.sum()), d.size, n1, n0, float(err.max(initial=0)))
+    if dt in (W.F8_E4M3, W.F8_E5M2):  # like the 16-bit floats: one unit of the output type
+        d = np.abs(_ordered8(got) - _ordered8(want))
+        n1, n0 = int((d > 1).sum()), int((d > 0).sum())
+        if slack is None:
+            return n1 == 0, "8-bit float ulp distance max %d, >1 at %d, !=0 at %d" % (int(d.max(initial=0)), n1, n0)
+        decode = W.e4m3_to_f32 if dt == W.F8_E4M3 else (lambda b: (b.astype(np.uint16) << 8).view(np.float16).astype(np.float32))
+        err = np.abs(decode(got).astype(np.float64) - decode(want).astype(np.float64))
+        bad = ~((err <= _ulp8(want, dt) + slack) | (got == want))
+        return not bad.any(), "beyond 1 ulp + slack: %d of %d (>1 ulp at %d)" % (int(bad.sum()), d.size, n1)
     if dt in (W.S8, W.U8):
         d = np.abs(got.astype(np.int32) - want.astype(np.int32))
         return int(d.max(initial=0)) <= 1, "8-bit int distance max %d, !=0 at %d" % (

@@ -255,7 +255,7 @@ def build(settings, desc, seed=None):
     if len(dts) != 3 or any(d not in DT for d in dts):
         raise Skip("data types " + settings["dt"])
     sdt, wdt, ddt = (DT[d] for d in dts)
-    if ddt not in (W.F32, W.S32, W.BF16, W.F16, W.S8, W.U8):
+    if ddt not in (W.F32, W.S32, W.BF16, W.F16, W.S8, W.U8, W.F8_E4M3, W.F8_E5M2):
         raise Skip("dst type " + dts[2])
     if settings["dtag"] not in ("ab", "any", "abx"):
         raise Skip("dst tag " + settings["dtag"])
@@ -425,7 +425,7 @@ def build_batched(settings, desc):
     sdt, wdt, ddt = (DT[d] for d in dts)
     if W.S4 in (sdt, wdt, ddt) or W.U4 in (sdt, wdt, ddt):
         raise Skip("4-bit types in a batched problem")
-    if ddt not in (W.F32, W.S32, W.BF16, W.F16, W.S8, W.U8):
+    if ddt not in (W.F32, W.S32, W.BF16, W.F16, W.S8, W.U8, W.F8_E4M3, W.F8_E5M2):
         raise Skip("dst type " + dts[2])
     bp = Batched()
     bp.ddt, bp.ddims = ddt, ddims
