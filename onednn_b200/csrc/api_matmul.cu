@@ -563,12 +563,15 @@ dnnl_memory_desc quant_md(const quant_entry_t &q, const dnnl_memory_desc &base) 
     md.data_type = q.dt;
     md.format_kind = dnnl_blocked;
     for (int i = 0; i < base.ndims; ++i) md.dims[i] = (q.mask & (1 << i)) ? base.dims[i] : 1;
-    if (q.group_ndims) {
-        md.dims[base.ndims - 2] /= q.groups[0];
-        md.dims[base.ndims - 1] /= q.groups[1];
+    if (q.group_ndims) { // a dim left open until execution stays open
+        if (md.dims[base.ndims - 2] != DNNL_RUNTIME_DIM_VAL) md.dims[base.ndims - 2] /= q.groups[0];
+        if (md.dims[base.ndims - 1] != DNNL_RUNTIME_DIM_VAL) md.dims[base.ndims - 1] /= q.groups[1];
     }
     dnnl_dim_t acc = 1;
-    for (int i = base.ndims - 1; i >= 0; --i) { md.strides[i] = acc; acc *= md.dims[i]; }
+    for (int i = base.ndims - 1; i >= 0; --i) {
+        md.strides[i] = acc;
+        acc = (acc == DNNL_RUNTIME_DIM_VAL || md.dims[i] == DNNL_RUNTIME_DIM_VAL) ? DNNL_RUNTIME_DIM_VAL : acc * md.dims[i];
+    }
     return md;
 }
 
@@ -585,6 +588,84 @@ void fill_quant_mds(dnnl_primitive_desc &pd) {
 }
 
 const dnnl_memory_desc g_zero_md;
+
+// prelu: f32 weights over the dst dims its mask names, dense, with dim 1 innermost beyond two
+// dims (ab, acb, acdb, acdeb: src/cpu/primitive_attr_postops.cpp:219-242); kept in src1 so that
+// the kernels see it as a binary operand
+void build_prelu_mds(dnnl_primitive_desc &pd) {
+    for (auto &e : pd.attr.post_ops.entries)
+        if (e.kind == dnnl_prelu && !pd.grouped) {
+            const int nd = pd.dst.ndims;
+            dnnl_memory_desc w;
+            w.ndims = nd;
+            w.data_type = dnnl_f32;
+            w.format_kind = dnnl_blocked;
+            for (int d = 0; d < nd; ++d) w.dims[d] = ((e.prelu_mask >> d) & 1) ? pd.dst.dims[d] : 1;
+            int order[DNNL_MAX_NDIMS]; // outermost first
+            int k = 0;
+            if (nd <= 2) for (int d = 0; d < nd; ++d) order[k++] = d;
+            else {
+                order[k++] = 0;
+                for (int d = 2; d < nd; ++d) order[k++] = d;
+                order[k++] = 1;
+            }
+            dnnl_dim_t acc = 1;
+            for (int i = nd - 1; i >= 0; --i) {
+                w.strides[order[i]] = acc;
+                acc *= w.dims[order[i]] == 0 ? 1 : w.dims[order[i]];
+            }
+            e.src1 = w;
+        }
+}
+
+dnnl_dim_t lcm_of(dnnl_dim_t a, dnnl_dim_t b) {
+    if (a <= 0 || b <= 0) return a > b ? a : b;
+    dnnl_dim_t x = a, y = b;
+    while (y) { const dnnl_dim_t t = x % y; x = y; y = t; }
+    return a / x * b;
+}
+
+// A 2D descriptor with run-time dims, made concrete for the checks at creation and for the
+// implementation list: every open dim takes the value another tensor gives it, else a stand-in
+// (1, or the least common multiple of the groups that must divide it); open strides become dense
+// row-major.  What executes is settled again from the memory objects.
+void apply_stand_ins(dnnl_primitive_desc &pd) {
+    const dnnl_dim_t RT = DNNL_RUNTIME_DIM_VAL;
+    dnnl_dim_t M = RT, K = RT, N = RT;
+    auto learn = [&](dnnl_dim_t &v, dnnl_dim_t d) { if (v == RT && d != RT) v = d; };
+    learn(M, pd.src.dims[0]); learn(M, pd.dst.dims[0]);
+    learn(K, pd.src.dims[1]); learn(K, pd.wei.dims[0]);
+    learn(N, pd.wei.dims[1]); learn(N, pd.dst.dims[1]);
+    dnnl_dim_t gk = 1, gn = 1;
+    for (auto *m : {&pd.attr.scales, &pd.attr.zero_points, &pd.attr.reductions})
+        for (auto &kv : *m)
+            if (kv.second.group_ndims) {
+                if (kv.first == DNNL_ARG_SRC) gk = lcm_of(gk, kv.second.groups[1]);
+                if (kv.first == DNNL_ARG_WEIGHTS) { gk = lcm_of(gk, kv.second.groups[0]); gn = lcm_of(gn, kv.second.groups[1]); }
+                if (kv.first == DNNL_ARG_DST) gn = lcm_of(gn, kv.second.groups[1]);
+            }
+    if (M == RT) M = 1;
+    if (K == RT) K = gk;
+    if (N == RT) N = gn;
+    // stated dims stay (contradictions between tensors are then found by the usual checks)
+    auto fix = [&](dnnl_memory_desc &md, dnnl_dim_t d0, dnnl_dim_t d1) {
+        if (md.ndims != 2) return;
+        const bool open = md.has_runtime_dims();
+        if (md.dims[0] == RT) md.dims[0] = d0;
+        if (md.dims[1] == RT) md.dims[1] = d1;
+        if (open || md.format_kind == dnnl_format_kind_any) {
+            md.format_kind = dnnl_blocked;
+            md.strides[1] = 1;
+            md.strides[0] = md.dims[1] == 0 ? 1 : md.dims[1];
+        }
+    };
+    fix(pd.src, M, K);
+    fix(pd.wei, K, N);
+    fix(pd.dst, M, N);
+    fix(pd.bias, M, N);
+    for (auto &e : pd.attr.post_ops.entries)
+        if (e.kind == dnnl_binary) fix(e.src1, M, N);
+}
 
 // The 2D core of a batched descriptor: the last two dims of every tensor, quantization masks
 // without the batch bits.  Parameters that vary along a batch dim are not built.
@@ -640,32 +721,50 @@ dnnl_status_t dnnl_matmul_primitive_desc_create(dnnl_primitive_desc_t *primitive
     if (attr) pd->attr = *attr;
     pd->grouped = src_desc->is_grouped();
 
-    // Run-time shapes (DNNL_RUNTIME_DIM_VAL, src/common/matmul.cpp:630-744): supported for the row
-    // count M of a 2D problem, the one the reference's tutorials leave open (a dynamic batch); every
-    // other dim, the weights and the strides must be known.  The descriptor is checked with M = 1
-    // and settled again, with the M of the memory objects, at every execution.
-    if (pd->src.has_runtime_dims() || pd->wei.has_runtime_dims() || pd->dst.has_runtime_dims()
-            || pd->bias.has_runtime_dims()) {
+    // Run-time shapes (DNNL_RUNTIME_DIM_VAL, src/common/matmul.cpp:630-744) of a dense 2D problem:
+    // any of M, K, N and the strides may be left open, in bias and binary operands too.  The
+    // descriptor is checked, and its implementation list made, with stand-ins for the open dims;
+    // what the queries report stays as the caller gave it; every execution settles the shapes
+    // again from the memory objects.
+    bool has_open = pd->src.has_runtime_dims() || pd->wei.has_runtime_dims() || pd->dst.has_runtime_dims()
+            || pd->bias.has_runtime_dims();
+    for (auto &e : pd->attr.post_ops.entries) has_open = has_open || (e.kind == dnnl_binary && e.src1.has_runtime_dims());
+    if (has_open) {
         const bool ok = !pd->grouped && pd->src.ndims == 2 && pd->dst.ndims == 2 && pd->wei.ndims == 2
-                && pd->src.dims[0] == DNNL_RUNTIME_DIM_VAL && pd->dst.dims[0] == DNNL_RUNTIME_DIM_VAL
-                && pd->src.dims[1] != DNNL_RUNTIME_DIM_VAL && pd->dst.dims[1] != DNNL_RUNTIME_DIM_VAL
-                && !pd->wei.has_runtime_dims() && !pd->bias.has_runtime_dims()
-                && (pd->bias.ndims == 0 || pd->bias.dims[0] == 1);
-        bool strides_known = true;
-        for (auto *md : {&pd->src, &pd->dst})
-            if (md->format_kind == dnnl_blocked)
-                strides_known = strides_known && md->strides[0] != DNNL_RUNTIME_DIM_VAL && md->strides[1] != DNNL_RUNTIME_DIM_VAL;
-        bool binary_known = true;
-        for (auto &e : pd->attr.post_ops.entries)
-            if ((e.kind == dnnl_binary && (e.src1.has_runtime_dims() || (e.src1.ndims == 2 && e.src1.dims[0] != 1)))
-                    || (e.kind == dnnl_prelu && (e.prelu_mask & 1)))
-                binary_known = false; // an operand with M rows needs the M
-        if (!ok || !strides_known || !binary_known) {
+                && (pd->bias.ndims == 0 || pd->bias.ndims == 2);
+        if (!ok) {
             delete pd;
             return dnnl_unimplemented;
         }
+        dnnl_primitive_desc chk = *pd;
+        apply_stand_ins(chk);
+        dnnl_status_t rst = dense_desc_check(chk.src, chk.wei, chk.bias.ndims ? &chk.bias : nullptr, chk.dst);
+        if (rst == dnnl_success) {
+            for (auto &e : chk.attr.post_ops.entries)
+                if (e.kind == dnnl_sum && e.sum_dt == dnnl_data_type_undef) e.sum_dt = chk.dst.data_type;
+            build_prelu_mds(chk);
+            rst = dense_attr_check(chk);
+        }
+        if (rst == dnnl_success) rst = select_impl(chk, 0);
+        if (rst != dnnl_success) {
+            delete pd;
+            return rst;
+        }
         pd->runtime_m = true;
-        pd->src.dims[0] = pd->dst.dims[0] = 1;
+        pd->impl = chk.impl; pd->impl_name = chk.impl_name;
+        pd->scratch_bytes = chk.scratch_bytes; pd->scratchpad = chk.scratchpad;
+        for (auto &e : pd->attr.post_ops.entries)
+            if (e.kind == dnnl_sum && e.sum_dt == dnnl_data_type_undef) e.sum_dt = pd->dst.data_type;
+        // `any` resolves to row-major here as everywhere; strides that depend on an open dim stay open
+        for (auto *md : {&pd->src, &pd->wei, &pd->dst, &pd->bias})
+            if (md->ndims == 2 && md->format_kind == dnnl_format_kind_any) {
+                md->format_kind = dnnl_blocked;
+                md->strides[1] = 1;
+                md->strides[0] = md->dims[1];
+            }
+        fill_quant_mds(*pd);
+        *primitive_desc = pd;
+        return dnnl_success;
     }
 
     dnnl_status_t st = pd->grouped ? grouped_desc_check(pd->src, pd->wei, bias, pd->dst)
@@ -680,39 +779,14 @@ dnnl_status_t dnnl_matmul_primitive_desc_create(dnnl_primitive_desc_t *primitive
             if (e.kind == dnnl_binary) set_default_format(e.src1);
         for (auto &e : pd->attr.post_ops.entries)
             if (e.kind == dnnl_sum && e.sum_dt == dnnl_data_type_undef) e.sum_dt = pd->dst.data_type;
-        // prelu: f32 weights over the dst dims its mask names, dense, with dim 1 innermost beyond two
-        // dims (ab, acb, acdb, acdeb: src/cpu/primitive_attr_postops.cpp:219-242); kept in src1 so that
-        // the kernels see it as a binary operand
-        for (auto &e : pd->attr.post_ops.entries)
-            if (e.kind == dnnl_prelu && !pd->grouped) {
-                const int nd = pd->dst.ndims;
-                dnnl_memory_desc w;
-                w.ndims = nd;
-                w.data_type = dnnl_f32;
-                w.format_kind = dnnl_blocked;
-                for (int d = 0; d < nd; ++d) w.dims[d] = ((e.prelu_mask >> d) & 1) ? pd->dst.dims[d] : 1;
-                int order[DNNL_MAX_NDIMS]; // outermost first
-                int k = 0;
-                if (nd <= 2) for (int d = 0; d < nd; ++d) order[k++] = d;
-                else {
-                    order[k++] = 0;
-                    for (int d = 2; d < nd; ++d) order[k++] = d;
-                    order[k++] = 1;
-                }
-                dnnl_dim_t acc = 1;
-                for (int i = nd - 1; i >= 0; --i) {
-                    w.strides[order[i]] = acc;
-                    acc *= w.dims[order[i]] == 0 ? 1 : w.dims[order[i]];
-                }
-                e.src1 = w;
-            }
+        build_prelu_mds(*pd);
         st = pd->grouped ? grouped_attr_check(*pd) : dense_attr_check(*pd);
     }
     // Batched (ndims > 2, src/common/matmul.cpp:630-744 with broadcast of size-1 batch dims): the
     // implementation is chosen for the 2D core and run once per matrix of the batch.
     const bool batched = st == dnnl_success && !pd->grouped && pd->dst.ndims > 2;
     if (batched) {
-        if (pd->runtime_m || pd->src.format_kind != dnnl_blocked || pd->wei.format_kind != dnnl_blocked
+        if (pd->src.format_kind != dnnl_blocked || pd->wei.format_kind != dnnl_blocked
                 || pd->dst.format_kind != dnnl_blocked)
             st = dnnl_unimplemented;
         dnnl_primitive_desc core;
@@ -731,7 +805,6 @@ dnnl_status_t dnnl_matmul_primitive_desc_create(dnnl_primitive_desc_t *primitive
         return st;
     }
     fill_quant_mds(*pd);
-    if (pd->runtime_m) pd->src.dims[0] = pd->dst.dims[0] = DNNL_RUNTIME_DIM_VAL; // what queries report
     *primitive_desc = pd;
     return dnnl_success;
 }
@@ -740,7 +813,10 @@ dnnl_status_t dnnl_primitive_desc_next_impl(dnnl_primitive_desc_t pd) {
     if (!pd) return dnnl_invalid_arguments;
     if (pd->kind != dnnl_matmul) return dnnl_last_impl_reached; // one reorder implementation
     dnnl_primitive_desc tmp = *pd;
-    if (tmp.runtime_m) tmp.src.dims[0] = tmp.dst.dims[0] = 1;
+    if (tmp.runtime_m) {
+        apply_stand_ins(tmp);
+        build_prelu_mds(tmp);
+    }
     if (pd->batched && batch_core(*pd, tmp) != dnnl_success) return dnnl_last_impl_reached;
     dnnl_status_t st = select_impl(tmp, pd->impl + 1);
     if (st != dnnl_success) return dnnl_last_impl_reached;
@@ -1108,23 +1184,36 @@ extern "C" dnnl_status_t dnnl_primitive_execute(const_dnnl_primitive_t primitive
         if (!args[i].memory) return dnnl_invalid_arguments;
     if (primitive->pd.kind == dnnl_reorder) return execute_reorder(primitive->pd, stream, nargs, args);
     arg_map_t am {args, nargs};
-    // A primitive created with M left open takes M from the src / dst memory objects, checks the
-    // rest of their descriptors against its own and chooses the implementation (and the scratch
-    // it needs) for this M.
+    // A primitive created with dims left open takes them from the memory objects: every descriptor
+    // must agree with what the primitive descriptor does state (rank, data type, the known dims);
+    // then the shapes are checked together and the implementation (and its scratch) chosen.
     dnnl_primitive_desc settled;
     if (primitive->pd.runtime_m) {
-        dnnl_memory_t s = am.find(DNNL_ARG_SRC), d = am.find(DNNL_ARG_DST);
-        if (!s || !d) return dnnl_invalid_arguments;
         settled = primitive->pd;
-        const dnnl_memory_desc &sm = s->md, &dm = d->md;
-        if (sm.ndims != 2 || dm.ndims != 2 || sm.has_runtime_dims() || dm.has_runtime_dims() || sm.dims[0] != dm.dims[0]
-                || sm.dims[1] != settled.src.dims[1] || dm.dims[1] != settled.dst.dims[1]
-                || sm.data_type != settled.src.data_type || dm.data_type != settled.dst.data_type
-                || sm.format_kind != dnnl_blocked || dm.format_kind != dnnl_blocked)
-            return dnnl_invalid_arguments;
-        settled.src = sm;
-        settled.dst = dm;
         settled.runtime_m = false;
+        auto take = [&](dnnl_memory_desc &want, int arg) -> bool {
+            dnnl_memory_t m = am.find(arg);
+            if (!m) return false;
+            const dnnl_memory_desc &got = m->md;
+            if (got.ndims != want.ndims || got.has_runtime_dims() || got.data_type != want.data_type
+                    || got.format_kind != dnnl_blocked)
+                return false;
+            for (int d = 0; d < want.ndims; ++d)
+                if (want.dims[d] != DNNL_RUNTIME_DIM_VAL && want.dims[d] != got.dims[d]) return false;
+            want = got;
+            return true;
+        };
+        if (!take(settled.src, DNNL_ARG_SRC) || !take(settled.wei, DNNL_ARG_WEIGHTS) || !take(settled.dst, DNNL_ARG_DST))
+            return dnnl_invalid_arguments;
+        if (settled.bias.ndims && !take(settled.bias, DNNL_ARG_BIAS)) return dnnl_invalid_arguments;
+        for (size_t i = 0; i < settled.attr.post_ops.entries.size(); ++i) {
+            auto &e = settled.attr.post_ops.entries[i];
+            if (e.kind == dnnl_binary && e.src1.has_runtime_dims()
+                    && !take(e.src1, DNNL_ARG_ATTR_MULTIPLE_POST_OP((int)i) | DNNL_ARG_SRC_1))
+                return dnnl_invalid_arguments;
+        }
+        build_prelu_mds(settled);
+        fill_quant_mds(settled);
         dnnl_status_t rst = dense_desc_check(settled.src, settled.wei, settled.bias.ndims ? &settled.bias : nullptr, settled.dst);
         if (rst == dnnl_success) rst = dense_attr_check(settled);
         if (rst == dnnl_success) rst = select_impl(settled, 0);

@@ -150,8 +150,9 @@ struct dnnl_primitive_desc {
     dnnl_memory_desc src, wei, bias, dst, scratchpad;
     dnnl_primitive_attr attr;
     bool grouped = false;
-    // M is DNNL_RUNTIME_DIM_VAL in src / dst: shapes, implementation and scratch are settled per
-    // execution from the memory objects' descriptors (impl / impl_name describe M = 1)
+    // some of M, K, N (or strides) are DNNL_RUNTIME_DIM_VAL: shapes, implementation and scratch are
+    // settled per execution from the memory objects' descriptors (impl / impl_name describe the
+    // stand-in shape the descriptor was checked with at creation)
     bool runtime_m = false;
     bool batched = false; // ndims > 2: the implementation runs once per matrix of the batch
     int impl = IMPL_REF;

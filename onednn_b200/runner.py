@@ -19,7 +19,10 @@ def _md(t: W.QTensor):
 class Prepared:
     def __init__(self, p: W.Problem, eng, impl=None, user_scratchpad=False, runtime_m=False, dst_ld=None):
         """runtime_m: the primitive is created with M = DNNL_RUNTIME_DIM_VAL in src and dst (their
-        strides given), and learns M from the memory objects at execution.
+        strides given), and learns M from the memory objects at execution.  A pair (src mask, weights
+        mask) instead of True leaves open the dims whose bits are set (src: bit 0 = M, bit 1 = K;
+        weights: bit 0 = K, bit 1 = N), in dst, bias and binary operands too, together with the
+        strides that depend on them.
         dst_ld: row pitch of dst in elements when dst is a column slice of a wider matrix."""
         self.p, self.eng = p, eng
         self.user_scratchpad = user_scratchpad
@@ -69,11 +72,53 @@ class Prepared:
         if user_scratchpad:
             attr.set_scratchpad_mode(api.SCRATCHPAD_MODE_USER)
         self.attr = attr
-        pd_src, pd_dst = self.src_md, self.dst_md
-        if runtime_m:
+        pd_src, pd_wei, pd_dst, pd_bias, pd_attr = self.src_md, self.wei_md, self.dst_md, self.bias_md, attr
+        if runtime_m is True:
             pd_src = api.memory.desc((api.RUNTIME_DIM_VAL, p.K), p.src.dt, tuple(p.src.strides))
             pd_dst = api.memory.desc((api.RUNTIME_DIM_VAL, p.N), p.dst_dt, (p.N, 1))
-        self.pd = api.matmul.primitive_desc(eng, pd_src, self.wei_md, pd_dst, self.bias_md, attr)
+        elif runtime_m:
+            smask, wmask = runtime_m
+            open_m, open_k, open_n = bool(smask & 1), bool((smask & 2) or (wmask & 1)), bool(wmask & 2)
+
+            def opened(dims, strides, dt, flags):
+                """The descriptor with the flagged dims, and every stride that depends on one, left open."""
+                RT = api.RUNTIME_DIM_VAL
+                out, seen = list(strides), False
+                for d in sorted(range(len(dims)), key=lambda i: (strides[i], -i)):
+                    out[d] = RT if seen else strides[d]
+                    seen = seen or flags[d]
+                return api.memory.desc(tuple(RT if f else n for n, f in zip(dims, flags)), dt, tuple(out))
+
+            pd_src = opened((p.M, p.K), p.src.strides, p.src.dt, (bool(smask & 1), bool(smask & 2)))
+            pd_wei = opened((p.K, p.N), p.wei.strides, p.wei.dt, (bool(wmask & 1), bool(wmask & 2)))
+            pd_dst = opened((p.M, p.N), (p.N, 1), p.dst_dt, (open_m, open_n))
+            if p.bias is not None:
+                pd_bias = opened(p.bias.dims, p.bias.strides, p.bias.dt,
+                                 (open_m and p.bias.dims[0] > 1, open_n and p.bias.dims[1] > 1))
+            if any(e.kind == W.PO_BINARY for e in p.post_ops):
+                pd_attr = api.primitive_attr()
+                if p.apply_to_int or p.fpmath:
+                    pd_attr.set_fpmath_mode(p.fpmath, p.apply_to_int)
+                for name, q in p.quant.items():
+                    groups = tuple(q.groups) if tuple(q.groups) != (1, 1) else ()
+                    setter = pd_attr.set_scales if name.endswith("scale") else pd_attr.set_zero_points if name.endswith("zp") \
+                        else pd_attr.set_precomputed_reductions
+                    setter(arg_of[name[:3]], q.mask, groups, q.dt)
+                po2 = api.post_ops()
+                for e in p.post_ops:
+                    if e.kind == W.PO_SUM:
+                        po2.append_sum(e.scale, e.zero_point, 0)
+                    elif e.kind == W.PO_ELTWISE:
+                        po2.append_eltwise(e.alg, e.alpha, e.beta)
+                    elif e.kind == W.PO_PRELU:
+                        po2.append_prelu(sum(1 << d for d, n in enumerate(e.src1.dims) if n > 1))
+                    else:
+                        po2.append_binary(e.alg, opened(e.src1.dims, e.src1.strides, e.src1.dt,
+                                                        (open_m and e.src1.dims[0] > 1, open_n and e.src1.dims[1] > 1)))
+                pd_attr.set_post_ops(po2)
+                if user_scratchpad:
+                    pd_attr.set_scratchpad_mode(api.SCRATCHPAD_MODE_USER)
+        self.pd = api.matmul.primitive_desc(eng, pd_src, pd_wei, pd_dst, pd_bias, pd_attr)
         # descriptors of the quantization parameters come from a descriptor that knows M
         self.md_pd = api.matmul.primitive_desc(eng, self.src_md, self.wei_md, self.dst_md, self.bias_md, attr) \
             if runtime_m else self.pd

@@ -20,15 +20,15 @@ it is reported as SKIPPED with the reason (benchdnn's own word for a
 descriptor the library answers `unimplemented` to), never silently dropped.
 
 Handled: --reset, --batch, --dt, --stag/--wtag/--dtag (ab, ba, any), --bia-dt,
---bia_mask, --runtime_dims_masks (run-time M), --attr-scales,
+--bia_mask, --runtime_dims_masks (any of M, K, N of a 2D problem), --attr-scales,
 --attr-zero-points, --attr-post-ops (sum, eltwise, binary, prelu), --attr-fpmath,
 --attr-scratchpad.  Options that select implementations or engines
 (--skip-impl, --impl, --engine, --match ...) are accepted and ignored.
 Descriptors with batch dims (3D and more, size-1 dims broadcast, tags that
 permute the dims such as acb or bac) run as one batched primitive and are checked
 matrix by matrix against the oracle's 2D result.  --strides, --grouped,
-depthwise post-ops, run-time K or N and the remaining attributes are skipped with
-their name as the reason.
+depthwise post-ops, run-time dims of batched problems and the remaining attributes
+are skipped with their name as the reason.
 
 Policy names follow attr_t::policy2mask (tests/benchdnn/dnn_types.cpp:218-268):
 for the matmul's src / weights / dst, `per_oc` and `per_dim_1` are the last
@@ -278,10 +278,10 @@ def build(settings, desc, seed=None):
     rt = settings["runtime_dims_masks"] or "0"
     rs, _, rw = rt.partition(":")
     rs, rw = int(rs or 0), int(rw or 0)
-    if rs == 1 and rw == 0:
-        opts["runtime_m"] = True
-    elif rs or rw:
-        raise Skip("run-time K or N")
+    if rs > 3 or rw > 3:
+        raise Skip("run-time mask of a dim the problem does not have")
+    if rs or rw:
+        opts["runtime_m"] = True if (rs, rw) == (1, 0) else (rs, rw)
 
     dims_of = {"src": (M, K), "wei": (K, N), "dst": (M, N)}
     quant = {}

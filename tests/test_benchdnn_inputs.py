@@ -61,7 +61,9 @@ def test_policy_names_give_the_masks_benchdnn_gives_a_matmul():
     p, opts = B.build(s, "4x64:64x32")
     assert p.quant["src_scale"].mask == 1 and p.quant["src_zp"].mask == 2 and p.quant["dst_zp"].mask == 2
     assert float(p.quant["dst_scale"].data[0, 0]) == 4.0 and opts["runtime_m"]
-    for bad in ({"runtime_dims_masks": "3:1"}, {"strides": "8x1::"}, {"attr-post-ops": "dw:k3s1p1"},
+    _, opts = B.build(dict(s, runtime_dims_masks="3:1"), "4x64:64x32")
+    assert opts["runtime_m"] == (3, 1)
+    for bad in ({"runtime_dims_masks": "4:1"}, {"strides": "8x1::"}, {"attr-post-ops": "dw:k3s1p1"},
                 {"dt": "f64"}, {"dtag": "ba"}):
         with pytest.raises(B.Skip):
             B.build(dict(s, **bad), "4x64:64x32")

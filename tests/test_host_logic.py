@@ -235,8 +235,9 @@ def test_user_scratchpad_descriptor(host_engine):
 
 
 def test_runtime_m_descriptor(host_engine):
-    """DNNL_RUNTIME_DIM_VAL for M (src/common/matmul.cpp:630-744; the reference's int8 inference
-    tutorial): accepted for the rows of a 2D problem, reported back by the queries, refused elsewhere."""
+    """DNNL_RUNTIME_DIM_VAL (src/common/matmul.cpp:630-744; the reference's int8 inference tutorial
+    leaves M open): accepted for any of M, K, N of a dense 2D problem, reported back by the queries,
+    refused for batched and grouped problems."""
     RT = api.RUNTIME_DIM_VAL
     open_md = md((RT, 64), W.U8, (64, 1))
     assert open_md.get_dims() == (RT, 64) and open_md.get_strides() == (64, 1)
@@ -247,11 +248,20 @@ def test_runtime_m_descriptor(host_engine):
     pd = api.matmul.primitive_desc(host_engine, open_md, md((64, 48), W.S8, tag.any), md((RT, 48), W.S32, (48, 1)), None, a)
     assert pd.impl_info_str().startswith("cuda:")
     assert pd.src_desc().get_dims() == (RT, 64) and pd.weights_desc().get_strides() == (48, 1)
-    # K or N left open, or a row-dependent stride: not built
-    assert status_of(lambda: api.matmul.primitive_desc(host_engine, md((8, RT), W.U8, (64, 1)), md((RT, 48), W.S8, (48, 1)),
-                                                        md((8, 48), W.S32, (48, 1)))) == api.unimplemented
-    assert status_of(lambda: api.matmul.primitive_desc(host_engine, md((RT, 64), W.U8, tag.ba), md((64, 48), W.S8, tag.ab),
-                                                        md((RT, 48), W.S32, tag.ab))) == api.unimplemented
+    # K and N left open, with the strides that depend on them; the parameter descriptors stay open too
+    pd = api.matmul.primitive_desc(host_engine, md((8, RT), W.U8, (RT, 1)), md((RT, RT), W.S8, (RT, 1)),
+                                   md((8, RT), W.S32, (RT, 1)), None, a)
+    assert pd.impl_info_str().startswith("cuda:")
+    assert pd.weights_desc().get_dims() == (RT, RT) and pd.dst_desc().get_dims() == (8, RT)
+    assert pd.query_md(api.QUERY_EXEC_ARG_MD, api.ARG_ATTR_SCALES | WEI).get_dims() == (1, RT)
+    # a row-dependent stride (src stored transposed with M open)
+    pd = api.matmul.primitive_desc(host_engine, md((RT, 64), W.U8, tag.ba), md((64, 48), W.S8, tag.ab), md((RT, 48), W.S32, tag.ab))
+    assert pd.src_desc().get_dims() == (RT, 64)
+    # dims that contradict one another are refused at creation, batched problems with open dims are not built
+    assert status_of(lambda: api.matmul.primitive_desc(host_engine, md((RT, 64), W.U8, (64, 1)), md((32, 48), W.S8, (48, 1)),
+                                                        md((RT, 48), W.S32, (48, 1)))) == api.invalid_arguments
+    assert status_of(lambda: api.matmul.primitive_desc(host_engine, md((2, RT, 64), W.U8, (RT, 64, 1)), md((2, 64, 48), W.S8, tag.abc),
+                                                        md((2, RT, 48), W.S32, (RT, 48, 1)))) == api.unimplemented
 
 
 def test_value_names_and_late_post_op_calls():

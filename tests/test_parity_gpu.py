@@ -343,6 +343,37 @@ def test_runtime_m_matches_oracle(gpu, name):
         assert_parity(got, O.run_port(p), p.dst_dt, "%s M=%d" % (name, M), slack_for(p, impl))
 
 
+@pytest.mark.gpu
+def test_one_primitive_serves_several_shapes(gpu):
+    """M, K and N all DNNL_RUNTIME_DIM_VAL (and the strides that depend on them): ONE primitive
+    object executes problems of different shapes, settling shapes, implementation and the
+    zero-point scratch from the memory objects of each call."""
+    from onednn_b200.runner import Prepared
+    eng, strm = gpu
+    first = None
+    for M, K, N in ((24, 256, 128), (100, 512, 384), (7, 80, 48), (24, 256, 128)):
+        p = W.int8_zp(M, K, N, per_n_scales=True)
+        r = Prepared(p, eng, runtime_m=(3, 3)).upload()
+        first = first or r
+        assert first.pd.src_desc().get_dims() == (api_rt(), api_rt())
+        first.prim.execute(strm, r.args)
+        strm.wait()
+        assert_parity(r.download(), O.run_port(p), p.dst_dt, "run-time M, K, N = %d, %d, %d" % (M, K, N))
+    # memory objects that contradict what the descriptor states are refused
+    from onednn_b200 import api
+    p = W.int8_zp(16, 64, 32)
+    fixed_k = Prepared(p, eng, runtime_m=(1, 2)).upload()  # M and N open, K = 64 stated
+    other = Prepared(W.int8_zp(16, 128, 32), eng).upload()
+    with pytest.raises(api.error) as ei:
+        fixed_k.prim.execute(strm, other.args)
+    assert ei.value.status == api.invalid_arguments
+
+
+def api_rt():
+    from onednn_b200 import api
+    return api.RUNTIME_DIM_VAL
+
+
 def test_two_engines_in_one_process(gpu):
     """An engine per device in one process (the ordinary oneDNN usage): the opt-in to large shared
     memory belongs to the (kernel, device) pair, so every kernel family must launch on the second
