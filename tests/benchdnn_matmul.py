@@ -22,11 +22,11 @@ descriptor the library answers `unimplemented` to), never silently dropped.
 Handled: --reset, --batch, --dt, --stag/--wtag/--dtag (ab, ba, any), --bia-dt,
 --bia_mask, --runtime_dims_masks (any of M, K, N of a 2D problem), --attr-scales,
 --attr-zero-points, --attr-post-ops (sum, eltwise, binary, prelu), --attr-fpmath,
---attr-scratchpad.  Options that select implementations or engines
+--attr-scratchpad, --strides.  Options that select implementations or engines
 (--skip-impl, --impl, --engine, --match ...) are accepted and ignored.
 Descriptors with batch dims (3D and more, size-1 dims broadcast, tags that
 permute the dims such as acb or bac) run as one batched primitive and are checked
-matrix by matrix against the oracle's 2D result.  --strides, --grouped,
+matrix by matrix against the oracle's 2D result.  --grouped,
 depthwise post-ops, run-time dims of batched problems and the remaining attributes
 are skipped with their name as the reason.
 
@@ -50,7 +50,7 @@ from onednn_b200 import workloads as W  # noqa: E402
 DT = {"f16": W.F16, "bf16": W.BF16, "f32": W.F32, "s32": W.S32, "s8": W.S8, "u8": W.U8,
       "f8_e5m2": W.F8_E5M2, "f8_e4m3": W.F8_E4M3, "s4": W.S4, "u4": W.U4}
 
-DEFAULTS = {"dt": "f32", "stag": "ab", "wtag": "ab", "dtag": "ab", "bia-dt": "undef", "bia_mask": "2",
+DEFAULTS = {"dt": "f32", "stag": "abx", "wtag": "abx", "dtag": "abx", "bia-dt": "undef", "bia_mask": "2",
             "runtime_dims_masks": "0", "attr-scales": "", "attr-zero-points": "", "attr-post-ops": "",
             "attr-fpmath": "", "attr-scratchpad": "library", "strides": "", "grouped": "",
             "attr-precomputed-reductions": "", "attr-dropout": "", "attr-acc-mode": "", "encoding": "",
@@ -61,7 +61,7 @@ IGNORED = {"skip-impl", "impl", "engine", "match", "allow-enum-tags-only", "chec
            "cold-cache", "stream-kind", "global-impl", "global-skip-impl", "start", "repeats-per-prb",
            "summary", "bia_dt"}
 # named here so that a file using them is reported, not mis-run
-UNSUPPORTED = ("strides", "grouped", "attr-precomputed-reductions", "attr-dropout", "attr-acc-mode", "encoding",
+UNSUPPORTED = ("grouped", "attr-precomputed-reductions", "attr-dropout", "attr-acc-mode", "encoding",
                "attr-rounding-mode", "attr-deterministic")
 
 ELTWISE_ALIAS = {"srelu": "soft_relu"}
@@ -206,7 +206,43 @@ def _fill(r, dt, shape, role):
     return W.to_storage(v, dt)
 
 
-def _tensor(r, dt, dims, tag, role):
+def _split_strides(text, nd):
+    """'8x1::9x1' -> [(8, 1), None, (9, 1)]: element strides of src, weights and dst (None = by tag)."""
+    parts = (text.split(":") + ["", "", ""])[:3] if text else ["", "", ""]
+    out = []
+    for t in parts:
+        if not t:
+            out.append(None)
+            continue
+        st = tuple(int(x) for x in t.split("x"))
+        if len(st) != nd or any(v < 0 for v in st):
+            raise Skip("strides " + t)
+        out.append(st)
+    return out
+
+
+def _scatter(logical, strides):
+    """Storage of a logical array laid out with the given element strides (the gaps are zero)."""
+    offs = sum(np.arange(n).reshape([-1 if i == d else 1 for i in range(logical.ndim)]) * s
+               for d, (n, s) in enumerate(zip(logical.shape, strides)))
+    offs = np.broadcast_to(offs, logical.shape).reshape(-1)
+    if np.unique(offs).size != offs.size:
+        raise Skip("strides under which elements overlap")
+    storage = np.zeros(int(offs.max()) + 1 if offs.size else 0, logical.dtype)
+    storage[offs] = logical.reshape(-1)
+    return storage
+
+
+def _gather(storage, dims, strides):
+    isz = storage.itemsize
+    return np.lib.stride_tricks.as_strided(storage, dims, tuple(s * isz for s in strides))
+
+
+def _tensor(r, dt, dims, tag, role, strides=None):
+    if strides is not None:
+        if dt in (W.S4, W.U4):
+            raise Skip("strides of a 4-bit tensor")
+        return W.QTensor(_scatter(_fill(r, dt, dims, role), strides), dt, dims, strides)
     if tag in ("ab", "any", "abx"):
         return W.QTensor(_fill(r, dt, dims, role), dt, dims)
     if tag == "ba":
@@ -257,12 +293,15 @@ def build(settings, desc, seed=None):
     sdt, wdt, ddt = (DT[d] for d in dts)
     if ddt not in (W.F32, W.S32, W.BF16, W.F16, W.S8, W.U8, W.F8_E4M3, W.F8_E5M2):
         raise Skip("dst type " + dts[2])
-    if settings["dtag"] not in ("ab", "any", "abx"):
-        raise Skip("dst tag " + settings["dtag"])
     if wdt in (W.S4, W.U4) and N % 2 and settings["wtag"] != "ba":
         raise Skip("4-bit weights with odd N")
-    src = _tensor(r, sdt, (M, K), settings["stag"], "src")
-    wei = _tensor(r, wdt, (K, N), settings["wtag"], "wei")
+    s_st, w_st, d_st = _split_strides(settings["strides"], 2)
+    if d_st is None and settings["dtag"] not in ("ab", "any", "abx"):
+        raise Skip("dst tag " + settings["dtag"])
+    if d_st is not None and (d_st[1] != 1 or d_st[0] < N):
+        raise Skip("dst strides other than a row pitch")
+    src = _tensor(r, sdt, (M, K), settings["stag"], "src", s_st)
+    wei = _tensor(r, wdt, (K, N), settings["wtag"], "wei", w_st)
 
     bias = None
     if settings["bia-dt"] != "undef":
@@ -274,7 +313,8 @@ def build(settings, desc, seed=None):
         bdims = (M if bm & 1 else 1, N if bm & 2 else 1)
         bias = W.QTensor(_fill(r, DT[settings["bia-dt"]], bdims, "bias"), DT[settings["bia-dt"]], bdims)
 
-    opts = {"runtime_m": False, "user_scratchpad": settings["attr-scratchpad"] == "user"}
+    opts = {"runtime_m": False, "user_scratchpad": settings["attr-scratchpad"] == "user",
+            "dst_ld": None if d_st is None else d_st[0]}
     rt = settings["runtime_dims_masks"] or "0"
     rs, _, rw = rt.partition(":")
     rs, rw = int(rs or 0), int(rw or 0)
@@ -351,6 +391,10 @@ def build(settings, desc, seed=None):
 
     p = W.Problem(name or desc, M, N, K, src, wei, ddt, bias, quant, post_ops, apply_to_int, fpmath)
     p.dst_init = dst_init
+    if s_st is not None or w_st is not None:  # the same problem with dense tensors, for the allowance formulas
+        dense = [W.QTensor(np.ascontiguousarray(_gather(t.data, t.dims, t.strides)), t.dt, t.dims) for t in (src, wei)]
+        opts["dense"] = W.Problem(p.name, M, N, K, dense[0], dense[1], ddt, bias, quant, post_ops, apply_to_int, fpmath)
+        opts["dense"].dst_init = dst_init
     return p, opts
 
 
@@ -432,9 +476,12 @@ def build_batched(settings, desc):
     bp.user_scratchpad = settings["attr-scratchpad"] == "user"
     src_l = _fill(r, sdt, sdims, "src")
     wei_l = _fill(r, wdt, wdims, "wei")
-    bp.tensors["src"] = (*_layout(src_l, _tag_order(settings["stag"], nd)), sdt, sdims)
-    bp.tensors["wei"] = (*_layout(wei_l, _tag_order(settings["wtag"], nd)), wdt, wdims)
-    bp.dst_order = _tag_order(settings["dtag"], nd)
+    s_st, w_st, d_st = _split_strides(settings["strides"], nd)
+    bp.tensors["src"] = (_scatter(src_l, s_st), s_st, sdt, sdims) if s_st is not None \
+        else (*_layout(src_l, _tag_order(settings["stag"], nd)), sdt, sdims)
+    bp.tensors["wei"] = (_scatter(wei_l, w_st), w_st, wdt, wdims) if w_st is not None \
+        else (*_layout(wei_l, _tag_order(settings["wtag"], nd)), wdt, wdims)
+    bp.dst_strides = d_st if d_st is not None else _layout(np.empty(ddims, np.uint8), _tag_order(settings["dtag"], nd))[1]
     bias_l = None
     if settings["bia-dt"] != "undef":
         if settings["bia-dt"] not in DT:
@@ -509,7 +556,7 @@ def build_batched(settings, desc):
         if mode not in modes:
             raise Skip("fpmath " + mode)
         bp.fpmath, bp.apply_to_int = modes[mode], flag == "true"
-    bp.dst_init = None if dst_init_l is None else _layout(dst_init_l, bp.dst_order)[0]
+    bp.dst_init = None if dst_init_l is None else _scatter(dst_init_l, bp.dst_strides)
 
     def pick(arr, idx):  # the matrix of `arr` that batch index idx sees (size-1 dims broadcast)
         return arr[tuple(i if arr.shape[d] > 1 else 0 for d, i in enumerate(idx))]
@@ -541,8 +588,7 @@ def run_batched(bp, eng, strm, impl=None):
     from onednn_b200 import api
     md = {k: api.memory.desc(dims, dt, strides) for k, (_, strides, dt, dims) in bp.tensors.items()}
     nd = len(bp.ddims)
-    dst_strides = _layout(np.empty(bp.ddims, np.uint8), bp.dst_order)[1]
-    dst_md = api.memory.desc(bp.ddims, bp.ddt, dst_strides)
+    dst_md = api.memory.desc(bp.ddims, bp.ddt, tuple(bp.dst_strides))
     attr = api.primitive_attr()
     if bp.apply_to_int or bp.fpmath:
         attr.set_fpmath_mode(bp.fpmath, bp.apply_to_int)
@@ -603,9 +649,7 @@ def run_batched(bp, eng, strm, impl=None):
     prim.execute(strm, args)
     strm.wait()
     raw = args[api.ARG_DST].read(np.uint8, 0).view(W.NP_STORAGE[bp.ddt])
-    phys_shape = tuple(bp.ddims[d] for d in bp.dst_order)
-    inverse = np.argsort(bp.dst_order)
-    return raw[:int(np.prod(phys_shape))].reshape(phys_shape).transpose(inverse), pd.impl_info_str(), pd
+    return _gather(raw, bp.ddims, bp.dst_strides), pd.impl_info_str(), pd
 
 
 # ------------------------------------------------------------------ checking
@@ -665,25 +709,37 @@ def run_one(settings, desc, eng, strm, all_impls=False):
             return _run_one_batched(settings, desc, eng, strm, all_impls)
         return "SKIPPED", str(e)
     try:
-        first = Prepared(p, eng, None, opts["user_scratchpad"], opts["runtime_m"])
+        first = Prepared(p, eng, None, opts["user_scratchpad"], opts["runtime_m"], opts["dst_ld"])
     except api.error as e:
         if e.status == api.unimplemented:
             return "SKIPPED", "unimplemented"
         return "FAILED", "create: %s" % e
     want = O.run_port(p)
-    libm_slack = cancellation_slack(p)
+    dense = opts.get("dense", p)
+    libm_slack = cancellation_slack(dense)
+    ld = opts["dst_ld"]
+    p_lib = p
+    if ld is not None and p.dst_init is not None:  # the old dst values at the row pitch the library is given
+        import copy
+        p_lib = copy.copy(p)
+        p_lib.dst_init = _scatter(p.dst_init.reshape(p.M, p.N), (ld, 1))
     impls = [first.impl]
     if all_impls:
         while first.pd.next_impl():
             impls.append(first.pd.impl_info_str())
     for impl in impls:
-        run = Prepared(p, eng, impl, opts["user_scratchpad"], opts["runtime_m"]).upload()
+        run = Prepared(p_lib, eng, impl, opts["user_scratchpad"], opts["runtime_m"], ld).upload()
         run.execute(strm)
         strm.wait()
         slack = libm_slack
         if not impl.startswith("cuda:ref") and p.src.dt not in (W.S8, W.U8):
-            slack = summation_slack(p) + (0.0 if libm_slack is None else libm_slack)
-        ok, why = compare(run.download(), want, p.dst_dt, slack)
+            slack = summation_slack(dense) + (0.0 if libm_slack is None else libm_slack)
+        if ld is None:
+            got = run.download()
+        else:
+            raw = run.args[api.ARG_DST].read(np.uint8, 0).view(W.NP_STORAGE[p.dst_dt])
+            got = np.ascontiguousarray(_gather(raw, (p.M, p.N), (ld, 1)))
+        ok, why = compare(got, want, p.dst_dt, slack)
         if not ok:
             return "FAILED", "%s: %s" % (impl, why)
     return "PASSED", ",".join(impls)

@@ -63,7 +63,9 @@ def test_policy_names_give_the_masks_benchdnn_gives_a_matmul():
     assert float(p.quant["dst_scale"].data[0, 0]) == 4.0 and opts["runtime_m"]
     _, opts = B.build(dict(s, runtime_dims_masks="3:1"), "4x64:64x32")
     assert opts["runtime_m"] == (3, 1)
-    for bad in ({"runtime_dims_masks": "4:1"}, {"strides": "8x1::"}, {"attr-post-ops": "dw:k3s1p1"},
+    sp, so = B.build(dict(s, strides="80x1::40x1"), "4x64:64x32")
+    assert sp.src.strides == (80, 1) and sp.src.data.size == 3 * 80 + 64 and so["dst_ld"] == 40 and so["dense"].src.strides == (64, 1)
+    for bad in ({"runtime_dims_masks": "4:1"}, {"strides": "8x1::"}, {"strides": "::1x4"}, {"attr-post-ops": "dw:k3s1p1"},
                 {"dt": "f64"}, {"dtag": "ba"}):
         with pytest.raises(B.Skip):
             B.build(dict(s, **bad), "4x64:64x32")
@@ -115,7 +117,7 @@ def _pin(path, host_engine, max_macs, known_stricter=()):
         except RuntimeError:
             want = None
         try:
-            Prepared(p, host_engine, None, opts["user_scratchpad"], opts["runtime_m"])
+            Prepared(p, host_engine, None, opts["user_scratchpad"], opts["runtime_m"], opts["dst_ld"])
             mine = True
         except api.error as e:
             assert e.status == api.unimplemented, line
