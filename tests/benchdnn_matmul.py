@@ -21,7 +21,8 @@ descriptor the library answers `unimplemented` to), never silently dropped.
 
 Handled: --reset, --batch, --dt, --stag/--wtag/--dtag (ab, ba, any), --bia-dt,
 --bia_mask, --runtime_dims_masks (any of M, K, N of a 2D problem), --attr-scales,
---attr-zero-points, --attr-post-ops (sum, eltwise, binary, prelu), --attr-fpmath,
+--attr-zero-points, --attr-precomputed-reductions, --attr-post-ops (sum, eltwise,
+binary, prelu), --attr-fpmath,
 --attr-scratchpad, --strides.  Options that select implementations or engines
 (--skip-impl, --impl, --engine, --match ...) are accepted and ignored.
 Descriptors with batch dims (3D and more, size-1 dims broadcast, tags that
@@ -61,7 +62,7 @@ IGNORED = {"skip-impl", "impl", "engine", "match", "allow-enum-tags-only", "chec
            "cold-cache", "stream-kind", "global-impl", "global-skip-impl", "start", "repeats-per-prb",
            "summary", "bia_dt"}
 # named here so that a file using them is reported, not mis-run
-UNSUPPORTED = ("grouped", "attr-precomputed-reductions", "attr-dropout", "attr-acc-mode", "encoding",
+UNSUPPORTED = ("grouped", "attr-dropout", "attr-acc-mode", "encoding",
                "attr-rounding-mode", "attr-deterministic")
 
 ELTWISE_ALIAS = {"srelu": "soft_relu"}
@@ -160,6 +161,7 @@ def _quant_entries(text):
     for entry in filter(None, text.split("+")):
         f = entry.split(":")
         arg, policy = f[0], (f[1] if len(f) > 1 else "common")
+        arg = {"src0": "src", "src1": "wei"}.get(arg, arg)
         if arg not in ("src", "wei", "dst"):
             raise Skip("argument " + arg)
         value, dt, groups = None, None, (1, 1)
@@ -345,10 +347,22 @@ def build(settings, desc, seed=None):
             vals = r.integers(lo, hi, shp)
         quant[arg + "_zp"] = W.Quant(W.to_storage(vals, dt), dt, mask, groups)
 
+    for arg, policy, value, dt, groups in _quant_entries(settings["attr-precomputed-reductions"]):
+        # the sums of the src values over each K group, which the library may use in place of
+        # adding them up itself when it applies weights zero-points
+        mask = _policy_mask(policy, 2, True)
+        if arg != "src" or sdt not in (W.S8, W.U8) or mask != 3 or groups[0] != 1 or K % groups[1]:
+            raise Skip("precomputed reductions other than src sums per K group")
+        logical = _gather(src.data, src.dims, src.strides).astype(np.int64)
+        sums = logical.reshape(M, K // groups[1], groups[1]).sum(axis=2)
+        dt = W.S32 if dt is None else dt
+        quant["src_pr"] = W.Quant(W.to_storage(sums, dt), dt, mask, groups)
+
     post_ops, dst_init = [], None
     for entry in filter(None, settings["attr-post-ops"].split("+")):
         f = entry.split(":")
-        kind = ELTWISE_ALIAS.get(f[0], f[0])
+        kind = f[0][8:] if f[0].startswith("eltwise_") else f[0][7:] if f[0].startswith("binary_") else f[0]
+        kind = ELTWISE_ALIAS.get(kind, kind)
         if kind == "sum":
             scale = float(f[1]) if len(f) > 1 and f[1] else 1.0
             zp = int(f[2]) if len(f) > 2 and f[2] else 0

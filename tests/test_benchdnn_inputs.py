@@ -142,7 +142,9 @@ def test_own_input_file_restatement_matches_the_live_reference(host_engine):
     assert ran > 2000 and rejected > 0  # a sum zero-point with a float dst is refused by both
 
 
-@pytest.mark.parametrize("name,max_macs,least", [("test_matmul_all", 2000000, 9000), ("test_matmul_ci", 300000, 100)])
+@pytest.mark.parametrize("name,max_macs,least", [
+    ("test_matmul_all", 2000000, 9000), ("test_matmul_ci", 300000, 100), ("harness_matmul_strides", 300000, 150),
+    ("harness_matmul_precomp_reductions", 3000000, 20), ("harness_matmul_regression", 300000, 30)])
 def test_reference_input_files_restatement_matches_the_live_reference(host_engine, name, max_macs, least):
     ref = reference_dir()
     if ref is None or not O.ref_available():
