@@ -531,7 +531,8 @@ def build_batched(settings, desc):
     binaries = {}
     for i, entry in enumerate(filter(None, settings["attr-post-ops"].split("+"))):
         f = entry.split(":")
-        kind = ELTWISE_ALIAS.get(f[0], f[0])
+        kind = f[0][8:] if f[0].startswith("eltwise_") else f[0][7:] if f[0].startswith("binary_") else f[0]
+        kind = ELTWISE_ALIAS.get(kind, kind)
         if kind == "sum":
             if len(f) > 3 and f[3] and DT.get(f[3]) != ddt:
                 raise Skip("sum with a data type other than dst's")
@@ -544,7 +545,7 @@ def build_batched(settings, desc):
             bp.post_ops.append(W.PostOp(W.PO_ELTWISE, W.ELTWISE[kind], float(f[1]) if len(f) > 1 and f[1] else 0.0,
                                         float(f[2]) if len(f) > 2 and f[2] else 0.0, 1.0))
         elif kind in W.BINARY:
-            if len(f) < 2 or f[1] not in DT or (len(f) > 3 and f[3] not in ("", "any", "abx")):
+            if len(f) < 2 or f[1] not in DT or (len(f) > 3 and f[3] and _tag_order(f[3], nd) != tuple(range(nd))):
                 raise Skip("binary post-op " + entry)
             mask = _policy_mask(f[2] if len(f) > 2 and f[2] else "common", nd, False)
             odims = tuple(d if (mask >> j) & 1 else 1 for j, d in enumerate(ddims))
