@@ -258,8 +258,9 @@ def _tensor(r, dt, dims, tag, role, strides=None):
     raise Skip("tag " + tag)
 
 
-def build(settings, desc, seed=None):
-    """(Problem, run options) of one expanded benchdnn problem, or raises Skip."""
+def build(settings, desc, seed=None, max_macs=None):
+    """(Problem, run options) of one expanded benchdnn problem, or raises Skip.
+    max_macs: problems with more multiply-adds are skipped before any data is made."""
     if settings.get("_unknown"):
         raise Skip("option --" + settings["_unknown"][0])
     for k in UNSUPPORTED:
@@ -284,6 +285,8 @@ def build(settings, desc, seed=None):
         raise Skip("descriptor " + desc)
     if 0 in (M, K, N):
         raise Skip("zero dim")
+    if max_macs is not None and M * K * N > max_macs:
+        raise Skip("larger than the cap")
     r = np.random.Generator(np.random.PCG64(zlib.crc32((command_line(settings, desc)).encode())
                                             if seed is None else seed))
 
