@@ -27,8 +27,8 @@ binary, prelu), --attr-fpmath,
 (--skip-impl, --impl, --engine, --match ...) are accepted and ignored.
 Descriptors with batch dims (3D and more, size-1 dims broadcast, tags that
 permute the dims such as acb or bac) run as one batched primitive and are checked
-matrix by matrix against the oracle's 2D result.  --grouped,
-depthwise post-ops, run-time dims of batched problems and the remaining attributes
+matrix by matrix against the oracle's 2D result.  --grouped=0:G:sizes with a
+MxK:GxKxN descriptor is a grouped (MoE) problem.  Depthwise post-ops, run-time dims of batched problems and the remaining attributes
 are skipped with their name as the reason.
 
 Policy names follow attr_t::policy2mask (tests/benchdnn/dnn_types.cpp:218-268):
@@ -62,7 +62,7 @@ IGNORED = {"skip-impl", "impl", "engine", "match", "allow-enum-tags-only", "chec
            "cold-cache", "stream-kind", "global-impl", "global-skip-impl", "start", "repeats-per-prb",
            "summary", "bia_dt"}
 # named here so that a file using them is reported, not mis-run
-UNSUPPORTED = ("grouped", "attr-dropout", "attr-acc-mode", "encoding",
+UNSUPPORTED = ( "attr-dropout", "attr-acc-mode", "encoding",
                "attr-rounding-mode", "attr-deterministic")
 
 ELTWISE_ALIAS = {"srelu": "soft_relu"}
@@ -415,6 +415,108 @@ def build(settings, desc, seed=None, max_macs=None):
     return p, opts
 
 
+# ------------------------------------------------------------------- grouped
+def build_grouped(settings, desc, max_macs=None):
+    """Problem of a grouped (MoE) descriptor `--grouped=0:G:s0+s1+... MxK:GxKxN`: the rows of src
+    and dst are split into G groups of the given sizes, group g multiplying weights [g].  Masks are
+    written as numbers in these inputs: src 1 = per row, 3 with groups 1xg = per row and K group;
+    weights 5 = per (expert, column), 7 with groups gx1 = per (expert, K group, column)."""
+    if settings.get("_unknown"):
+        raise Skip("option --" + settings["_unknown"][0])
+    for k in UNSUPPORTED:
+        if settings[k] not in ("", DEFAULTS[k]):
+            raise Skip("--" + k)
+    g = settings["grouped"].split(":")
+    if len(g) < 3 or g[0] != "0":
+        raise Skip("grouping of a dim other than M")
+    G, sizes = int(g[1]), [int(x) for x in g[2].split("+")]
+    m = re.fullmatch(r'([0-9x:]+)(?:_?n"?([^"]*)"?)?', desc)
+    parts = m.group(1).split(":") if m else []
+    if len(parts) != 2:
+        raise Skip("descriptor " + desc)
+    sdims = tuple(int(x) for x in parts[0].split("x"))
+    wdims = tuple(int(x) for x in parts[1].split("x"))
+    if len(sdims) != 2 or len(wdims) != 3 or wdims[0] != G or len(sizes) != G or sum(sizes) != sdims[0] \
+            or sdims[1] != wdims[1]:
+        raise Skip("descriptor " + desc)
+    (M, K), N = sdims, wdims[2]
+    if max_macs is not None and M * K * N > max_macs:
+        raise Skip("larger than the cap")
+    if settings["strides"] or (settings["runtime_dims_masks"] or "0") not in ("0", "0:0"):
+        raise Skip("strides / run-time dims of a grouped problem")
+    r = np.random.Generator(np.random.PCG64(zlib.crc32(command_line(settings, desc).encode())))
+    dts = settings["dt"].split(":")
+    dts = dts * 3 if len(dts) == 1 else dts
+    if len(dts) != 3 or any(d not in DT for d in dts):
+        raise Skip("data types " + settings["dt"])
+    sdt, wdt, ddt = (DT[d] for d in dts)
+    if ddt not in (W.F32, W.BF16, W.F16, W.S8, W.U8, W.S32) or sdt in (W.S4, W.U4):
+        raise Skip("data types " + settings["dt"])
+    if settings["stag"] not in ("ab", "abx", "any") or settings["dtag"] not in ("ab", "abx", "any"):
+        raise Skip("tags of src / dst of a grouped problem")
+    src = W.QTensor(_fill(r, sdt, (M, K), "src"), sdt, (M, K))
+    if settings["wtag"] in ("abc", "abx", "any"):
+        if wdt in (W.S4, W.U4) and N % 2:
+            raise Skip("4-bit weights with odd N")
+        wei = W.QTensor(_fill(r, wdt, (G, K, N), "wei"), wdt, (G, K, N))
+    elif settings["wtag"] == "acb":
+        if wdt in (W.S4, W.U4) and K % 2:
+            raise Skip("4-bit weights with odd K stored transposed")
+        wei = W.QTensor(_fill(r, wdt, (G, N, K), "wei"), wdt, (G, K, N), (K * N, 1, K))
+    else:
+        raise Skip("tag " + settings["wtag"])
+    bias = None
+    if settings["bia-dt"] != "undef":
+        if settings["bia-dt"] not in DT or settings["bia_mask"] != "2":
+            raise Skip("bias of a grouped problem other than [G, N]")
+        bias = W.QTensor(_fill(r, DT[settings["bia-dt"]], (G, N), "bias"), DT[settings["bia-dt"]], (G, N))
+    quant = {}
+    for text, suffix, default_dt in ((settings["attr-scales"], "_scale", W.F32), (settings["attr-zero-points"], "_zp", W.S32)):
+        for arg, policy, value, dt, groups in _quant_entries(text):
+            if not policy.isdigit():
+                raise Skip("policy %s of a grouped problem" % policy)
+            mask, dt = int(policy), default_dt if dt is None else dt
+            if arg == "src" and mask in (1, 3) and groups[0] == 1 and K % groups[1] == 0 and (mask == 3) == (groups[1] > 1):
+                shp = (M, K // groups[1] if mask == 3 else 1)
+            elif arg == "wei" and mask in (5, 7) and groups[1] == 1 and K % groups[0] == 0 and (mask == 7) == (groups[0] > 1):
+                shp = (G, K // groups[0] if mask == 7 else 1, N)
+            elif mask == 0:
+                shp = (1,) * (3 if arg == "wei" else 2)
+            else:
+                raise Skip("mask %d on %s of a grouped problem" % (mask, arg))
+            if suffix == "_scale":
+                vals = np.full(shp, 1.0 if value is None else value, np.float32) if mask == 0 \
+                    else np.exp2(r.integers(-3, 2, shp)).astype(np.float32)
+            elif mask == 0:
+                vals = np.full(shp, 0 if value is None else int(value), np.int64)
+            else:
+                vals = r.integers(*((0, 6) if dt in (W.U8, W.U4) else (-3, 4)), shp)
+            quant[arg + suffix] = W.Quant(W.to_storage(vals, dt), dt, mask, groups)
+    post_ops = []
+    for entry in filter(None, settings["attr-post-ops"].split("+")):
+        f = entry.split(":")
+        kind = f[0][8:] if f[0].startswith("eltwise_") else f[0][7:] if f[0].startswith("binary_") else f[0]
+        kind = ELTWISE_ALIAS.get(kind, kind)
+        if kind in W.ELTWISE:
+            if len(f) > 3 and f[3] and float(f[3]) != 1.0:
+                raise Skip("eltwise with a scale")
+            post_ops.append(W.PostOp(W.PO_ELTWISE, W.ELTWISE[kind], float(f[1]) if len(f) > 1 and f[1] else 0.0,
+                                     float(f[2]) if len(f) > 2 and f[2] else 0.0, 1.0))
+        elif kind in W.BINARY and len(f) >= 3 and f[1] in DT and f[2] == "1" and len(f) == 3:
+            post_ops.append(W.PostOp(W.PO_BINARY, W.BINARY[kind], src1=W.QTensor(_fill(r, DT[f[1]], (M, 1), "binary"), DT[f[1]], (M, 1))))
+        else:
+            raise Skip("post-op %s of a grouped problem" % entry)
+    fpmath, apply_to_int = 0, False
+    if settings["attr-fpmath"]:
+        mode, _, flag = settings["attr-fpmath"].partition(":")
+        modes = {"strict": 0, "bf16": 1, "f16": 2, "any": 3, "tf32": 4}
+        if mode not in modes:
+            raise Skip("fpmath " + mode)
+        fpmath, apply_to_int = modes[mode], flag == "true"
+    return W.Problem(desc, M, N, K, src, wei, ddt, bias, quant, post_ops, apply_to_int, fpmath,
+                     offsets=np.cumsum(sizes).astype(np.int32))
+
+
 # ------------------------------------------------------------------- batched
 class Batched:
     """A descriptor with batch dims: the tensors as the library gets them (storage
@@ -719,9 +821,12 @@ def run_one(settings, desc, eng, strm, all_impls=False):
     from onednn_b200 import api
     from onednn_b200.runner import Prepared
     from oracle import oracle as O
-    from oracle.parity import compare, summation_slack
+    from oracle.parity import compare, summation_slack, summation_slack_grouped
     try:
-        p, opts = build(settings, desc)
+        if settings["grouped"]:
+            p, opts = build_grouped(settings, desc), {"user_scratchpad": False, "runtime_m": False, "dst_ld": None}
+        else:
+            p, opts = build(settings, desc)
     except Skip as e:
         if str(e) == "batched descriptor":
             return _run_one_batched(settings, desc, eng, strm, all_impls)
@@ -751,7 +856,8 @@ def run_one(settings, desc, eng, strm, all_impls=False):
         strm.wait()
         slack = libm_slack
         if not impl.startswith("cuda:ref") and p.src.dt not in (W.S8, W.U8):
-            slack = summation_slack(dense) + (0.0 if libm_slack is None else libm_slack)
+            base = summation_slack_grouped(p) if p.offsets is not None else summation_slack(dense)
+            slack = base + (0.0 if libm_slack is None else libm_slack)
         if ld is None:
             got = run.download()
         else:
@@ -766,7 +872,7 @@ def run_one(settings, desc, eng, strm, all_impls=False):
 def _run_one_batched(settings, desc, eng, strm, all_impls):
     from onednn_b200 import api
     from oracle import oracle as O
-    from oracle.parity import compare, summation_slack
+    from oracle.parity import compare, summation_slack, summation_slack_grouped
     try:
         bp = build_batched(settings, desc)
     except Skip as e:

@@ -152,6 +152,39 @@ def test_reference_input_files_restatement_matches_the_live_reference(host_engin
     assert ran >= least
 
 
+@pytest.mark.parametrize("name,least", [("harness_matmul_grouped_2dby3d", 300)])
+def test_reference_grouped_inputs_restatement_matches_the_live_reference(host_engine, name, least):
+    """Grouped (MoE) problems of the reference's own harness: `--grouped=0:G:sizes MxK:GxKxN` with
+    row-wise / K-grouped src scales, per-(expert, column) / K-grouped weight scales and zero-points,
+    [G, N] bias, eltwise and per-row binary post-ops.  Wherever the reference accepts a problem the
+    restatement equals it bit for bit and this library creates a primitive descriptor too."""
+    from onednn_b200 import api
+    from onednn_b200.runner import Prepared
+    ref = reference_dir()
+    if ref is None or not O.ref_available():
+        pytest.skip("reference checkout or library not present")
+    ran = 0
+    for settings, desc in B.expand(os.path.join(ref, "tests", "benchdnn", "inputs", "matmul", name)):
+        if not settings["grouped"]:
+            continue
+        try:
+            p = B.build_grouped(settings, desc, max_macs=3000000)
+        except B.Skip:
+            continue
+        line = B.command_line(settings, desc)
+        try:
+            want, _, _ = O.run_ref(p, pin_ref=True)
+        except RuntimeError:
+            continue
+        assert np.array_equal(O.run_port(p).view(np.uint8), want.view(np.uint8)), line
+        try:
+            Prepared(p, host_engine)
+        except api.error as e:
+            raise AssertionError("accepted by the reference only (%s): %s" % (e, line))
+        ran += 1
+    assert ran >= least
+
+
 @pytest.mark.gpu
 def test_own_input_file_through_every_implementation(gpu):
     eng, strm = gpu
