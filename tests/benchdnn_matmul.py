@@ -794,7 +794,7 @@ def cancellation_slack(p):
         return None
     quant = {k: v for k, v in p.quant.items() if k not in ("dst_scale", "dst_zp")}
     q = W.Problem(p.name + "/pre", p.M, p.N, p.K, p.src, p.wei, W.F32, p.bias, quant, p.post_ops[:idx],
-                  p.apply_to_int, p.fpmath)
+                  p.apply_to_int, p.fpmath, offsets=p.offsets)
     if p.dst_init is not None:
         init = p.dst_init if p.dst_dt in (W.S4, W.U4) else p.dst_init.reshape(p.M, p.N)
         q.dst_init = np.ascontiguousarray(W.to_f32(init, p.dst_dt), dtype=np.float32)
