@@ -89,11 +89,13 @@ def _logical_lines(path):
             yield pending
 
 
-def expand(path, state=None):
+def expand(path, state=None, defaults=None):
     """Yields (settings, descriptor) for every problem of an input file, in
-    file order.  `settings` maps option names to ONE value each."""
+    file order.  `settings` maps option names to ONE value each.  `defaults`:
+    the options of the driver the file is written for (this module's, for matmul)."""
+    defaults = DEFAULTS if defaults is None else defaults
     if state is None:
-        state = {"lists": {k: [v] for k, v in DEFAULTS.items()}, "unknown": set()}
+        state = {"lists": {k: [v] for k, v in defaults.items()}, "unknown": set()}
     lists = state["lists"]
     here = os.path.dirname(os.path.abspath(path))
     for line in _logical_lines(path):
@@ -107,16 +109,16 @@ def expand(path, state=None):
                 continue
             name, _, val = tok[2:].partition("=")
             if name == "reset":
-                lists.update({k: [v] for k, v in DEFAULTS.items()})
+                lists.update({k: [v] for k, v in defaults.items()})
                 state["unknown"].clear()
             elif name == "batch":
-                yield from expand(os.path.join(here, val), state)
-            elif name == "matmul" or name in IGNORED:
+                yield from expand(os.path.join(here, val), state, defaults)
+            elif name in ("matmul", "reorder") or name in IGNORED:
                 continue
-            elif name not in DEFAULTS:
+            elif name not in defaults:
                 state["unknown"].add(name)
             else:
-                lists[name] = val.split(",") if val != "" else [DEFAULTS[name] if name in ("dt",) else ""]
+                lists[name] = val.split(",") if val != "" else [defaults[name] if name in ("dt",) else ""]
 
 
 def command_line(settings, desc):

@@ -195,3 +195,51 @@ def test_own_input_file_through_every_implementation(gpu):
     for impl in ("cuda:tcgen05:int8", "cuda:tcgen05:fp8", "cuda:tcgen05:woq4", "cuda:woq:skinny", "cuda:tcgen05:woq8",
                  "cuda:ref_int8:any", "cuda:ref:any"):
         assert rep["impls"].get(impl, 0) >= 20, (impl, rep["impls"])
+
+
+@pytest.mark.parametrize("name,least", [("test_reorder_ci", 2000), ("test_reorder_all", 2500), ("harness_reorder_scales", 700),
+                                        ("harness_reorder_saturation", 120)])
+def test_reference_reorder_inputs_restatement_matches_the_live_reference(host_engine, name, least):
+    """The reference's reorder input files (tests/benchdnn_reorder.py reads their syntax): every
+    plain-layout problem the reference library accepts must give the restatement's bits, and this
+    library must create a reorder primitive descriptor for it too."""
+    import benchdnn_reorder as R
+    from onednn_b200 import api
+    ref = reference_dir()
+    if ref is None or not O.ref_available():
+        pytest.skip("reference checkout or library not present")
+    ran = 0
+    for settings, desc in R.expand(os.path.join(ref, "tests", "benchdnn", "inputs", "reorder", name)):
+        try:
+            ro = R.build(settings, desc)
+        except R.Skip:
+            continue
+        if int(np.prod(ro.src.dims)) > 200000:
+            continue
+        try:
+            want, _ = O.run_ref_reorder(ro)
+        except RuntimeError:
+            continue
+        line = "%s %s" % ({k: v for k, v in settings.items() if v != R.DEFAULTS.get(k)}, desc)
+        got = O.run_port_reorder(ro)
+        assert np.array_equal(np.asarray(got).view(np.uint8), np.asarray(want).view(np.uint8)), line
+        try:
+            R.primitive_desc(ro, host_engine)
+        except api.error as e:
+            raise AssertionError("accepted by the reference only (%s): %s" % (e, line))
+        ran += 1
+    assert ran >= least
+
+
+def test_reorder_tags_follow_benchdnn():
+    import benchdnn_reorder as R
+    assert R.tag_order("abx", 4) == (0, 1, 2, 3) and R.tag_order("axb", 4) == (0, 2, 3, 1)
+    assert R.tag_order("xba", 4) == (2, 3, 1, 0) and R.tag_order("xba", 2) == (1, 0) and R.tag_order("axb", 2) == (0, 1)
+    assert R.tag_order("adbc", 4) == (0, 3, 1, 2)
+    with pytest.raises(R.Skip):
+        R.tag_order("aBx16b", 4)
+    s = dict(R.DEFAULTS, _unknown=[])
+    s.update({"sdt": "f32", "ddt": "s8", "dtag": "axb", "attr-scales": "src:per_dim_1+dst:common:2", "attr-post-ops": "sum:0.5"})
+    ro = R.build(s, "2x16x3x4")
+    assert ro.dst_strides == (192, 1, 64, 16) and ro.quant["src_scale"].data.shape == (1, 16, 1, 1) and ro.beta == 0.5
+    assert ro.dst_init is not None and ro.dst_init.size == 2 * 16 * 3 * 4
