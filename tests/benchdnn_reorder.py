@@ -10,8 +10,9 @@ objects for the CPU oracle and for `dnnl::reorder` of this library.
 Plain layouts only: a tag names the dims from the outermost to the innermost,
 `x` standing for the dims the tag does not name, in order (normalize_tag,
 tests/benchdnn/dnn_types.cpp:1884-1912).  Blocked tags, compensation flags
-(--oflag), run-time dim masks and 4-bit / fp4 / f64 types are skipped with
-their name as the reason."""
+(--oflag), run-time dim masks and fp4 / f64 types are skipped with their name
+as the reason; 4-bit tensors are packed two elements a byte along their
+innermost dim."""
 import re
 import zlib
 
@@ -59,8 +60,8 @@ def _values(r, dt, dims):
     as in benchdnn's own fill (integers converted to floats): the reference's reorder
     implementations do not agree on the sign of a zero result (its jit kernels keep -0, the
     scalar `simple:any` path with scales returns +0)."""
-    if dt in (W.S8, W.U8, W.S32):
-        lo, hi = (0, 256) if dt == W.U8 else (-128, 128) if dt == W.S8 else (-300, 301)
+    if dt in (W.S8, W.U8, W.S32, W.S4, W.U4):
+        lo, hi = {W.U8: (0, 256), W.S8: (-128, 128), W.S32: (-300, 301), W.S4: (-8, 8), W.U4: (0, 16)}[dt]
         return r.integers(lo, hi, dims)
     if dt in (W.F8_E4M3, W.F8_E5M2):
         return r.integers(-16, 17, dims).astype(np.float32) * 0.5
@@ -79,8 +80,6 @@ def build(settings, desc):
     if settings["sdt"] not in B.DT or settings["ddt"] not in B.DT:
         raise Skip("data types %s -> %s" % (settings["sdt"], settings["ddt"]))
     sdt, ddt = B.DT[settings["sdt"]], B.DT[settings["ddt"]]
-    if W.S4 in (sdt, ddt) or W.U4 in (sdt, ddt):
-        raise Skip("4-bit types")
     m = re.fullmatch(r'([0-9x]+)(?:_?n"?([^"]*)"?)?', desc)
     if m is None:
         raise Skip("descriptor " + desc)
@@ -90,8 +89,16 @@ def build(settings, desc):
         raise Skip("descriptor " + desc)
     r = np.random.Generator(np.random.PCG64(zlib.crc32(("--reorder %s %s" % (sorted(settings.items(), key=str), desc)).encode())))
     s_order, d_order = tag_order(settings["stag"], nd), tag_order(settings["dtag"], nd)
-    logical = W.to_storage(_values(r, sdt, dims), sdt)
-    src = W.QTensor(np.ascontiguousarray(logical.transpose(s_order)).reshape(-1), sdt, dims, _strides(dims, s_order))
+    four = (W.S4, W.U4)
+    if sdt in four:  # two elements a byte along the innermost dim
+        if s_order != tuple(range(nd)) or dims[-1] % 2:
+            raise Skip("4-bit src that is not row-major with an even innermost dim")
+        src = W.QTensor(W.pack_int4(_values(r, sdt, dims)).reshape(-1), sdt, dims)
+    else:
+        logical = W.to_storage(_values(r, sdt, dims), sdt)
+        src = W.QTensor(np.ascontiguousarray(logical.transpose(s_order)).reshape(-1), sdt, dims, _strides(dims, s_order))
+    if ddt in four and dims[d_order[-1]] % 2:
+        raise Skip("4-bit dst with an odd innermost dim")
     quant = {}
     for text, suffix, default_dt in ((settings["attr-scales"], "_scale", W.F32), (settings["attr-zero-points"], "_zp", W.S32)):
         for arg, policy, value, dt, groups in B._quant_entries(text):
@@ -101,6 +108,8 @@ def build(settings, desc):
             if mask >= (1 << nd):
                 raise Skip("policy %s for %d dims" % (policy, nd))
             dt = default_dt if dt is None else dt
+            if dt in four and mask == 0:
+                raise Skip("a single 4-bit parameter")
             if nd < 2 and groups != (1, 1):
                 raise Skip("groups of a 1D tensor")
             shp = [d if (mask >> i) & 1 else 1 for i, d in enumerate(dims)]
@@ -116,6 +125,10 @@ def build(settings, desc):
                 vals = np.full(shp, 0 if value is None else int(value), np.int64)
             else:
                 vals = r.integers(-3, 4, shp)
+            if dt in four and shp[-1] % 2:
+                raise Skip("4-bit parameters with an odd innermost dim")
+            if dt == W.U4 and suffix == "_zp" and mask:
+                vals = r.integers(0, 6, shp)
             quant[arg + suffix] = W.Quant(W.to_storage(vals, dt), dt, mask, groups)
     beta = 0.0
     for entry in filter(None, settings["attr-post-ops"].split("+")):
@@ -125,6 +138,8 @@ def build(settings, desc):
         beta = float(f[1]) if len(f) > 1 and f[1] else 1.0
     ro = W.Reorder(desc, src, ddt, _strides(dims, d_order), quant, beta)
     if beta:
+        if ddt in four:
+            raise Skip("sum into a 4-bit dst")
         init = W.to_storage(_values(r, ddt, dims), ddt)
         ro.dst_init = np.ascontiguousarray(init.transpose(d_order)).reshape(-1)
     return ro

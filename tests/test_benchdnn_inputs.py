@@ -198,7 +198,8 @@ def test_own_input_file_through_every_implementation(gpu):
 
 
 @pytest.mark.parametrize("name,least", [("test_reorder_ci", 2000), ("test_reorder_all", 2500), ("harness_reorder_scales", 700),
-                                        ("harness_reorder_saturation", 120)])
+                                        ("harness_reorder_saturation", 120), ("harness_reorder_decompression", 500),
+                                        ("test_reorder_int4", 80)])
 def test_reference_reorder_inputs_restatement_matches_the_live_reference(host_engine, name, least):
     """The reference's reorder input files (tests/benchdnn_reorder.py reads their syntax): every
     plain-layout problem the reference library accepts must give the restatement's bits, and this
