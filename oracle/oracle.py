@@ -194,6 +194,78 @@ def run_ref(p: W.Problem, pin_ref=True, iters=0):
     return _view(dst, p), name.value.decode(), (ms.value if iters > 0 else None)
 
 
+class _NdTensor(C.Structure):
+    _fields_ = [("ptr", C.c_void_p), ("dt", C.c_int32), ("ndims", C.c_int32),
+                ("dims", C.c_int64 * 6), ("strides", C.c_int64 * 6)]
+
+
+class _NdQuant(C.Structure):
+    _fields_ = [("ptr", C.c_void_p), ("dt", C.c_int32), ("mask", C.c_int32), ("arg", C.c_int32), ("kind", C.c_int32),
+                ("g0", C.c_int64), ("g1", C.c_int64)]
+
+
+class _NdPostOp(C.Structure):
+    _fields_ = [("kind", C.c_int32), ("alg", C.c_int32), ("zero_point", C.c_int32), ("mask", C.c_int32),
+                ("alpha", C.c_float), ("beta", C.c_float), ("scale", C.c_float), ("src1", _NdTensor)]
+
+
+class _NdProblem(C.Structure):
+    _fields_ = [("src", _NdTensor), ("wei", _NdTensor), ("dst", _NdTensor), ("bias", _NdTensor),
+                ("n_quant", C.c_int32), ("n_po", C.c_int32), ("apply_to_int", C.c_int32), ("fpmath_mode", C.c_int32),
+                ("quant", _NdQuant * 8), ("po", _NdPostOp * 8)]
+
+
+def run_ref_nd(src, wei, bias, dst_dims, dst_dt, dst_strides, quant, post_ops, dst_init=None,
+               apply_to_int=False, fpmath=0, pin_ref=True):
+    """A matmul of any rank on the reference library (batched problems).  src / wei / bias:
+    (storage, element strides, data type, dims) or None; quant: name -> Quant with a mask over all
+    dims; post_ops: PostOp whose binary src1 is a QTensor of dst's rank; a prelu carries its mask in
+    zero_point and its weights in src1.data in the layout the reference defines.  Returns (dst
+    storage spanning dst_strides, implementation name)."""
+    lib = _load_ref()
+    keep = []
+
+    def tensor(t, ptr, dt, dims, strides):
+        t.ptr, t.dt, t.ndims = ptr, dt, len(dims)
+        for i, (d, st) in enumerate(zip(dims, strides)):
+            t.dims[i], t.strides[i] = d, st
+
+    s = _NdProblem()
+    for field, given in (("src", src), ("wei", wei), ("bias", bias)):
+        if given is not None:
+            storage, strides, dt, dims = given
+            keep.append(storage)
+            tensor(getattr(s, field), _ptr(storage).value, dt, dims, strides)
+    span = 1 + sum((d - 1) * st for d, st in zip(dst_dims, dst_strides))
+    dst = np.zeros(W.nbytes(dst_dt, span), np.uint8)
+    if dst_init is not None:
+        dst[:] = np.ascontiguousarray(dst_init).view(np.uint8).reshape(-1)
+    tensor(s.dst, _ptr(dst).value, dst_dt, dst_dims, dst_strides)
+    arg_of = {"src": 1, "wei": 33, "dst": 17}  # DNNL_ARG_SRC, DNNL_ARG_WEIGHTS, DNNL_ARG_DST
+    for i, (name, q) in enumerate(quant.items()):
+        cq = s.quant[i]
+        cq.ptr, cq.dt, cq.mask, cq.arg = _ptr(q.data).value, q.dt, q.mask, arg_of[name[:3]]
+        cq.kind = 0 if name.endswith("scale") else 1
+        cq.g0, cq.g1 = q.groups
+    s.n_quant = len(quant)
+    for i, po in enumerate(post_ops):
+        e = s.po[i]
+        e.kind, e.alg, e.alpha, e.beta, e.scale, e.zero_point = po.kind, po.alg, po.alpha, po.beta, po.scale, po.zero_point
+        if po.kind == W.PO_PRELU:
+            e.mask = po.zero_point
+            e.src1.ptr = _ptr(po.src1.data).value
+        elif po.src1 is not None:
+            tensor(e.src1, _ptr(po.src1.data).value, po.src1.dt, po.src1.dims, po.src1.strides)
+    s.n_po = len(post_ops)
+    s.apply_to_int, s.fpmath_mode = int(apply_to_int), fpmath
+    name = C.create_string_buffer(256)
+    rc = lib.ref_runner_run_nd(C.byref(s), int(pin_ref), name, 256)
+    if rc != 0:
+        raise RuntimeError("reference status %d: %s" % (rc, name.value.decode()))
+    out = dst if dst_dt in (W.S4, W.U4) else dst.view(W.NP_STORAGE[dst_dt])
+    return out, name.value.decode()
+
+
 def _marshal_reorder(r: W.Reorder):
     s = _Reorder()
     nd = len(r.src.dims)

@@ -206,6 +206,119 @@ int ref_runner_run(const qmm_problem_t *p, int pin_ref, int iters,
     }
 }
 
+// ---- problems with batch dims ----------------------------------------------
+// A matmul of any rank, described by plain tensors (dims and element strides): the batched
+// problems of the tests, whose matrices the 2D restatement computes one by one.  The reference
+// decides the broadcast of size-1 batch dims, the layout of prelu weights and the meaning of
+// masks over batch dims; this entry point lets the tests ask it.
+#define QMM_ND_MAX 6
+typedef struct {
+    const void *ptr; // null: absent
+    int32_t dt, ndims;
+    int64_t dims[QMM_ND_MAX], strides[QMM_ND_MAX];
+} qmm_nd_tensor_t;
+typedef struct {
+    const void *ptr;
+    int32_t dt, mask, arg /* DNNL_ARG_SRC / WEIGHTS / DST */, kind /* 0 scales, 1 zero-points */;
+    int64_t g0, g1;
+} qmm_nd_quant_t;
+typedef struct {
+    int32_t kind /* QMM_PO_* */, alg, zero_point, mask /* prelu */;
+    float alpha, beta, scale;
+    qmm_nd_tensor_t src1; // binary operand; prelu: ptr only (f32, the layout the library defines)
+} qmm_nd_postop_t;
+typedef struct {
+    qmm_nd_tensor_t src, wei, dst, bias;
+    int32_t n_quant, n_po, apply_to_int, fpmath_mode;
+    qmm_nd_quant_t quant[8];
+    qmm_nd_postop_t po[8];
+} qmm_nd_problem_t;
+
+static memory::desc nd_md(const qmm_nd_tensor_t &t) {
+    return memory::desc(dims(t.dims, t.dims + t.ndims), to_dt(t.dt), dims(t.strides, t.strides + t.ndims));
+}
+
+int ref_runner_run_nd(const qmm_nd_problem_t *p, int pin_ref, char *impl_name, int impl_len) {
+    try {
+        engine eng(engine::kind::cpu, 0);
+        stream s(eng);
+        std::unordered_map<int, memory> args;
+        primitive_attr attr;
+        if (p->apply_to_int || p->fpmath_mode)
+            attr.set_fpmath_mode(static_cast<fpmath_mode>(p->fpmath_mode), p->apply_to_int != 0);
+        const memory::desc src_md = nd_md(p->src), wei_md = nd_md(p->wei), dst_md = nd_md(p->dst);
+        const int nd = p->dst.ndims;
+        for (int i = 0; i < p->n_quant; ++i) {
+            const qmm_nd_quant_t &q = p->quant[i];
+            const qmm_nd_tensor_t &base = q.arg == DNNL_ARG_SRC ? p->src : q.arg == DNNL_ARG_WEIGHTS ? p->wei : p->dst;
+            const bool grouped = q.g0 > 1 || q.g1 > 1;
+            dims groups = grouped ? dims {q.g0, q.g1} : dims {};
+            if (q.kind == 0) attr.set_scales(q.arg, q.mask, groups, to_dt(q.dt));
+            else attr.set_zero_points(q.arg, q.mask, groups, to_dt(q.dt));
+            dims qd(nd, 1);
+            for (int d = 0; d < nd; ++d)
+                if ((q.mask >> d) & 1) qd[d] = base.dims[d];
+            qd[nd - 2] /= (q.mask >> (nd - 2)) & 1 ? q.g0 : 1;
+            qd[nd - 1] /= (q.mask >> (nd - 1)) & 1 ? q.g1 : 1;
+            dims qs(nd, 1);
+            for (int d = nd - 2; d >= 0; --d) qs[d] = qs[d + 1] * qd[d + 1];
+            args.emplace((q.kind == 0 ? DNNL_ARG_ATTR_SCALES : DNNL_ARG_ATTR_ZERO_POINTS) | q.arg,
+                    make_mem(memory::desc(qd, to_dt(q.dt), qs), eng, q.ptr));
+        }
+        post_ops po;
+        for (int i = 0; i < p->n_po; ++i) {
+            const qmm_nd_postop_t &e = p->po[i];
+            if (e.kind == QMM_PO_SUM) po.append_sum(e.scale, e.zero_point);
+            else if (e.kind == QMM_PO_ELTWISE) po.append_eltwise(static_cast<algorithm>(e.alg), e.alpha, e.beta);
+            else if (e.kind == QMM_PO_PRELU) po.append_prelu(e.mask);
+            else po.append_binary(static_cast<algorithm>(e.alg), nd_md(e.src1));
+        }
+        if (p->n_po) attr.set_post_ops(po);
+        matmul::primitive_desc pd = p->bias.ptr
+                ? matmul::primitive_desc(eng, src_md, wei_md, nd_md(p->bias), dst_md, attr)
+                : matmul::primitive_desc(eng, src_md, wei_md, dst_md, attr);
+        if (pin_ref)
+            while (std::string(pd.impl_info_str()).rfind("ref", 0) != 0)
+                if (!pd.next_impl()) throw error(dnnl_unimplemented, "no ref impl");
+        for (int i = 0; i < p->n_po; ++i) {
+            const qmm_nd_postop_t &e = p->po[i];
+            if (e.kind == QMM_PO_BINARY)
+                args.emplace(DNNL_ARG_ATTR_MULTIPLE_POST_OP(i) | DNNL_ARG_SRC_1, make_mem(nd_md(e.src1), eng, e.src1.ptr));
+            else if (e.kind == QMM_PO_PRELU) {
+                // the library states the weights' descriptor: dims masked, its own dense layout
+                memory::desc wmd = pd.query_md(query::exec_arg_md, DNNL_ARG_ATTR_MULTIPLE_POST_OP(i) | DNNL_ARG_WEIGHTS);
+                if (wmd.get_ndims() == 0) { // not answered: ab, acb, acdb, acdeb (src/cpu/primitive_attr_postops.cpp:219-242)
+                    dims wd(nd, 1);
+                    for (int d = 0; d < nd; ++d)
+                        if ((e.mask >> d) & 1) wd[d] = p->dst.dims[d];
+                    static const memory::format_tag tags[] = {memory::format_tag::a, memory::format_tag::ab,
+                            memory::format_tag::acb, memory::format_tag::acdb, memory::format_tag::acdeb};
+                    if (nd > 5) throw error(dnnl_unimplemented, "prelu beyond five dims");
+                    wmd = memory::desc(wd, dt::f32, tags[nd - 1]);
+                }
+                args.emplace(DNNL_ARG_ATTR_MULTIPLE_POST_OP(i) | DNNL_ARG_WEIGHTS, make_mem(wmd, eng, e.src1.ptr));
+            }
+        }
+        args.emplace(DNNL_ARG_SRC, make_mem(src_md, eng, p->src.ptr));
+        args.emplace(DNNL_ARG_WEIGHTS, make_mem(wei_md, eng, p->wei.ptr));
+        args.emplace(DNNL_ARG_DST, make_mem(dst_md, eng, p->dst.ptr));
+        if (p->bias.ptr) args.emplace(DNNL_ARG_BIAS, make_mem(nd_md(p->bias), eng, p->bias.ptr));
+        if (impl_name && impl_len > 0) {
+            std::strncpy(impl_name, pd.impl_info_str(), impl_len - 1);
+            impl_name[impl_len - 1] = 0;
+        }
+        matmul(pd).execute(s, args);
+        s.wait();
+        return 0;
+    } catch (const error &e) {
+        if (impl_name && impl_len > 0) {
+            std::strncpy(impl_name, e.message, impl_len - 1);
+            impl_name[impl_len - 1] = 0;
+        }
+        return e.status ? (int)e.status : -1;
+    }
+}
+
 // Runs a reorder on the reference CPU engine (whatever implementation the
 // library dispatches; the reorder primitive descriptor has no iterator).
 int ref_runner_reorder(const qmm_reorder_t *r, char *impl_name, int impl_len) {

@@ -244,3 +244,34 @@ def test_reorder_tags_follow_benchdnn():
     ro = R.build(s, "2x16x3x4")
     assert ro.dst_strides == (192, 1, 64, 16) and ro.quant["src_scale"].data.shape == (1, 16, 1, 1) and ro.beta == 0.5
     assert ro.dst_init is not None and ro.dst_init.size == 2 * 16 * 3 * 4
+
+
+def test_batched_problems_match_the_live_reference_matrix_by_matrix():
+    """The batched problems of this repository's input file on the reference library itself (one
+    batched primitive: oracle.run_ref_nd) against the 2D restatement applied to every matrix of
+    the batch: the broadcast of size-1 batch dims, bias and binary operands along any dims, masks
+    that skip the batch dims and the layout of prelu weights are the reference's own."""
+    if not O.ref_available():
+        pytest.skip("reference library not built")
+    ran = 0
+    for settings, desc in B.expand(OWN):
+        try:
+            B.build(settings, desc)
+            continue
+        except B.Skip as e:
+            if str(e) != "batched descriptor":
+                continue
+        bp = B.build_batched(settings, desc)
+        fpmath, apply_to_int = bp.fpmath, bp.apply_to_int
+        if bp.tensors["src"][2] in (W.S8, W.U8):  # the reference's generic int8 kernel refuses an fpmath setting
+            fpmath, apply_to_int = 0, False
+        line = B.command_line(settings, desc)
+        got, impl = O.run_ref_nd(bp.tensors["src"], bp.tensors["wei"], bp.tensors.get("bias"), bp.ddims, bp.ddt,
+                                 bp.dst_strides, bp.quant, bp.post_ops, bp.dst_init, apply_to_int, fpmath)
+        assert impl.startswith("ref"), (impl, line)
+        full = B._gather(np.asarray(got), bp.ddims, bp.dst_strides)
+        for idx, p in bp.mats:
+            want = O.run_port(p)
+            assert np.array_equal(np.ascontiguousarray(full[idx]).view(np.uint8), want.view(np.uint8)), (line, idx)
+        ran += 1
+    assert ran > 1500
