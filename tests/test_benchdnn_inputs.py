@@ -275,3 +275,36 @@ def test_batched_problems_match_the_live_reference_matrix_by_matrix():
             assert np.array_equal(np.ascontiguousarray(full[idx]).view(np.uint8), want.view(np.uint8)), (line, idx)
         ran += 1
     assert ran > 1500
+
+
+@pytest.mark.parametrize("name,least", [("test_matmul_all", 4000), ("test_matmul_multidims", 400)])
+def test_reference_batched_inputs_match_the_live_reference_matrix_by_matrix(name, least):
+    """The same check on the batched descriptors of the reference's own input files (three to six
+    dims, broadcast batch dims, permuted tags, bias masks, binary operands along any dims)."""
+    import re
+    ref = reference_dir()
+    if ref is None or not O.ref_available():
+        pytest.skip("reference checkout or library not present")
+    ran = 0
+    for settings, desc in B.expand(os.path.join(ref, "tests", "benchdnn", "inputs", "matmul", name)):
+        m = re.fullmatch(r"([0-9x]+):([0-9x]+).*", desc)
+        if m is None or m.group(1).count("x") < 2:
+            continue
+        macs = int(np.prod([int(x) for x in m.group(1).split("x")])) * int(m.group(2).split("x")[-1])
+        if macs > 300000:
+            continue
+        try:
+            bp = B.build_batched(settings, desc)
+        except B.Skip:
+            continue
+        try:
+            got, impl = O.run_ref_nd(bp.tensors["src"], bp.tensors["wei"], bp.tensors.get("bias"), bp.ddims, bp.ddt,
+                                     bp.dst_strides, bp.quant, bp.post_ops, bp.dst_init, bp.apply_to_int, bp.fpmath)
+        except RuntimeError:
+            continue
+        full = B._gather(np.asarray(got), bp.ddims, bp.dst_strides)
+        for idx, p in bp.mats:
+            assert np.array_equal(np.ascontiguousarray(full[idx]).view(np.uint8), O.run_port(p).view(np.uint8)), \
+                (B.command_line(settings, desc), idx)
+        ran += 1
+    assert ran >= least
