@@ -1,6 +1,11 @@
 """Builds the CUDA library in-tree with nvcc for sm_100a.
 
-    python -m onednn_b200.build [--force] [--verbose]
+    python -m onednn_b200.build [--force] [--verbose] [--ptxas]
+
+Extra compiler flags can be given in the environment, e.g. the kernels' timing
+switches for a profiling build: ``QMM_NVCC_EXTRA=-DQMM_PROFILE python -m
+onednn_b200.build --force`` (a later plain ``--force`` build restores the
+shipped library).
 
 Output: ``onednn_b200/lib/libdnnl.so.3`` (plus the ``libdnnl.so`` link name a
 linker looks for).  Every ``csrc/*.cu`` is one translation unit; objects are
@@ -147,7 +152,7 @@ def build(force=False, verbose=False, ptxas_info=False):
         + glob.glob(os.path.join(CSRC, "*.cuh")) + glob.glob(os.path.join(ROOT, "include", "*.h"))
     newest_hdr = max(os.path.getmtime(h) for h in headers)
     jobs, objs = [], []
-    extra = ["-Xptxas", "-v"] if ptxas_info else []
+    extra = (["-Xptxas", "-v"] if ptxas_info else []) + os.environ.get("QMM_NVCC_EXTRA", "").split()
     for s in sources:
         o = os.path.join(LIBDIR, "obj", os.path.basename(s)[:-3] + ".o")
         objs.append(o)
