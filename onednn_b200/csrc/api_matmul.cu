@@ -736,6 +736,8 @@ dnnl_status_t dnnl_matmul_primitive_desc_create(dnnl_primitive_desc_t *primitive
             delete pd;
             return dnnl_unimplemented;
         }
+        for (auto &e : pd->attr.post_ops.entries) // `any` on an operand whose dims are known: row-major
+            if (e.kind == dnnl_binary && !e.src1.has_runtime_dims()) set_default_format(e.src1);
         dnnl_primitive_desc chk = *pd;
         apply_stand_ins(chk);
         dnnl_status_t rst = dense_desc_check(chk.src, chk.wei, chk.bias.ndims ? &chk.bias : nullptr, chk.dst);

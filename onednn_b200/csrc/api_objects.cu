@@ -905,7 +905,8 @@ dnnl_status_t dnnl_post_ops_append_binary(dnnl_post_ops_t post_ops, dnnl_alg_kin
     if (!po_has_room(post_ops)) return post_ops ? dnnl_out_of_memory : dnnl_invalid_arguments;
     if (!src1) return dnnl_invalid_arguments;
     if ((int)alg < (int)dnnl_binary_add || (int)alg > (int)dnnl_binary_ne) return dnnl_invalid_arguments;
-    if (src1->format_kind == dnnl_format_kind_any) return dnnl_invalid_arguments;
+    // `any` is allowed as in the reference (src/common/primitive_attr.cpp:228-258): the primitive
+    // descriptor resolves it to the plain row-major layout
     post_op_entry_t e;
     e.kind = dnnl_binary;
     e.alg = alg;

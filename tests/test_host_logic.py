@@ -257,6 +257,15 @@ def test_runtime_m_descriptor(host_engine):
     # a row-dependent stride (src stored transposed with M open)
     pd = api.matmul.primitive_desc(host_engine, md((RT, 64), W.U8, tag.ba), md((64, 48), W.S8, tag.ab), md((RT, 48), W.S32, tag.ab))
     assert pd.src_desc().get_dims() == (RT, 64)
+    # a binary operand given with format `any` (allowed as in the reference) resolves to row-major, with M open or not
+    for rows in (RT, 16):
+        po = api.post_ops()
+        po.append_binary(W.BINARY["add"], md((1, 48), W.F32, tag.any))
+        b = api.primitive_attr()
+        b.set_post_ops(po)
+        pd = api.matmul.primitive_desc(host_engine, md((rows, 64), W.U8, (64, 1)), md((64, 48), W.S8, tag.ab),
+                                       md((rows, 48), W.S32, (48, 1)), None, b)
+        assert pd.query_md(api.QUERY_EXEC_ARG_MD, api.ARG_ATTR_MULTIPLE_POST_OP(0) | api.ARG_SRC_1).get_strides() == (48, 1)
     # dims that contradict one another are refused at creation, batched problems with open dims are not built
     assert status_of(lambda: api.matmul.primitive_desc(host_engine, md((RT, 64), W.U8, (64, 1)), md((32, 48), W.S8, (48, 1)),
                                                         md((RT, 48), W.S32, (48, 1)))) == api.invalid_arguments
