@@ -229,12 +229,16 @@ typedef enum {
 #define DNNL_ARG_FROM DNNL_ARG_SRC_0
 #define DNNL_ARG_TO DNNL_ARG_DST
 #define DNNL_ARG_WEIGHTS 33
+#define DNNL_ARG_WEIGHTS_1 34
+#define DNNL_ARG_WEIGHTS_2 35
 #define DNNL_ARG_BIAS 41
 #define DNNL_ARG_SCRATCHPAD 80
 #define DNNL_ARG_HINT_MAX_GROUP_SIZE 384
 #define DNNL_ARG_ATTR_PRECOMPUTED_REDUCTIONS 512
+#define DNNL_ARG_MULTIPLE_SRC 1024
 #define DNNL_ARG_ATTR_SCALES 4096
 #define DNNL_ARG_ATTR_ZERO_POINTS 8192
+#define DNNL_ARG_ATTR_POST_OP_DW 16384
 #define DNNL_ARG_ATTR_MULTIPLE_POST_OP_BASE 32768
 #define DNNL_ARG_ATTR_MULTIPLE_POST_OP(idx) (DNNL_ARG_ATTR_MULTIPLE_POST_OP_BASE * ((idx) + 1))
 

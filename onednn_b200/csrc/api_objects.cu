@@ -264,9 +264,9 @@ dnnl_status_t dnnl_memory_desc_create_with_strides(dnnl_memory_desc_t *memory_de
     md->ndims = ndims;
     md->data_type = data_type;
     md->format_kind = dnnl_blocked;
-    bool runtime = false;
+    bool runtime = false; // open dims, or open strides of known dims
     for (int i = 0; i < ndims; ++i) {
-        runtime = runtime || dims[i] == DNNL_RUNTIME_DIM_VAL;
+        runtime = runtime || dims[i] == DNNL_RUNTIME_DIM_VAL || (strides && strides[i] == DNNL_RUNTIME_DIM_VAL);
         md->dims[i] = dims[i];
     }
     if (runtime) {
@@ -333,6 +333,10 @@ dnnl_status_t dnnl_memory_desc_create_with_tag(dnnl_memory_desc_t *memory_desc, 
         return dnnl_success;
     }
     if (tag == dnnl_format_tag_any) {
+        // a layout the library is to choose needs the dims (src/common/memory_desc.cpp: `any` with
+        // run-time dims is refused)
+        for (int i = 0; i < ndims; ++i)
+            if (dims[i] == DNNL_RUNTIME_DIM_VAL) return dnnl_invalid_arguments;
         auto *md = new dnnl_memory_desc;
         md->ndims = ndims;
         md->data_type = data_type;
@@ -362,9 +366,10 @@ dnnl_status_t dnnl_memory_desc_create_with_tag(dnnl_memory_desc_t *memory_desc, 
     if (tag_ndims != ndims) return dnnl_invalid_arguments;
     dnnl_dims_t strides = {};
     dnnl_dim_t acc = 1;
-    for (int i = ndims - 1; i >= 0; --i) {
+    for (int i = ndims - 1; i >= 0; --i) { // a stride beyond an open dim is open too
         strides[order[i]] = acc;
-        acc *= dims[order[i]] == 0 ? 1 : dims[order[i]];
+        const dnnl_dim_t d = dims[order[i]];
+        acc = (acc == DNNL_RUNTIME_DIM_VAL || d == DNNL_RUNTIME_DIM_VAL) ? DNNL_RUNTIME_DIM_VAL : acc * (d == 0 ? 1 : d);
     }
     return dnnl_memory_desc_create_with_strides(memory_desc, ndims, dims, data_type, strides);
 }
@@ -767,9 +772,24 @@ static dnnl_status_t set_quant(std::map<int, quant_entry_t> &m, int arg, int mas
     return dnnl_success;
 }
 
+// the arguments scales / zero-points may be set for (src/common/primitive_attr_quant.hpp:337-359, 390-406)
+static bool scales_arg_ok(int arg) {
+    if (arg == DNNL_ARG_SRC || arg == DNNL_ARG_WEIGHTS || arg == DNNL_ARG_DST || arg == DNNL_ARG_SRC_1 || arg == DNNL_ARG_SRC_2
+            || arg == DNNL_ARG_WEIGHTS_1 || arg == DNNL_ARG_WEIGHTS_2)
+        return true;
+    if (arg & DNNL_ARG_MULTIPLE_SRC) return true;
+    for (int a : {DNNL_ARG_SRC, DNNL_ARG_WEIGHTS, DNNL_ARG_DST})
+        if (arg == (DNNL_ARG_ATTR_POST_OP_DW | a)) return true;
+    return false;
+}
+static bool zero_points_arg_ok(int arg) {
+    return arg == DNNL_ARG_SRC || arg == DNNL_ARG_WEIGHTS || arg == DNNL_ARG_DST || arg == DNNL_ARG_SRC_2
+            || arg == DNNL_ARG_WEIGHTS_1 || arg == DNNL_ARG_WEIGHTS_2;
+}
+
 dnnl_status_t dnnl_primitive_attr_set_scales_v3(dnnl_primitive_attr_t attr, int arg, int mask, int ndims,
         const dnnl_dims_t group_dims, dnnl_data_type_t dt, int is_on_host, dnnl_quantization_mode_t qmode) {
-    if (!attr || arg < 0 || mask < 0) return dnnl_invalid_arguments;
+    if (!attr || arg < 0 || mask < 0 || !scales_arg_ok(arg)) return dnnl_invalid_arguments;
     if (qmode != dnnl_quantization_mode_static_sazp && qmode != dnnl_quantization_mode_dynamic_mx
             && qmode != dnnl_quantization_mode_dynamic_fp)
         return dnnl_invalid_arguments;
@@ -787,12 +807,12 @@ dnnl_status_t dnnl_primitive_attr_set_scales(dnnl_primitive_attr_t attr, int arg
     return dnnl_primitive_attr_set_scales_v3(attr, arg, mask, group_ndims, group_dims, dt, 0, dnnl_quantization_mode_static_sazp);
 }
 dnnl_status_t dnnl_primitive_attr_set_scales_mask(dnnl_primitive_attr_t attr, int arg, int mask) {
-    if (!attr || arg < 0 || mask < 0) return dnnl_invalid_arguments;
+    if (!attr || arg < 0 || mask < 0 || !scales_arg_ok(arg)) return dnnl_invalid_arguments;
     return set_quant(attr->scales, arg, mask, 0, nullptr, dnnl_f32, 0, dnnl_quantization_mode_static_sazp);
 }
 dnnl_status_t dnnl_primitive_attr_set_zero_points_v2(dnnl_primitive_attr_t attr, int arg, int mask, int ndims,
         const dnnl_dims_t group_dims, dnnl_data_type_t dt, int is_on_host) {
-    if (!attr || arg < 0 || mask < 0) return dnnl_invalid_arguments;
+    if (!attr || arg < 0 || mask < 0 || !zero_points_arg_ok(arg)) return dnnl_invalid_arguments;
     if (dt != dnnl_s32 && dt != dnnl_s8 && dt != dnnl_u8 && dt != dnnl_s4 && dt != dnnl_u4) return dnnl_invalid_arguments;
     if ((dt == dnnl_s4 || dt == dnnl_u4) && mask <= 0) return dnnl_invalid_arguments;
     if (arg != DNNL_ARG_SRC && arg != DNNL_ARG_WEIGHTS && !(dt == dnnl_s32 && ndims == 0)) return dnnl_invalid_arguments;
@@ -803,7 +823,7 @@ dnnl_status_t dnnl_primitive_attr_set_zero_points(dnnl_primitive_attr_t attr, in
     return dnnl_primitive_attr_set_zero_points_v2(attr, arg, mask, group_ndims, group_dims, dt, 0);
 }
 dnnl_status_t dnnl_primitive_attr_set_zero_points_mask(dnnl_primitive_attr_t attr, int arg, int mask) {
-    if (!attr || mask < 0) return dnnl_invalid_arguments;
+    if (!attr || mask < 0 || !zero_points_arg_ok(arg)) return dnnl_invalid_arguments;
     return set_quant(attr->zero_points, arg, mask, 0, nullptr, dnnl_s32, 0, dnnl_quantization_mode_static_sazp);
 }
 dnnl_status_t dnnl_primitive_attr_set_precomputed_reductions(dnnl_primitive_attr_t attr, int arg, int mask,
