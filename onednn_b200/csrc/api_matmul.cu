@@ -41,12 +41,13 @@ void set_default_format(dnnl_memory_desc &md) {
 // types::default_accum_data_type (src/common/type_helpers.hpp:515-548): the
 // combination must have a defined accumulation type
 bool dt_combo_ok(dnnl_data_type_t s, dnnl_data_type_t w, dnnl_data_type_t d) {
-    const bool fp_s = one_of(s, {dnnl_f32, dnnl_bf16, dnnl_f16, dnnl_f8_e4m3, dnnl_f8_e5m2});
-    const bool fp_w = one_of(w, {dnnl_f32, dnnl_bf16, dnnl_f16, dnnl_f8_e4m3, dnnl_f8_e5m2});
-    if (is_int8(s)) return is_int_wei(w);
-    if (fp_s) return fp_w || is_int_wei(w);
-    (void)d;
-    return false;
+    if (s == dnnl_f32 && w == dnnl_f32) return true;
+    if (is_int8(s) && is_int_wei(w)) return true;
+    if (s == dnnl_f16 || w == dnnl_f16) return true;
+    if (one_of(s, {dnnl_bf16, dnnl_f32}) && is_int_wei(w)) return true; // weights decompression
+    for (dnnl_data_type_t t : {s, w, d})
+        if (one_of(t, {dnnl_f4_e2m1, dnnl_f8_e5m2, dnnl_f8_e4m3, dnnl_bf16, dnnl_f16})) return true;
+    return false; // no accumulation type: the descriptor is invalid, not merely without an implementation
 }
 
 dnnl_status_t dense_desc_check(const dnnl_memory_desc &src, const dnnl_memory_desc &wei,
@@ -103,7 +104,10 @@ dnnl_status_t dense_attr_check(const dnnl_primitive_desc &pd) {
     dnnl_dim_t ssg_k = 1, wsg_k = 1, wsg_n = 1;
     const auto &ss = attr.scale(DNNL_ARG_SRC);
     if (ss.set) {
-        UNIMPL_IF(!one_of(ss.mask, {0, qM, qK, qM + qK, full}));
+        // per tensor, per row, or per K group (with or without the rows): what the reference's
+        // matmuls take for src (attr_scales_ok with src_qmask_M, src/cpu/matmul/ref_matmul_int8.hpp:79-82)
+        UNIMPL_IF(!(ss.mask == 0 || (ss.mask == qM && !ss.group_ndims)
+                || (one_of(ss.mask, {qK, qM + qK}) && ss.group_ndims)));
         if (ss.group_ndims && (ss.mask & qK)) ssg_k = ss.group(1);
         UNIMPL_IF(ssg_k > 1 && ssg_k < K && ssg_k % 16 != 0);
     }

@@ -301,7 +301,9 @@ dnnl_status_t dnnl_memory_desc_create_with_strides(dnnl_memory_desc_t *memory_de
             for (int j = i + 1; j < ndims; ++j)
                 if (md->strides[perm[j]] < md->strides[perm[i]]) std::swap(perm[i], perm[j]);
         dnnl_dim_t min_stride = 1;
-        for (int idx = 0; idx < ndims; ++idx) {
+        bool empty = false; // a tensor without elements has no layout to check
+        for (int i = 0; i < ndims; ++i) empty = empty || md->dims[i] == 0;
+        for (int idx = 0; idx < ndims && !empty; ++idx) {
             const int d = perm[idx];
             if (md->strides[d] == 0 || md->dims[d] == 1) continue;
             if (md->strides[d] < min_stride) { delete md; return dnnl_invalid_arguments; }

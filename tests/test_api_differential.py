@@ -194,3 +194,117 @@ def test_attribute_setters(libs):
 
 # (setter, argument, value) combinations where this library deliberately answers differently
 KNOWN = set()
+
+
+def _engine(L, kind):
+    e = C.c_void_p()
+    L.dnnl_engine_create.argtypes = [C.c_void_p, C.c_int, C.c_size_t]
+    assert L.dnnl_engine_create(C.byref(e), kind, 0) == 0
+    return e
+
+
+def test_matmul_primitive_descriptor_statuses(libs, host_engine):
+    """dnnl_matmul_primitive_desc_create on the reference's CPU engine and on this library's engine:
+    shapes that agree, disagree, broadcast or are empty, every triple of eight data types, bias of
+    several shapes and types.  success / invalid_arguments / unimplemented must be the same answer."""
+    ref, mine = libs
+    engines = (_engine(ref, 1), _engine(mine, 2))
+    tags = {2: 3, 3: 4}
+
+    def md(L, dims, dt):
+        h = C.c_void_p()
+        return h if L.dnnl_memory_desc_create_with_tag(C.byref(h), len(dims), DIMS(*dims), dt, tags[len(dims)]) == 0 else None
+
+    def status(L, e, sd, wd, dd, dts, bias=None):
+        s, w, d = md(L, sd, dts[0]), md(L, wd, dts[1]), md(L, dd, dts[2])
+        b = md(L, bias[0], bias[1]) if bias else None
+        if None in (s, w, d) or (bias and b is None):
+            return "md"
+        h = C.c_void_p()
+        L.dnnl_matmul_primitive_desc_create.argtypes = [C.c_void_p] * 7
+        return L.dnnl_matmul_primitive_desc_create(C.byref(h), e, s, w, b, d, None)
+
+    dts = [W.F32, W.BF16, W.F16, W.S8, W.U8, W.S32, W.F8_E4M3, W.S4]
+    shapes = [((4, 8), (8, 6), (4, 6)), ((4, 8), (7, 6), (4, 6)), ((4, 8), (8, 6), (5, 6)), ((4, 8), (8, 6), (4, 7)),
+              ((2, 4, 8), (2, 8, 6), (2, 4, 6)), ((2, 4, 8), (1, 8, 6), (2, 4, 6)), ((2, 4, 8), (3, 8, 6), (2, 4, 6)),
+              ((4, 8), (2, 8, 6), (4, 6)), ((0, 8), (8, 6), (0, 6)), ((4, 0), (0, 6), (4, 6))]
+    checked = 0
+    for (sd, wd, dd), a, b, c in itertools.product(shapes, dts, dts, dts):
+        r, m = status(ref, engines[0], sd, wd, dd, (a, b, c)), status(mine, engines[1], sd, wd, dd, (a, b, c))
+        assert r == m, (sd, wd, dd, W.DT_NAME[a], W.DT_NAME[b], W.DT_NAME[c], "reference %s, this library %s" % (r, m))
+        checked += 1
+    for bias_dims, bias_dt, (a, b, c) in itertools.product(
+            ((1, 6), (4, 6), (4, 1), (1, 1), (1, 5), (2, 6), (6,), (1, 1, 6)), (W.F32, W.BF16, W.F16, W.S8, W.S32, W.F8_E4M3),
+            ((W.F32, W.F32, W.F32), (W.BF16, W.BF16, W.F32), (W.F16, W.F16, W.F16), (W.U8, W.S8, W.S32), (W.S8, W.S8, W.F32),
+             (W.F8_E4M3, W.F8_E4M3, W.BF16))):
+        if len(bias_dims) != 2:
+            tags[len(bias_dims)] = {1: 2, 3: 4}[len(bias_dims)]
+        args = ((4, 8), (8, 6), (4, 6), (a, b, c), (bias_dims, bias_dt))
+        r, m = status(ref, engines[0], *args), status(mine, engines[1], *args)
+        if (r, m) in KNOWN_BIAS.get((W.DT_NAME[a], W.DT_NAME[bias_dt]), ()):
+            continue
+        assert r == m, (bias_dims, W.DT_NAME[bias_dt], W.DT_NAME[a], "reference %s, this library %s" % (r, m))
+        checked += 1
+    assert checked > 5200
+
+
+# (src type, bias type) -> (reference status, this library's) pairs that are kept
+KNOWN_BIAS = {}
+
+
+def test_matmul_descriptor_with_one_quantization_attribute(libs):
+    """One scales or zero-points entry at a time (argument x mask x groups x data type) on seven kinds
+    of problem: the two libraries must give the same status, except where this library is stricter on
+    purpose (the cases named in `stricter`); nowhere may it accept what the reference refuses."""
+    ref, mine = libs
+    engines = (_engine(ref, 1), _engine(mine, 2))
+
+    def md(L, dims, dt):
+        h = C.c_void_p()
+        assert L.dnnl_memory_desc_create_with_tag(C.byref(h), len(dims), DIMS(*dims), dt, 3) == 0
+        return h
+
+    def status(L, e, dts, fpmath, fn, arg, mask, groups, dt):
+        a = C.c_void_p()
+        assert L.dnnl_primitive_attr_create(C.byref(a)) == 0
+        if fpmath:
+            assert L.dnnl_primitive_attr_set_fpmath_mode_v2(a, fpmath, 1) == 0
+        f = getattr(L, fn)
+        f.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.POINTER(C.c_int64), C.c_int]
+        st = f(a, arg, mask, len(groups), (C.c_int64 * 12)(*groups) if groups else None, dt)
+        if st != 0:
+            return "setter %d" % st
+        h = C.c_void_p()
+        L.dnnl_matmul_primitive_desc_create.argtypes = [C.c_void_p] * 7
+        return L.dnnl_matmul_primitive_desc_create(C.byref(h), e, md(L, (4, 8), dts[0]), md(L, (8, 6), dts[1]), None,
+                                                   md(L, (4, 6), dts[2]), a)
+
+    problems = {"u8s8s32": ((W.U8, W.S8, W.S32), 0), "s8s8f32": ((W.S8, W.S8, W.F32), 0), "woq": ((W.BF16, W.S8, W.BF16), 1),
+                "woq4": ((W.F16, W.U4, W.F16), 2), "f32": ((W.F32, W.F32, W.F32), 0), "f8": ((W.F8_E4M3, W.F8_E4M3, W.BF16), 0),
+                "bf16": ((W.BF16, W.BF16, W.F32), 0)}
+
+    def stricter(pn, fn, an, mask, groups):
+        if fn.endswith("scales"):
+            if an == "dst" and mask != 0:
+                return True  # the reference takes the mask and applies scale [0]: refused here
+            if an == "wei" and (mask & 1) and pn in ("f32", "bf16"):
+                return True  # K-dependent scales of floating-point weights
+            return False
+        if pn.startswith("woq") and an in ("src", "dst") and mask == 0:
+            return True  # zero-points of a floating-point src / dst
+        return an == "wei" and mask == 1 and len(groups) == 2 and groups[0] == 1  # N groups without the N bit
+
+    checked = kept = 0
+    for (pn, (dts, fpmath)), fn, (an, arg), mask, groups, dt in itertools.product(
+            problems.items(), ("dnnl_primitive_attr_set_scales", "dnnl_primitive_attr_set_zero_points"),
+            {"src": 1, "wei": 33, "dst": 17}.items(), (0, 1, 2, 3), ((), (1, 4), (4, 1), (2, 2), (1, 8), (8, 1)),
+            (W.F32, W.BF16, W.F16, W.S32, W.S8, W.U8, W.U4)):
+        r = status(ref, engines[0], dts, fpmath, fn, arg, mask, groups, dt)
+        m = status(mine, engines[1], dts, fpmath, fn, arg, mask, groups, dt)
+        checked += 1
+        if r == m:
+            continue
+        assert (r, m) == (0, 3) and stricter(pn, fn, an, mask, groups), \
+            (pn, fn, an, mask, groups, W.DT_NAME[dt], "reference %s, this library %s" % (r, m))
+        kept += 1
+    assert checked == 7056 and kept < 250
