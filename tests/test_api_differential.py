@@ -292,7 +292,7 @@ def test_matmul_descriptor_with_one_quantization_attribute(libs):
             return False
         if pn.startswith("woq") and an in ("src", "dst") and mask == 0:
             return True  # zero-points of a floating-point src / dst
-        return an == "wei" and mask == 1 and len(groups) == 2 and groups[0] == 1  # N groups without the N bit
+        return an == "wei" and len(groups) == 2 and groups[0] == 1  # groups along N that the mask or N do not fit
 
     checked = kept = 0
     for (pn, (dts, fpmath)), fn, (an, arg), mask, groups, dt in itertools.product(
