@@ -252,7 +252,7 @@ def test_matmul_primitive_descriptor_statuses(libs, host_engine):
 KNOWN_BIAS = {}
 
 
-def test_matmul_descriptor_with_one_quantization_attribute(libs):
+def test_matmul_descriptor_with_one_quantization_attribute(libs, host_engine):
     """One scales or zero-points entry at a time (argument x mask x groups x data type) on seven kinds
     of problem: the two libraries must give the same status, except where this library is stricter on
     purpose (the cases named in `stricter`); nowhere may it accept what the reference refuses."""
@@ -310,7 +310,7 @@ def test_matmul_descriptor_with_one_quantization_attribute(libs):
     assert checked == 7056 and kept < 250
 
 
-def test_matmul_descriptor_with_one_post_op(libs):
+def test_matmul_descriptor_with_one_post_op(libs, host_engine):
     """One post-op at a time on eight kinds of problem: sum (scale, zero-point, data type), every
     eltwise algorithm value and a few that are none, every binary algorithm with operands of several
     shapes, ranks and data types, prelu masks.  (binary_select is left out: without its third
