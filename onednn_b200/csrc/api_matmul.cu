@@ -640,6 +640,15 @@ void apply_stand_ins(dnnl_primitive_desc &pd) {
     learn(M, pd.src.dims[0]); learn(M, pd.dst.dims[0]);
     learn(K, pd.src.dims[1]); learn(K, pd.wei.dims[0]);
     learn(N, pd.wei.dims[1]); learn(N, pd.dst.dims[1]);
+    // an operand that states a full extent (a residual with M rows while M is open) tells it too
+    auto learn_from = [&](const dnnl_memory_desc &md) {
+        if (md.ndims != 2) return;
+        if (md.dims[0] != RT && md.dims[0] > 1) learn(M, md.dims[0]);
+        if (md.dims[1] != RT && md.dims[1] > 1) learn(N, md.dims[1]);
+    };
+    learn_from(pd.bias);
+    for (auto &e : pd.attr.post_ops.entries)
+        if (e.kind == dnnl_binary) learn_from(e.src1);
     dnnl_dim_t gk = 1, gn = 1;
     for (auto *m : {&pd.attr.scales, &pd.attr.zero_points, &pd.attr.reductions})
         for (auto &kv : *m)
