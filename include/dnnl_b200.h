@@ -310,6 +310,12 @@ dnnl_status_t DNNL_API dnnl_memory_desc_create_with_strides(dnnl_memory_desc_t *
         const dnnl_dims_t dims, dnnl_data_type_t data_type, const dnnl_dims_t strides);
 dnnl_status_t DNNL_API dnnl_memory_desc_create_with_tag(dnnl_memory_desc_t *memory_desc, int ndims,
         const dnnl_dims_t dims, dnnl_data_type_t data_type, dnnl_format_tag_t tag);
+/* exported by the reference library for its own test driver, which declares them itself
+ * (src/common/memory_desc.cpp:1140-1158, tests/benchdnn/dnnl_memory.cpp:49-54): a tag written as
+ * letters, outermost dim first; the data type of an existing descriptor changed in place */
+dnnl_status_t DNNL_API dnnl_memory_desc_create_with_string_tag(dnnl_memory_desc_t *memory_desc, int ndims,
+        const dnnl_dims_t dims, dnnl_data_type_t data_type, const char *tag);
+dnnl_status_t DNNL_API dnnl_memory_desc_set_data_type(dnnl_memory_desc_t memory_desc, dnnl_data_type_t data_type);
 dnnl_status_t DNNL_API dnnl_memory_desc_create_with_grouped_encoding(dnnl_memory_desc_t *memory_desc,
         int ndims, const dnnl_dims_t dims, dnnl_data_type_t data_type, int variable_dim_idx,
         dnnl_dim_t group_count, dnnl_data_type_t offsets_dt);

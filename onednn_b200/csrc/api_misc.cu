@@ -358,6 +358,12 @@ const char *dnnl_runtime2str(unsigned v) {
 }
 
 /* ---- profiling (dnnl.h:4063-4085) ------------------------------------------ */
+// What the reference's test driver calls after reading the profiling data of a GPU stream
+// (src/common/stream_profiler.cpp:55-63): the events recorded here need no such notice.
+dnnl_status_t dnnl_impl_notify_profiling_complete(dnnl_stream_t stream) {
+    if (!stream) return dnnl_invalid_arguments;
+    return (stream->flags & dnnl_stream_profiling) ? dnnl_success : dnnl_invalid_arguments;
+}
 dnnl_status_t dnnl_reset_profiling(dnnl_stream_t stream) {
     if (!stream) return dnnl_invalid_arguments;
     if (!(stream->flags & dnnl_stream_profiling)) return dnnl_invalid_arguments;
@@ -493,6 +499,8 @@ QMM_STUB(dnnl_reduction_primitive_desc_create)
 QMM_STUB(dnnl_resampling_backward_primitive_desc_create)
 QMM_STUB(dnnl_resampling_forward_primitive_desc_create)
 QMM_STUB(dnnl_sgemm)
+QMM_STUB(dnnl_gemm_bf16bf16f32)
+QMM_STUB(dnnl_impl_zero_pad) // plain layouts have no padding to clear
 QMM_STUB(dnnl_shuffle_backward_primitive_desc_create)
 QMM_STUB(dnnl_shuffle_forward_primitive_desc_create)
 QMM_STUB(dnnl_softmax_backward_primitive_desc_create)

@@ -324,6 +324,39 @@ dnnl_status_t dnnl_memory_desc_create_with_strides(dnnl_memory_desc_t *memory_de
     return dnnl_success;
 }
 
+// The two entry points the reference's test driver declares for itself (src/common/memory_desc.cpp:1140-1158):
+// a descriptor from a tag written as letters, outermost dim first ("acb"), and a data type changed in place.
+// Plain permutations only: a tag with blocks (capital letters, digits) is unimplemented.
+dnnl_status_t dnnl_memory_desc_create_with_string_tag(dnnl_memory_desc_t *memory_desc, int ndims, const dnnl_dims_t dims,
+        dnnl_data_type_t data_type, const char *tag) {
+    if (!memory_desc || !tag) return dnnl_invalid_arguments;
+    dnnl_status_t st = md_check_common(ndims, dims, data_type);
+    if (st != dnnl_success) return st;
+    if ((int)std::strlen(tag) != ndims || ndims == 0) return dnnl_invalid_arguments;
+    int order[DNNL_MAX_NDIMS];
+    bool seen[DNNL_MAX_NDIMS] = {};
+    for (int i = 0; i < ndims; ++i) {
+        const char c = tag[i];
+        if (c >= 'A' && c <= 'L') return dnnl_unimplemented;
+        if (c < 'a' || c >= 'a' + ndims || seen[c - 'a']) return dnnl_invalid_arguments;
+        seen[c - 'a'] = true;
+        order[i] = c - 'a';
+    }
+    dnnl_dims_t strides = {};
+    dnnl_dim_t acc = 1;
+    for (int i = ndims - 1; i >= 0; --i) {
+        strides[order[i]] = acc;
+        const dnnl_dim_t d = dims[order[i]];
+        acc = (acc == DNNL_RUNTIME_DIM_VAL || d == DNNL_RUNTIME_DIM_VAL) ? DNNL_RUNTIME_DIM_VAL : acc * (d == 0 ? 1 : d);
+    }
+    return dnnl_memory_desc_create_with_strides(memory_desc, ndims, dims, data_type, strides);
+}
+dnnl_status_t dnnl_memory_desc_set_data_type(dnnl_memory_desc_t memory_desc, dnnl_data_type_t data_type) {
+    if (!memory_desc) return dnnl_invalid_arguments;
+    memory_desc->data_type = data_type;
+    return dnnl_success;
+}
+
 dnnl_status_t dnnl_memory_desc_create_with_tag(dnnl_memory_desc_t *memory_desc, int ndims,
         const dnnl_dims_t dims, dnnl_data_type_t data_type, dnnl_format_tag_t tag) {
     if (!memory_desc) return dnnl_invalid_arguments;

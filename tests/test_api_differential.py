@@ -373,3 +373,33 @@ def test_matmul_descriptor_with_one_post_op(libs, host_engine):
             continue
         assert r == m, (pn, step, "reference %s, this library %s" % (r, m))
     assert checked > 5000
+
+
+def test_every_exported_entry_point_of_the_reference_is_exported_here(libs):
+    import subprocess
+    def names(path):
+        out = subprocess.run(["nm", "-D", "--defined-only", path], capture_output=True, text=True, check=True).stdout
+        return {line.split()[-1] for line in out.splitlines() if " T dnnl_" in line}
+    from onednn_b200.build import lib_path
+    missing = names(REF_LIB) - names(lib_path())
+    assert not missing, sorted(missing)
+
+
+def test_string_tags_and_data_type_change(libs):
+    """The two descriptor entry points the reference exports for its test driver."""
+    cases = [((4, 6), "ab"), ((4, 6), "ba"), ((3, 4, 5), "abc"), ((3, 4, 5), "acb"), ((3, 4, 5), "bac"), ((3, 4, 5), "cab"),
+             ((2, 3, 4, 5), "abcd"), ((2, 3, 4, 5), "acdb"), ((2, 3, 4, 5), "abdc"), ((RT, 6), "ab"), ((4, RT, 6), "acb"),
+             ((4, 6), "any"), ((4, 6), "abc"), ((4, 6), "aa"), ((4, 6), "ac"), ((3, 4, 5), "ab")]
+    for dims, tag in cases:
+        def call(L):
+            h = C.c_void_p()
+            L.dnnl_memory_desc_create_with_string_tag.argtypes = [C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_char_p]
+            st = L.dnnl_memory_desc_create_with_string_tag(C.byref(h), len(dims), DIMS(*dims), W.BF16, tag.encode())
+            if st != 0:
+                return st, None, None
+            before = _describe(L, h.value)
+            L.dnnl_memory_desc_set_data_type.argtypes = [C.c_void_p, C.c_int]
+            st2 = L.dnnl_memory_desc_set_data_type(h, W.S8)
+            return st, before, (st2, _describe(L, h.value))
+        r, m = call(libs[0]), call(libs[1])
+        assert r == m, (dims, tag, r, m)
