@@ -40,11 +40,12 @@ def libs():
 
 def _describe(L, h):
     """What the queries say about a memory descriptor."""
+    h = C.c_void_p(h)  # a bare Python int would be passed as a 32-bit C int
     nd, dt, fk = C.c_int(), C.c_int(), C.c_int()
     L.dnnl_memory_desc_query(h, Q_NDIMS, C.byref(nd))
     L.dnnl_memory_desc_query(h, Q_DT, C.byref(dt))
     L.dnnl_memory_desc_query(h, Q_FORMAT_KIND, C.byref(fk))
-    out = [nd.value, dt.value, fk.value, L.dnnl_memory_desc_get_size(C.c_void_p(h))]
+    out = [nd.value, dt.value, fk.value, L.dnnl_memory_desc_get_size(h)]
     p = C.POINTER(DIMS)()
     if L.dnnl_memory_desc_query(h, Q_DIMS, C.byref(p)) == 0 and p:
         out.append(tuple(p.contents[:nd.value]))
