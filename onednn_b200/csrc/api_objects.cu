@@ -466,13 +466,57 @@ dnnl_status_t dnnl_memory_desc_reshape(dnnl_memory_desc_t *out, const_dnnl_memor
     dnnl_dim_t n = 1;
     for (int i = 0; i < ndims; ++i) n *= dims[i];
     if (n != in->nelems()) return dnnl_invalid_arguments;
-    // only dense row-major descriptors reshape without a copy here
+    if (in->has_runtime_dims()) return dnnl_invalid_arguments;
+    // dense row-major: the new shape is dense row-major too
+    bool dense = true;
     dnnl_dim_t acc = 1;
     for (int i = in->ndims - 1; i >= 0; --i) {
-        if (in->dims[i] != 1 && in->strides[i] != acc) return dnnl_invalid_arguments;
+        if (in->dims[i] != 1 && in->strides[i] != acc) dense = false;
         acc *= in->dims[i];
     }
-    return dnnl_memory_desc_create_with_strides(out, ndims, dims, in->data_type, nullptr);
+    if (dense || n == 0) return dnnl_memory_desc_create_with_strides(out, ndims, dims, in->data_type, nullptr);
+    // Any other plain layout: old and new dims are matched from the left in groups of equal
+    // products (unit dims come and go freely); the old dims of a group must follow one another in
+    // memory without gaps, and the new dims of the group then split that run.
+    dnnl_dims_t st = {};
+    bool assigned[DNNL_MAX_NDIMS] = {};
+    int i = 0, j = 0;
+    while (true) {
+        while (i < in->ndims && in->dims[i] == 1) ++i;
+        while (j < ndims && dims[j] == 1) ++j;
+        if (i >= in->ndims || j >= ndims) break;
+        int i1 = i, j1 = j;
+        dnnl_dim_t po = in->dims[i], pn = dims[j];
+        while (po != pn) {
+            if (po < pn) {
+                if (++i1 >= in->ndims) return dnnl_invalid_arguments;
+                po *= in->dims[i1];
+            } else {
+                if (++j1 >= ndims) return dnnl_invalid_arguments;
+                pn *= dims[j1];
+            }
+        }
+        int last = i1; // the innermost old dim of the group that is not a unit dim
+        while (in->dims[last] == 1) --last;
+        dnnl_dim_t run = in->strides[last] * in->dims[last];
+        for (int k = last - 1; k >= i; --k) {
+            if (in->dims[k] == 1) continue;
+            if (in->strides[k] != run) return dnnl_invalid_arguments; // a gap or another order inside the group
+            run *= in->dims[k];
+        }
+        dnnl_dim_t s = in->strides[last];
+        for (int t = j1; t >= j; --t) {
+            st[t] = s;
+            assigned[t] = true;
+            s *= dims[t];
+        }
+        i = i1 + 1;
+        j = j1 + 1;
+    }
+    if (i < in->ndims || j < ndims) return dnnl_invalid_arguments;
+    for (int t = ndims - 1; t >= 0; --t) // unit dims: the extent of what lies to their right
+        if (!assigned[t]) st[t] = t + 1 < ndims ? st[t + 1] * dims[t + 1] : 1;
+    return dnnl_memory_desc_create_with_strides(out, ndims, dims, in->data_type, st);
 }
 
 dnnl_status_t dnnl_memory_desc_permute_axes(dnnl_memory_desc_t *out, const_dnnl_memory_desc_t in, const int *perm) {

@@ -404,3 +404,41 @@ def test_string_tags_and_data_type_change(libs):
             return st, before, (st2, _describe(L, h.value))
         r, m = call(libs[0]), call(libs[1])
         assert r == m, (dims, tag, r, m)
+
+
+def test_reshape_and_permute_axes(libs):
+    """dnnl_memory_desc_reshape on dense, transposed and padded layouts (dims split, joined, unit
+    dims added and removed, impossible shapes) and dnnl_memory_desc_permute_axes."""
+    def make(L, dims, tag, strides):
+        h = C.c_void_p()
+        if strides is None:
+            assert L.dnnl_memory_desc_create_with_tag(C.byref(h), len(dims), DIMS(*dims), W.F32, tag) == 0
+        else:
+            assert L.dnnl_memory_desc_create_with_strides(C.byref(h), len(dims), DIMS(*dims), W.F32, DIMS(*strides)) == 0
+        return h
+
+    cases = []
+    for new in ((24,), (2, 12), (4, 2, 3), (2, 2, 6), (4, 6, 1), (1, 4, 6), (4, 1, 6), (8, 3), (3, 8), (2, 2, 2, 3), (6, 4), (5, 5)):
+        cases += [((4, 6), 3, None, new), ((4, 6), 14, None, new), ((4, 6), None, (8, 1), new), ((4, 6), None, (1, 4), new),
+                  ((4, 6), None, (12, 2), new)]
+    for new in ((6, 4), (2, 12), (24,), (2, 3, 2, 2), (3, 2, 4), (2, 1, 3, 4), (4, 6)):
+        cases += [((2, 3, 4), 4, None, new), ((2, 3, 4), 15, None, new), ((2, 3, 4), 16, None, new),
+                  ((2, 3, 4), None, (24, 4, 1), new), ((2, 3, 4), None, (12, 1, 3), new)]
+    for dims, tag, strides, new in cases:
+        def call(L):
+            o = C.c_void_p()
+            L.dnnl_memory_desc_reshape.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]
+            st = L.dnnl_memory_desc_reshape(C.byref(o), make(L, dims, tag, strides), len(new), DIMS(*new))
+            return [st, _describe(L, o.value) if st == 0 else None]
+        r, m = call(libs[0]), call(libs[1])
+        if r[0] == 0 and m[0] == 0 and r[1][3] > m[1][3]:  # gaps: the exact span is the smaller size
+            r[1][3] = m[1][3]
+        assert r == m, ("reshape", dims, tag, strides, new, r, m)
+    for dims, tag, perm in (((4, 6), 3, (1, 0)), ((4, 6), 3, (0, 1)), ((2, 3, 4), 4, (2, 0, 1)), ((2, 3, 4), 15, (1, 2, 0)),
+                            ((2, 3, 4), 4, (0, 0, 1)), ((2, 3, 4), 4, (0, 1, 3))):
+        def call(L):
+            o = C.c_void_p()
+            L.dnnl_memory_desc_permute_axes.argtypes = [C.c_void_p, C.c_void_p, C.POINTER(C.c_int)]
+            st = L.dnnl_memory_desc_permute_axes(C.byref(o), make(L, dims, tag, None), (C.c_int * len(perm))(*perm))
+            return st, _describe(L, o.value) if st == 0 else None
+        assert call(libs[0]) == call(libs[1]), ("permute", dims, tag, perm)
